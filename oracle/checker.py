@@ -1,0 +1,231 @@
+"""ctypes access to the CPU checkers.  TEST INFRASTRUCTURE - not the product.
+
+Three libraries, all built by the Makefile in this directory:
+
+* ``liboracle.so``            the plain-C restatement (``embedding_oracle.c``)
+* ``_ref/libfbgemm_ref.so``   the reference's own scalar and auto-vectorised
+                              sources compiled where they lie (``ref_shim.cc``)
+* ``_ref/libfbgemm_jit.so``   the reference's asmjit kernels as bundled in
+                              ``libtorch_cpu.so`` (``ref_jit_shim.cc``)
+
+Only ``tests/``, ``__graft_entry__.smoke()`` and the CPU legs of ``bench.py``
+may import this module.  All arrays are numpy arrays in host memory.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(HERE, "liboracle.so")
+REF_SO = os.path.join(HERE, "_ref", "libfbgemm_ref.so")
+JIT_SO = os.path.join(HERE, "_ref", "libfbgemm_jit.so")
+
+_i64 = C.c_int64
+_int = C.c_int
+_p = C.c_void_p
+
+_LOOKUP_ARGS = [_i64, _i64, _i64, _i64, _p, _p, _int, _p, _int, _p, _int, _p,
+                _int, _int, _int, _i64, _i64]
+_SPARSE_ARGS = [_int, _i64, _i64, _i64, _i64, _p, _p, _int, _p, _p, _int, _p,
+                _int, _p, _int, _int]
+
+
+def build(targets=("oracle",), ref_root="/root/reference") -> None:
+    """Run ``make`` for the named targets (oracle, ref, jit)."""
+    subprocess.run(["make", "-C", HERE, "-j8", f"REF_ROOT={ref_root}", *targets],
+                   check=True, stdout=subprocess.DEVNULL)
+
+
+def _ptr(a):
+    if a is None:
+        return None
+    assert a.flags["C_CONTIGUOUS"], "checker arrays must be contiguous"
+    return a.ctypes.data
+
+
+def _load(path):
+    if not os.path.exists(path):
+        return None
+    return C.CDLL(path)
+
+
+class _Lookups:
+    """Shared calling code for the three libraries (same argument order)."""
+
+    def __init__(self, lib, prefix, has_8bit_entry=True):
+        self.lib = lib
+        self.prefix = prefix
+        self.has_8bit_entry = has_8bit_entry
+
+    def _fn(self, name, argtypes, restype=_int):
+        f = getattr(self.lib, name)
+        f.argtypes = argtypes
+        f.restype = restype
+        return f
+
+    def spmdm(self, bit_rate, block_size, data_size, table, indices, offsets_or_lengths,
+              weights=None, normalize_by_lengths=False, out_dtype=np.float32,
+              is_weight_positional=False, use_offsets=True, output_stride=-1,
+              input_stride=-1, output_size=None, index_size=None, out=None):
+        """Pooled lookup; returns (ok, out).  ``out_dtype`` float32 or float16."""
+        indices = np.ascontiguousarray(indices)
+        offsets_or_lengths = np.ascontiguousarray(offsets_or_lengths)
+        if output_size is None:
+            output_size = len(offsets_or_lengths) - (1 if use_offsets else 0)
+        if index_size is None:
+            index_size = len(indices)
+        ostride = block_size if output_stride == -1 else output_stride
+        half = np.dtype(out_dtype) == np.float16
+        if out is None:
+            out = np.zeros(max(output_size, 1) * ostride, dtype=np.float16 if half else np.float32)
+        common = (block_size, output_size, index_size, data_size, _ptr(table),
+                  _ptr(indices), indices.dtype.itemsize, _ptr(offsets_or_lengths),
+                  offsets_or_lengths.dtype.itemsize, _ptr(weights),
+                  int(normalize_by_lengths), _ptr(out), int(half),
+                  int(is_weight_positional), int(use_offsets), output_stride, input_stride)
+        if bit_rate == 8 and self.has_8bit_entry:
+            ok = self._fn(self.prefix + "_embedding_spmdm_8bit", _LOOKUP_ARGS)(*common)
+        elif self.has_8bit_entry:
+            ok = self._fn(self.prefix + "_embedding_spmdm_nbit", [_int] + _LOOKUP_ARGS)(bit_rate, *common)
+        else:
+            ok = self._fn(self.prefix + "_embedding_spmdm", [_int] + _LOOKUP_ARGS)(bit_rate, *common)
+        return bool(ok), out
+
+    def spmdm_rowwise_sparse(self, bit_rate, block_size, uncompressed_data_size, table,
+                             indices, compressed_indices_table, offsets_or_lengths,
+                             weights=None, normalize_by_lengths=False,
+                             is_weight_positional=False, use_offsets=True,
+                             output_size=None, index_size=None):
+        indices = np.ascontiguousarray(indices)
+        offsets_or_lengths = np.ascontiguousarray(offsets_or_lengths)
+        if output_size is None:
+            output_size = len(offsets_or_lengths) - (1 if use_offsets else 0)
+        if index_size is None:
+            index_size = len(indices)
+        out = np.zeros(max(output_size, 1) * block_size, dtype=np.float32)
+        f = self._fn(self.prefix + "_embedding_spmdm_rowwise_sparse", _SPARSE_ARGS)
+        ok = f(bit_rate, block_size, output_size, index_size, uncompressed_data_size,
+               _ptr(table), _ptr(indices), indices.dtype.itemsize,
+               _ptr(compressed_indices_table), _ptr(offsets_or_lengths),
+               offsets_or_lengths.dtype.itemsize, _ptr(weights),
+               int(normalize_by_lengths), _ptr(out), int(is_weight_positional),
+               int(use_offsets))
+        return bool(ok), out
+
+
+class Oracle(_Lookups):
+    """The plain-C restatement."""
+
+    def __init__(self):
+        if not os.path.exists(ORACLE_SO):
+            build(("oracle",))
+        super().__init__(C.CDLL(ORACLE_SO), "oracle")
+        self.lib.oracle_float_to_half_rn.argtypes = [C.c_float]
+        self.lib.oracle_float_to_half_rn.restype = C.c_uint16
+        self.lib.oracle_half_to_float.argtypes = [C.c_uint16]
+        self.lib.oracle_half_to_float.restype = C.c_float
+
+    def quantize_8bit(self, x):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        rows, cols = x.shape
+        out = np.zeros((rows, cols + 8), dtype=np.uint8)
+        f = self._fn("oracle_float_to_fused_8bit_rowwise_sbfloat", [_p, _i64, _int, _p], None)
+        f(_ptr(x), rows, cols, _ptr(out))
+        return out
+
+    def quantize_nbit(self, bit_rate, x):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        rows, cols = x.shape
+        epb = 8 // bit_rate
+        out = np.zeros((rows, (cols + epb - 1) // epb + 4), dtype=np.uint8)
+        f = self._fn("oracle_float_to_fused_nbit_rowwise_sbhalf", [_int, _p, _i64, _int, _p], None)
+        f(bit_rate, _ptr(x), rows, cols, _ptr(out))
+        return out
+
+    def remap(self, indices, mapping, offsets, weights=None):
+        indices = np.ascontiguousarray(indices)
+        offsets = np.ascontiguousarray(offsets, dtype=indices.dtype)
+        out_i = np.zeros_like(indices)
+        out_o = np.zeros_like(offsets)
+        out_w = np.zeros(len(indices), dtype=np.float32) if weights is not None else None
+        f = self._fn("oracle_compressed_indices_remap", [C.c_int32, _p, _int, _p, _p, _p, _p, _p, _p], None)
+        f(len(offsets), _ptr(indices), indices.dtype.itemsize, _ptr(mapping), _ptr(offsets),
+          _ptr(weights), _ptr(out_i), _ptr(out_o), _ptr(out_w))
+        n = int(out_o[-1])
+        return out_i[:n], out_o, (out_w[:n] if out_w is not None else None)
+
+    def float_to_half(self, f):
+        return int(self.lib.oracle_float_to_half_rn(float(f)))
+
+    def half_to_float(self, h):
+        return float(self.lib.oracle_half_to_float(int(h)))
+
+
+class Reference(_Lookups):
+    """The reference's own scalar code; None-like (``available`` False) when the
+    library was not built (it needs the reference tree at build time)."""
+
+    def __init__(self):
+        lib = _load(REF_SO)
+        self.available = lib is not None
+        super().__init__(lib, "ref")
+
+    def autovec(self, *args, **kw):
+        saved = (self.prefix, self.has_8bit_entry)
+        self.prefix, self.has_8bit_entry = "ref_autovec", False
+        try:
+            return self.spmdm(*args, **kw)
+        finally:
+            self.prefix, self.has_8bit_entry = saved
+
+    def quantize_8bit(self, x, use_ref=True):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        rows, cols = x.shape
+        out = np.zeros((rows, cols + 8), dtype=np.uint8)
+        f = self._fn("ref_float_to_fused_8bit_rowwise_sbfloat", [_p, _i64, _int, _p, _int], None)
+        f(_ptr(x), rows, cols, _ptr(out), int(use_ref))
+        return out
+
+    def quantize_nbit(self, bit_rate, x, use_ref=True):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        rows, cols = x.shape
+        epb = 8 // bit_rate
+        out = np.zeros((rows, (cols + epb - 1) // epb + 4), dtype=np.uint8)
+        f = self._fn("ref_float_to_fused_nbit_rowwise_sbhalf", [_int, _p, _i64, _int, _p, _int], None)
+        f(bit_rate, _ptr(x), rows, cols, _ptr(out), int(use_ref))
+        return out
+
+    def remap(self, indices, mapping, offsets, weights=None):
+        indices = np.ascontiguousarray(indices)
+        offsets = np.ascontiguousarray(offsets, dtype=indices.dtype)
+        out_i = np.zeros_like(indices)
+        out_o = np.zeros_like(offsets)
+        out_w = np.zeros(len(indices), dtype=np.float32) if weights is not None else None
+        f = self._fn("ref_compressed_indices_remap", [C.c_int32, _p, _int, _p, _p, _p, _p, _p, _p], None)
+        f(len(offsets), _ptr(indices), indices.dtype.itemsize, _ptr(mapping), _ptr(offsets),
+          _ptr(weights), _ptr(out_i), _ptr(out_o), _ptr(out_w))
+        n = int(out_o[-1])
+        return out_i[:n], out_o, (out_w[:n] if out_w is not None else None)
+
+    def float_to_half(self, f):
+        self.lib.ref_float_to_half_rn.argtypes = [C.c_float]
+        self.lib.ref_float_to_half_rn.restype = C.c_uint16
+        return int(self.lib.ref_float_to_half_rn(float(f)))
+
+    def half_to_float(self, h):
+        self.lib.ref_half_to_float.argtypes = [C.c_uint16]
+        self.lib.ref_half_to_float.restype = C.c_float
+        return float(self.lib.ref_half_to_float(int(h)))
+
+
+class ReferenceJit(_Lookups):
+    """The reference's asmjit (AVX2/AVX-512) kernels via libtorch_cpu.so."""
+
+    def __init__(self):
+        lib = _load(JIT_SO)
+        self.available = lib is not None
+        super().__init__(lib, "jit", has_8bit_entry=False)

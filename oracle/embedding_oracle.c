@@ -1,0 +1,534 @@
+/*
+ * TEST INFRASTRUCTURE - NOT PART OF THE PRODUCT.
+ *
+ * A scalar, single-threaded CPU restatement (plain C) of the arithmetic of
+ * FBGEMM's quantized embedding-bag path.  It exists only so that tests can
+ * check the CUDA kernels, and so that the benchmark can time a CPU leg; the
+ * library itself never links, loads or calls anything in this file.
+ *
+ * Parity status: PINNED.  This file is checked (a) against the quantizer
+ * known-answer vectors of test/QuantUtilsTest.cc:550-667 of the reference,
+ * and (b) bit-for-bit against the reference's own scalar functions compiled
+ * from the reference tree (see ref_shim.cc / Makefile in this directory) on
+ * seeded inputs; the outputs of that comparison are committed as fixtures.
+ *
+ * Every function names the reference lines it restates (paths are relative to
+ * the FBGEMM source tree).
+ *
+ * Build: gcc -O2 -ffp-contract=off -mfma -shared -fPIC (see Makefile).
+ * -ffp-contract=off matters: `acc + bias` followed by fma() must stay two
+ * roundings, exactly as in the reference.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#if defined(__GNUC__)
+#define ORACLE_API __attribute__((visibility("default")))
+#else
+#define ORACLE_API
+#endif
+
+/* ------------------------------------------------------------------------- */
+/* fp16 <-> fp32, software, round-to-nearest-even.                            */
+/* Restates include/fbgemm/FloatConversion.h:211-217 (cpu_float2half_rn) and  */
+/* :229-291 (cpu_half2float_ref).                                             */
+/* ------------------------------------------------------------------------- */
+
+static inline uint32_t f32_bits(float f) {
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  return u;
+}
+
+static inline float bits_f32(uint32_t u) {
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+
+ORACLE_API uint16_t oracle_float_to_half_rn(float f) {
+  const uint32_t x = f32_bits(f);
+  const uint32_t sign = (x >> 16) & 0x8000u;
+  const uint32_t absx = x & 0x7fffffffu;
+  if (absx >= 0x7f800000u) { /* inf / nan */
+    if (absx > 0x7f800000u) {
+      return (uint16_t)(sign | 0x7e00u | ((absx >> 13) & 0x3ffu));
+    }
+    return (uint16_t)(sign | 0x7c00u);
+  }
+  if (absx >= 0x477ff000u) { /* rounds to >= 65520 -> inf */
+    return (uint16_t)(sign | 0x7c00u);
+  }
+  if (absx < 0x33000001u) { /* <= 2^-25: rounds to zero (tie goes to even=0) */
+    return (uint16_t)sign;
+  }
+  int32_t exp = (int32_t)(absx >> 23) - 127;
+  uint32_t man = (absx & 0x7fffffu) | 0x800000u; /* 24-bit significand */
+  uint32_t shift;
+  uint32_t half_exp;
+  if (exp < -14) { /* subnormal half */
+    shift = (uint32_t)(13 + (-14 - exp));
+    half_exp = 0;
+  } else {
+    shift = 13;
+    half_exp = (uint32_t)(exp + 15);
+  }
+  uint32_t q = man >> shift;
+  const uint32_t rem = man & ((1u << shift) - 1u);
+  const uint32_t halfway = 1u << (shift - 1);
+  if (rem > halfway || (rem == halfway && (q & 1u))) {
+    ++q;
+  }
+  uint32_t out;
+  if (half_exp == 0) {
+    out = q; /* a carry into bit 10 lands on the smallest normal: correct */
+  } else {
+    out = ((half_exp - 1) << 10) + q; /* q carries the implicit 1 (bit 10) */
+  }
+  return (uint16_t)(sign | out);
+}
+
+ORACLE_API float oracle_half_to_float(uint16_t h) {
+  const uint32_t sign = ((uint32_t)h & 0x8000u) << 16;
+  uint32_t exp = (h >> 10) & 0x1fu;
+  uint32_t man = (uint32_t)(h & 0x3ffu) << 13;
+  if (exp == 0x1fu) {
+    if (man) {
+      return bits_f32(0x7fffffffu); /* FloatConversion.h:262-266 */
+    }
+    return bits_f32(sign | 0x7f800000u);
+  }
+  if (exp == 0) {
+    if (man == 0) {
+      return bits_f32(sign);
+    }
+    exp = 127 - 15 + 1;
+    uint32_t msb;
+    do {
+      msb = man & 0x400000u;
+      man <<= 1;
+      --exp;
+    } while (!msb);
+    man &= 0x7fffffu;
+  } else {
+    exp += 127 - 15;
+  }
+  return bits_f32(sign | (exp << 23) | man);
+}
+
+/* ------------------------------------------------------------------------- */
+/* Index / offset accessors: the reference is templated on int32/int64; the  */
+/* oracle takes the element width in bytes.                                   */
+/* ------------------------------------------------------------------------- */
+
+static inline int64_t load_int(const void* p, int64_t i, int width) {
+  return width == 8 ? ((const int64_t*)p)[i] : (int64_t)((const int32_t*)p)[i];
+}
+
+static inline void store_out(void* out, int64_t i, float v, int out_is_half) {
+  if (out_is_half) {
+    ((uint16_t*)out)[i] = oracle_float_to_half_rn(v);
+  } else {
+    ((float*)out)[i] = v;
+  }
+}
+
+/* ------------------------------------------------------------------------- */
+/* Pooled lookup, 8-bit rows with trailing fp32 scale, bias.                  */
+/* Restates src/RefImplementations.cc:1196-1346 (EmbeddingSpMDM_ref, the      */
+/* uint8_t / scale_bias_last / bag branch).  Returns 1 for true, 0 for false. */
+/* ------------------------------------------------------------------------- */
+ORACLE_API int oracle_embedding_spmdm_8bit(
+    int64_t block_size,
+    int64_t output_size,
+    int64_t index_size,
+    int64_t data_size,
+    const uint8_t* input,
+    const void* indices,
+    int index_bytes,
+    const void* offsets_or_lengths,
+    int offset_bytes,
+    const float* weights, /* nullable */
+    int normalize_by_lengths,
+    void* out,
+    int out_is_half,
+    int is_weight_positional,
+    int use_offsets,
+    int64_t output_stride, /* -1: block_size */
+    int64_t input_stride /* -1: block_size + 8 */) {
+  if (output_stride == -1) {
+    output_stride = block_size; /* RefImplementations.cc:1217-1219 */
+  }
+  if (input_stride == -1) {
+    input_stride = block_size + 2 * (int64_t)sizeof(float); /* :1226-1232 */
+  }
+  float* buf = (float*)malloc(sizeof(float) * (size_t)(block_size > 0 ? block_size : 1));
+  int64_t current = 0;
+  int64_t out_base = 0;
+  int ok = 1;
+  for (int64_t m = 0; m < output_size; ++m) {
+    memset(buf, 0, sizeof(float) * (size_t)block_size);
+    /* `int len` in the reference: the difference is narrowed to 32 bits. */
+    const int len = use_offsets
+        ? (int)(load_int(offsets_or_lengths, m + 1, offset_bytes) -
+                load_int(offsets_or_lengths, m, offset_bytes))
+        : (int)load_int(offsets_or_lengths, m, offset_bytes);
+    if (current + len > index_size) { /* :1294-1296 */
+      ok = 0;
+      goto done;
+    }
+    for (int i = 0; i < len; ++i, ++current) {
+      const int64_t idx = load_int(indices, current, index_bytes);
+      if (idx < 0 || idx >= data_size) { /* :1304-1306 */
+        ok = 0;
+        goto done;
+      }
+      const uint8_t* row = input + input_stride * idx;
+      float sb[2];
+      memcpy(sb, row + block_size, sizeof(sb)); /* :1308-1309 */
+      float weight = 1.0f;
+      if (weights) {
+        weight = weights[is_weight_positional ? i : current]; /* :1311-1314 */
+      }
+      const float scale = weight * sb[0]; /* :1316-1318 */
+      const float bias = weight * sb[1];
+      for (int64_t j = 0; j < block_size; ++j) {
+        /* :1326-1333: fma(scale, q, buf + bias) - two roundings. */
+        const float t = buf[j] + bias;
+        buf[j] = fmaf(scale, (float)row[j], t);
+      }
+    }
+    if (normalize_by_lengths && len) { /* :1335-1340 */
+      const float inv = 1.f / (float)len;
+      for (int64_t j = 0; j < block_size; ++j) {
+        buf[j] *= inv;
+      }
+    }
+    for (int64_t j = 0; j < block_size; ++j) { /* :1341-1343 */
+      store_out(out, out_base + j, buf[j], out_is_half);
+    }
+    out_base += output_stride;
+  }
+  ok = (current == index_size); /* :1346 */
+done:
+  free(buf);
+  return ok;
+}
+
+/* ------------------------------------------------------------------------- */
+/* Pooled lookup, 4-bit / 2-bit rows with trailing fp16 scale, bias.          */
+/* Restates src/RefImplementations.cc:1427-1541 (EmbeddingSpMDMNBit_ref,      */
+/* scale_bias_last, bag branch).                                              */
+/* ------------------------------------------------------------------------- */
+ORACLE_API int oracle_embedding_spmdm_nbit(
+    int bit_rate,
+    int64_t block_size,
+    int64_t output_size,
+    int64_t index_size,
+    int64_t data_size,
+    const uint8_t* input,
+    const void* indices,
+    int index_bytes,
+    const void* offsets_or_lengths,
+    int offset_bytes,
+    const float* weights,
+    int normalize_by_lengths,
+    void* out,
+    int out_is_half,
+    int is_weight_positional,
+    int use_offsets,
+    int64_t output_stride,
+    int64_t input_stride) {
+  if (bit_rate != 2 && bit_rate != 4) {
+    return 0;
+  }
+  const int epb = 8 / bit_rate; /* :1452 */
+  const int64_t data_bytes = (block_size + epb - 1) / epb;
+  if (output_stride == -1) {
+    output_stride = block_size;
+  }
+  if (input_stride == -1) {
+    input_stride = data_bytes + 2 * (int64_t)sizeof(uint16_t); /* :1460-1465 */
+  }
+  float* buf = (float*)malloc(sizeof(float) * (size_t)(block_size > 0 ? block_size : 1));
+  int64_t current = 0;
+  int64_t out_base = 0;
+  int ok = 1;
+  const unsigned mask = (1u << bit_rate) - 1u;
+  for (int64_t m = 0; m < output_size; ++m) {
+    memset(buf, 0, sizeof(float) * (size_t)block_size);
+    const int len = use_offsets
+        ? (int)(load_int(offsets_or_lengths, m + 1, offset_bytes) -
+                load_int(offsets_or_lengths, m, offset_bytes))
+        : (int)load_int(offsets_or_lengths, m, offset_bytes);
+    if (current + len > index_size) { /* :1492-1494 */
+      ok = 0;
+      goto done;
+    }
+    for (int i = 0; i < len; ++i, ++current) {
+      const int64_t idx = load_int(indices, current, index_bytes);
+      if (idx < 0 || idx >= data_size) { /* :1502-1504 */
+        ok = 0;
+        goto done;
+      }
+      const uint8_t* row = input + input_stride * idx;
+      uint16_t sb[2];
+      memcpy(sb, row + data_bytes, sizeof(sb)); /* :1506-1510 */
+      float weight = 1.0f;
+      if (weights) {
+        weight = weights[is_weight_positional ? i : current];
+      }
+      const float scale = weight * oracle_half_to_float(sb[0]); /* :1516 */
+      const float bias = weight * oracle_half_to_float(sb[1]); /* :1517 */
+      for (int64_t j = 0; j < block_size; ++j) {
+        /* :1519-1526: element j sits in byte j/epb at bit (j%epb)*bit_rate. */
+        unsigned q = row[j / epb];
+        q >>= (unsigned)(j % epb) * (unsigned)bit_rate;
+        q &= mask;
+        const float t = buf[j] + bias;
+        buf[j] = fmaf(scale, (float)q, t);
+      }
+    }
+    if (normalize_by_lengths && len) {
+      const float inv = 1.f / (float)len;
+      for (int64_t j = 0; j < block_size; ++j) {
+        buf[j] *= inv;
+      }
+    }
+    for (int64_t j = 0; j < block_size; ++j) {
+      store_out(out, out_base + j, buf[j], out_is_half);
+    }
+    out_base += output_stride;
+  }
+  ok = (current == index_size);
+done:
+  free(buf);
+  return ok;
+}
+
+/* ------------------------------------------------------------------------- */
+/* Pruned (row-wise sparse) pooled lookup: indices address an uncompressed    */
+/* row space and go through compressed_indices_table; -1 there means the row  */
+/* was pruned: it contributes nothing but still consumes its index/weight     */
+/* slot and counts towards the bag length.  fp32 output, dense strides.       */
+/* bit_rate == 8 restates src/RefImplementations.cc:1617-1688                 */
+/* (EmbeddingSpMDMRowWiseSparse_ref<uint8_t>); 4 and 2 restate :1746-1822     */
+/* (EmbeddingSpMDMNBitRowWiseSparse_ref).                                     */
+/* ------------------------------------------------------------------------- */
+ORACLE_API int oracle_embedding_spmdm_rowwise_sparse(
+    int bit_rate,
+    int64_t block_size,
+    int64_t output_size,
+    int64_t index_size,
+    int64_t uncompressed_data_size,
+    const uint8_t* input,
+    const void* indices,
+    int index_bytes,
+    const int32_t* compressed_indices_table,
+    const void* offsets_or_lengths,
+    int offset_bytes,
+    const float* weights,
+    int normalize_by_lengths,
+    float* out,
+    int is_weight_positional,
+    int use_offsets) {
+  if (bit_rate != 2 && bit_rate != 4 && bit_rate != 8) {
+    return 0;
+  }
+  const int epb = 8 / bit_rate;
+  const int64_t data_bytes = (block_size + epb - 1) / epb;
+  const int64_t sb_bytes = bit_rate == 8 ? 8 : 4;
+  const int64_t fused = data_bytes + sb_bytes; /* :1637-1638 / :1769-1771 */
+  const unsigned mask = (1u << bit_rate) - 1u;
+  int64_t current = 0;
+  for (int64_t m = 0; m < output_size; ++m) {
+    memset(out, 0, sizeof(float) * (size_t)block_size); /* accumulates in out */
+    const int len = use_offsets
+        ? (int)(load_int(offsets_or_lengths, m + 1, offset_bytes) -
+                load_int(offsets_or_lengths, m, offset_bytes))
+        : (int)load_int(offsets_or_lengths, m, offset_bytes);
+    if (current + len > index_size) {
+      return 0;
+    }
+    for (int i = 0; i < len; ++i, ++current) {
+      const int64_t uidx = load_int(indices, current, index_bytes);
+      if (uidx < 0 || uidx >= uncompressed_data_size) { /* :1782-1784 */
+        return 0;
+      }
+      const int64_t idx = compressed_indices_table[uidx];
+      if (idx == -1) { /* :1786-1788: pruned, slot still consumed */
+        continue;
+      }
+      /* the compressed index itself is not range-checked (:1789-1791) */
+      const uint8_t* row = input + fused * idx;
+      float weight = 1.0f;
+      if (weights) {
+        weight = weights[is_weight_positional ? i : current];
+      }
+      float scale, bias;
+      if (bit_rate == 8) {
+        float sb[2];
+        memcpy(sb, row + data_bytes, sizeof(sb));
+        scale = weight * sb[0];
+        bias = weight * sb[1];
+      } else {
+        uint16_t sb[2];
+        memcpy(sb, row + data_bytes, sizeof(sb));
+        scale = weight * oracle_half_to_float(sb[0]);
+        bias = weight * oracle_half_to_float(sb[1]);
+      }
+      for (int64_t j = 0; j < block_size; ++j) {
+        unsigned q = row[j / epb];
+        q >>= (unsigned)(j % epb) * (unsigned)bit_rate;
+        q &= mask;
+        const float t = out[j] + bias;
+        out[j] = fmaf(scale, (float)q, t);
+      }
+    }
+    if (normalize_by_lengths && len) {
+      const float inv = 1.f / (float)len;
+      for (int64_t j = 0; j < block_size; ++j) {
+        out[j] *= inv;
+      }
+    }
+    out += block_size;
+  }
+  return current == index_size;
+}
+
+/* ------------------------------------------------------------------------- */
+/* Row-wise quantizers that produce the fused rows the lookups read.          */
+/* ------------------------------------------------------------------------- */
+
+/* Restates src/QuantUtils.cc:677-718                                        */
+/* (FloatOrHalfToFused8BitRowwiseQuantizedSBFloatRef<float>).                 */
+ORACLE_API void oracle_float_to_fused_8bit_rowwise_sbfloat(
+    const float* input,
+    int64_t input_rows,
+    int input_columns,
+    uint8_t* output) {
+  const float kEpsilon = 1e-8f;
+  if (input_rows == 0 || input_columns == 0) {
+    return;
+  }
+  const int64_t output_columns = (int64_t)input_columns + 8;
+  for (int64_t r = 0; r < input_rows; ++r) {
+    const float* in = input + r * input_columns;
+    uint8_t* o = output + r * output_columns;
+    float mn = in[0], mx = in[0];
+    for (int c = 1; c < input_columns; ++c) {
+      if (in[c] < mn) mn = in[c];
+      if (in[c] > mx) mx = in[c];
+    }
+    const float range = mx - mn;
+    const float sb[2] = {range / 255.0f, mn};
+    memcpy(o + input_columns, sb, sizeof(sb));
+    const float inverse_scale = 255.0f / (range + kEpsilon);
+    for (int c = 0; c < input_columns; ++c) {
+      o[c] = (uint8_t)lrintf((in[c] - mn) * inverse_scale);
+    }
+  }
+}
+
+/* Restates src/QuantUtils.cc:534-611                                        */
+/* (FloatOrHalfToFusedNBitRowwiseQuantizedSBHalfRef<float>); bit_rate may be  */
+/* 2, 4 or 8 there.                                                           */
+ORACLE_API void oracle_float_to_fused_nbit_rowwise_sbhalf(
+    int bit_rate,
+    const float* input,
+    int64_t input_rows,
+    int input_columns,
+    uint8_t* output) {
+  if (input_rows == 0 || input_columns == 0) {
+    return;
+  }
+  const int epb = 8 / bit_rate;
+  const int64_t data_bytes = ((int64_t)input_columns + epb - 1) / epb;
+  const int64_t output_columns = data_bytes + 4;
+  const int qmax = (1 << bit_rate) - 1;
+  for (int64_t r = 0; r < input_rows; ++r) {
+    const float* in = input + r * input_columns;
+    uint8_t* o = output + r * output_columns;
+    float mn = in[0], mx = in[0];
+    for (int c = 1; c < input_columns; ++c) {
+      if (in[c] < mn) mn = in[c];
+      if (in[c] > mx) mx = in[c];
+    }
+    /* the bias is stored as fp16, so the minimum is rounded first (:572-575) */
+    const uint16_t mn_h = oracle_float_to_half_rn(mn);
+    mn = oracle_half_to_float(mn_h);
+    const float range = mx - mn;
+    float scale = range == 0 ? 1.0f : range / (float)qmax;
+    const uint16_t scale_h = oracle_float_to_half_rn(scale);
+    scale = oracle_half_to_float(scale_h);
+    if (scale == 0) { /* :580-584 */
+      scale = 1.0f;
+    }
+    float inverse_scale = 1.0f / scale;
+    if (isinf(inverse_scale)) { /* :586-589 */
+      scale = 1.0f;
+      inverse_scale = 1.0f;
+    }
+    const uint16_t sb[2] = {oracle_float_to_half_rn(scale), mn_h};
+    memcpy(o + data_bytes, sb, sizeof(sb));
+    for (int c = 0; c < input_columns; ++c) {
+      long q = lrintf((in[c] - mn) * inverse_scale);
+      if (q > qmax) q = qmax;
+      if (q < 0) q = 0;
+      if (c % epb == 0) {
+        o[c / epb] = (uint8_t)q;
+      } else {
+        o[c / epb] |= (uint8_t)(q << ((c % epb) * bit_rate));
+      }
+    }
+  }
+}
+
+/* ------------------------------------------------------------------------- */
+/* Index remapping for pruned tables (drops pruned entries up front).         */
+/* Restates src/RefImplementations.cc:2308-2333 (compressed_indices_remap_ref)*/
+/* ------------------------------------------------------------------------- */
+ORACLE_API void oracle_compressed_indices_remap(
+    int32_t offsets_len,
+    const void* indices,
+    int index_bytes, /* offsets share the index type in the reference */
+    const int32_t* compressed_indices_mapping,
+    const void* offsets,
+    const float* weights, /* nullable */
+    void* out_indices,
+    void* out_offsets,
+    float* out_weights) {
+  const int has_w = weights != NULL;
+  int64_t k = 0;
+  if (index_bytes == 8) {
+    ((int64_t*)out_offsets)[0] = ((const int64_t*)offsets)[0];
+  } else {
+    ((int32_t*)out_offsets)[0] = ((const int32_t*)offsets)[0];
+  }
+  for (int32_t i = 1; i < offsets_len; ++i) {
+    const int64_t lo = load_int(offsets, i - 1, index_bytes);
+    const int64_t hi = load_int(offsets, i, index_bytes);
+    for (int64_t j = lo; j < hi; ++j) {
+      const int64_t idx = load_int(indices, j, index_bytes);
+      const int32_t mapped = compressed_indices_mapping[idx];
+      if (mapped != -1) {
+        if (index_bytes == 8) {
+          ((int64_t*)out_indices)[k] = mapped;
+        } else {
+          ((int32_t*)out_indices)[k] = mapped;
+        }
+        if (has_w) {
+          out_weights[k] = weights[j];
+        }
+        ++k;
+      }
+    }
+    if (index_bytes == 8) {
+      ((int64_t*)out_offsets)[i] = k;
+    } else {
+      ((int32_t*)out_offsets)[i] = (int32_t)k;
+    }
+  }
+}
