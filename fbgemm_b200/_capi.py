@@ -1,0 +1,101 @@
+"""ctypes binding of libfbgemm_b200.so (include/fbgemm_b200/embedding_c_api.h).
+
+The library is loaded from the package directory (it is built in-tree by
+``fbgemm_b200.build``).  There is no fallback of any kind: if the library is
+missing it is built with nvcc, and if that is impossible the import of the
+binding raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from . import build as _build
+
+STATUS_SLOTS = 1024
+HOST_LANES = 8
+OUT_F32 = 0
+OUT_F16 = 1
+
+EINVAL, ECUDA, ENOMEM, EBUSY = -1, -2, -3, -4
+
+
+class SpmdmConfig(C.Structure):
+    """``fbgemm_b200_spmdm_config``."""
+
+    _fields_ = [
+        ("bit_rate", C.c_int32),
+        ("index_bytes", C.c_int32),
+        ("offset_bytes", C.c_int32),
+        ("out_dtype", C.c_int32),
+        ("block_size", C.c_int64),
+        ("output_stride", C.c_int64),
+        ("input_stride", C.c_int64),
+        ("has_weight", C.c_int32),
+        ("normalize_by_lengths", C.c_int32),
+        ("is_weight_positional", C.c_int32),
+        ("use_offsets", C.c_int32),
+    ]
+
+
+class Fbgemmb200Error(RuntimeError):
+    pass
+
+
+_p = C.c_void_p
+_i64 = C.c_int64
+_cfgp = C.POINTER(SpmdmConfig)
+
+# name -> (restype, argtypes); exactly the symbols the header declares.
+SIGNATURES = {
+    "fbgemm_b200_ctx_create": (C.c_int, [C.c_int, C.POINTER(_p)]),
+    "fbgemm_b200_ctx_destroy": (None, [_p]),
+    "fbgemm_b200_last_error": (C.c_char_p, []),
+    "fbgemm_b200_launch_count": (C.c_uint64, []),
+    "fbgemm_b200_spmdm_check_config": (C.c_int, [_cfgp]),
+    "fbgemm_b200_spmdm_launch": (C.c_int, [_p, _cfgp, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, C.c_int, _p]),
+    "fbgemm_b200_status_read": (C.c_int, [_p, C.c_int, _p, C.POINTER(C.c_int32)]),
+    "fbgemm_b200_spmdm": (C.c_int, [_p, _cfgp, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, _p]),
+    "fbgemm_b200_table_register": (C.c_int, [_p, _p, C.c_size_t]),
+    "fbgemm_b200_table_unregister": (C.c_int, [_p, _p]),
+    "fbgemm_b200_table_device_ptr": (_p, [_p, _p]),
+    "fbgemm_b200_spmdm_host_submit": (C.c_int, [_p, C.c_int, _cfgp, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p]),
+    "fbgemm_b200_spmdm_host_wait": (C.c_int, [_p, C.c_int]),
+    "fbgemm_b200_spmdm_host": (C.c_int, [_p, _cfgp, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p]),
+    "fbgemm_b200_float_to_fused_8bit_rowwise": (C.c_int, [_p, _i64, C.c_int32, _p, _p]),
+    "fbgemm_b200_float_to_fused_nbit_rowwise": (C.c_int, [C.c_int32, _p, _i64, C.c_int32, _p, _p]),
+}
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """The loaded library (built first if the sources changed)."""
+    global _lib
+    if _lib is None:
+        path = _build.LIB_PATH
+        if _build.needs_build():
+            try:
+                path = _build.build()
+            except Exception as e:  # no nvcc on this box: use the prebuilt file as is
+                if not os.path.exists(path):
+                    raise Fbgemmb200Error(
+                        f"libfbgemm_b200.so is missing and cannot be built: {e}") from e
+        handle = C.CDLL(path)
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = handle
+    return _lib
+
+
+def last_error() -> str:
+    return lib().fbgemm_b200_last_error().decode()
+
+
+def check(rc: int, what: str) -> int:
+    """Raise on a negative return code; pass 0/1 through."""
+    if rc < 0:
+        raise Fbgemmb200Error(f"{what} failed (code {rc}): {last_error()}")
+    return rc

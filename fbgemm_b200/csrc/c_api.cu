@@ -1,0 +1,830 @@
+// The C ABI of libfbgemm_b200.so: context, status slots, table registry,
+// device-pointer and host-pointer functor calls.  See
+// include/fbgemm_b200/embedding_c_api.h for the contract of each entry point.
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <unordered_map>
+#include <vector>
+
+#include "internal.h"
+
+namespace fbgemm_b200 {
+
+namespace {
+thread_local std::string t_error;
+}
+
+void set_error(const std::string& msg) {
+  t_error = msg;
+}
+
+int fail_cuda(cudaError_t e, const char* what) {
+  set_error(std::string(what) + ": " + cudaGetErrorString(e));
+  return e == cudaErrorMemoryAllocation ? FBGEMM_B200_ENOMEM : FBGEMM_B200_ECUDA;
+}
+
+int max_chunks_per_bag(int bit_rate);  // spmdm_kernels.cu
+
+namespace {
+
+struct DeviceBuffer {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+};
+
+// Grow-only device buffer; contents are not preserved.
+cudaError_t reserve(DeviceBuffer& b, size_t bytes) {
+  if (bytes <= b.bytes) {
+    return cudaSuccess;
+  }
+  if (b.ptr) {
+    cudaFree(b.ptr);
+    b.ptr = nullptr;
+    b.bytes = 0;
+  }
+  const size_t want = bytes + bytes / 4 + 256;
+  cudaError_t e = cudaMalloc(&b.ptr, want);
+  if (e == cudaSuccess) {
+    b.bytes = want;
+  }
+  return e;
+}
+
+struct PinnedBuffer {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+};
+
+cudaError_t reserve(PinnedBuffer& b, size_t bytes) {
+  if (bytes <= b.bytes) {
+    return cudaSuccess;
+  }
+  if (b.ptr) {
+    cudaFreeHost(b.ptr);
+    b.ptr = nullptr;
+    b.bytes = 0;
+  }
+  const size_t want = bytes + bytes / 4 + 256;
+  cudaError_t e = cudaMallocHost(&b.ptr, want);
+  if (e == cudaSuccess) {
+    b.bytes = want;
+  }
+  return e;
+}
+
+// One staging lane of the host-pointer pipeline.
+struct Lane {
+  cudaStream_t stream = nullptr;
+  DeviceBuffer d_in;    // indices | offsets | weights
+  DeviceBuffer d_out;   // pooled rows
+  DeviceBuffer d_scan;  // lengths-mode scratch of this lane
+  PinnedBuffer h_in;
+  PinnedBuffer h_out;
+  PinnedBuffer h_status;
+  bool busy = false;
+  // what to do at wait()
+  void* user_out = nullptr;
+  size_t out_row_bytes = 0;   // bytes of one pooled row (block_size elements)
+  size_t out_pitch_bytes = 0; // bytes between rows in the user's buffer
+  int64_t out_rows = 0;
+  bool trivially_true = false;
+  bool trivially_false = false;
+};
+
+struct Derived {
+  int data_bytes;
+  int sb_bytes;
+  int64_t input_stride;
+  int64_t output_stride;
+};
+
+}  // namespace
+
+}  // namespace fbgemm_b200
+
+using namespace fbgemm_b200;
+
+struct fbgemm_b200_ctx {
+  int device = 0;
+  std::mutex mu;
+  int32_t* status = nullptr;         // device, FBGEMM_B200_STATUS_SLOTS x 4
+  int32_t* status_host = nullptr;    // pinned, same shape (read-back)
+  DeviceBuffer scan;                 // lengths-mode scratch (device-pointer path)
+  std::unordered_map<const void*, DeviceBuffer> tables;
+  Lane lanes[FBGEMM_B200_HOST_LANES];
+};
+
+namespace {
+
+class DeviceGuard {
+ public:
+  explicit DeviceGuard(int dev) {
+    cudaGetDevice(&prev_);
+    if (prev_ != dev) {
+      cudaSetDevice(dev);
+      changed_ = true;
+    }
+  }
+  ~DeviceGuard() {
+    if (changed_) {
+      cudaSetDevice(prev_);
+    }
+  }
+
+ private:
+  int prev_ = 0;
+  bool changed_ = false;
+};
+
+int check_config(const fbgemm_b200_spmdm_config* c, Derived* d) {
+  if (!c) {
+    set_error("null config");
+    return FBGEMM_B200_EINVAL;
+  }
+  if (c->bit_rate != 8 && c->bit_rate != 4 && c->bit_rate != 2) {
+    set_error("bit_rate must be 8, 4 or 2");
+    return FBGEMM_B200_EINVAL;
+  }
+  if ((c->index_bytes != 4 && c->index_bytes != 8) || (c->offset_bytes != 4 && c->offset_bytes != 8)) {
+    set_error("index/offset types must be int32 or int64");
+    return FBGEMM_B200_EINVAL;
+  }
+  if (c->out_dtype != FBGEMM_B200_OUT_F32 && c->out_dtype != FBGEMM_B200_OUT_F16) {
+    set_error("output type must be fp32 or fp16");
+    return FBGEMM_B200_EINVAL;
+  }
+  if (c->block_size <= 0 || c->block_size > (1 << 20)) {
+    set_error("block_size out of range");
+    return FBGEMM_B200_EINVAL;
+  }
+  const int epb = 8 / c->bit_rate;
+  const int64_t data_bytes = (c->block_size + epb - 1) / epb;
+  if ((data_bytes + 3) / 4 > max_chunks_per_bag(c->bit_rate)) {
+    set_error("block_size too large for the sm_100a kernels (1024 columns at most)");
+    return FBGEMM_B200_EINVAL;
+  }
+  const int sb_bytes = c->bit_rate == 8 ? 8 : 4;
+  const int64_t in_stride = c->input_stride == -1 ? data_bytes + sb_bytes : c->input_stride;
+  const int64_t out_stride = c->output_stride == -1 ? c->block_size : c->output_stride;
+  if (in_stride < data_bytes + sb_bytes) {
+    set_error("input_stride smaller than a fused row");
+    return FBGEMM_B200_EINVAL;
+  }
+  if (out_stride < c->block_size) {
+    set_error("output_stride smaller than block_size");
+    return FBGEMM_B200_EINVAL;
+  }
+  if (d) {
+    d->data_bytes = (int)data_bytes;
+    d->sb_bytes = sb_bytes;
+    d->input_stride = in_stride;
+    d->output_stride = out_stride;
+  }
+  return 0;
+}
+
+// Build the kernel parameters for one functor call and enqueue it.  All
+// pointers are device pointers.  `scan` is the scratch for lengths mode.
+int enqueue_lookup(
+    const fbgemm_b200_spmdm_config* cfg,
+    int64_t output_size,
+    int64_t index_size,
+    int64_t data_size,
+    const void* input,
+    const void* indices,
+    const void* offsets_or_lengths,
+    const float* weights,
+    void* out,
+    const int32_t* cit,
+    int32_t* status,
+    DeviceBuffer& scan,
+    cudaStream_t stream) {
+  Derived d;
+  int rc = check_config(cfg, &d);
+  if (rc) {
+    return rc;
+  }
+  if (output_size < 0 || index_size < 0 || data_size < 0) {
+    set_error("negative size");
+    return FBGEMM_B200_EINVAL;
+  }
+  if (cfg->has_weight && !weights && index_size > 0) {
+    set_error("has_weight set but weights is null");
+    return FBGEMM_B200_EINVAL;
+  }
+  if (cit && (cfg->out_dtype != FBGEMM_B200_OUT_F32 || cfg->output_stride != -1 || cfg->input_stride != -1)) {
+    // EmbeddingSpMDMRowWiseSparseKernelSignature: float* out, dense strides.
+    set_error("row-wise sparse lookup takes fp32 output and default strides");
+    return FBGEMM_B200_EINVAL;
+  }
+
+  SpmdmParams p{};
+  p.table = static_cast<const uint8_t*>(input);
+  p.indices = indices;
+  p.weights = cfg->has_weight ? weights : nullptr;
+  p.cit = cit;
+  p.out = out;
+  p.status = status;
+  p.data_size = data_size;
+  p.input_stride = d.input_stride;
+  p.output_stride = d.output_stride;
+  p.output_size = output_size;
+  p.index_size = index_size;
+  p.block_size = (int32_t)cfg->block_size;
+  p.data_bytes = d.data_bytes;
+  p.sb_off = (d.data_bytes + 3) & ~3;
+  p.row_bytes = d.data_bytes + d.sb_bytes;
+  p.pitch = p.sb_off + d.sb_bytes;
+
+  // cp.async granule: the widest of 16/8/4 bytes that divides the table
+  // address, the row pitch and the row width; otherwise byte loads.
+  const uintptr_t base = reinterpret_cast<uintptr_t>(input);
+  p.copy_width = 0;
+  if (d.data_bytes % 4 == 0) {
+    for (int w = 16; w >= 4; w >>= 1) {
+      if (base % w == 0 && d.input_stride % w == 0 && p.row_bytes % w == 0) {
+        p.copy_width = w;
+        break;
+      }
+    }
+  }
+  if (p.copy_width > 4) {
+    p.pitch = (p.pitch + p.copy_width - 1) / p.copy_width * p.copy_width;
+  }
+
+  uint32_t flags = 0;
+  flags |= cfg->index_bytes == 8 ? kIdx64 : 0;
+  flags |= cfg->out_dtype == FBGEMM_B200_OUT_F16 ? kOutHalf : 0;
+  flags |= p.weights ? kWeighted : 0;
+  flags |= (p.weights && cfg->is_weight_positional) ? kPositional : 0;
+  flags |= cfg->normalize_by_lengths ? kNormalize : 0;
+  flags |= cit ? kPruned : 0;
+  const size_t esize = cfg->out_dtype == FBGEMM_B200_OUT_F16 ? 2 : 4;
+  if (reinterpret_cast<uintptr_t>(out) % 16 == 0 && (d.output_stride * esize) % 16 == 0) {
+    flags |= kOutVec;
+  }
+
+  if (cfg->use_offsets) {
+    p.offsets = offsets_or_lengths;
+    flags |= cfg->offset_bytes == 8 ? kOff64 : 0;
+  } else {
+    // lengths -> int64 offsets in scratch
+    const size_t need = ((size_t)output_size + 1 + scan_scratch_elems(output_size)) * sizeof(int64_t);
+    cudaError_t e = reserve(scan, need);
+    if (e != cudaSuccess) {
+      return fail_cuda(e, "scratch for the length scan");
+    }
+    int64_t* offs = static_cast<int64_t*>(scan.ptr);
+    e = launch_length_scan(offsets_or_lengths, cfg->offset_bytes, output_size, offs, offs + output_size + 1, stream);
+    if (e != cudaSuccess) {
+      return fail_cuda(e, "length scan launch");
+    }
+    p.offsets = offs;
+    flags |= kOff64;
+  }
+  p.flags = flags;
+
+  cudaError_t e = launch_spmdm(p, cfg->bit_rate, stream);
+  if (e != cudaSuccess) {
+    return fail_cuda(e, "lookup launch");
+  }
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fbgemm_b200_ctx_create(int device, fbgemm_b200_ctx** out) {
+  if (!out) {
+    set_error("null ctx out");
+    return FBGEMM_B200_EINVAL;
+  }
+  *out = nullptr;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0) {
+    set_error(std::string("no usable CUDA device: ") + cudaGetErrorString(e));
+    return FBGEMM_B200_ECUDA;
+  }
+  if (device < 0 || device >= count) {
+    set_error("device ordinal out of range");
+    return FBGEMM_B200_EINVAL;
+  }
+  cudaDeviceProp prop;
+  e = cudaGetDeviceProperties(&prop, device);
+  if (e != cudaSuccess) {
+    return fail_cuda(e, "cudaGetDeviceProperties");
+  }
+  if (prop.major != 10) {
+    set_error("fbgemm_b200 kernels are built for sm_100a only; device is sm_" + std::to_string(prop.major) +
+              std::to_string(prop.minor));
+    return FBGEMM_B200_ECUDA;
+  }
+  DeviceGuard guard(device);
+  auto* ctx = new (std::nothrow) fbgemm_b200_ctx();
+  if (!ctx) {
+    return FBGEMM_B200_ENOMEM;
+  }
+  ctx->device = device;
+  const size_t sbytes = sizeof(int32_t) * 4 * FBGEMM_B200_STATUS_SLOTS;
+  e = cudaMalloc(&ctx->status, sbytes);
+  if (e == cudaSuccess) {
+    e = cudaMemset(ctx->status, 0, sbytes);
+  }
+  if (e == cudaSuccess) {
+    e = cudaMallocHost(&ctx->status_host, sbytes);
+  }
+  if (e != cudaSuccess) {
+    fbgemm_b200_ctx_destroy(ctx);
+    return fail_cuda(e, "status slots");
+  }
+  *out = ctx;
+  return 0;
+}
+
+void fbgemm_b200_ctx_destroy(fbgemm_b200_ctx* ctx) {
+  if (!ctx) {
+    return;
+  }
+  DeviceGuard guard(ctx->device);
+  cudaDeviceSynchronize();
+  for (auto& l : ctx->lanes) {
+    if (l.stream) {
+      cudaStreamDestroy(l.stream);
+    }
+    cudaFree(l.d_in.ptr);
+    cudaFree(l.d_out.ptr);
+    cudaFree(l.d_scan.ptr);
+    cudaFreeHost(l.h_in.ptr);
+    cudaFreeHost(l.h_out.ptr);
+    cudaFreeHost(l.h_status.ptr);
+  }
+  for (auto& kv : ctx->tables) {
+    cudaFree(kv.second.ptr);
+  }
+  cudaFree(ctx->scan.ptr);
+  cudaFree(ctx->status);
+  cudaFreeHost(ctx->status_host);
+  delete ctx;
+}
+
+const char* fbgemm_b200_last_error(void) {
+  return t_error.c_str();
+}
+
+uint64_t fbgemm_b200_launch_count(void) {
+  return g_launch_count.load(std::memory_order_relaxed);
+}
+
+int fbgemm_b200_spmdm_check_config(const fbgemm_b200_spmdm_config* cfg) {
+  return check_config(cfg, nullptr);
+}
+
+int fbgemm_b200_spmdm_launch(
+    fbgemm_b200_ctx* ctx,
+    const fbgemm_b200_spmdm_config* cfg,
+    int64_t output_size,
+    int64_t index_size,
+    int64_t data_size,
+    const void* input,
+    const void* indices,
+    const void* offsets_or_lengths,
+    const float* weights,
+    void* out,
+    const int32_t* compressed_indices_table,
+    int slot,
+    void* stream) {
+  if (!ctx || slot < 0 || slot >= FBGEMM_B200_STATUS_SLOTS) {
+    set_error("bad context or status slot");
+    return FBGEMM_B200_EINVAL;
+  }
+  DeviceGuard guard(ctx->device);
+  if (output_size == 0) {
+    // No bag to pool: the reference returns `0 == index_size`.
+    int rc = check_config(cfg, nullptr);
+    if (rc) {
+      return rc;
+    }
+    if (index_size != 0) {
+      const int32_t rec[4] = {FBGEMM_B200_STATUS_SIZE_MISMATCH, 0, 0, (int32_t)index_size};
+      cudaError_t e = cudaMemcpyAsync(ctx->status + 4 * slot, rec, sizeof(rec), cudaMemcpyHostToDevice,
+                                      static_cast<cudaStream_t>(stream));
+      if (e != cudaSuccess) {
+        return fail_cuda(e, "status write");
+      }
+    }
+    return 0;
+  }
+  std::unique_lock<std::mutex> lock(ctx->mu, std::defer_lock);
+  if (cfg && !cfg->use_offsets) {
+    lock.lock();  // the scan scratch is shared by device-pointer calls
+  }
+  return enqueue_lookup(cfg, output_size, index_size, data_size, input, indices, offsets_or_lengths, weights, out,
+                        compressed_indices_table, ctx->status + 4 * slot, ctx->scan,
+                        static_cast<cudaStream_t>(stream));
+}
+
+int fbgemm_b200_status_read(fbgemm_b200_ctx* ctx, int slot, void* stream, int32_t* info) {
+  if (!ctx || slot < 0 || slot >= FBGEMM_B200_STATUS_SLOTS) {
+    set_error("bad context or status slot");
+    return FBGEMM_B200_EINVAL;
+  }
+  DeviceGuard guard(ctx->device);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int32_t* h = ctx->status_host + 4 * slot;
+  cudaError_t e = cudaMemcpyAsync(h, ctx->status + 4 * slot, 16, cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) {
+    e = cudaStreamSynchronize(s);
+  }
+  if (e != cudaSuccess) {
+    return fail_cuda(e, "status read");
+  }
+  int32_t rec[4] = {h[0], h[1], h[2], h[3]};
+  if (info) {
+    std::memcpy(info, rec, sizeof(rec));
+  }
+  if (rec[0] != 0) {
+    e = cudaMemsetAsync(ctx->status + 4 * slot, 0, 16, s);
+    if (e != cudaSuccess) {
+      return fail_cuda(e, "status clear");
+    }
+  }
+  return rec[0] == 0 ? 1 : 0;
+}
+
+int fbgemm_b200_spmdm(
+    fbgemm_b200_ctx* ctx,
+    const fbgemm_b200_spmdm_config* cfg,
+    int64_t output_size,
+    int64_t index_size,
+    int64_t data_size,
+    const void* input,
+    const void* indices,
+    const void* offsets_or_lengths,
+    const float* weights,
+    void* out,
+    const int32_t* compressed_indices_table,
+    void* stream) {
+  if (!ctx) {
+    set_error("null context");
+    return FBGEMM_B200_EINVAL;
+  }
+  // Slot 0 is shared by all synchronous calls of this context.
+  static std::mutex sync_mu;
+  std::lock_guard<std::mutex> lock(sync_mu);
+  int rc = fbgemm_b200_spmdm_launch(ctx, cfg, output_size, index_size, data_size, input, indices,
+                                    offsets_or_lengths, weights, out, compressed_indices_table, 0, stream);
+  if (rc) {
+    return rc;
+  }
+  return fbgemm_b200_status_read(ctx, 0, stream, nullptr);
+}
+
+/* ---- table registry ----------------------------------------------------- */
+
+int fbgemm_b200_table_register(fbgemm_b200_ctx* ctx, const void* host_ptr, size_t bytes) {
+  if (!ctx || !host_ptr) {
+    set_error("null context or table");
+    return FBGEMM_B200_EINVAL;
+  }
+  DeviceGuard guard(ctx->device);
+  DeviceBuffer buf;
+  // 16 bytes of slack: no vector access of the last row can leave the buffer.
+  cudaError_t e = cudaMalloc(&buf.ptr, bytes + 16);
+  if (e != cudaSuccess) {
+    return fail_cuda(e, "table allocation");
+  }
+  buf.bytes = bytes;
+  e = cudaMemcpy(buf.ptr, host_ptr, bytes, cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    cudaFree(buf.ptr);
+    return fail_cuda(e, "table upload");
+  }
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  auto it = ctx->tables.find(host_ptr);
+  if (it != ctx->tables.end()) {
+    cudaFree(it->second.ptr);
+    it->second = buf;
+  } else {
+    ctx->tables.emplace(host_ptr, buf);
+  }
+  return 0;
+}
+
+int fbgemm_b200_table_unregister(fbgemm_b200_ctx* ctx, const void* host_ptr) {
+  if (!ctx) {
+    return FBGEMM_B200_EINVAL;
+  }
+  DeviceGuard guard(ctx->device);
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  auto it = ctx->tables.find(host_ptr);
+  if (it == ctx->tables.end()) {
+    set_error("table not registered");
+    return FBGEMM_B200_EINVAL;
+  }
+  cudaDeviceSynchronize();
+  cudaFree(it->second.ptr);
+  ctx->tables.erase(it);
+  return 0;
+}
+
+const void* fbgemm_b200_table_device_ptr(fbgemm_b200_ctx* ctx, const void* host_ptr) {
+  if (!ctx) {
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  auto it = ctx->tables.find(host_ptr);
+  return it == ctx->tables.end() ? nullptr : it->second.ptr;
+}
+
+/* ---- host-pointer pipeline ---------------------------------------------- */
+
+int fbgemm_b200_spmdm_host_submit(
+    fbgemm_b200_ctx* ctx,
+    int lane_id,
+    const fbgemm_b200_spmdm_config* cfg,
+    int64_t output_size,
+    int64_t index_size,
+    int64_t data_size,
+    const void* input,
+    const void* indices,
+    const void* offsets_or_lengths,
+    const float* weights,
+    void* out,
+    const int32_t* cit) {
+  if (!ctx || lane_id < 0 || lane_id >= FBGEMM_B200_HOST_LANES) {
+    set_error("bad context or lane");
+    return FBGEMM_B200_EINVAL;
+  }
+  Derived d;
+  int rc = check_config(cfg, &d);
+  if (rc) {
+    return rc;
+  }
+  if (output_size < 0 || index_size < 0 || data_size < 0) {
+    set_error("negative size");
+    return FBGEMM_B200_EINVAL;
+  }
+  DeviceGuard guard(ctx->device);
+  Lane& L = ctx->lanes[lane_id];
+  if (L.busy) {
+    set_error("lane has work in flight; call fbgemm_b200_spmdm_host_wait first");
+    return FBGEMM_B200_EBUSY;
+  }
+  cudaError_t e;
+  if (!L.stream) {
+    e = cudaStreamCreateWithFlags(&L.stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) {
+      return fail_cuda(e, "lane stream");
+    }
+    e = reserve(L.h_status, 16);
+    if (e != cudaSuccess) {
+      return fail_cuda(e, "lane status");
+    }
+  }
+  L.trivially_true = L.trivially_false = false;
+  L.user_out = out;
+  L.out_rows = 0;
+  if (output_size == 0) {
+    L.trivially_true = index_size == 0;
+    L.trivially_false = !L.trivially_true;
+    L.busy = true;
+    return 0;
+  }
+
+  // Tables live on the device; find (or create) the resident copies.
+  const void* d_table = fbgemm_b200_table_device_ptr(ctx, input);
+  if (!d_table) {
+    const int64_t rows = cit ? 0 : data_size;
+    if (cit) {
+      // The compressed row count is not part of the signature (the reference
+      // has the same gap: FbgemmEmbedding.h:212 "TODO: add compressed_data_size").
+      set_error("pruned lookup: register the compressed table first (its size is not part of the call)");
+      return FBGEMM_B200_EINVAL;
+    }
+    rc = fbgemm_b200_table_register(ctx, input, (size_t)(rows * d.input_stride));
+    if (rc) {
+      return rc;
+    }
+    d_table = fbgemm_b200_table_device_ptr(ctx, input);
+  }
+  const int32_t* d_cit = nullptr;
+  if (cit) {
+    d_cit = static_cast<const int32_t*>(fbgemm_b200_table_device_ptr(ctx, cit));
+    if (!d_cit) {
+      rc = fbgemm_b200_table_register(ctx, cit, (size_t)data_size * sizeof(int32_t));
+      if (rc) {
+        return rc;
+      }
+      d_cit = static_cast<const int32_t*>(fbgemm_b200_table_device_ptr(ctx, cit));
+    }
+  }
+
+  // Pack indices | offsets | weights into one pinned block, one H2D copy.
+  const size_t n_off = (size_t)output_size + (cfg->use_offsets ? 1 : 0);
+  const size_t idx_bytes = (size_t)index_size * cfg->index_bytes;
+  const size_t off_bytes = n_off * cfg->offset_bytes;
+  size_t n_w = 0;
+  if (cfg->has_weight) {
+    if (!weights) {
+      set_error("has_weight set but weights is null");
+      return FBGEMM_B200_EINVAL;
+    }
+    n_w = (size_t)index_size;
+    if (cfg->is_weight_positional) {
+      // weights[i] with i the position inside a bag: the array is only as
+      // long as the longest bag.
+      int64_t longest = 0;
+      for (int64_t m = 0; m < output_size; ++m) {
+        int64_t len;
+        if (cfg->offset_bytes == 8) {
+          const int64_t* o = static_cast<const int64_t*>(offsets_or_lengths);
+          len = cfg->use_offsets ? o[m + 1] - o[m] : o[m];
+        } else {
+          const int32_t* o = static_cast<const int32_t*>(offsets_or_lengths);
+          len = cfg->use_offsets ? (int64_t)o[m + 1] - o[m] : o[m];
+        }
+        longest = len > longest ? len : longest;
+      }
+      n_w = (size_t)(longest < index_size ? longest : index_size);
+    }
+  }
+  auto up16 = [](size_t v) { return (v + 15) & ~size_t(15); };
+  const size_t off_at = up16(idx_bytes);
+  const size_t w_at = off_at + up16(off_bytes);
+  const size_t in_bytes = w_at + up16(n_w * sizeof(float));
+  const size_t esize = cfg->out_dtype == FBGEMM_B200_OUT_F16 ? 2 : 4;
+  // The device copy of the output is dense in block_size-wide rows only when
+  // the user's rows are; otherwise keep the user's pitch.
+  const size_t out_pitch = (size_t)d.output_stride * esize;
+  const size_t out_bytes = (size_t)output_size * out_pitch;
+
+  if ((e = reserve(L.h_in, in_bytes)) != cudaSuccess || (e = reserve(L.d_in, in_bytes)) != cudaSuccess ||
+      (e = reserve(L.d_out, out_bytes)) != cudaSuccess) {
+    return fail_cuda(e, "lane staging buffers");
+  }
+  uint8_t* h = static_cast<uint8_t*>(L.h_in.ptr);
+  if (idx_bytes) {
+    std::memcpy(h, indices, idx_bytes);
+  }
+  std::memcpy(h + off_at, offsets_or_lengths, off_bytes);
+  if (n_w) {
+    std::memcpy(h + w_at, weights, n_w * sizeof(float));
+  }
+  e = cudaMemcpyAsync(L.d_in.ptr, h, in_bytes, cudaMemcpyHostToDevice, L.stream);
+  if (e != cudaSuccess) {
+    return fail_cuda(e, "input upload");
+  }
+  uint8_t* di = static_cast<uint8_t*>(L.d_in.ptr);
+
+  // Status of this lane: the last FBGEMM_B200_HOST_LANES slots of the context.
+  const int slot = FBGEMM_B200_STATUS_SLOTS - FBGEMM_B200_HOST_LANES + lane_id;
+  rc = enqueue_lookup(cfg, output_size, index_size, data_size, d_table, di, di + off_at,
+                      cfg->has_weight ? reinterpret_cast<const float*>(di + w_at) : nullptr, L.d_out.ptr, d_cit,
+                      ctx->status + 4 * slot, L.d_scan, L.stream);
+  if (rc) {
+    return rc;
+  }
+  // Results: into pinned memory when the user's buffer is pageable, so that
+  // the copy stays asynchronous; straight into the user's buffer otherwise.
+  cudaPointerAttributes attr{};
+  const bool user_pinned = cudaPointerGetAttributes(&attr, out) == cudaSuccess && attr.type == cudaMemoryTypeHost;
+  cudaGetLastError();  // pageable memory reports an error on older drivers
+  void* dst = out;
+  if (!user_pinned) {
+    if ((e = reserve(L.h_out, out_bytes)) != cudaSuccess) {
+      return fail_cuda(e, "lane output staging");
+    }
+    dst = L.h_out.ptr;
+    L.out_rows = output_size;
+    L.out_row_bytes = (size_t)cfg->block_size * esize;
+    L.out_pitch_bytes = out_pitch;
+  }
+  const size_t row_bytes = (size_t)cfg->block_size * esize;
+  if (row_bytes == out_pitch) {
+    e = cudaMemcpyAsync(dst, L.d_out.ptr, out_bytes, cudaMemcpyDeviceToHost, L.stream);
+  } else {
+    // Only block_size columns of each row are this call's: the caller's rows
+    // may hold other tables' columns in between (output_stride).
+    e = cudaMemcpy2DAsync(dst, out_pitch, L.d_out.ptr, out_pitch, row_bytes, (size_t)output_size,
+                          cudaMemcpyDeviceToHost, L.stream);
+  }
+  if (e == cudaSuccess) {
+    e = cudaMemcpyAsync(L.h_status.ptr, ctx->status + 4 * slot, 16, cudaMemcpyDeviceToHost, L.stream);
+  }
+  if (e != cudaSuccess) {
+    return fail_cuda(e, "result download");
+  }
+  L.busy = true;
+  return 0;
+}
+
+int fbgemm_b200_spmdm_host_wait(fbgemm_b200_ctx* ctx, int lane_id) {
+  if (!ctx || lane_id < 0 || lane_id >= FBGEMM_B200_HOST_LANES) {
+    set_error("bad context or lane");
+    return FBGEMM_B200_EINVAL;
+  }
+  Lane& L = ctx->lanes[lane_id];
+  if (!L.busy) {
+    set_error("lane has nothing in flight");
+    return FBGEMM_B200_EINVAL;
+  }
+  L.busy = false;
+  if (L.trivially_true) {
+    return 1;
+  }
+  if (L.trivially_false) {
+    return 0;
+  }
+  DeviceGuard guard(ctx->device);
+  cudaError_t e = cudaStreamSynchronize(L.stream);
+  if (e != cudaSuccess) {
+    return fail_cuda(e, "lane synchronize");
+  }
+  if (L.out_rows) {
+    // Only the block_size columns of each row belong to this call: the user's
+    // buffer may hold other tables' columns between them (output_stride).
+    const uint8_t* src = static_cast<const uint8_t*>(L.h_out.ptr);
+    uint8_t* dst = static_cast<uint8_t*>(L.user_out);
+    if (L.out_row_bytes == L.out_pitch_bytes) {
+      std::memcpy(dst, src, (size_t)L.out_rows * L.out_pitch_bytes);
+    } else {
+      for (int64_t r = 0; r < L.out_rows; ++r) {
+        std::memcpy(dst + r * L.out_pitch_bytes, src + r * L.out_pitch_bytes, L.out_row_bytes);
+      }
+    }
+  }
+  const int32_t code = static_cast<const int32_t*>(L.h_status.ptr)[0];
+  if (code != 0) {
+    const int slot = FBGEMM_B200_STATUS_SLOTS - FBGEMM_B200_HOST_LANES + lane_id;
+    cudaMemsetAsync(ctx->status + 4 * slot, 0, 16, L.stream);
+  }
+  return code == 0 ? 1 : 0;
+}
+
+int fbgemm_b200_spmdm_host(
+    fbgemm_b200_ctx* ctx,
+    const fbgemm_b200_spmdm_config* cfg,
+    int64_t output_size,
+    int64_t index_size,
+    int64_t data_size,
+    const void* input,
+    const void* indices,
+    const void* offsets_or_lengths,
+    const float* weights,
+    void* out,
+    const int32_t* compressed_indices_table) {
+  static std::mutex lane0_mu;
+  std::lock_guard<std::mutex> lock(lane0_mu);
+  int rc = fbgemm_b200_spmdm_host_submit(ctx, 0, cfg, output_size, index_size, data_size, input, indices,
+                                         offsets_or_lengths, weights, out, compressed_indices_table);
+  if (rc) {
+    return rc;
+  }
+  return fbgemm_b200_spmdm_host_wait(ctx, 0);
+}
+
+/* ---- quantizers ---------------------------------------------------------- */
+
+int fbgemm_b200_float_to_fused_8bit_rowwise(
+    const float* input,
+    int64_t rows,
+    int32_t cols,
+    uint8_t* output,
+    void* stream) {
+  if (rows < 0 || cols < 0) {
+    set_error("negative shape");
+    return FBGEMM_B200_EINVAL;
+  }
+  if (rows == 0 || cols == 0) {
+    return 0;
+  }
+  cudaError_t e = launch_quantize_8bit(input, rows, cols, output, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? 0 : fail_cuda(e, "8-bit quantizer launch");
+}
+
+int fbgemm_b200_float_to_fused_nbit_rowwise(
+    int32_t bit_rate,
+    const float* input,
+    int64_t rows,
+    int32_t cols,
+    uint8_t* output,
+    void* stream) {
+  if (bit_rate != 2 && bit_rate != 4 && bit_rate != 8) {
+    set_error("bit_rate must be 2, 4 or 8");
+    return FBGEMM_B200_EINVAL;
+  }
+  if (rows < 0 || cols < 0 || cols % (8 / bit_rate) != 0) {
+    set_error("Unsupported number of columns");
+    return FBGEMM_B200_EINVAL;
+  }
+  if (rows == 0 || cols == 0) {
+    return 0;
+  }
+  cudaError_t e = launch_quantize_nbit(bit_rate, input, rows, cols, output, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? 0 : fail_cuda(e, "N-bit quantizer launch");
+}
+
+}  // extern "C"

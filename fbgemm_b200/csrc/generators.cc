@@ -1,0 +1,369 @@
+// The C++ kernel-generator API over the C ABI: explicit instantiations of the
+// templates declared in include/fbgemm_b200/FbgemmEmbedding.h, for the type
+// combinations the reference instantiates for quantized rows
+// (src/EmbeddingSpMDM.cc:1680-1703, src/EmbeddingSpMDMNBit.cc:1461-1484).
+#include <cuda_runtime.h>
+
+#include <map>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <type_traits>
+
+#include "fbgemm_b200/FbgemmEmbedding.h"
+
+namespace fbgemm_b200 {
+
+namespace {
+
+thread_local void* t_stream = nullptr;
+
+std::mutex g_ctx_mu;
+std::map<int, fbgemm_b200_ctx*> g_ctx;
+
+[[noreturn]] void throw_runtime(const char* what) {
+  throw std::runtime_error(std::string(what) + ": " + fbgemm_b200_last_error());
+}
+
+int resolve_device(int device) {
+  if (device >= 0) {
+    return device;
+  }
+  int cur = 0;
+  if (cudaGetDevice(&cur) != cudaSuccess) {
+    throw std::runtime_error("fbgemm_b200: no CUDA device (there is no CPU fallback)");
+  }
+  return cur;
+}
+
+// Device pointers (and managed ones) go straight to the kernel; everything
+// else is host memory and takes the staging path.
+bool on_device(const void* p) {
+  cudaPointerAttributes attr{};
+  if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+}
+
+template <typename OutType>
+constexpr int out_dtype() {
+  static_assert(
+      std::is_same<OutType, float>::value || std::is_same<OutType, std::uint16_t>::value ||
+          std::is_same<OutType, float16>::value,
+      "OutType must be float, uint16_t (fp16 bits) or float16");
+  return std::is_same<OutType, float>::value ? FBGEMM_B200_OUT_F32 : FBGEMM_B200_OUT_F16;
+}
+
+fbgemm_b200_spmdm_config make_config(
+    int bit_rate,
+    int index_bytes,
+    int offset_bytes,
+    int out_dt,
+    std::int64_t block_size,
+    bool has_weight,
+    bool normalize_by_lengths,
+    bool is_weight_positional,
+    bool use_offsets,
+    std::int64_t output_stride,
+    std::int64_t input_stride) {
+  fbgemm_b200_spmdm_config c{};
+  c.bit_rate = bit_rate;
+  c.index_bytes = index_bytes;
+  c.offset_bytes = offset_bytes;
+  c.out_dtype = out_dt;
+  c.block_size = block_size;
+  c.output_stride = output_stride;
+  c.input_stride = input_stride;
+  c.has_weight = has_weight;
+  c.normalize_by_lengths = normalize_by_lengths;
+  c.is_weight_positional = is_weight_positional;
+  c.use_offsets = use_offsets;
+  if (fbgemm_b200_spmdm_check_config(&c) != 0) {
+    throw std::invalid_argument(std::string("fbgemm_b200: ") + fbgemm_b200_last_error());
+  }
+  GetContext(-1);  // fail at generation time when there is no sm_100 device
+  return c;
+}
+
+// One functor call.  Returns the reference's bool; throws on runtime errors
+// (CUDA failures), which have no counterpart in the reference.
+bool call(
+    const fbgemm_b200_spmdm_config& cfg,
+    std::int64_t output_size,
+    std::int64_t index_size,
+    std::int64_t data_size,
+    const void* input,
+    const void* indices,
+    const void* offsets_or_lengths,
+    const float* weights,
+    void* out,
+    const std::int32_t* cit) {
+  fbgemm_b200_ctx* ctx = GetContext(-1);
+  int rc;
+  if (on_device(input)) {
+    rc = fbgemm_b200_spmdm(
+        ctx, &cfg, output_size, index_size, data_size, input, indices, offsets_or_lengths,
+        cfg.has_weight ? weights : nullptr, out, cit, t_stream);
+  } else {
+    rc = fbgemm_b200_spmdm_host(
+        ctx, &cfg, output_size, index_size, data_size, input, indices, offsets_or_lengths,
+        cfg.has_weight ? weights : nullptr, out, cit);
+  }
+  if (rc < 0) {
+    throw_runtime("fbgemm_b200 lookup failed");
+  }
+  return rc == 1;
+}
+
+}  // namespace
+
+void SetStream(void* stream) {
+  t_stream = stream;
+}
+
+fbgemm_b200_ctx* GetContext(int device) {
+  device = resolve_device(device);
+  std::lock_guard<std::mutex> lock(g_ctx_mu);
+  auto it = g_ctx.find(device);
+  if (it != g_ctx.end()) {
+    return it->second;
+  }
+  fbgemm_b200_ctx* ctx = nullptr;
+  if (fbgemm_b200_ctx_create(device, &ctx) != 0) {
+    throw_runtime("fbgemm_b200: cannot create a context (there is no CPU fallback)");
+  }
+  g_ctx[device] = ctx;
+  return ctx;
+}
+
+void RegisterTable(const void* host_table, std::size_t bytes, int device) {
+  if (fbgemm_b200_table_register(GetContext(device), host_table, bytes) != 0) {
+    throw_runtime("fbgemm_b200: table registration failed");
+  }
+}
+
+void InvalidateTable(const void* host_table, int device) {
+  fbgemm_b200_table_unregister(GetContext(device), host_table);
+}
+
+template <typename InType, typename IndexType, typename OffsetType, typename OutType, bool THREAD_LOCAL>
+typename EmbeddingSpMDMKernelSignature<InType, IndexType, OffsetType, OutType>::Type
+GenerateEmbeddingSpMDMWithStrides(
+    const std::int64_t block_size,
+    bool has_weight,
+    bool normalize_by_lengths,
+    int /*prefetch*/,
+    bool is_weight_positional,
+    bool use_offsets,
+    std::int64_t output_stride,
+    std::int64_t input_stride,
+    bool scale_bias_last,
+    bool no_bag,
+    bool is_bf16_out,
+    bool is_bf16_in) {
+  static_assert(std::is_same<InType, std::uint8_t>::value, "only fused 8-bit rows (InType = uint8_t)");
+  if (!scale_bias_last || no_bag || is_bf16_out || is_bf16_in) {
+    throw std::invalid_argument(
+        "fbgemm_b200: scale_bias_last=false, no_bag and bf16 are not provided by the sm_100a path");
+  }
+  const fbgemm_b200_spmdm_config cfg = make_config(
+      8, sizeof(IndexType), sizeof(OffsetType), out_dtype<OutType>(), block_size, has_weight,
+      normalize_by_lengths, is_weight_positional, use_offsets, output_stride, input_stride);
+  return [cfg](
+             std::int64_t output_size,
+             std::int64_t index_size,
+             std::int64_t data_size,
+             const InType* input,
+             const IndexType* indices,
+             const OffsetType* offsets_or_lengths,
+             const float* weights,
+             OutType* out) {
+    return call(cfg, output_size, index_size, data_size, input, indices, offsets_or_lengths, weights, out, nullptr);
+  };
+}
+
+template <typename InType, typename IndexType, typename OffsetType, typename OutType, bool THREAD_LOCAL>
+typename EmbeddingSpMDMKernelSignature<InType, IndexType, OffsetType, OutType>::Type GenerateEmbeddingSpMDM(
+    const std::int64_t block_size,
+    bool has_weight,
+    bool normalize_by_lengths,
+    int prefetch,
+    bool is_weight_positional,
+    bool use_offsets,
+    bool is_bf16_out,
+    bool is_bf16_in) {
+  return GenerateEmbeddingSpMDMWithStrides<InType, IndexType, OffsetType, OutType, THREAD_LOCAL>(
+      block_size, has_weight, normalize_by_lengths, prefetch, is_weight_positional, use_offsets, -1, -1, true,
+      false, is_bf16_out, is_bf16_in);
+}
+
+template <typename IndexType, typename OffsetType, typename OutType, bool THREAD_LOCAL>
+typename EmbeddingSpMDMKernelSignature<std::uint8_t, IndexType, OffsetType, OutType>::Type
+GenerateEmbeddingSpMDMNBitWithStrides(
+    const int input_bit_rate,
+    const std::int64_t block_size,
+    bool has_weight,
+    bool normalize_by_lengths,
+    int /*prefetch*/,
+    bool is_weight_positional,
+    bool use_offsets,
+    std::int64_t output_stride,
+    std::int64_t input_stride,
+    bool scale_bias_last,
+    const bool is_bf16_out,
+    const bool no_bag,
+    int output_bit_rate) {
+  if (input_bit_rate != 2 && input_bit_rate != 4) {
+    throw std::invalid_argument("fbgemm_b200: bit_rate must be 2 or 4");
+  }
+  if (!scale_bias_last || no_bag || is_bf16_out ||
+      (output_bit_rate != -1 && output_bit_rate != (int)(8 * sizeof(OutType)))) {
+    throw std::invalid_argument(
+        "fbgemm_b200: scale_bias_last=false, no_bag, bf16 and N-bit output are not provided by the sm_100a path");
+  }
+  const fbgemm_b200_spmdm_config cfg = make_config(
+      input_bit_rate, sizeof(IndexType), sizeof(OffsetType), out_dtype<OutType>(), block_size, has_weight,
+      normalize_by_lengths, is_weight_positional, use_offsets, output_stride, input_stride);
+  return [cfg](
+             std::int64_t output_size,
+             std::int64_t index_size,
+             std::int64_t data_size,
+             const std::uint8_t* input,
+             const IndexType* indices,
+             const OffsetType* offsets_or_lengths,
+             const float* weights,
+             OutType* out) {
+    return call(cfg, output_size, index_size, data_size, input, indices, offsets_or_lengths, weights, out, nullptr);
+  };
+}
+
+template <typename IndexType, typename OffsetType, typename OutType>
+typename EmbeddingSpMDMKernelSignature<std::uint8_t, IndexType, OffsetType, OutType>::Type
+GenerateEmbeddingSpMDMNBit(
+    int bit_rate,
+    const std::int64_t block_size,
+    bool has_weight,
+    bool normalize_by_lengths,
+    int prefetch,
+    bool is_weight_positional,
+    bool use_offsets) {
+  return GenerateEmbeddingSpMDMNBitWithStrides<IndexType, OffsetType, OutType, false>(
+      bit_rate, block_size, has_weight, normalize_by_lengths, prefetch, is_weight_positional, use_offsets, -1, -1,
+      true, false, false, -1);
+}
+
+template <typename InType, typename IndexType, typename OffsetType>
+typename EmbeddingSpMDMRowWiseSparseKernelSignature<InType, IndexType, OffsetType>::Type
+GenerateEmbeddingSpMDMRowWiseSparse(
+    const std::int64_t block_size,
+    bool has_weight,
+    bool normalize_by_lengths,
+    int /*prefetch*/,
+    bool is_weight_positional,
+    bool use_offsets) {
+  static_assert(std::is_same<InType, std::uint8_t>::value, "only fused 8-bit rows (InType = uint8_t)");
+  const fbgemm_b200_spmdm_config cfg = make_config(
+      8, sizeof(IndexType), sizeof(OffsetType), FBGEMM_B200_OUT_F32, block_size, has_weight, normalize_by_lengths,
+      is_weight_positional, use_offsets, -1, -1);
+  return [cfg](
+             std::int64_t output_size,
+             std::int64_t index_size,
+             std::int64_t uncompressed_data_size,
+             const InType* input,
+             const IndexType* indices,
+             const OffsetType* offsets_or_lengths,
+             const float* weights,
+             float* out,
+             const std::int32_t* compressed_indices_table) {
+    if (!compressed_indices_table) {
+      throw std::invalid_argument("fbgemm_b200: compressed_indices_table is null");
+    }
+    return call(
+        cfg, output_size, index_size, uncompressed_data_size, input, indices, offsets_or_lengths, weights, out,
+        compressed_indices_table);
+  };
+}
+
+template <typename IndexType, typename OffsetType>
+typename EmbeddingSpMDMRowWiseSparseKernelSignature<std::uint8_t, IndexType, OffsetType>::Type
+GenerateEmbeddingSpMDMNBitRowWiseSparse(
+    int bit_rate,
+    const std::int64_t block_size,
+    bool has_weight,
+    bool normalize_by_lengths,
+    int /*prefetch*/,
+    bool is_weight_positional,
+    bool use_offsets) {
+  if (bit_rate != 2 && bit_rate != 4) {
+    throw std::invalid_argument("fbgemm_b200: bit_rate must be 2 or 4");
+  }
+  const fbgemm_b200_spmdm_config cfg = make_config(
+      bit_rate, sizeof(IndexType), sizeof(OffsetType), FBGEMM_B200_OUT_F32, block_size, has_weight,
+      normalize_by_lengths, is_weight_positional, use_offsets, -1, -1);
+  return [cfg](
+             std::int64_t output_size,
+             std::int64_t index_size,
+             std::int64_t uncompressed_data_size,
+             const std::uint8_t* input,
+             const IndexType* indices,
+             const OffsetType* offsets_or_lengths,
+             const float* weights,
+             float* out,
+             const std::int32_t* compressed_indices_table) {
+    if (!compressed_indices_table) {
+      throw std::invalid_argument("fbgemm_b200: compressed_indices_table is null");
+    }
+    return call(
+        cfg, output_size, index_size, uncompressed_data_size, input, indices, offsets_or_lengths, weights, out,
+        compressed_indices_table);
+  };
+}
+
+// ---- explicit instantiations -------------------------------------------------
+
+#define INST_8BIT(IDX, OFF, OUT, TL)                                                                           \
+  template FBGEMM_B200_API typename EmbeddingSpMDMKernelSignature<std::uint8_t, IDX, OFF, OUT>::Type           \
+  GenerateEmbeddingSpMDM<std::uint8_t, IDX, OFF, OUT, TL>(                                                     \
+      const std::int64_t, bool, bool, int, bool, bool, bool, bool);                                            \
+  template FBGEMM_B200_API typename EmbeddingSpMDMKernelSignature<std::uint8_t, IDX, OFF, OUT>::Type           \
+  GenerateEmbeddingSpMDMWithStrides<std::uint8_t, IDX, OFF, OUT, TL>(                                          \
+      const std::int64_t, bool, bool, int, bool, bool, std::int64_t, std::int64_t, bool, bool, bool, bool);
+
+#define INST_NBIT(IDX, OFF, OUT)                                                                               \
+  template FBGEMM_B200_API typename EmbeddingSpMDMKernelSignature<std::uint8_t, IDX, OFF, OUT>::Type           \
+  GenerateEmbeddingSpMDMNBit<IDX, OFF, OUT>(int, const std::int64_t, bool, bool, int, bool, bool);             \
+  template FBGEMM_B200_API typename EmbeddingSpMDMKernelSignature<std::uint8_t, IDX, OFF, OUT>::Type           \
+  GenerateEmbeddingSpMDMNBitWithStrides<IDX, OFF, OUT, false>(                                                 \
+      const int, const std::int64_t, bool, bool, int, bool, bool, std::int64_t, std::int64_t, bool, const bool, \
+      const bool, int);                                                                                        \
+  template FBGEMM_B200_API typename EmbeddingSpMDMKernelSignature<std::uint8_t, IDX, OFF, OUT>::Type           \
+  GenerateEmbeddingSpMDMNBitWithStrides<IDX, OFF, OUT, true>(                                                  \
+      const int, const std::int64_t, bool, bool, int, bool, bool, std::int64_t, std::int64_t, bool, const bool, \
+      const bool, int);
+
+#define INST_SPARSE(IDX, OFF)                                                                                  \
+  template FBGEMM_B200_API typename EmbeddingSpMDMRowWiseSparseKernelSignature<std::uint8_t, IDX, OFF>::Type   \
+  GenerateEmbeddingSpMDMRowWiseSparse<std::uint8_t, IDX, OFF>(const std::int64_t, bool, bool, int, bool, bool); \
+  template FBGEMM_B200_API typename EmbeddingSpMDMRowWiseSparseKernelSignature<std::uint8_t, IDX, OFF>::Type   \
+  GenerateEmbeddingSpMDMNBitRowWiseSparse<IDX, OFF>(int, const std::int64_t, bool, bool, int, bool, bool);
+
+#define INST_OUT(IDX, OFF)                 \
+  INST_8BIT(IDX, OFF, float, false)        \
+  INST_8BIT(IDX, OFF, float, true)         \
+  INST_8BIT(IDX, OFF, std::uint16_t, false) \
+  INST_8BIT(IDX, OFF, std::uint16_t, true) \
+  INST_8BIT(IDX, OFF, float16, false)      \
+  INST_8BIT(IDX, OFF, float16, true)       \
+  INST_NBIT(IDX, OFF, float)               \
+  INST_NBIT(IDX, OFF, std::uint16_t)       \
+  INST_NBIT(IDX, OFF, float16)             \
+  INST_SPARSE(IDX, OFF)
+
+INST_OUT(std::int32_t, std::int32_t)
+INST_OUT(std::int32_t, std::int64_t)
+INST_OUT(std::int64_t, std::int32_t)
+INST_OUT(std::int64_t, std::int64_t)
+
+}  // namespace fbgemm_b200

@@ -1,0 +1,77 @@
+// Declarations shared by the translation units of libfbgemm_b200.so.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdint>
+#include <string>
+
+#include "fbgemm_b200/embedding_c_api.h"
+
+namespace fbgemm_b200 {
+
+// Flag bits of SpmdmParams::flags.
+enum : uint32_t {
+  kIdx64 = 1u << 0,       // indices are int64 (else int32)
+  kOff64 = 1u << 1,       // offsets are int64 (else int32)
+  kOutHalf = 1u << 2,     // fp16 output (else fp32)
+  kWeighted = 1u << 3,    // per-sample weights present
+  kPositional = 1u << 4,  // weights indexed by position inside the bag
+  kNormalize = 1u << 5,   // multiply the pooled row by 1/len
+  kPruned = 1u << 6,      // indices go through compressed_indices_table
+  kOutVec = 1u << 7,      // output rows allow vector stores
+};
+
+// Everything one lookup launch needs; passed by value to the kernel.
+struct SpmdmParams {
+  const uint8_t* table;       // fused rows
+  const void* indices;        // int32/int64 [index_size]
+  const void* offsets;        // int32/int64 [output_size + 1]
+  const float* weights;       // [index_size] or positional, may be null
+  const int32_t* cit;         // compressed_indices_table or null
+  void* out;                  // fp32/fp16 [output_size x output_stride]
+  int32_t* status;            // {code, bag, position, value}
+  int64_t data_size;          // rows an index may address
+  int64_t input_stride;       // bytes between table rows
+  int64_t output_stride;      // elements between output rows
+  int64_t output_size;        // bags
+  int64_t index_size;         // indices
+  int32_t block_size;         // D
+  int32_t data_bytes;         // packed payload bytes per row
+  int32_t sb_off;             // offset of scale,bias inside a staged row
+  int32_t row_bytes;          // payload + scale,bias bytes actually read
+  int32_t pitch;              // bytes between staged rows in shared memory
+  int32_t rows_per_wave;      // rows one bag stages at a time
+  int32_t group_smem;         // shared-memory bytes per bag slot
+  int32_t copy_width;         // 16/8/4: cp.async granule; 0: byte-wise path
+  uint32_t flags;
+};
+
+// One lookup kernel launch (spmdm_kernels.cu).  Returns cudaSuccess or the
+// launch error; never synchronises.
+cudaError_t launch_spmdm(const SpmdmParams& p, int bit_rate, cudaStream_t stream);
+
+// Exclusive scan of `n` int32/int64 lengths into int64 offsets[n + 1]
+// (scan_kernels.cu).  `block_sums` is scratch of scan_scratch_elems(n) int64.
+size_t scan_scratch_elems(int64_t n);
+cudaError_t launch_length_scan(
+    const void* lengths,
+    int length_bytes,
+    int64_t n,
+    int64_t* offsets,
+    int64_t* block_sums,
+    cudaStream_t stream);
+
+// Row-wise quantizers (quantize_kernels.cu).
+cudaError_t launch_quantize_8bit(const float* in, int64_t rows, int cols, uint8_t* out, cudaStream_t s);
+cudaError_t launch_quantize_nbit(int bit_rate, const float* in, int64_t rows, int cols, uint8_t* out, cudaStream_t s);
+
+// Process-wide count of kernels launched by this library.
+extern std::atomic<uint64_t> g_launch_count;
+
+// Thread-local error text behind fbgemm_b200_last_error().
+void set_error(const std::string& msg);
+int fail_cuda(cudaError_t e, const char* what);
+
+}  // namespace fbgemm_b200

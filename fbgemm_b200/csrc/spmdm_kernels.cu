@@ -1,0 +1,481 @@
+// Pooled lookup over fused row-wise quantized tables (8-, 4- and 2-bit) for
+// sm_100a.  Stands in for the x86 code FBGEMM generates at run time
+// (src/EmbeddingSpMDM.cc:161-968, src/EmbeddingSpMDMNBit.cc:149-971) and
+// follows the arithmetic of its scalar reference
+// (src/RefImplementations.cc:1290-1346, :1485-1541, :1746-1822) operation for
+// operation, so that fp32 results are bit-equal:
+//
+//     acc[j] = fma(w*scale, q[j], acc[j] + w*bias)    rows in index order
+//
+// Scheduling.  A bag is owned by a group of LPB lanes (8, 16 or a full warp,
+// chosen from the row width), so a warp pools 4, 2 or 1 bags at once and the
+// rows of one bag are accumulated strictly in order (no cross-lane reduction:
+// that would change the rounding).  What IS parallel inside a bag is the
+// memory traffic: a wave of up to `rows_per_wave` rows is copied from HBM/L2
+// into the group's shared-memory stage with cp.async, all rows in flight at
+// once, every lane of the group issuing a slice of the flat word list.  Only
+// then are the staged rows walked in order: each lane owns CPL 4-byte chunks
+// of the packed payload (4, 8 or 16 columns each), unpacks them with byte
+// permutes into exact fp32 integers and applies the two roundings above.
+//
+// The kernel is HBM/L2-latency bound (about 2 flop per byte); tensor cores
+// have no role here.
+#include <cuda_fp16.h>
+
+#include <cstdlib>
+
+#include "internal.h"
+
+namespace fbgemm_b200 {
+
+namespace {
+
+constexpr int kWarpsPerBlock = 4;
+constexpr int kThreads = kWarpsPerBlock * 32;
+
+__device__ __forceinline__ int64_t load_int(const void* p, int64_t i, bool is64) {
+  return is64 ? (int64_t)__ldg(reinterpret_cast<const long long*>(p) + i)
+              : (int64_t)__ldg(reinterpret_cast<const int*>(p) + i);
+}
+
+// First error wins; the rest of the record is diagnostics only.
+__device__ __noinline__ void report(int32_t* st, int code, int64_t bag, int64_t pos, int64_t val) {
+  if (atomicCAS(st, 0, code) == 0) {
+    st[1] = (int32_t)bag;
+    st[2] = (int32_t)pos;
+    st[3] = (int32_t)val;
+  }
+}
+
+template <int W>
+__device__ __forceinline__ void cp_async(uint32_t dst, const void* src) {
+  if constexpr (W == 16) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+  } else if constexpr (W == 8) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(dst), "l"(src) : "memory");
+  } else {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src) : "memory");
+  }
+}
+
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.wait_all;\n" ::: "memory");
+}
+
+// Copy rows [0, n) of the wave into the stage.  The rows are seen as one flat
+// list of W-byte words; lane `gl` of `lpb` takes words gl, gl+lpb, ...
+template <int W>
+__device__ __forceinline__ void stage_rows(
+    const SpmdmParams& p,
+    uint8_t* s_rows,
+    const long long* s_off,
+    int n,
+    int gl,
+    int lpb) {
+  const int wpr = p.row_bytes / W;  // words per row
+  const int drow = lpb / wpr;
+  const int dw = lpb - drow * wpr;
+  int row = gl / wpr;
+  int w = gl - row * wpr;
+  const uint32_t s_base = (uint32_t)__cvta_generic_to_shared(s_rows);
+  while (row < n) {
+    const long long off = s_off[row];
+    if (off >= 0) {
+      cp_async<W>(s_base + row * p.pitch + w * W, p.table + off + w * W);
+    }
+    w += dw;
+    row += drow;
+    if (w >= wpr) {
+      w -= wpr;
+      ++row;
+    }
+  }
+}
+
+// Rows whose address, pitch or width is not a multiple of 4 bytes: plain byte
+// loads.  The payload lands at [0, data_bytes), scale,bias at sb_off.
+__device__ __forceinline__ void stage_rows_bytewise(
+    const SpmdmParams& p,
+    uint8_t* s_rows,
+    const long long* s_off,
+    int n,
+    int gl,
+    int lpb) {
+  const int total = n * p.row_bytes;
+  for (int k = gl; k < total; k += lpb) {
+    const int row = k / p.row_bytes;
+    const int b = k - row * p.row_bytes;
+    const long long off = s_off[row];
+    if (off >= 0) {
+      const int dst = b < p.data_bytes ? b : p.sb_off + (b - p.data_bytes);
+      s_rows[row * p.pitch + dst] = __ldg(p.table + off + b);
+    }
+  }
+}
+
+// Byte `i` of x as an exact fp32 integer: the byte is planted in the mantissa
+// of 2^23 and 2^23 is subtracted.
+template <int I>
+__device__ __forceinline__ float byte_to_float(uint32_t x) {
+  return __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7540u | I)) - 8388608.0f;
+}
+
+__device__ __forceinline__ float pool(float acc, float q, float scale, float bias) {
+  // Two roundings, as in std::fma(scale, q, buf[j] + bias).
+  return __fmaf_rn(scale, q, __fadd_rn(acc, bias));
+}
+
+template <int BITS>
+__device__ __forceinline__ void accumulate(float* acc, uint32_t x, float scale, float bias) {
+  if constexpr (BITS == 8) {
+    acc[0] = pool(acc[0], byte_to_float<0>(x), scale, bias);
+    acc[1] = pool(acc[1], byte_to_float<1>(x), scale, bias);
+    acc[2] = pool(acc[2], byte_to_float<2>(x), scale, bias);
+    acc[3] = pool(acc[3], byte_to_float<3>(x), scale, bias);
+  } else if constexpr (BITS == 4) {
+    // element 2k is the low nibble of byte k, element 2k+1 the high nibble
+    const uint32_t lo = x & 0x0F0F0F0Fu;
+    const uint32_t hi = (x >> 4) & 0x0F0F0F0Fu;
+    acc[0] = pool(acc[0], byte_to_float<0>(lo), scale, bias);
+    acc[1] = pool(acc[1], byte_to_float<0>(hi), scale, bias);
+    acc[2] = pool(acc[2], byte_to_float<1>(lo), scale, bias);
+    acc[3] = pool(acc[3], byte_to_float<1>(hi), scale, bias);
+    acc[4] = pool(acc[4], byte_to_float<2>(lo), scale, bias);
+    acc[5] = pool(acc[5], byte_to_float<2>(hi), scale, bias);
+    acc[6] = pool(acc[6], byte_to_float<3>(lo), scale, bias);
+    acc[7] = pool(acc[7], byte_to_float<3>(hi), scale, bias);
+  } else {
+    // element 4k+i sits in bits [2i+1 : 2i] of byte k
+    const uint32_t t0 = x & 0x03030303u;
+    const uint32_t t1 = (x >> 2) & 0x03030303u;
+    const uint32_t t2 = (x >> 4) & 0x03030303u;
+    const uint32_t t3 = (x >> 6) & 0x03030303u;
+    acc[0] = pool(acc[0], byte_to_float<0>(t0), scale, bias);
+    acc[1] = pool(acc[1], byte_to_float<0>(t1), scale, bias);
+    acc[2] = pool(acc[2], byte_to_float<0>(t2), scale, bias);
+    acc[3] = pool(acc[3], byte_to_float<0>(t3), scale, bias);
+    acc[4] = pool(acc[4], byte_to_float<1>(t0), scale, bias);
+    acc[5] = pool(acc[5], byte_to_float<1>(t1), scale, bias);
+    acc[6] = pool(acc[6], byte_to_float<1>(t2), scale, bias);
+    acc[7] = pool(acc[7], byte_to_float<1>(t3), scale, bias);
+    acc[8] = pool(acc[8], byte_to_float<2>(t0), scale, bias);
+    acc[9] = pool(acc[9], byte_to_float<2>(t1), scale, bias);
+    acc[10] = pool(acc[10], byte_to_float<2>(t2), scale, bias);
+    acc[11] = pool(acc[11], byte_to_float<2>(t3), scale, bias);
+    acc[12] = pool(acc[12], byte_to_float<3>(t0), scale, bias);
+    acc[13] = pool(acc[13], byte_to_float<3>(t1), scale, bias);
+    acc[14] = pool(acc[14], byte_to_float<3>(t2), scale, bias);
+    acc[15] = pool(acc[15], byte_to_float<3>(t3), scale, bias);
+  }
+}
+
+template <int COLS>
+__device__ __forceinline__ void store_chunk(
+    const SpmdmParams& p,
+    int64_t bag,
+    int col0,
+    const float* v) {
+  const bool full = col0 + COLS <= p.block_size;
+  if (p.flags & kOutHalf) {
+    __half* o = reinterpret_cast<__half*>(p.out) + bag * p.output_stride + col0;
+    if (full && (p.flags & kOutVec)) {
+      uint32_t w[COLS / 2];
+#pragma unroll
+      for (int i = 0; i < COLS / 2; ++i) {
+        const __half2 h = __halves2half2(__float2half_rn(v[2 * i]), __float2half_rn(v[2 * i + 1]));
+        w[i] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+      if constexpr (COLS == 4) {
+        *reinterpret_cast<uint2*>(o) = make_uint2(w[0], w[1]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < COLS / 8; ++i) {
+          reinterpret_cast<uint4*>(o)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < COLS; ++i) {
+        if (col0 + i < p.block_size) {
+          o[i] = __float2half_rn(v[i]);
+        }
+      }
+    }
+  } else {
+    float* o = reinterpret_cast<float*>(p.out) + bag * p.output_stride + col0;
+    if (full && (p.flags & kOutVec)) {
+#pragma unroll
+      for (int i = 0; i < COLS / 4; ++i) {
+        reinterpret_cast<float4*>(o)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < COLS; ++i) {
+        if (col0 + i < p.block_size) {
+          o[i] = v[i];
+        }
+      }
+    }
+  }
+}
+
+// BITS: 8, 4, 2.  LPB: lanes per bag.  CPL: 4-byte payload chunks per lane.
+template <int BITS, int LPB, int CPL>
+__global__ void __launch_bounds__(kThreads)
+spmdm_kernel(const __grid_constant__ SpmdmParams p) {
+  constexpr int GPW = 32 / LPB;    // bags per warp
+  constexpr int COLS = 32 / BITS;  // columns per 4-byte chunk
+  extern __shared__ __align__(16) uint8_t smem[];
+
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int grp = lane / LPB;
+  const int gl = lane % LPB;
+  const unsigned gmask = LPB == 32 ? 0xffffffffu : (((1u << LPB) - 1u) << (grp * LPB));
+  const bool idx64 = p.flags & kIdx64;
+  const bool off64 = p.flags & kOff64;
+  const bool weighted = p.flags & kWeighted;
+  const bool positional = p.flags & kPositional;
+  const bool pruned = p.flags & kPruned;
+
+  const int64_t off_base = load_int(p.offsets, 0, off64);
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    // `return current == index_size` of the reference
+    const int64_t total = load_int(p.offsets, p.output_size, off64) - off_base;
+    if (total != p.index_size) {
+      report(p.status, FBGEMM_B200_STATUS_SIZE_MISMATCH, p.output_size, total, p.index_size);
+    }
+  }
+
+  const int64_t bag = ((int64_t)blockIdx.x * kWarpsPerBlock + warp) * GPW + grp;
+  if (bag >= p.output_size) {
+    return;
+  }
+
+  const int64_t o0 = load_int(p.offsets, bag, off64);
+  const int64_t o1 = load_int(p.offsets, bag + 1, off64);
+  const int64_t start = o0 - off_base;
+  const int bag_len = (int)(o1 - o0);  // the reference narrows to 32 bits too
+  int len = bag_len < 0 ? 0 : bag_len;
+  if (start < 0 || start + len > p.index_size) {
+    if (gl == 0) {
+      report(p.status, FBGEMM_B200_STATUS_BAG_OVERRUN, bag, start, len);
+    }
+    len = 0;  // never read past the caller's arrays
+  }
+
+  const int S = p.rows_per_wave;
+  uint8_t* s_rows = smem + (size_t)(warp * GPW + grp) * p.group_smem;
+  long long* s_off = reinterpret_cast<long long*>(s_rows + ((S * p.pitch + 15) & ~15));
+  float* s_w = reinterpret_cast<float*>(s_off + S);
+  const int nchunks = (p.data_bytes + 3) >> 2;
+
+  float acc[CPL][COLS];
+#pragma unroll
+  for (int ci = 0; ci < CPL; ++ci) {
+#pragma unroll
+    for (int j = 0; j < COLS; ++j) {
+      acc[ci][j] = 0.f;
+    }
+  }
+
+  for (int wave0 = 0; wave0 < len; wave0 += S) {
+    const int n = min(S, len - wave0);
+
+    // 1. indices (and the pruning map, and weights) of this wave
+    for (int r = gl; r < n; r += LPB) {
+      const int64_t pos = start + wave0 + r;
+      int64_t idx = load_int(p.indices, pos, idx64);
+      long long off = -1;
+      if (idx < 0 || idx >= p.data_size) {
+        report(p.status, FBGEMM_B200_STATUS_BAD_INDEX, bag, pos, idx);
+      } else {
+        if (pruned) {
+          idx = __ldg(p.cit + idx);  // -1: pruned row, contributes nothing
+        }
+        if (idx >= 0) {
+          off = idx * p.input_stride;
+        }
+      }
+      s_off[r] = off;
+      if (weighted) {
+        s_w[r] = __ldg(p.weights + (positional ? (int64_t)(wave0 + r) : pos));
+      }
+    }
+    __syncwarp(gmask);
+
+    // 2. all rows of the wave in flight at once
+    if (p.copy_width == 4) {
+      stage_rows<4>(p, s_rows, s_off, n, gl, LPB);
+    } else if (p.copy_width == 8) {
+      stage_rows<8>(p, s_rows, s_off, n, gl, LPB);
+    } else if (p.copy_width == 16) {
+      stage_rows<16>(p, s_rows, s_off, n, gl, LPB);
+    } else {
+      stage_rows_bytewise(p, s_rows, s_off, n, gl, LPB);
+    }
+    cp_async_wait_all();
+    __syncwarp(gmask);
+
+    // 3. pool the staged rows in index order
+    for (int r = 0; r < n; ++r) {
+      if (s_off[r] < 0) {
+        continue;
+      }
+      const uint8_t* srow = s_rows + r * p.pitch;
+      float scale, bias;
+      if constexpr (BITS == 8) {
+        scale = *reinterpret_cast<const float*>(srow + p.sb_off);
+        bias = *reinterpret_cast<const float*>(srow + p.sb_off + 4);
+      } else {
+        const uint32_t sb = *reinterpret_cast<const uint32_t*>(srow + p.sb_off);
+        scale = __half2float(__ushort_as_half((unsigned short)(sb & 0xffffu)));
+        bias = __half2float(__ushort_as_half((unsigned short)(sb >> 16)));
+      }
+      if (weighted) {
+        const float w = s_w[r];
+        scale = __fmul_rn(w, scale);
+        bias = __fmul_rn(w, bias);
+      }
+#pragma unroll
+      for (int ci = 0; ci < CPL; ++ci) {
+        const int c = gl + ci * LPB;
+        if (c < nchunks) {
+          const uint32_t x = *reinterpret_cast<const uint32_t*>(srow + 4 * c);
+          accumulate<BITS>(acc[ci], x, scale, bias);
+        }
+      }
+    }
+    __syncwarp(gmask);
+  }
+
+  if ((p.flags & kNormalize) && bag_len != 0) {
+    const float inv = __fdiv_rn(1.f, (float)bag_len);
+#pragma unroll
+    for (int ci = 0; ci < CPL; ++ci) {
+#pragma unroll
+      for (int j = 0; j < COLS; ++j) {
+        acc[ci][j] = __fmul_rn(acc[ci][j], inv);
+      }
+    }
+  }
+
+#pragma unroll
+  for (int ci = 0; ci < CPL; ++ci) {
+    const int c = gl + ci * LPB;
+    if (c < nchunks) {
+      store_chunk<COLS>(p, bag, c * COLS, acc[ci]);
+    }
+  }
+}
+
+using KernelFn = void (*)(const SpmdmParams);
+
+struct Variant {
+  KernelFn fn;
+  int lpb;
+  int cpl;
+};
+
+template <int BITS>
+const Variant* variants(int* count) {
+  if constexpr (BITS == 8) {
+    static const Variant v[] = {
+        {spmdm_kernel<8, 8, 1>, 8, 1},   {spmdm_kernel<8, 16, 1>, 16, 1}, {spmdm_kernel<8, 32, 1>, 32, 1},
+        {spmdm_kernel<8, 8, 2>, 8, 2},   {spmdm_kernel<8, 16, 2>, 16, 2}, {spmdm_kernel<8, 32, 2>, 32, 2},
+        {spmdm_kernel<8, 8, 4>, 8, 4},   {spmdm_kernel<8, 16, 4>, 16, 4}, {spmdm_kernel<8, 32, 4>, 32, 4},
+        {spmdm_kernel<8, 32, 8>, 32, 8},
+    };
+    *count = sizeof(v) / sizeof(v[0]);
+    return v;
+  } else if constexpr (BITS == 4) {
+    static const Variant v[] = {
+        {spmdm_kernel<4, 8, 1>, 8, 1}, {spmdm_kernel<4, 16, 1>, 16, 1}, {spmdm_kernel<4, 32, 1>, 32, 1},
+        {spmdm_kernel<4, 8, 2>, 8, 2}, {spmdm_kernel<4, 16, 2>, 16, 2}, {spmdm_kernel<4, 32, 2>, 32, 2},
+        {spmdm_kernel<4, 8, 4>, 8, 4}, {spmdm_kernel<4, 16, 4>, 16, 4}, {spmdm_kernel<4, 32, 4>, 32, 4},
+    };
+    *count = sizeof(v) / sizeof(v[0]);
+    return v;
+  } else {
+    static const Variant v[] = {
+        {spmdm_kernel<2, 8, 1>, 8, 1}, {spmdm_kernel<2, 16, 1>, 16, 1}, {spmdm_kernel<2, 32, 1>, 32, 1},
+        {spmdm_kernel<2, 8, 2>, 8, 2}, {spmdm_kernel<2, 16, 2>, 16, 2}, {spmdm_kernel<2, 32, 2>, 32, 2},
+    };
+    *count = sizeof(v) / sizeof(v[0]);
+    return v;
+  }
+}
+
+int env_int(const char* name, int dflt) {
+  const char* s = std::getenv(name);
+  return (s && *s) ? std::atoi(s) : dflt;
+}
+
+}  // namespace
+
+std::atomic<uint64_t> g_launch_count{0};
+
+int max_chunks_per_bag(int bit_rate) {
+  return 32 * (bit_rate == 8 ? 8 : bit_rate == 4 ? 4 : 2);
+}
+
+cudaError_t launch_spmdm(const SpmdmParams& p_in, int bit_rate, cudaStream_t stream) {
+  SpmdmParams p = p_in;
+  int count = 0;
+  const Variant* v = bit_rate == 8 ? variants<8>(&count) : bit_rate == 4 ? variants<4>(&count) : variants<2>(&count);
+  const int nchunks = (p.data_bytes + 3) / 4;
+
+  // Smallest lane group that covers the payload with one chunk per lane; wide
+  // rows take a full warp and several chunks per lane.  FBGEMM_B200_LPB /
+  // FBGEMM_B200_CPL override the choice (tuning aid).
+  int want_lpb = nchunks <= 8 ? 8 : nchunks <= 16 ? 16 : 32;
+  int want_cpl = 1;
+  while (want_lpb * want_cpl < nchunks) {
+    want_cpl *= 2;
+  }
+  const int env_lpb = env_int("FBGEMM_B200_LPB", 0);
+  const int env_cpl = env_int("FBGEMM_B200_CPL", 0);
+  if (env_lpb > 0 && env_cpl > 0 && env_lpb * env_cpl >= nchunks) {
+    want_lpb = env_lpb;
+    want_cpl = env_cpl;
+  }
+  const Variant* pick = nullptr;
+  for (int i = 0; i < count; ++i) {
+    if (v[i].lpb == want_lpb && v[i].cpl == want_cpl) {
+      pick = &v[i];
+    }
+  }
+  if (!pick) {
+    return cudaErrorInvalidValue;
+  }
+
+  // Shared-memory stage: per bag slot `rows_per_wave` rows, their byte offsets
+  // (8 B) and weights (4 B).
+  const int gpw = 32 / pick->lpb;
+  const int warp_budget = env_int("FBGEMM_B200_SMEM_PER_WARP", 6144);
+  const int max_rows = env_int("FBGEMM_B200_WAVE_ROWS", 64);
+  int rows = (warp_budget / gpw) / (p.pitch + 12);
+  rows = rows < 1 ? 1 : rows > max_rows ? max_rows : rows;
+  p.rows_per_wave = rows;
+  p.group_smem = ((((rows * p.pitch + 15) & ~15) + rows * 12) + 15) & ~15;
+  const size_t smem = (size_t)p.group_smem * gpw * kWarpsPerBlock;
+  if (smem > 200 * 1024) {
+    return cudaErrorInvalidValue;
+  }
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(pick->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+      return e;
+    }
+  }
+  const int64_t bags_per_block = (int64_t)kWarpsPerBlock * gpw;
+  const int64_t blocks = (p.output_size + bags_per_block - 1) / bags_per_block;
+  if (blocks <= 0 || blocks > 0x7fffffffLL) {
+    return cudaErrorInvalidValue;
+  }
+  pick->fn<<<(unsigned)blocks, kThreads, smem, stream>>>(p);
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError();
+}
+
+}  // namespace fbgemm_b200

@@ -1,0 +1,326 @@
+"""Python mirror of the reference's kernel-generator API for the quantized
+embedding-bag path, over the C ABI of libfbgemm_b200.so.
+
+The generator functions carry the reference's names and argument meaning
+(include/fbgemm/FbgemmEmbedding.h:65-262 of FBGEMM); template parameters become
+keyword arguments (``index_dtype``, ``offset_dtype``, ``out_dtype``).  Each
+returns a functor with the reference's call signature
+
+    ok = kernel(output_size, index_size, data_size, input, indices,
+                offsets_or_lengths, weights, out[, compressed_indices_table])
+
+where the arrays are either CUDA ``torch.Tensor`` s (zero-copy, enqueued on the
+current torch stream) or host ``numpy`` arrays (the table is made resident in
+HBM on first use; per-call arrays travel through pinned staging buffers).
+``ok`` is the reference's bool.  Nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import threading
+
+import numpy as np
+
+from . import _capi
+from ._capi import OUT_F16, OUT_F32, SpmdmConfig
+
+_ctx_lock = threading.Lock()
+_ctxs: dict[int, "Context"] = {}
+
+
+class Context:
+    """``fbgemm_b200_ctx`` of one device."""
+
+    def __init__(self, device: int):
+        self.device = device
+        self._h = C.c_void_p()
+        _capi.check(_capi.lib().fbgemm_b200_ctx_create(device, C.byref(self._h)), "fbgemm_b200_ctx_create")
+
+    @property
+    def handle(self):
+        return self._h
+
+    def close(self):
+        if self._h:
+            _capi.lib().fbgemm_b200_ctx_destroy(self._h)
+            self._h = C.c_void_p()
+
+    # -- table registry ------------------------------------------------------
+    def register_table(self, host_array: np.ndarray) -> None:
+        a = host_array
+        assert a.flags["C_CONTIGUOUS"]
+        _capi.check(_capi.lib().fbgemm_b200_table_register(self._h, a.ctypes.data, a.nbytes), "table_register")
+
+    def unregister_table(self, host_array: np.ndarray) -> None:
+        _capi.lib().fbgemm_b200_table_unregister(self._h, host_array.ctypes.data)
+
+    def table_device_ptr(self, host_array: np.ndarray):
+        return _capi.lib().fbgemm_b200_table_device_ptr(self._h, host_array.ctypes.data)
+
+
+def get_context(device: int | None = None) -> Context:
+    """The process-wide context of ``device`` (default: torch's current device)."""
+    if device is None:
+        import torch
+
+        if not torch.cuda.is_available():
+            raise _capi.Fbgemmb200Error("no CUDA device: fbgemm_b200 has no CPU fallback")
+        device = torch.cuda.current_device()
+    with _ctx_lock:
+        ctx = _ctxs.get(device)
+        if ctx is None:
+            ctx = _ctxs[device] = Context(device)
+        return ctx
+
+
+def launch_count() -> int:
+    """Kernels launched by the library in this process so far."""
+    return int(_capi.lib().fbgemm_b200_launch_count())
+
+
+def _np_itemsize(dt) -> int:
+    return np.dtype(dt).itemsize
+
+
+def _out_code(out_dtype) -> int:
+    """OutType of the reference generators: fp32, or fp16 (also as raw uint16)."""
+    try:
+        name = np.dtype(out_dtype).name
+    except TypeError:
+        name = str(out_dtype).rsplit(".", 1)[-1]  # torch.float16 -> float16
+    if name == "float32":
+        return OUT_F32
+    if name in ("float16", "uint16"):
+        return OUT_F16
+    raise ValueError(f"OutType must be float32 or float16, got {out_dtype}")
+
+
+def _is_tensor(x) -> bool:
+    return hasattr(x, "data_ptr")
+
+
+def _ptr(x):
+    if x is None:
+        return None
+    if _is_tensor(x):
+        assert x.is_contiguous(), "tensors must be contiguous"
+        return x.data_ptr()
+    assert x.flags["C_CONTIGUOUS"], "arrays must be contiguous"
+    return x.ctypes.data
+
+
+class SpmdmKernel:
+    """The functor a generator returns.  Holds only the configuration."""
+
+    def __init__(self, cfg: SpmdmConfig, rowwise_sparse: bool):
+        self.cfg = cfg
+        self.rowwise_sparse = rowwise_sparse
+        _capi.check(_capi.lib().fbgemm_b200_spmdm_check_config(C.byref(cfg)), "generator arguments")
+
+    # -- the reference's functor signature ----------------------------------
+    def __call__(self, output_size, index_size, data_size, input, indices, offsets_or_lengths,
+                 weights, out, compressed_indices_table=None) -> bool:
+        if self.rowwise_sparse and compressed_indices_table is None:
+            raise ValueError("row-wise sparse kernels need a compressed_indices_table")
+        if not self.rowwise_sparse and compressed_indices_table is not None:
+            raise ValueError("this kernel was not generated for row-wise sparse tables")
+        self._check_dtypes(indices, offsets_or_lengths)
+        lib = _capi.lib()
+        if _is_tensor(input):
+            import torch
+
+            dev = input.device.index
+            ctx = get_context(dev)
+            stream = torch.cuda.current_stream(dev).cuda_stream
+            rc = lib.fbgemm_b200_spmdm(
+                ctx.handle, C.byref(self.cfg), output_size, index_size, data_size, _ptr(input), _ptr(indices),
+                _ptr(offsets_or_lengths), _ptr(weights) if self.cfg.has_weight else None, _ptr(out),
+                _ptr(compressed_indices_table), stream)
+        else:
+            ctx = get_context()
+            rc = lib.fbgemm_b200_spmdm_host(
+                ctx.handle, C.byref(self.cfg), output_size, index_size, data_size, _ptr(input), _ptr(indices),
+                _ptr(offsets_or_lengths), _ptr(weights) if self.cfg.has_weight else None, _ptr(out),
+                _ptr(compressed_indices_table))
+        return bool(_capi.check(rc, "fbgemm_b200 lookup"))
+
+    # -- asynchronous forms (no counterpart in the reference) ------------------
+    def launch(self, output_size, index_size, data_size, input, indices, offsets_or_lengths, weights, out,
+               compressed_indices_table=None, slot: int = 0, stream=None) -> None:
+        """Enqueue on ``stream`` (int handle; default torch's current stream)
+        without synchronising; errors land in status slot ``slot``."""
+        import torch
+
+        dev = input.device.index
+        ctx = get_context(dev)
+        if stream is None:
+            stream = torch.cuda.current_stream(dev).cuda_stream
+        rc = _capi.lib().fbgemm_b200_spmdm_launch(
+            ctx.handle, C.byref(self.cfg), output_size, index_size, data_size, _ptr(input), _ptr(indices),
+            _ptr(offsets_or_lengths), _ptr(weights) if self.cfg.has_weight else None, _ptr(out),
+            _ptr(compressed_indices_table), slot, stream)
+        _capi.check(rc, "fbgemm_b200_spmdm_launch")
+
+    def host_submit(self, lane, output_size, index_size, data_size, input, indices, offsets_or_lengths,
+                    weights, out, compressed_indices_table=None) -> None:
+        ctx = get_context()
+        rc = _capi.lib().fbgemm_b200_spmdm_host_submit(
+            ctx.handle, lane, C.byref(self.cfg), output_size, index_size, data_size, _ptr(input), _ptr(indices),
+            _ptr(offsets_or_lengths), _ptr(weights) if self.cfg.has_weight else None, _ptr(out),
+            _ptr(compressed_indices_table))
+        _capi.check(rc, "fbgemm_b200_spmdm_host_submit")
+
+    @staticmethod
+    def host_wait(lane) -> bool:
+        ctx = get_context()
+        return bool(_capi.check(_capi.lib().fbgemm_b200_spmdm_host_wait(ctx.handle, lane), "host_wait"))
+
+    def _check_dtypes(self, indices, offsets):
+        for arr, want, what in ((indices, self.cfg.index_bytes, "indices"), (offsets, self.cfg.offset_bytes, "offsets")):
+            if arr is None:
+                continue
+            size = arr.element_size() if _is_tensor(arr) else arr.dtype.itemsize
+            if size != want:
+                raise TypeError(f"{what} have {size}-byte elements, kernel was generated for {want}")
+
+
+def status_read(slot: int = 0, device: int | None = None, stream=None):
+    """(ok, info[4]) of status slot ``slot`` after waiting for ``stream``."""
+    import torch
+
+    ctx = get_context(device)
+    if stream is None:
+        stream = torch.cuda.current_stream(ctx.device).cuda_stream
+    info = (C.c_int32 * 4)()
+    rc = _capi.check(_capi.lib().fbgemm_b200_status_read(ctx.handle, slot, stream, info), "status_read")
+    return bool(rc), list(info)
+
+
+def _config(bit_rate, block_size, has_weight, normalize_by_lengths, is_weight_positional, use_offsets,
+            output_stride, input_stride, index_dtype, offset_dtype, out_dtype) -> SpmdmConfig:
+    return SpmdmConfig(
+        bit_rate=bit_rate,
+        index_bytes=_np_itemsize(index_dtype),
+        offset_bytes=_np_itemsize(offset_dtype),
+        out_dtype=_out_code(out_dtype),
+        block_size=block_size,
+        output_stride=output_stride,
+        input_stride=input_stride,
+        has_weight=int(bool(has_weight)),
+        normalize_by_lengths=int(bool(normalize_by_lengths)),
+        is_weight_positional=int(bool(is_weight_positional)),
+        use_offsets=int(bool(use_offsets)),
+    )
+
+
+def _reject(scale_bias_last=True, no_bag=False, is_bf16_out=False, is_bf16_in=False):
+    if not scale_bias_last or no_bag or is_bf16_out or is_bf16_in:
+        raise ValueError("scale_bias_last=False, no_bag and bf16 are not provided by the sm_100a path")
+
+
+def GenerateEmbeddingSpMDM(block_size, has_weight, normalize_by_lengths, prefetch=16,
+                           is_weight_positional=False, use_offsets=True, is_bf16_out=False, is_bf16_in=False, *,
+                           index_dtype=np.int64, offset_dtype=np.int32, out_dtype=np.float32) -> SpmdmKernel:
+    """fbgemm::GenerateEmbeddingSpMDM<uint8_t, Index, Offset, Out>
+    (include/fbgemm/FbgemmEmbedding.h:65-84): 8-bit rows + fp32 scale, bias."""
+    return GenerateEmbeddingSpMDMWithStrides(
+        block_size, has_weight, normalize_by_lengths, prefetch, is_weight_positional, use_offsets, -1, -1, True,
+        False, is_bf16_out, is_bf16_in, index_dtype=index_dtype, offset_dtype=offset_dtype, out_dtype=out_dtype)
+
+
+def GenerateEmbeddingSpMDMWithStrides(block_size, has_weight, normalize_by_lengths, prefetch=16,
+                                      is_weight_positional=False, use_offsets=True, output_stride=-1,
+                                      input_stride=-1, scale_bias_last=True, no_bag=False, is_bf16_out=False,
+                                      is_bf16_in=False, *, index_dtype=np.int64, offset_dtype=np.int32,
+                                      out_dtype=np.float32) -> SpmdmKernel:
+    """fbgemm::GenerateEmbeddingSpMDMWithStrides<uint8_t, ...>
+    (include/fbgemm/FbgemmEmbedding.h:94-117)."""
+    _reject(scale_bias_last, no_bag, is_bf16_out, is_bf16_in)
+    return SpmdmKernel(_config(8, block_size, has_weight, normalize_by_lengths, is_weight_positional, use_offsets,
+                               output_stride, input_stride, index_dtype, offset_dtype, out_dtype), False)
+
+
+def GenerateEmbeddingSpMDMNBit(bit_rate, block_size, has_weight, normalize_by_lengths, prefetch=16,
+                               is_weight_positional=False, use_offsets=True, *, index_dtype=np.int64,
+                               offset_dtype=np.int32, out_dtype=np.float32) -> SpmdmKernel:
+    """fbgemm::GenerateEmbeddingSpMDMNBit (include/fbgemm/FbgemmEmbedding.h:124-140):
+    4- or 2-bit rows + fp16 scale, bias."""
+    return GenerateEmbeddingSpMDMNBitWithStrides(
+        bit_rate, block_size, has_weight, normalize_by_lengths, prefetch, is_weight_positional, use_offsets,
+        index_dtype=index_dtype, offset_dtype=offset_dtype, out_dtype=out_dtype)
+
+
+def GenerateEmbeddingSpMDMNBitWithStrides(input_bit_rate, block_size, has_weight, normalize_by_lengths,
+                                          prefetch=16, is_weight_positional=False, use_offsets=True,
+                                          output_stride=-1, input_stride=-1, scale_bias_last=True,
+                                          is_bf16_out=False, no_bag=False, output_bit_rate=-1, *,
+                                          index_dtype=np.int64, offset_dtype=np.int32,
+                                          out_dtype=np.float32) -> SpmdmKernel:
+    """fbgemm::GenerateEmbeddingSpMDMNBitWithStrides
+    (include/fbgemm/FbgemmEmbedding.h:149-174)."""
+    if input_bit_rate not in (2, 4):
+        raise ValueError("bit_rate must be 2 or 4")  # src/EmbeddingSpMDMNBit.cc:999-1001
+    _reject(scale_bias_last, no_bag, is_bf16_out)
+    if output_bit_rate not in (-1, 8 * (2 if _out_code(out_dtype) == OUT_F16 else 4)):
+        raise ValueError("N-bit output is not provided by the sm_100a path")
+    return SpmdmKernel(_config(input_bit_rate, block_size, has_weight, normalize_by_lengths, is_weight_positional,
+                               use_offsets, output_stride, input_stride, index_dtype, offset_dtype, out_dtype), False)
+
+
+def GenerateEmbeddingSpMDMRowWiseSparse(block_size, has_weight, normalize_by_lengths, prefetch=16,
+                                        is_weight_positional=False, use_offsets=True, *, index_dtype=np.int64,
+                                        offset_dtype=np.int32) -> SpmdmKernel:
+    """fbgemm::GenerateEmbeddingSpMDMRowWiseSparse<uint8_t, ...>
+    (include/fbgemm/FbgemmEmbedding.h:229-243): pruned 8-bit table."""
+    return SpmdmKernel(_config(8, block_size, has_weight, normalize_by_lengths, is_weight_positional, use_offsets,
+                               -1, -1, index_dtype, offset_dtype, np.float32), True)
+
+
+def GenerateEmbeddingSpMDMNBitRowWiseSparse(bit_rate, block_size, has_weight, normalize_by_lengths, prefetch=16,
+                                            is_weight_positional=False, use_offsets=True, *,
+                                            index_dtype=np.int64, offset_dtype=np.int32) -> SpmdmKernel:
+    """fbgemm::GenerateEmbeddingSpMDMNBitRowWiseSparse
+    (include/fbgemm/FbgemmEmbedding.h:250-262): pruned 4-/2-bit table."""
+    if bit_rate not in (2, 4):
+        raise ValueError("bit_rate must be 2 or 4")
+    return SpmdmKernel(_config(bit_rate, block_size, has_weight, normalize_by_lengths, is_weight_positional,
+                               use_offsets, -1, -1, index_dtype, offset_dtype, np.float32), True)
+
+
+# ---- quantizers (device tensors) ---------------------------------------------
+
+def FloatToFused8BitRowwiseQuantizedSBFloat(x, out=None):
+    """fbgemm::FloatOrHalfToFused8BitRowwiseQuantizedSBFloat<float>
+    (include/fbgemm/QuantUtils.h:312) on a CUDA fp32 tensor [rows, cols] ->
+    uint8 [rows, cols + 8]."""
+    import torch
+
+    assert x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.is_contiguous()
+    rows, cols = x.shape
+    if out is None:
+        out = torch.empty((rows, cols + 8), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        _capi.check(_capi.lib().fbgemm_b200_float_to_fused_8bit_rowwise(
+            x.data_ptr(), rows, cols, out.data_ptr(), stream), "8-bit quantizer")
+    return out
+
+
+def FloatToFusedNBitRowwiseQuantizedSBHalf(bit_rate, x, out=None):
+    """fbgemm::FloatOrHalfToFusedNBitRowwiseQuantizedSBHalf<float>
+    (include/fbgemm/QuantUtils.h:277) on a CUDA fp32 tensor [rows, cols] ->
+    uint8 [rows, cols / (8/bit_rate) + 4]."""
+    import torch
+
+    assert x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.is_contiguous()
+    rows, cols = x.shape
+    epb = 8 // bit_rate
+    if cols % epb:
+        raise ValueError("Unsupported number of columns")  # src/QuantUtils.cc:624-627
+    if out is None:
+        out = torch.empty((rows, cols // epb + 4), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        _capi.check(_capi.lib().fbgemm_b200_float_to_fused_nbit_rowwise(
+            bit_rate, x.data_ptr(), rows, cols, out.data_ptr(), stream), "N-bit quantizer")
+    return out

@@ -1,0 +1,254 @@
+/*
+ * fbgemm_b200 - C ABI of the B200 (sm_100a) quantized embedding-bag path.
+ *
+ * This is the drop-in boundary: plain pointers and sizes, no C++ or torch
+ * types.  The C++ generator templates in FbgemmEmbedding.h (same directory)
+ * and the Python mirror in fbgemm_b200/ are thin layers over these entry
+ * points.  Each entry point names the interface of the reference (FBGEMM,
+ * paths relative to its source tree) that it stands in for.
+ *
+ * Conventions
+ *   - "lookup" entry points return 1 where the reference functor returns
+ *     true, 0 where it returns false (index out of range, a bag that runs
+ *     past index_size, or offsets that do not add up to index_size), and a
+ *     negative FBGEMM_B200_E* code when the call itself failed.  As in the
+ *     reference, the output is unspecified when the result is 0.
+ *   - Nothing here falls back to the CPU: without a usable CUDA device every
+ *     call fails with FBGEMM_B200_ECUDA.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default
+ *     stream).
+ */
+#ifndef FBGEMM_B200_EMBEDDING_C_API_H_
+#define FBGEMM_B200_EMBEDDING_C_API_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define FBGEMM_B200_API __attribute__((visibility("default")))
+#else
+#define FBGEMM_B200_API
+#endif
+
+/* Error codes (negative). */
+#define FBGEMM_B200_EINVAL (-1) /* bad or unsupported argument              */
+#define FBGEMM_B200_ECUDA (-2)  /* a CUDA runtime call failed               */
+#define FBGEMM_B200_ENOMEM (-3) /* device or pinned allocation failed       */
+#define FBGEMM_B200_EBUSY (-4)  /* pipeline lane still has work in flight   */
+
+/* Output element types (OutType of the reference generators). */
+#define FBGEMM_B200_OUT_F32 0
+#define FBGEMM_B200_OUT_F16 1
+
+/* Why a lookup returned 0 (first word of the status record). */
+#define FBGEMM_B200_STATUS_OK 0
+#define FBGEMM_B200_STATUS_BAD_INDEX 1   /* idx < 0 || idx >= data_size      */
+#define FBGEMM_B200_STATUS_BAG_OVERRUN 2 /* current + len > index_size       */
+#define FBGEMM_B200_STATUS_SIZE_MISMATCH 3 /* sum of lengths != index_size   */
+
+/* Number of status slots a context owns (see fbgemm_b200_spmdm_launch). */
+#define FBGEMM_B200_STATUS_SLOTS 1024
+/* Number of staging lanes of the host-pointer pipeline. */
+#define FBGEMM_B200_HOST_LANES 8
+
+typedef struct fbgemm_b200_ctx fbgemm_b200_ctx;
+
+/*
+ * What a generator call fixes.  Mirrors the arguments of
+ *   GenerateEmbeddingSpMDMWithStrides      include/fbgemm/FbgemmEmbedding.h:94-117
+ *   GenerateEmbeddingSpMDMNBitWithStrides  include/fbgemm/FbgemmEmbedding.h:149-174
+ *   GenerateEmbeddingSpMDM[NBit]RowWiseSparse               ...:229-262
+ * (`prefetch` and THREAD_LOCAL have no meaning on a GPU and are not carried.)
+ */
+typedef struct fbgemm_b200_spmdm_config {
+  int32_t bit_rate;     /* 8: rows of uint8 + fp32 scale,bias; 4 or 2: packed
+                           little-endian within the byte + fp16 scale,bias   */
+  int32_t index_bytes;  /* sizeof(IndexType): 4 or 8                         */
+  int32_t offset_bytes; /* sizeof(OffsetType): 4 or 8                        */
+  int32_t out_dtype;    /* FBGEMM_B200_OUT_F32 / _F16                        */
+  int64_t block_size;   /* embedding dimension D (elements)                  */
+  int64_t output_stride; /* elements between output rows; -1 = block_size    */
+  int64_t input_stride; /* bytes between table rows; -1 = fused row size     */
+  int32_t has_weight;
+  int32_t normalize_by_lengths;
+  int32_t is_weight_positional;
+  int32_t use_offsets;  /* 1: offsets[output_size+1]; 0: lengths[output_size]*/
+} fbgemm_b200_spmdm_config;
+
+/* ---- context ----------------------------------------------------------- */
+
+/* One context per (process, device).  Owns the status slots, the scratch used
+ * by the lengths (use_offsets = 0) mode, the registry of device-resident
+ * tables and the staging lanes of the host-pointer pipeline.  Thread-safe. */
+FBGEMM_B200_API int fbgemm_b200_ctx_create(int device, fbgemm_b200_ctx** ctx);
+FBGEMM_B200_API void fbgemm_b200_ctx_destroy(fbgemm_b200_ctx* ctx);
+
+/* Text of the last error raised on the calling thread ("" if none). */
+FBGEMM_B200_API const char* fbgemm_b200_last_error(void);
+
+/* Kernels launched by this library in this process so far. */
+FBGEMM_B200_API uint64_t fbgemm_b200_launch_count(void);
+
+/* Generation-time check of a configuration.  Stands in for the argument
+ * checks of the reference generators (src/EmbeddingSpMDMNBit.cc:999-1001,
+ * src/EmbeddingSpMDM.cc:999-1017).  Returns 0 or FBGEMM_B200_EINVAL. */
+FBGEMM_B200_API int fbgemm_b200_spmdm_check_config(const fbgemm_b200_spmdm_config* cfg);
+
+/* ---- pooled lookup, device pointers ------------------------------------ */
+
+/*
+ * One call of the functor that the reference generators return
+ * (EmbeddingSpMDMKernelSignature<>::Type, include/fbgemm/FbgemmEmbedding.h:41-49;
+ * with a non-NULL compressed_indices_table the row-wise-sparse signature,
+ * ...:205-222, whose third argument is the UNCOMPRESSED row count and whose
+ * output is fp32 with dense strides).  Arithmetic follows
+ * src/RefImplementations.cc:1290-1346 (8-bit), :1485-1541 (N-bit) and
+ * :1746-1822 (pruned) operation for operation, so fp32 results are bit-equal.
+ *
+ * All pointers are device pointers valid on the context's device.  The call
+ * enqueues work on `stream` and returns without synchronising; it allocates
+ * nothing except, in lengths mode, a one-off growth of the context's scratch.
+ * Errors found by the kernel are recorded first-writer-wins in status slot
+ * `slot` (0 <= slot < FBGEMM_B200_STATUS_SLOTS); read it with
+ * fbgemm_b200_status_read once the stream has caught up.  Calls that overlap
+ * on the GPU should use distinct slots.
+ *
+ * Returns 0 when enqueued, or a negative error code.
+ */
+FBGEMM_B200_API int fbgemm_b200_spmdm_launch(
+    fbgemm_b200_ctx* ctx,
+    const fbgemm_b200_spmdm_config* cfg,
+    int64_t output_size,
+    int64_t index_size,
+    int64_t data_size,
+    const void* input,
+    const void* indices,
+    const void* offsets_or_lengths,
+    const float* weights, /* NULL unless cfg->has_weight */
+    void* out,
+    const int32_t* compressed_indices_table, /* NULL = dense table */
+    int slot,
+    void* stream);
+
+/* Waits for `stream`, reads status slot `slot` into info[4] = {code, bag,
+ * position in indices, offending value (low 32 bits)} and clears the slot.
+ * Returns 1 if the code is 0 (functor result true), 0 otherwise, negative on
+ * a CUDA error.  `info` may be NULL. */
+FBGEMM_B200_API int fbgemm_b200_status_read(
+    fbgemm_b200_ctx* ctx,
+    int slot,
+    void* stream,
+    int32_t* info);
+
+/* fbgemm_b200_spmdm_launch + fbgemm_b200_status_read on slot 0: the
+ * synchronous functor call.  Returns 1 / 0 / negative. */
+FBGEMM_B200_API int fbgemm_b200_spmdm(
+    fbgemm_b200_ctx* ctx,
+    const fbgemm_b200_spmdm_config* cfg,
+    int64_t output_size,
+    int64_t index_size,
+    int64_t data_size,
+    const void* input,
+    const void* indices,
+    const void* offsets_or_lengths,
+    const float* weights,
+    void* out,
+    const int32_t* compressed_indices_table,
+    void* stream);
+
+/* ---- pooled lookup, host pointers -------------------------------------- */
+
+/*
+ * The reference functor is called with host pointers.  A caller that keeps
+ * its buffers in host memory registers each table once (the table then lives
+ * in HBM) and afterwards passes the same host address as `input`; indices,
+ * offsets/lengths, weights and the output travel through pinned staging
+ * buffers on every call.
+ */
+
+/* Copy `bytes` of a fused-row table (or of a compressed_indices_table) to the
+ * device and remember it under its host address.  Registering the same
+ * address again replaces the copy. */
+FBGEMM_B200_API int fbgemm_b200_table_register(
+    fbgemm_b200_ctx* ctx,
+    const void* host_ptr,
+    size_t bytes);
+FBGEMM_B200_API int fbgemm_b200_table_unregister(fbgemm_b200_ctx* ctx, const void* host_ptr);
+/* Device address of a registered table, NULL if unknown. */
+FBGEMM_B200_API const void* fbgemm_b200_table_device_ptr(fbgemm_b200_ctx* ctx, const void* host_ptr);
+
+/* Asynchronous host-pointer functor call on pipeline lane `lane`
+ * (0 <= lane < FBGEMM_B200_HOST_LANES): host->device copies of indices,
+ * offsets/lengths and weights, the lookup kernel, and the device->host copy
+ * of the output rows into `out` are enqueued on the lane's own stream.
+ * `input` (and compressed_indices_table, if any) must have been registered;
+ * an unregistered table is registered on the spot using
+ * data_size * input_stride bytes (for the compressed_indices_table:
+ * data_size * 4 bytes).  The host buffers must stay valid until
+ * fbgemm_b200_spmdm_host_wait(lane) returns.  Returns 0 or a negative code
+ * (FBGEMM_B200_EBUSY if the lane has un-waited work). */
+FBGEMM_B200_API int fbgemm_b200_spmdm_host_submit(
+    fbgemm_b200_ctx* ctx,
+    int lane,
+    const fbgemm_b200_spmdm_config* cfg,
+    int64_t output_size,
+    int64_t index_size,
+    int64_t data_size,
+    const void* input,
+    const void* indices,
+    const void* offsets_or_lengths,
+    const float* weights,
+    void* out,
+    const int32_t* compressed_indices_table);
+
+/* Wait for lane `lane`; returns the functor result 1 / 0, or negative. */
+FBGEMM_B200_API int fbgemm_b200_spmdm_host_wait(fbgemm_b200_ctx* ctx, int lane);
+
+/* submit on lane 0 + wait: the synchronous functor call with host pointers. */
+FBGEMM_B200_API int fbgemm_b200_spmdm_host(
+    fbgemm_b200_ctx* ctx,
+    const fbgemm_b200_spmdm_config* cfg,
+    int64_t output_size,
+    int64_t index_size,
+    int64_t data_size,
+    const void* input,
+    const void* indices,
+    const void* offsets_or_lengths,
+    const float* weights,
+    void* out,
+    const int32_t* compressed_indices_table);
+
+/* ---- row-wise quantizers, device pointers ------------------------------ */
+
+/* fbgemm::FloatOrHalfToFused8BitRowwiseQuantizedSBFloat<float>
+ * (include/fbgemm/QuantUtils.h:312; arithmetic of src/QuantUtils.cc:677-718):
+ * fp32 [rows x cols] -> uint8 [rows x (cols + 8)].  Enqueued on `stream`. */
+FBGEMM_B200_API int fbgemm_b200_float_to_fused_8bit_rowwise(
+    const float* input,
+    int64_t rows,
+    int32_t cols,
+    uint8_t* output,
+    void* stream);
+
+/* fbgemm::FloatOrHalfToFusedNBitRowwiseQuantizedSBHalf<float>
+ * (include/fbgemm/QuantUtils.h:277; arithmetic of src/QuantUtils.cc:534-611):
+ * fp32 [rows x cols] -> uint8 [rows x (ceil(cols / (8/bit_rate)) + 4)].
+ * bit_rate 2, 4 or 8; cols must be a multiple of 8/bit_rate, as in the
+ * reference (src/QuantUtils.cc:624-627). */
+FBGEMM_B200_API int fbgemm_b200_float_to_fused_nbit_rowwise(
+    int32_t bit_rate,
+    const float* input,
+    int64_t rows,
+    int32_t cols,
+    uint8_t* output,
+    void* stream);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+
+#endif /* FBGEMM_B200_EMBEDDING_C_API_H_ */

@@ -1,0 +1,64 @@
+"""Input builders shared by the CPU and GPU tests (seeded numpy)."""
+import numpy as np
+
+# (batch, table rows, embedding dim, average bag length): the shapes the
+# reference's lookup tests run (test/EmbeddingSpMDM8BitTest.cc:20-43,
+# test/EmbeddingSpMDMNBitTest.cc:21-46 of FBGEMM).
+REFERENCE_SHAPES = [
+    (1, 8, 8, 4), (2, 8, 16, 4), (10, 4000, 32, 100), (100, 4000, 32, 100), (10, 4000, 64, 100),
+    (10, 4000, 128, 100), (4, 400, 256, 10), (4, 400, 512, 10), (10, 4000, 48, 100), (10, 4000, 40, 100),
+    (10, 4000, 56, 100), (10, 4000, 2, 100), (10, 4000, 4, 100), (10, 4000, 7, 100), (10, 40, 16, 10),
+    (10, 40, 86, 10), (10, 40, 8, 10), (10, 40, 96, 10), (10, 40, 164, 10),
+]
+
+
+def row_bytes(bit_rate, dim):
+    epb = 8 // bit_rate
+    return (dim + epb - 1) // epb + (8 if bit_rate == 8 else 4)
+
+
+def random_fused_table(rng, rows, dim, bit_rate, stride=None):
+    """Rows as the reference tests build them: small random payload values and
+    N(0,1) scale/bias (test/EmbeddingSpMDM8BitTest.cc:120-154,
+    test/EmbeddingSpMDMNBitTest.cc:137-166) - not quantizer output, so every
+    payload bit pattern and awkward scales occur."""
+    epb = 8 // bit_rate
+    data_bytes = (dim + epb - 1) // epb
+    rb = row_bytes(bit_rate, dim)
+    stride = stride or rb
+    t = np.zeros((rows, stride), dtype=np.uint8)
+    t[:, :data_bytes] = rng.integers(0, 256, (rows, data_bytes), dtype=np.uint8)
+    sb = rng.standard_normal((rows, 2)).astype(np.float32)
+    if bit_rate == 8:
+        t[:, data_bytes:data_bytes + 8] = sb.view(np.uint8).reshape(rows, 8)
+    else:
+        t[:, data_bytes:data_bytes + 4] = sb.astype(np.float16).view(np.uint8).reshape(rows, 4)
+    return t
+
+
+def lengths_indices_weights(rng, batch, rows, avg_len, index_dtype, offset_dtype, corner=None):
+    """As GenerateLengthsIndicesWeights (test/EmbeddingSpMDMTestUtils.cc:18-95),
+    seeded.  corner: None, 'empty', 'oob', 'unmatched+', 'unmatched-'."""
+    hi = min(2 * avg_len + 1, rows)
+    lengths = np.zeros(batch, dtype=np.int64) if corner == "empty" else rng.integers(1, hi + 1, batch)
+    n = int(lengths.sum())
+    indices = rng.integers(0, rows, n).astype(index_dtype)
+    if corner != "empty":
+        indices[0] = rows - 1  # probe the upper bound
+    if corner == "oob":
+        indices[rng.integers(0, n)] = rows
+    if corner == "unmatched+":
+        lengths[-1] += 1
+    if corner == "unmatched-":
+        lengths[-1] -= 1
+    offsets = np.concatenate([[0], np.cumsum(lengths)]).astype(offset_dtype)
+    weights = rng.standard_normal(n).astype(np.float32)
+    return lengths.astype(offset_dtype), offsets, indices, weights, n
+
+
+def mapping_table(rng, rows, sparsity):
+    """As CreateMappingTableForRowWiseSparsity (test/EmbeddingSpMDMTestUtils.cc:97-109)."""
+    pruned = rng.random(rows) < sparsity
+    m = np.full(rows, -1, dtype=np.int32)
+    m[~pruned] = np.arange(int((~pruned).sum()), dtype=np.int32)
+    return m, int((~pruned).sum())

@@ -1,0 +1,294 @@
+"""Parity of the CUDA lookups with the CPU oracle, through the C ABI.
+
+Modelled on the reference's own differential tests
+(test/EmbeddingSpMDM8BitTest.cc, test/EmbeddingSpMDMNBitTest.cc of FBGEMM): the
+same shapes, weighting modes, corner cases and overrun sentries, with the
+coin-flipped options (index/offset width, normalize, offsets-vs-lengths)
+enumerated from a seed instead.  The bar is the reference's: EXPECT_EQ on every
+element, i.e. bit-exact fp32 and fp16.
+"""
+import itertools
+
+import numpy as np
+import pytest
+import torch
+
+import fbgemm_b200 as F
+from helpers import REFERENCE_SHAPES, lengths_indices_weights, mapping_table, random_fused_table, row_bytes
+from conftest import bits
+
+pytestmark = pytest.mark.gpu
+
+SENTRIES = 10
+
+
+def dev(a):
+    return None if a is None else torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def make_kernel(bit_rate, dim, has_weight, normalize, positional, use_offsets, idt, odt, out_dt, **strides):
+    if bit_rate == 8:
+        return F.GenerateEmbeddingSpMDMWithStrides(
+            dim, has_weight, normalize, 16, positional, use_offsets, index_dtype=idt, offset_dtype=odt,
+            out_dtype=out_dt, **strides)
+    return F.GenerateEmbeddingSpMDMNBitWithStrides(
+        bit_rate, dim, has_weight, normalize, 16, positional, use_offsets, index_dtype=idt, offset_dtype=odt,
+        out_dtype=out_dt, **strides)
+
+
+def run_case(oracle, rng, bit_rate, shape, weighting, corner, out_dt, idt, odt, normalize, use_offsets):
+    batch, rows, dim, avg_len = shape
+    table = random_fused_table(rng, rows, dim, bit_rate)
+    lengths, offsets, indices, weights, n = lengths_indices_weights(rng, batch, rows, avg_len, idt, odt, corner)
+    has_weight = weighting != "unweighted"
+    positional = weighting == "positional"
+    if positional:
+        weights = rng.standard_normal(max(int(lengths.max()), 1) + 1).astype(np.float32)
+    ol = offsets if use_offsets else lengths
+    ok_ref, out_ref = oracle.spmdm(bit_rate, dim, rows, table, indices, ol, weights if has_weight else None,
+                                   normalize, out_dt, positional, use_offsets, output_size=batch, index_size=n)
+    kern = make_kernel(bit_rate, dim, has_weight, normalize, positional, use_offsets, idt, odt, out_dt)
+    tdt = torch.float16 if out_dt == np.float16 else torch.float32
+    out = torch.ones(batch * dim + SENTRIES, dtype=tdt, device="cuda")
+    d_idx = dev(indices) if n else None  # the reference passes nullptr for empty indices
+    ok = kern(batch, n, rows, dev(table), d_idx, dev(ol), dev(weights) if has_weight else None, out)
+    assert ok == ok_ref
+    expected_false = corner in ("oob", "unmatched+", "unmatched-")
+    assert ok == (not expected_false)
+    got = out.cpu().numpy()
+    assert (got[batch * dim:] == 1).all(), "wrote past the output"
+    if ok:
+        np.testing.assert_array_equal(bits(got[:batch * dim]), bits(out_ref[:batch * dim]))
+
+
+@pytest.mark.parametrize("bit_rate", [8, 4, 2])
+@pytest.mark.parametrize("weighting", ["unweighted", "weighted", "positional"])
+@pytest.mark.parametrize("out_dt", [np.float32, np.float16])
+def test_reference_shapes(gpu_ctx, oracle, bit_rate, weighting, out_dt):
+    rng = np.random.default_rng(1000 + bit_rate)
+    flips = itertools.cycle(itertools.product([np.int32, np.int64], [np.int32, np.int64], [False, True], [True, False]))
+    for shape in REFERENCE_SHAPES:
+        idt, odt, normalize, use_offsets = next(flips)
+        run_case(oracle, rng, bit_rate, shape, weighting, None, out_dt, idt, odt, normalize, use_offsets)
+
+
+@pytest.mark.parametrize("bit_rate", [8, 4, 2])
+@pytest.mark.parametrize("corner", ["empty", "oob", "unmatched+", "unmatched-"])
+def test_corner_cases(gpu_ctx, oracle, bit_rate, corner):
+    rng = np.random.default_rng(2000 + bit_rate)
+    flips = itertools.cycle(itertools.product([np.int64, np.int32], [np.int64, np.int32], [True, False], [True, False]))
+    for shape in REFERENCE_SHAPES[::3]:
+        idt, odt, normalize, use_offsets = next(flips)
+        for weighting in ("unweighted", "weighted"):
+            run_case(oracle, rng, bit_rate, shape, weighting, corner, np.float32, idt, odt, normalize, use_offsets)
+
+
+@pytest.mark.parametrize("bit_rate", [8, 4, 2])
+def test_all_option_combinations_small(gpu_ctx, oracle, bit_rate):
+    """Every index/offset width x normalize x offsets-vs-lengths x output type
+    on one ragged shape with empty bags in the middle."""
+    rng = np.random.default_rng(3000 + bit_rate)
+    rows, dim, batch = 300, 72, 33
+    table = random_fused_table(rng, rows, dim, bit_rate)
+    lengths = rng.integers(0, 50, batch)
+    lengths[[3, 4, 17]] = 0
+    n = int(lengths.sum())
+    w = rng.standard_normal(n).astype(np.float32)
+    d_table, d_w = dev(table), dev(w)
+    for idt, odt, normalize, use_offsets, out_dt, has_weight in itertools.product(
+            [np.int32, np.int64], [np.int32, np.int64], [False, True], [True, False], [np.float32, np.float16],
+            [False, True]):
+        indices = rng.integers(0, rows, n).astype(idt)
+        ol = (np.concatenate([[0], np.cumsum(lengths)]) if use_offsets else lengths).astype(odt)
+        ok_ref, ref = oracle.spmdm(bit_rate, dim, rows, table, indices, ol, w if has_weight else None, normalize,
+                                   out_dt, False, use_offsets, output_size=batch, index_size=n)
+        kern = make_kernel(bit_rate, dim, has_weight, normalize, False, use_offsets, idt, odt, out_dt)
+        out = torch.zeros(batch * dim, dtype=torch.float16 if out_dt == np.float16 else torch.float32, device="cuda")
+        ok = kern(batch, n, rows, d_table, dev(indices), dev(ol), d_w if has_weight else None, out)
+        assert ok and ok_ref
+        np.testing.assert_array_equal(bits(out.cpu().numpy()), bits(ref))
+
+
+@pytest.mark.parametrize("bit_rate", [8, 4, 2])
+def test_offsets_not_zero_based(gpu_ctx, oracle, bit_rate):
+    """A multi-table caller passes a slice of a global offsets array together
+    with pre-advanced indices/weights: only differences of offsets matter."""
+    rng = np.random.default_rng(4000 + bit_rate)
+    rows, dim, batch = 500, 64, 20
+    table = random_fused_table(rng, rows, dim, bit_rate)
+    lengths, offsets, indices, weights, n = lengths_indices_weights(rng, batch, rows, 12, np.int32, np.int64)
+    shifted = offsets + 123457
+    ok_ref, ref = oracle.spmdm(bit_rate, dim, rows, table, indices, offsets, weights, False, np.float32)
+    kern = make_kernel(bit_rate, dim, True, False, False, True, np.int32, np.int64, np.float32)
+    out = torch.zeros(batch * dim, device="cuda")
+    assert kern(batch, n, rows, dev(table), dev(indices), dev(shifted), dev(weights), out) and ok_ref
+    np.testing.assert_array_equal(bits(out.cpu().numpy()), bits(ref))
+
+
+@pytest.mark.parametrize("bit_rate", [8, 4, 2])
+def test_strides(gpu_ctx, oracle, bit_rate):
+    """output_stride > block_size (a column slice of a wider output) and
+    input_stride > fused row size (padded rows); columns outside the slice
+    must stay untouched."""
+    rng = np.random.default_rng(5000 + bit_rate)
+    rows, dim, batch = 400, 96, 17
+    for in_pad, out_stride, out_dt in ((0, 200, np.float32), (12, 96, np.float16), (28, 131, np.float32)):
+        in_stride = row_bytes(bit_rate, dim) + in_pad
+        table = random_fused_table(rng, rows, dim, bit_rate, stride=in_stride)
+        lengths, offsets, indices, weights, n = lengths_indices_weights(rng, batch, rows, 9, np.int64, np.int32)
+        ref_buf = np.full(batch * out_stride, 7, dtype=out_dt)
+        ok_ref, ref = oracle.spmdm(bit_rate, dim, rows, table, indices, offsets, weights, True, out_dt, False, True,
+                                   out_stride, in_stride, out=ref_buf)
+        kern = make_kernel(bit_rate, dim, True, True, False, True, np.int64, np.int32, out_dt,
+                           output_stride=out_stride, input_stride=in_stride)
+        out = torch.full((batch * out_stride,), 7, dtype=torch.float16 if out_dt == np.float16 else torch.float32,
+                         device="cuda")
+        assert kern(batch, n, rows, dev(table), dev(indices), dev(offsets), dev(weights), out) and ok_ref
+        np.testing.assert_array_equal(bits(out.cpu().numpy()), bits(ref))
+
+
+@pytest.mark.parametrize("bit_rate", [8, 4, 2])
+def test_misaligned_table_pointer(gpu_ctx, oracle, bit_rate):
+    """A table that starts at an odd address takes the byte-wise staging path."""
+    rng = np.random.default_rng(6000 + bit_rate)
+    rows, dim, batch = 200, 64, 9
+    table = random_fused_table(rng, rows, dim, bit_rate)
+    lengths, offsets, indices, weights, n = lengths_indices_weights(rng, batch, rows, 7, np.int64, np.int64)
+    ok_ref, ref = oracle.spmdm(bit_rate, dim, rows, table, indices, offsets, None, False, np.float32)
+    for shift in (1, 2, 4, 8):
+        buf = torch.zeros(table.size + 64, dtype=torch.uint8, device="cuda")
+        buf[shift:shift + table.size] = torch.from_numpy(table.reshape(-1)).cuda()
+        view = buf[shift:shift + table.size]
+        kern = make_kernel(bit_rate, dim, False, False, False, True, np.int64, np.int64, np.float32)
+        out = torch.zeros(batch * dim, device="cuda")
+        assert kern(batch, n, rows, view, dev(indices), dev(offsets), None, out) and ok_ref
+        np.testing.assert_array_equal(bits(out.cpu().numpy()), bits(ref))
+
+
+@pytest.mark.parametrize("bit_rate", [8, 4, 2])
+@pytest.mark.parametrize("weighting", ["unweighted", "weighted", "positional"])
+def test_rowwise_sparse(gpu_ctx, oracle, bit_rate, weighting):
+    """Pruned tables (test/EmbeddingSpMDMNBitTest.cc rowwiseSparseTest): a -1 in
+    the mapping skips the row but keeps its weight slot and its place in the
+    bag length."""
+    rng = np.random.default_rng(7000 + bit_rate)
+    flips = itertools.cycle(itertools.product([np.int32, np.int64], [np.int64, np.int32], [True, False], [True, False]))
+    for shape in REFERENCE_SHAPES:
+        batch, rows, dim, avg_len = shape
+        idt, odt, normalize, use_offsets = next(flips)
+        mapping, n_dense = mapping_table(rng, rows, 0.7)
+        table = random_fused_table(rng, max(n_dense, 1), dim, bit_rate)
+        for corner in (None, "oob", "unmatched-"):
+            lengths, offsets, indices, weights, n = lengths_indices_weights(rng, batch, rows, avg_len, idt, odt, corner)
+            has_weight = weighting != "unweighted"
+            positional = weighting == "positional"
+            if positional:
+                weights = rng.standard_normal(int(lengths.max()) + 1).astype(np.float32)
+            ol = offsets if use_offsets else lengths
+            ok_ref, ref = oracle.spmdm_rowwise_sparse(
+                bit_rate, dim, rows, table, indices, mapping, ol, weights if has_weight else None, normalize,
+                positional, use_offsets, output_size=batch, index_size=n)
+            if bit_rate == 8:
+                kern = F.GenerateEmbeddingSpMDMRowWiseSparse(dim, has_weight, normalize, 16, positional, use_offsets,
+                                                             index_dtype=idt, offset_dtype=odt)
+            else:
+                kern = F.GenerateEmbeddingSpMDMNBitRowWiseSparse(bit_rate, dim, has_weight, normalize, 16, positional,
+                                                                 use_offsets, index_dtype=idt, offset_dtype=odt)
+            out = torch.ones(batch * dim + SENTRIES, device="cuda")
+            ok = kern(batch, n, rows, dev(table), dev(indices), dev(ol), dev(weights) if has_weight else None, out,
+                      dev(mapping))
+            assert ok == ok_ref == (corner is None)
+            got = out.cpu().numpy()
+            assert (got[batch * dim:] == 1).all()
+            if ok:
+                np.testing.assert_array_equal(bits(got[:batch * dim]), bits(ref[:batch * dim]))
+
+
+def test_long_bags_and_wide_rows(gpu_ctx, oracle):
+    """Bags longer than one staging wave and the widest supported rows."""
+    rng = np.random.default_rng(8000)
+    for bit_rate, dim in ((8, 1024), (4, 1024), (2, 1024), (8, 640), (4, 520), (2, 36)):
+        rows, batch = 300, 6
+        table = random_fused_table(rng, rows, dim, bit_rate)
+        lengths = np.array([0, 1, 700, 64, 65, 129])
+        offsets = np.concatenate([[0], np.cumsum(lengths)]).astype(np.int64)
+        n = int(offsets[-1])
+        indices = rng.integers(0, rows, n).astype(np.int64)
+        weights = rng.standard_normal(n).astype(np.float32)
+        ok_ref, ref = oracle.spmdm(bit_rate, dim, rows, table, indices, offsets, weights, True, np.float32)
+        kern = make_kernel(bit_rate, dim, True, True, False, True, np.int64, np.int64, np.float32)
+        out = torch.zeros(batch * dim, device="cuda")
+        assert kern(batch, n, rows, dev(table), dev(indices), dev(offsets), dev(weights), out) and ok_ref
+        np.testing.assert_array_equal(bits(out.cpu().numpy()), bits(ref))
+
+
+def test_unsupported_block_size_is_rejected_at_generation():
+    with pytest.raises(Exception):
+        F.GenerateEmbeddingSpMDM(2048, False, False)
+
+
+def test_host_pointer_path(gpu_ctx, oracle):
+    """The functor called with host (numpy) buffers: table made resident on
+    first use, per-call arrays staged, result written to the host buffer."""
+    rng = np.random.default_rng(9000)
+    for bit_rate, out_dt, out_stride in ((8, np.float32, -1), (4, np.float16, -1), (2, np.float32, 150)):
+        rows, dim, batch = 1000, 128, 50
+        table = random_fused_table(rng, rows, dim, bit_rate)
+        lengths, offsets, indices, weights, n = lengths_indices_weights(rng, batch, rows, 15, np.int64, np.int64)
+        ostride = dim if out_stride == -1 else out_stride
+        ref_buf = np.full(batch * ostride, 3, dtype=out_dt)
+        ok_ref, ref = oracle.spmdm(bit_rate, dim, rows, table, indices, offsets, weights, False, out_dt, False, True,
+                                   out_stride, -1, out=ref_buf)
+        kern = make_kernel(bit_rate, dim, True, False, False, True, np.int64, np.int64, out_dt,
+                           output_stride=out_stride)
+        out = np.full(batch * ostride, 3, dtype=out_dt)
+        for _ in range(2):  # second call hits the resident table
+            assert kern(batch, n, rows, table, indices, offsets, weights, out) and ok_ref
+            np.testing.assert_array_equal(bits(out), bits(ref))
+        bad = indices.copy()
+        bad[5] = rows
+        assert kern(batch, n, rows, table, bad, offsets, weights, out) is False
+        assert kern(batch, n, rows, table, indices, offsets, weights, out) is True  # status was cleared
+        gpu_ctx.unregister_table(table)
+
+
+def test_host_pipeline_lanes(gpu_ctx, oracle):
+    rng = np.random.default_rng(9100)
+    rows, dim, batch = 2000, 64, 64
+    table = random_fused_table(rng, rows, dim, 4)
+    gpu_ctx.register_table(table)
+    kern = make_kernel(4, dim, True, False, False, True, np.int32, np.int32, np.float16)
+    jobs = []
+    for lane in range(4):
+        lengths, offsets, indices, weights, n = lengths_indices_weights(rng, batch, rows, 20, np.int32, np.int32)
+        out = np.zeros(batch * dim, dtype=np.float16)
+        kern.host_submit(lane, batch, n, rows, table, indices, offsets, weights, out)
+        jobs.append((lane, offsets, indices, weights, out))
+    for lane, offsets, indices, weights, out in jobs:
+        assert kern.host_wait(lane)
+        _, ref = oracle.spmdm(4, dim, rows, table, indices, offsets, weights, False, np.float16)
+        np.testing.assert_array_equal(bits(out), bits(ref))
+    gpu_ctx.unregister_table(table)
+
+
+def test_async_launch_and_status_slots(gpu_ctx, oracle):
+    rng = np.random.default_rng(9200)
+    rows, dim, batch = 500, 32, 40
+    table = random_fused_table(rng, rows, dim, 8)
+    lengths, offsets, indices, weights, n = lengths_indices_weights(rng, batch, rows, 10, np.int64, np.int64)
+    kern = make_kernel(8, dim, False, False, False, True, np.int64, np.int64, np.float32)
+    d_table, d_off = dev(table), dev(offsets)
+    good, bad = dev(indices), indices.copy()
+    bad[7] = -1
+    out1 = torch.zeros(batch * dim, device="cuda")
+    out2 = torch.zeros(batch * dim, device="cuda")
+    kern.launch(batch, n, rows, d_table, good, d_off, None, out1, slot=5)
+    kern.launch(batch, n, rows, d_table, dev(bad), d_off, None, out2, slot=6)
+    ok5, _ = F.status_read(5)
+    ok6, info = F.status_read(6)
+    assert ok5 and not ok6
+    assert info[0] == 1 and info[2] == 7 and info[3] == -1  # BAD_INDEX at position 7, value -1
+    ok6_again, _ = F.status_read(6)
+    assert ok6_again  # reading clears the slot
+    _, ref = oracle.spmdm(8, dim, rows, table, indices, offsets, None, False, np.float32)
+    np.testing.assert_array_equal(bits(out1.cpu().numpy()), bits(ref))
