@@ -1,0 +1,460 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized embedding-bag lookup on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+                    [--workload 0|1|2] [--streams S] [--group G]
+
+One *step* is one functor call (one batch of bags) of the chosen workload.
+Prints ONE JSON line:
+
+* ``value``      gathered-row GB/s with every input resident in HBM: the K
+                 steps are K separate kernel launches on distinct pre-generated
+                 batches, issued from a CUDA graph over S streams.
+* ``e2e``        the same metric through the host-pointer C-ABI call
+                 (``fbgemm_b200_spmdm_host_submit/wait``): indices, offsets and
+                 weights leave pinned host memory and the pooled rows return to
+                 the host inside the timed region; only the table is resident.
+* ``roofline``   HBM roofline of the lookup kernel on gathered-row bytes.
+* ``cpu_baseline`` the reference's CPU path timed on this box's host cores on
+                 a bounded sample of the same batches.
+
+``--impl reference`` times only the CPU path (all host threads) and prints the
+same line shape with ``"impl": "reference"``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FALLBACK_HBM_GBS = 6650.0
+GRAPH_CHUNK = 500       # steps per captured graph
+NUM_BATCHES = 32        # distinct pre-generated batches the steps rotate over
+ESZ = {"torch.int32": 4, "torch.int64": 8, "torch.float32": 4, "torch.float16": 2}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20000)
+    ap.add_argument("--warmup", type=int, default=500)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", type=int, default=1, help="index into BASELINE.json configs (0, 1 or 2)")
+    ap.add_argument("--streams", type=int, default=4, help="streams the graph spreads the launches over")
+    ap.add_argument("--group", type=int, default=1, help="batches concatenated into one call (1 = the config's batch)")
+    ap.add_argument("--scale", type=float, default=1.0, help="shrink rows and batch (tests only)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-pointer leg")
+    ap.add_argument("--e2e-steps", type=int, default=2000)
+    ap.add_argument("--cpu-seconds", type=float, default=4.0, help="wall-time bound of the CPU sample")
+    return ap.parse_args()
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback (no MEASURED_PEAKS.json)"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with NVML while the timed region
+    runs (read-only queries)."""
+
+    def __init__(self, index: int, period_s: float = 0.01):
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._h = None
+        self.period = period_s
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._h = None
+
+    def _run(self):
+        nv = self._nv
+        names = {
+            nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+            nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self._h is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def concat_batches(batches):
+    """Several batches as one call (bags appended, offsets re-based)."""
+    import torch
+
+    from fbgemm_b200.workloads import Batch
+
+    idx = torch.cat([b.indices for b in batches])
+    offs, base = [batches[0].offsets.to(torch.int64)], int(batches[0].offsets[-1])
+    for b in batches[1:]:
+        offs.append(b.offsets[1:].to(torch.int64) + base)
+        base += int(b.offsets[-1])
+    off = torch.cat(offs).to(batches[0].offsets.dtype)
+    w = torch.cat([b.weights for b in batches]) if batches[0].weights is not None else None
+    return Batch(idx, off, w, sum(b.output_size for b in batches), int(idx.numel()),
+                 sum(b.valid_rows for b in batches))
+
+
+# ---- CPU leg (the reference arm and cpu_baseline) ----------------------------------
+
+def cpu_runner(workload, host_table, host_cit):
+    """Returns (call(batch_np) -> ok, kind, description).  Prefers the
+    reference's own JIT kernels (bundled in libtorch_cpu.so), then the
+    reference's scalar sources, then the oracle port."""
+    from oracle import checker
+
+    jit = checker.ReferenceJit()
+    ref = checker.Reference()
+    if jit.available:
+        impl, kind, desc = jit, "reference", "FBGEMM asmjit AVX2/AVX-512 kernels as bundled in libtorch_cpu.so"
+    elif ref.available:
+        impl, kind, desc = ref, "reference", "FBGEMM scalar EmbeddingSpMDM*_ref compiled from the reference tree"
+    else:
+        impl, kind, desc = checker.Oracle(), "port", "plain-C oracle port (oracle/embedding_oracle.c)"
+    out_dt = np.float16 if str(workload.out_dtype) == "torch.float16" else np.float32
+
+    def call(hb, lo, hi):
+        """Bags [lo, hi) of host batch hb, as one functor call on a slice (how
+        the reference's callers parallelise: one thread per bag range)."""
+        offs = hb["offsets"][lo:hi + 1]
+        i0, i1 = int(offs[0]), int(offs[-1])
+        idx = hb["indices"][i0:i1]
+        wts = hb["weights"][i0:i1] if hb["weights"] is not None else None
+        if host_cit is not None:
+            ok, _ = impl.spmdm_rowwise_sparse(workload.bit_rate, workload.dim, workload.rows, host_table, idx,
+                                              host_cit, offs, wts, workload.normalize_by_lengths)
+        else:
+            ok, _ = impl.spmdm(workload.bit_rate, workload.dim, workload.rows, host_table, idx, offs, wts,
+                               workload.normalize_by_lengths, out_dt)
+        return ok
+
+    return call, kind, desc
+
+
+def time_cpu(workload, batches, host_table, host_cit, threads, max_steps, max_seconds):
+    """Run whole batches, each split over `threads` host threads, until
+    max_steps batches or max_seconds have passed.  Returns (seconds, steps,
+    gathered bytes, kind, desc)."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    from fbgemm_b200.workloads import algorithmic_bytes
+
+    call, kind, desc = cpu_runner(workload, host_table, host_cit)
+    host_batches = []
+    for b in batches:
+        host_batches.append({
+            "indices": b.indices.cpu().numpy(), "offsets": b.offsets.cpu().numpy(),
+            "weights": b.weights.cpu().numpy() if b.weights is not None else None,
+            "B": b.output_size, "bytes": algorithmic_bytes(workload, b)})
+    pool = ThreadPoolExecutor(max_workers=threads)
+
+    def run_batch(hb):
+        B = hb["B"]
+        cuts = [B * t // threads for t in range(threads + 1)]
+        futs = [pool.submit(call, hb, cuts[t], cuts[t + 1]) for t in range(threads) if cuts[t + 1] > cuts[t]]
+        return all(f.result() for f in futs)
+
+    assert run_batch(host_batches[0]), "CPU reference returned false on a valid batch"  # warm-up, JIT generation
+    t0 = time.perf_counter()
+    steps, nbytes = 0, 0
+    while steps < max_steps and (time.perf_counter() - t0) < max_seconds:
+        hb = host_batches[steps % len(host_batches)]
+        run_batch(hb)
+        steps += 1
+        nbytes += hb["bytes"]
+    dt = time.perf_counter() - t0
+    pool.shutdown()
+    return dt, steps, nbytes, kind, desc
+
+
+# ---- main -----------------------------------------------------------------------
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference" and rank != 0:
+        return 0  # the CPU arm runs on rank 0 alone
+
+    import torch
+
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device: fbgemm_b200 has no CPU path"}))
+        return 1
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+
+        if args.impl != "reference":
+            dist.init_process_group("nccl", device_id=dev)
+
+    import fbgemm_b200 as F
+    from fbgemm_b200 import workloads as W
+
+    # Table-wise sharding, weak scaling: every rank owns one table of the
+    # workload's shape (its own seed) and pools the same number of bags.
+    w = W.CONFIGS[args.workload](dev, scale=args.scale, seed=W.SEED + 1000 * rank)
+    base = [w.make_batch(s) for s in range(NUM_BATCHES * args.group)]
+    batches = [concat_batches(base[i * args.group:(i + 1) * args.group]) if args.group > 1 else base[i]
+               for i in range(NUM_BATCHES)]
+    bytes_per_step = float(np.mean([W.algorithmic_bytes(w, b) for b in batches]))
+    all_bytes_per_step = float(np.mean([W.all_bytes(w, b) for b in batches]))
+    bags_per_step = batches[0].output_size
+    config = {
+        "workload": w.name, "baseline_config_index": args.workload,
+        "table_rows": int(w.table.shape[0]), "row_bytes": w.row_bytes, "table_MB": round(w.table.numel() / 1e6, 1),
+        "bags_per_step": bags_per_step, "gathered_rows_per_step": round(bytes_per_step / w.row_bytes, 1),
+        "gathered_bytes_per_step": round(bytes_per_step), "batches_per_call": args.group,
+        "distinct_batches": NUM_BATCHES, "launch": f"CUDA graph, {args.streams} streams",
+        "l2": "table (larger than the 126 MB L2) is the gathered input; steps rotate over distinct batches",
+        "sharding": "table-wise, one table per GPU" if world > 1 else "single table",
+    }
+
+    if args.impl == "reference":
+        threads = os.cpu_count() or 1
+        host_table = w.table.cpu().numpy()
+        host_cit = w.cit.cpu().numpy() if w.cit is not None else None
+        time_cpu(w, batches[:2], host_table, host_cit, threads, args.warmup, 2.0)
+        dt, steps, nbytes, kind, desc = time_cpu(w, batches, host_table, host_cit, threads, args.steps, 60.0)
+        gbs = nbytes / dt / 1e9
+        line = {
+            "impl": "reference", "metric": "gathered_row_GBps", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+            "steps": steps, "warmup": args.warmup, "ms_per_step": dt / steps * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": f"u{w.bit_rate}->f32 accumulate", "data": "synthetic",
+            "config": config, "bags_per_s": bags_per_step * steps / dt,
+            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": kind,
+                             "sample": f"{steps} whole batches, each split over {threads} host threads; {desc}"},
+            "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }
+        print(json.dumps(line))
+        return 0
+
+    kern = w.make_kernel()
+    outs = [torch.zeros(b.output_size * w.dim, dtype=w.out_dtype, device=dev) for b in batches]
+
+    def launch(i, stream=None):
+        b = batches[i % NUM_BATCHES]
+        kern.launch(b.output_size, b.index_size, w.rows, w.table, b.indices, b.offsets, b.weights,
+                    outs[i % NUM_BATCHES], w.cit, slot=i % 256, stream=stream)
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- value: device-resident inputs ------------------------------------
+    launches_before = F.launch_count()
+    for i in range(max(args.warmup, 3)):
+        launch(i)
+    torch.cuda.synchronize()
+    assert all(F.status_read(s)[0] for s in range(256)), "a warm-up lookup reported an error"
+
+    chunk = min(GRAPH_CHUNK, args.steps)
+    streams = [torch.cuda.Stream(device=dev) for _ in range(max(1, args.streams))]
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        cur = torch.cuda.current_stream()
+        for s in streams:
+            s.wait_stream(cur)
+        for i in range(chunk):
+            with torch.cuda.stream(streams[i % len(streams)]):
+                launch(i)
+        for s in streams:
+            cur.wait_stream(s)
+    graph_launches = F.launch_count()  # capture counted `chunk` launches that did not run
+    replays, rest = divmod(args.steps, chunk)
+    graph.replay()
+    torch.cuda.synchronize()
+
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        e0.record()
+        for _ in range(replays):
+            graph.replay()
+        for i in range(rest):
+            launch(i)
+        e1.record()
+        torch.cuda.synchronize()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    ok = all(F.status_read(s)[0] for s in range(256))
+    timed_launches = replays * chunk + rest
+    if world > 1:
+        import torch.distributed as dist
+
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        tot = torch.tensor([bytes_per_step, float(bags_per_step)], device=dev, dtype=torch.float64)
+        dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+        job_bytes_per_step, job_bags_per_step = float(tot[0]), float(tot[1])
+    else:
+        job_bytes_per_step, job_bags_per_step = bytes_per_step, float(bags_per_step)
+    sec = ms / 1e3
+    value = job_bytes_per_step * args.steps / sec / 1e9
+    per_launch_us = ms * 1e3 / timed_launches
+    peak, peak_src = measured_peak()
+    achieved = bytes_per_step / (per_launch_us * 1e-6) / 1e9
+
+    # ---- e2e: host buffers through the C ABI -------------------------------------
+    e2e = None
+    if not args.no_e2e:
+        lanes = 8
+        hb = []
+        for b in batches:
+            pin = lambda t: t.cpu().pin_memory().numpy() if t is not None else None  # noqa: E731
+            hb.append((pin(b.indices), pin(b.offsets), pin(b.weights),
+                       torch.zeros(b.output_size * w.dim, dtype=w.out_dtype).pin_memory().numpy(), b))
+        ctx = F.get_context(local_rank)
+        import ctypes as C
+
+        from fbgemm_b200 import _capi
+        steps_e2e = min(args.e2e_steps, args.steps)
+
+        def submit(i):
+            idx, off, wts, out, b = hb[i % NUM_BATCHES]
+            rc = _capi.lib().fbgemm_b200_spmdm_host_submit(
+                ctx.handle, i % lanes, C.byref(kern.cfg), b.output_size, b.index_size, w.rows,
+                host_key, idx.ctypes.data, off.ctypes.data, wts.ctypes.data if wts is not None else None,
+                out.ctypes.data, cit_key)
+            _capi.check(rc, "host_submit")
+
+        # The caller's table lives in host memory; it is registered once (one
+        # upload) and stays resident in HBM under its host address.
+        host_tbl = w.table.cpu().numpy()
+        ctx.register_table(host_tbl)
+        host_key = host_tbl.ctypes.data
+        cit_key = None
+        if w.cit is not None:
+            host_cit = w.cit.cpu().numpy()
+            ctx.register_table(host_cit)
+            cit_key = host_cit.ctypes.data
+        for i in range(lanes):
+            submit(i)
+        for i in range(lanes):
+            assert kern.host_wait(i % lanes)
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(steps_e2e):
+            if i >= lanes:
+                kern.host_wait(i % lanes)
+            submit(i)
+        for i in range(min(lanes, steps_e2e)):
+            kern.host_wait((steps_e2e + i) % lanes)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        barrier()
+        if world > 1:
+            import torch.distributed as dist
+
+            t = torch.tensor([dt], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t.item())
+        h2d = float(np.mean([x[0].nbytes + x[1].nbytes + (x[2].nbytes if x[2] is not None else 0) for x in hb]))
+        d2h = float(np.mean([x[3].nbytes for x in hb])) + 16
+        e2e = {"value": job_bytes_per_step * steps_e2e / dt / 1e9, "unit": "GB/s",
+               "h2d_bytes_per_step": round(h2d), "d2h_bytes_per_step": round(d2h), "steps": steps_e2e,
+               "ms_per_step": dt / steps_e2e * 1e3, "bags_per_s": job_bags_per_step * steps_e2e / dt,
+               "path": "fbgemm_b200_spmdm_host_submit/wait, 8 pipelined lanes, pinned host buffers, table resident",
+               "timer": "host perf_counter bracketed by device synchronisation"}
+        ctx.unregister_table(host_tbl)
+        if w.cit is not None:
+            ctx.unregister_table(host_cit)
+
+    total_launches = F.launch_count() - launches_before
+
+    # ---- cpu_baseline (rank 0, one GPU only) ------------------------------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        threads = os.cpu_count() or 1
+        host_table = w.table.cpu().numpy()
+        host_cit = w.cit.cpu().numpy() if w.cit is not None else None
+        dt, steps, nbytes, kind, desc = time_cpu(w, batches, host_table, host_cit, threads, 10 ** 9, args.cpu_seconds)
+        cpu = {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": kind,
+               "sample": f"{steps} whole batches in {dt:.1f} s, each split over {threads} host threads; {desc}",
+               "bags_per_s": bags_per_step * steps / dt}
+
+    if rank == 0:
+        line = {
+            "metric": "gathered_row_GBps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": f"u{w.bit_rate}->f32 accumulate", "data": "synthetic",
+            "config": config, "results_ok": bool(ok),
+            "bags_per_s": job_bags_per_step * args.steps / sec,
+            "all_bytes_GBps": all_bytes_per_step * world * args.steps / sec / 1e9,
+            "frac_of_hbm_peak": value / world / peak,
+            "clocks": clocks.summary(),
+            "e2e": e2e,
+            "gpu_launches": timed_launches,
+            "gpu_launches_whole_run": int(total_launches),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": peak_src,
+                         "per_launch_us": per_launch_us,
+                         "note": "achieved = gathered-row bytes per launch / (timed region / launches); launches "
+                                 "of different streams overlap"},
+            "cpu_baseline": cpu,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
