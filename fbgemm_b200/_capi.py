@@ -14,6 +14,7 @@ from . import build as _build
 
 STATUS_SLOTS = 1024
 HOST_LANES = 8
+NOALLOC_MAX_BAGS = 1 << 20
 OUT_F32 = 0
 OUT_F16 = 1
 
@@ -56,6 +57,7 @@ SIGNATURES = {
     "fbgemm_b200_spmdm_launch": (C.c_int, [_p, _cfgp, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, C.c_int, _p]),
     "fbgemm_b200_status_read": (C.c_int, [_p, C.c_int, _p, C.POINTER(C.c_int32)]),
     "fbgemm_b200_spmdm": (C.c_int, [_p, _cfgp, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, _p]),
+    "fbgemm_b200_spmdm_lengths_noalloc": (C.c_int, [_cfgp, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, _p]),
     "fbgemm_b200_table_register": (C.c_int, [_p, _p, C.c_size_t]),
     "fbgemm_b200_table_unregister": (C.c_int, [_p, _p]),
     "fbgemm_b200_table_device_ptr": (_p, [_p, _p]),

@@ -28,11 +28,6 @@ int max_chunks_per_bag(int bit_rate);  // spmdm_kernels.cu
 
 namespace {
 
-struct DeviceBuffer {
-  void* ptr = nullptr;
-  size_t bytes = 0;
-};
-
 // Grow-only device buffer; contents are not preserved.
 cudaError_t reserve(DeviceBuffer& b, size_t bytes) {
   if (bytes <= b.bytes) {
@@ -184,9 +179,11 @@ int check_config(const fbgemm_b200_spmdm_config* c, Derived* d) {
   return 0;
 }
 
+}  // namespace
+
 // Build the kernel parameters for one functor call and enqueue it.  All
 // pointers are device pointers.  `scan` is the scratch for lengths mode.
-int enqueue_lookup(
+int fbgemm_b200::enqueue_lookup(
     const fbgemm_b200_spmdm_config* cfg,
     int64_t output_size,
     int64_t index_size,
@@ -291,8 +288,6 @@ int enqueue_lookup(
   }
   return 0;
 }
-
-}  // namespace
 
 extern "C" {
 

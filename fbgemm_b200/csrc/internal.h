@@ -67,6 +67,31 @@ cudaError_t launch_length_scan(
 cudaError_t launch_quantize_8bit(const float* in, int64_t rows, int cols, uint8_t* out, cudaStream_t s);
 cudaError_t launch_quantize_nbit(int bit_rate, const float* in, int64_t rows, int cols, uint8_t* out, cudaStream_t s);
 
+// A device allocation and its size.
+struct DeviceBuffer {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+};
+
+// Validate `cfg`, build the kernel parameters of one functor call and enqueue
+// it on `stream` (c_api.cu).  All pointers are device pointers; `status` is
+// the 4-word error record.  In lengths mode `scan` is grown on demand to hold
+// the scanned offsets.  Returns 0 or a negative FBGEMM_B200_E* code.
+int enqueue_lookup(
+    const fbgemm_b200_spmdm_config* cfg,
+    int64_t output_size,
+    int64_t index_size,
+    int64_t data_size,
+    const void* input,
+    const void* indices,
+    const void* offsets_or_lengths,
+    const float* weights,
+    void* out,
+    const int32_t* cit,
+    int32_t* status,
+    DeviceBuffer& scan,
+    cudaStream_t stream);
+
 // Process-wide count of kernels launched by this library.
 extern std::atomic<uint64_t> g_launch_count;
 

@@ -160,6 +160,45 @@ FBGEMM_B200_API int fbgemm_b200_spmdm(
     const int32_t* compressed_indices_table,
     void* stream);
 
+/*
+ * The lengths flavour of the lookup (cfg->use_offsets == 0) for callers that
+ * may not allocate device memory: programs whose own allocator owns the whole
+ * device, or whose serving loop forbids cudaMalloc after start-up because an
+ * allocation can stall the device or find the pool already taken.  It has no
+ * counterpart in the reference (whose functors run on the CPU and need no
+ * scratch); arguments and result are those of fbgemm_b200_spmdm without the
+ * context, and the pooled rows are bit-equal to that call's.
+ *
+ * The scratch that holds the scanned offsets and the status record is a
+ * fixed array in the library's device image (about 8.4 MB on every GPU that
+ * loads the library, held until the process exits) instead of a buffer from
+ * cudaMalloc; no allocating call is made, directly or indirectly.
+ *   - output_size may not exceed FBGEMM_B200_NOALLOC_MAX_BAGS; larger calls
+ *     are refused with FBGEMM_B200_EINVAL and an explanatory error text.
+ *   - The first call on a device looks up the array's device address (with
+ *     that device current); make that first call before any stream capture.
+ *   - All calls on a GPU share the one array, which keeps the previous
+ *     call's contents (the entry point clears what has to start at zero):
+ *     calls that overlap on the GPU race.  Run them one after another, e.g.
+ *     on one stream.
+ *   - The call synchronises `stream` to read the status record.
+ * All pointers are device pointers on the current device.
+ * Returns 1 / 0 (the functor's bool) or a negative error code.
+ */
+#define FBGEMM_B200_NOALLOC_MAX_BAGS (1 << 20)
+FBGEMM_B200_API int fbgemm_b200_spmdm_lengths_noalloc(
+    const fbgemm_b200_spmdm_config* cfg,
+    int64_t output_size,
+    int64_t index_size,
+    int64_t data_size,
+    const void* input,
+    const void* indices,
+    const void* lengths,
+    const float* weights,
+    void* out,
+    const int32_t* compressed_indices_table,
+    void* stream);
+
 /* ---- pooled lookup, host pointers -------------------------------------- */
 
 /*
