@@ -1,0 +1,469 @@
+// The fast lookup kernel: rows go from HBM/L2 straight into registers.
+//
+// Same arithmetic as the staged kernel in spmdm_kernels.cu (and therefore as
+// the scalar reference, src/RefImplementations.cc:1290-1346, :1485-1541,
+// :1746-1822): per output column, rows strictly in index order,
+// acc = fma(w*scale, q, acc + w*bias).  What differs is how the work is laid
+// out, because the lookup turned out to be bound by instruction issue, not by
+// HBM, once enough rows are in flight:
+//
+//  * A bag belongs to a group of LPB lanes (4..32); each lane owns CPL
+//    "chunks" of VEC bytes of the packed payload, i.e. up to 32 columns kept in
+//    registers as 16 fp32x2 pairs.  Narrow groups mean the per-row work that
+//    does not scale with D (index fetch, bounds check, address, scale/bias,
+//    weight) is paid by few lanes while 32/LPB bags advance per warp
+//    instruction.
+//  * No shared-memory stage.  The work per row that is independent of the
+//    column (index fetch, range check, pruning map, weight) is done by one
+//    lane of the group per row and broadcast by shuffle; every lane then issues
+//    its own VEC loads for U rows back to back, so U rows per bag (U * 32/LPB
+//    per warp) are in flight before the first use, and the indices of the next
+//    step are fetched before the arithmetic of the current one.
+//  * The two roundings per column per row are done two columns at a time with
+//    the packed fp32 instructions of sm_100 (add.rn.f32x2, fma.rn.f32x2), which
+//    round each half exactly like the scalar instructions.
+//  * Integer -> float: each byte / nibble / crumb is planted with one prmt in
+//    the mantissa of 2^23 and 2^23 is subtracted (packed as well).
+//
+// Requirements (checked by the dispatcher): table address, row pitch and
+// payload width are multiples of VEC (4 or 8 bytes).  Everything else takes
+// the staged kernel.
+#pragma once
+
+#include <cuda_fp16.h>
+
+#include "internal.h"
+
+namespace fbgemm_b200 {
+namespace direct {
+
+constexpr int kWarpsPerBlock = 4;
+constexpr int kThreads = kWarpsPerBlock * 32;
+
+using u64 = unsigned long long;
+
+__device__ __forceinline__ u64 pack2(float lo, float hi) {
+  u64 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(u64 v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ u64 add2(u64 a, u64 b) {
+  u64 r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ u64 mul2(u64 a, u64 b) {
+  u64 r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ u64 fma2(u64 a, u64 b, u64 c) {
+  u64 r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
+// Bytes I of xa and J of xb as the fp32 pair (2^23 + byte, 2^23 + byte).
+template <int I, int J>
+__device__ __forceinline__ u64 magic_pair(uint32_t xa, uint32_t xb) {
+  return pack2(
+      __uint_as_float(__byte_perm(xa, 0x4B000000u, 0x7540u | I)),
+      __uint_as_float(__byte_perm(xb, 0x4B000000u, 0x7540u | J)));
+}
+
+// acc = fma(scale, q, acc + bias) on a pair of columns; `m` holds 2^23 + q.
+__device__ __forceinline__ u64 pool2(u64 acc, u64 m, u64 scale2, u64 bias2, u64 neg_magic2) {
+  return fma2(scale2, add2(m, neg_magic2), add2(acc, bias2));
+}
+
+// One 32-bit word of packed payload into 32/BITS columns = 16/BITS pairs.
+template <int BITS>
+__device__ __forceinline__ void accumulate_word(u64* acc, uint32_t x, u64 s2, u64 b2, u64 nm2) {
+  if constexpr (BITS == 8) {
+    acc[0] = pool2(acc[0], magic_pair<0, 1>(x, x), s2, b2, nm2);
+    acc[1] = pool2(acc[1], magic_pair<2, 3>(x, x), s2, b2, nm2);
+  } else if constexpr (BITS == 4) {
+    // element 2k = low nibble of byte k, element 2k+1 = high nibble
+    const uint32_t lo = x & 0x0F0F0F0Fu;
+    const uint32_t hi = (x >> 4) & 0x0F0F0F0Fu;
+    acc[0] = pool2(acc[0], magic_pair<0, 0>(lo, hi), s2, b2, nm2);
+    acc[1] = pool2(acc[1], magic_pair<1, 1>(lo, hi), s2, b2, nm2);
+    acc[2] = pool2(acc[2], magic_pair<2, 2>(lo, hi), s2, b2, nm2);
+    acc[3] = pool2(acc[3], magic_pair<3, 3>(lo, hi), s2, b2, nm2);
+  } else {
+    // element 4k+i = bits [2i+1:2i] of byte k
+    const uint32_t t0 = x & 0x03030303u;
+    const uint32_t t1 = (x >> 2) & 0x03030303u;
+    const uint32_t t2 = (x >> 4) & 0x03030303u;
+    const uint32_t t3 = (x >> 6) & 0x03030303u;
+    acc[0] = pool2(acc[0], magic_pair<0, 0>(t0, t1), s2, b2, nm2);
+    acc[1] = pool2(acc[1], magic_pair<0, 0>(t2, t3), s2, b2, nm2);
+    acc[2] = pool2(acc[2], magic_pair<1, 1>(t0, t1), s2, b2, nm2);
+    acc[3] = pool2(acc[3], magic_pair<1, 1>(t2, t3), s2, b2, nm2);
+    acc[4] = pool2(acc[4], magic_pair<2, 2>(t0, t1), s2, b2, nm2);
+    acc[5] = pool2(acc[5], magic_pair<2, 2>(t2, t3), s2, b2, nm2);
+    acc[6] = pool2(acc[6], magic_pair<3, 3>(t0, t1), s2, b2, nm2);
+    acc[7] = pool2(acc[7], magic_pair<3, 3>(t2, t3), s2, b2, nm2);
+  }
+}
+
+template <int VEC>
+struct Vec;
+template <>
+struct Vec<4> {
+  uint32_t w[1];
+  __device__ __forceinline__ void load(const uint8_t* p) { w[0] = __ldg(reinterpret_cast<const uint32_t*>(p)); }
+};
+template <>
+struct Vec<8> {
+  uint32_t w[2];
+  __device__ __forceinline__ void load(const uint8_t* p) {
+    const uint2 v = __ldg(reinterpret_cast<const uint2*>(p));
+    w[0] = v.x;
+    w[1] = v.y;
+  }
+};
+
+// Raw scale,bias bits of one row: fp32 pair for 8-bit rows, fp16 pair else.
+template <int BITS, int VEC>
+struct ScaleBias {
+  uint32_t raw[BITS == 8 ? 2 : 1];
+  __device__ __forceinline__ void load(const uint8_t* p) {
+    if constexpr (BITS != 8) {
+      raw[0] = __ldg(reinterpret_cast<const uint32_t*>(p));
+    } else if constexpr (VEC >= 8) {
+      const uint2 v = __ldg(reinterpret_cast<const uint2*>(p));
+      raw[0] = v.x;
+      raw[1] = v.y;
+    } else {
+      raw[0] = __ldg(reinterpret_cast<const uint32_t*>(p));
+      raw[1] = __ldg(reinterpret_cast<const uint32_t*>(p + 4));
+    }
+  }
+  __device__ __forceinline__ void get(float& scale, float& bias) const {
+    if constexpr (BITS == 8) {
+      scale = __uint_as_float(raw[0]);
+      bias = __uint_as_float(raw[1]);
+    } else {
+      scale = __half2float(__ushort_as_half((unsigned short)(raw[0] & 0xffffu)));
+      bias = __half2float(__ushort_as_half((unsigned short)(raw[0] >> 16)));
+    }
+  }
+};
+
+__device__ __forceinline__ int64_t load_int(const void* p, int64_t i, bool is64) {
+  return is64 ? (int64_t)__ldg(reinterpret_cast<const long long*>(p) + i)
+              : (int64_t)__ldg(reinterpret_cast<const int*>(p) + i);
+}
+
+static __device__ __noinline__ void report(int32_t* st, int code, int64_t bag, int64_t pos, int64_t val) {
+  if (atomicCAS(st, 0, code) == 0) {
+    st[1] = (int32_t)bag;
+    st[2] = (int32_t)pos;
+    st[3] = (int32_t)val;
+  }
+}
+
+constexpr uint32_t kSkipRow = 0xFFFFFFFFu;
+
+// The per-row work that does not depend on the column - index fetch, range
+// check, pruning map, weight fetch - is done once per row by ONE lane of the
+// bag's group: in a step of U rows, lane gl resolves rows gl, gl+LPB, ...
+// The results reach the other lanes of the group by shuffle in pool_step.
+// id = row to read (after pruning), or kSkipRow for a row that contributes
+// nothing (pruned, out of range, or beyond the `nvalid` rows of a short step).
+template <int LPB, int U>
+__device__ __forceinline__ void fetch_rows(
+    const SpmdmParams& p,
+    int gl,
+    int64_t bag,
+    int64_t pos0,
+    int r0,
+    int nvalid,
+    uint32_t (&id)[(U + LPB - 1) / LPB],
+    float (&w)[(U + LPB - 1) / LPB]) {
+  constexpr int OWN = (U + LPB - 1) / LPB;
+#pragma unroll
+  for (int j = 0; j < OWN; ++j) {
+    const int u = gl + j * LPB;
+    id[j] = kSkipRow;
+    w[j] = 0.f;
+    if (u < nvalid) {
+      const int64_t pos = pos0 + u;
+      const int64_t idx = load_int(p.indices, pos, p.flags & kIdx64);
+      if ((unsigned long long)idx >= (unsigned long long)p.data_size) {
+        report(p.status, FBGEMM_B200_STATUS_BAD_INDEX, bag, pos, idx);
+      } else if (p.flags & kPruned) {
+        const int32_t c = __ldg(p.cit + idx);  // -1: pruned row
+        if (c >= 0) {
+          id[j] = (uint32_t)c;
+        }
+      } else {
+        id[j] = (uint32_t)idx;
+      }
+      if (p.flags & kWeighted) {
+        w[j] = __ldg(p.weights + ((p.flags & kPositional) ? (int64_t)(r0 + u) : pos));
+      }
+    }
+  }
+}
+
+// One step: U rows of the bag.  All row loads are issued before the first
+// use; then the rows are pooled in order.
+template <int BITS, int VEC, int LPB, int CPL, int U>
+__device__ __forceinline__ void pool_step(
+    const uint8_t* const (&chunk_base)[CPL],  // table + byte offset of this lane's chunk ci
+    const uint8_t* sb_base,                   // table + data_bytes
+    uint32_t stride,
+    unsigned gmask,
+    int lane0,  // first lane of the group
+    bool weighted,
+    const uint32_t (&id_own)[(U + LPB - 1) / LPB],
+    const float (&w_own)[(U + LPB - 1) / LPB],
+    u64 (&acc)[CPL][(VEC / 4) * (16 / BITS)]) {
+  constexpr int PAIRS_PER_WORD = 16 / BITS;
+  uint32_t rid[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    rid[u] = LPB == 1 ? id_own[u] : __shfl_sync(gmask, id_own[u / LPB], lane0 + (u % LPB));
+  }
+  Vec<VEC> d[U][CPL];
+  ScaleBias<BITS, VEC> sb[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    // a skipped row reads row 0 (always there) and is then pooled with zeros
+    const unsigned long long off = (unsigned long long)(rid[u] == kSkipRow ? 0u : rid[u]) * stride;
+#pragma unroll
+    for (int ci = 0; ci < CPL; ++ci) {
+      d[u][ci].load(chunk_base[ci] + off);
+    }
+    sb[u].load(sb_base + off);
+  }
+  const u64 nm2 = pack2(-8388608.0f, -8388608.0f);
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    float scale, bias;
+    sb[u].get(scale, bias);
+    if (weighted) {
+      const float w = LPB == 1 ? w_own[u] : __shfl_sync(gmask, w_own[u / LPB], lane0 + (u % LPB));
+      scale = __fmul_rn(w, scale);
+      bias = __fmul_rn(w, bias);
+    }
+    // scale = bias = 0 leaves every accumulator unchanged: acc + 0 = acc and
+    // 0 * q = 0 for the finite q that prmt makes of any bit pattern.
+    scale = rid[u] == kSkipRow ? 0.f : scale;
+    bias = rid[u] == kSkipRow ? 0.f : bias;
+    const u64 s2 = pack2(scale, scale);
+    const u64 b2 = pack2(bias, bias);
+#pragma unroll
+    for (int ci = 0; ci < CPL; ++ci) {
+#pragma unroll
+      for (int wd = 0; wd < VEC / 4; ++wd) {
+        accumulate_word<BITS>(&acc[ci][wd * PAIRS_PER_WORD], d[u][ci].w[wd], s2, b2, nm2);
+      }
+    }
+  }
+}
+
+// Store CPC consecutive columns starting at col0 of output row `bag`.
+template <int CPC>
+__device__ __forceinline__ void store_columns(const SpmdmParams& p, int64_t bag, int col0, const u64* pairs) {
+  float v[CPC];
+#pragma unroll
+  for (int i = 0; i < CPC / 2; ++i) {
+    unpack2(pairs[i], v[2 * i], v[2 * i + 1]);
+  }
+  const bool full = col0 + CPC <= p.block_size;
+  if (p.flags & kOutHalf) {
+    __half* o = reinterpret_cast<__half*>(p.out) + bag * p.output_stride + col0;
+    if (full && (p.flags & kOutVec)) {
+      uint32_t h[CPC / 2];
+#pragma unroll
+      for (int i = 0; i < CPC / 2; ++i) {
+        const __half2 hh = __halves2half2(__float2half_rn(v[2 * i]), __float2half_rn(v[2 * i + 1]));
+        h[i] = *reinterpret_cast<const uint32_t*>(&hh);
+      }
+      if constexpr (CPC == 4) {
+        *reinterpret_cast<uint2*>(o) = make_uint2(h[0], h[1]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < CPC / 8; ++i) {
+          reinterpret_cast<uint4*>(o)[i] = make_uint4(h[4 * i], h[4 * i + 1], h[4 * i + 2], h[4 * i + 3]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < CPC; ++i) {
+        if (col0 + i < p.block_size) {
+          o[i] = __float2half_rn(v[i]);
+        }
+      }
+    }
+  } else {
+    float* o = reinterpret_cast<float*>(p.out) + bag * p.output_stride + col0;
+    if (full && (p.flags & kOutVec)) {
+#pragma unroll
+      for (int i = 0; i < CPC / 4; ++i) {
+        reinterpret_cast<float4*>(o)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < CPC; ++i) {
+        if (col0 + i < p.block_size) {
+          o[i] = v[i];
+        }
+      }
+    }
+  }
+}
+
+template <int BITS, int VEC, int LPB, int CPL>
+__global__ void __launch_bounds__(kThreads)
+spmdm_direct_kernel(const __grid_constant__ SpmdmParams p) {
+  constexpr int GPW = 32 / LPB;                       // bags per warp
+  constexpr int CPC = VEC * 8 / BITS;                 // columns per chunk
+  constexpr int PAIRS = (VEC / 4) * (16 / BITS);      // fp32x2 pairs per chunk
+  // Rows in flight per bag: bounded by the registers the row data takes.
+  constexpr int UMAX = (CPL * VEC / 4 <= 4) ? 8 : 4;
+  constexpr int OWN = (UMAX + LPB - 1) / LPB;
+
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int grp = lane / LPB;
+  const int gl = lane % LPB;
+  const int lane0 = grp * LPB;
+  const unsigned gmask = LPB == 32 ? 0xffffffffu : (((1u << LPB) - 1u) << lane0);
+  const bool off64 = p.flags & kOff64;
+  const bool weighted = p.flags & kWeighted;
+
+  const int64_t off_base = load_int(p.offsets, 0, off64);
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    // `return current == index_size` of the reference
+    const int64_t total = load_int(p.offsets, p.output_size, off64) - off_base;
+    if (total != p.index_size) {
+      report(p.status, FBGEMM_B200_STATUS_SIZE_MISMATCH, p.output_size, total, p.index_size);
+    }
+  }
+  const int64_t bag = ((int64_t)blockIdx.x * kWarpsPerBlock + warp) * GPW + grp;
+  if (bag >= p.output_size) {
+    return;
+  }
+  const int64_t o0 = load_int(p.offsets, bag, off64);
+  const int64_t o1 = load_int(p.offsets, bag + 1, off64);
+  const int64_t start = o0 - off_base;
+  const int bag_len = (int)(o1 - o0);  // the reference narrows to 32 bits too
+  int len = bag_len < 0 ? 0 : bag_len;
+  if (start < 0 || start + len > p.index_size) {
+    if (gl == 0) {
+      report(p.status, FBGEMM_B200_STATUS_BAG_OVERRUN, bag, start, len);
+    }
+    len = 0;  // never read past the caller's arrays
+  }
+
+  // Lanes whose chunk lies beyond the payload (row width not a multiple of
+  // LPB*CPL chunks) read chunk 0 instead and simply do not store.
+  const int nchunks = p.data_bytes / VEC;
+  const uint8_t* chunk_base[CPL];
+#pragma unroll
+  for (int ci = 0; ci < CPL; ++ci) {
+    const int c = gl + ci * LPB;
+    chunk_base[ci] = p.table + (c < nchunks ? c * VEC : 0);
+  }
+  const uint8_t* sb_base = p.table + p.data_bytes;
+  const uint32_t stride = (uint32_t)p.input_stride;
+
+  u64 acc[CPL][PAIRS];
+#pragma unroll
+  for (int ci = 0; ci < CPL; ++ci) {
+#pragma unroll
+    for (int j = 0; j < PAIRS; ++j) {
+      acc[ci][j] = 0ull;  // (+0.f, +0.f)
+    }
+  }
+
+  // Full steps of UMAX rows; the indices of step s+1 are fetched before the
+  // arithmetic of step s so that their latency hides behind it.
+  const int nfull = len / UMAX;
+  uint32_t id_cur[OWN];
+  float w_cur[OWN];
+  if (nfull > 0) {
+    fetch_rows<LPB, UMAX>(p, gl, bag, start, 0, UMAX, id_cur, w_cur);
+  }
+#pragma unroll 1
+  for (int s = 0; s < nfull; ++s) {
+    uint32_t id_nxt[OWN];
+    float w_nxt[OWN];
+    if (s + 1 < nfull) {
+      fetch_rows<LPB, UMAX>(p, gl, bag, start + (int64_t)(s + 1) * UMAX, (s + 1) * UMAX, UMAX, id_nxt, w_nxt);
+    }
+    pool_step<BITS, VEC, LPB, CPL, UMAX>(chunk_base, sb_base, stride, gmask, lane0, weighted, id_cur, w_cur, acc);
+#pragma unroll
+    for (int j = 0; j < OWN; ++j) {
+      id_cur[j] = id_nxt[j];
+      w_cur[j] = w_nxt[j];
+    }
+  }
+  // The remaining rows, largest power of two first (each such step is full).
+  int r = nfull * UMAX;
+  if constexpr (UMAX >= 8) {
+    if (len - r >= 4) {
+      uint32_t id4[(4 + LPB - 1) / LPB];
+      float w4[(4 + LPB - 1) / LPB];
+      fetch_rows<LPB, 4>(p, gl, bag, start + r, r, 4, id4, w4);
+      pool_step<BITS, VEC, LPB, CPL, 4>(chunk_base, sb_base, stride, gmask, lane0, weighted, id4, w4, acc);
+      r += 4;
+    }
+  }
+  if (len - r >= 2) {
+    uint32_t id2[(2 + LPB - 1) / LPB];
+    float w2[(2 + LPB - 1) / LPB];
+    fetch_rows<LPB, 2>(p, gl, bag, start + r, r, 2, id2, w2);
+    pool_step<BITS, VEC, LPB, CPL, 2>(chunk_base, sb_base, stride, gmask, lane0, weighted, id2, w2, acc);
+    r += 2;
+  }
+  if (len - r >= 1) {
+    uint32_t id1[1];
+    float w1[1];
+    fetch_rows<LPB, 1>(p, gl, bag, start + r, r, 1, id1, w1);
+    pool_step<BITS, VEC, LPB, CPL, 1>(chunk_base, sb_base, stride, gmask, lane0, weighted, id1, w1, acc);
+  }
+
+  if ((p.flags & kNormalize) && bag_len != 0) {
+    const float inv = __fdiv_rn(1.f, (float)bag_len);
+    const u64 inv2 = pack2(inv, inv);
+#pragma unroll
+    for (int ci = 0; ci < CPL; ++ci) {
+#pragma unroll
+      for (int j = 0; j < PAIRS; ++j) {
+        acc[ci][j] = mul2(acc[ci][j], inv2);
+      }
+    }
+  }
+#pragma unroll
+  for (int ci = 0; ci < CPL; ++ci) {
+    const int c = gl + ci * LPB;
+    if (c < nchunks) {
+      store_columns<CPC>(p, bag, c * CPC, acc[ci]);
+    }
+  }
+}
+
+using KernelFn = void (*)(const SpmdmParams);
+
+struct Variant {
+  KernelFn fn;
+  int vec, lpb, cpl;
+};
+
+}  // namespace direct
+
+// Tables of instantiated variants, one translation unit per bit rate
+// (spmdm_direct_{8,4,2}.cu).
+const direct::Variant* direct_variants_8(int* count);
+const direct::Variant* direct_variants_4(int* count);
+const direct::Variant* direct_variants_2(int* count);
+
+}  // namespace fbgemm_b200

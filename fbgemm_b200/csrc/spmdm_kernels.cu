@@ -25,6 +25,7 @@
 #include <cstdlib>
 
 #include "internal.h"
+#include "spmdm_direct.cuh"
 
 namespace fbgemm_b200 {
 
@@ -419,7 +420,78 @@ int max_chunks_per_bag(int bit_rate) {
   return 32 * (bit_rate == 8 ? 8 : bit_rate == 4 ? 4 : 2);
 }
 
+// The direct kernel (spmdm_direct.cuh) when the rows allow 4- or 8-byte vector
+// loads; returns cudaErrorNotSupported when they do not.
+static cudaError_t launch_direct(SpmdmParams p, int bit_rate, cudaStream_t stream) {
+  const uintptr_t base = reinterpret_cast<uintptr_t>(p.table);
+  auto divides = [&](int v) { return base % v == 0 && p.input_stride % v == 0 && p.data_bytes % v == 0; };
+  // Row ids travel between lanes as 32-bit values and skipped rows read row 0.
+  if (!divides(4) || p.data_bytes == 0 || p.data_size == 0 || p.data_size > 0xfffffffeLL ||
+      p.input_stride > 0xffffffffLL) {
+    return cudaErrorNotSupported;
+  }
+  int vec = divides(8) ? 8 : 4;
+  const int env_vec = env_int("FBGEMM_B200_VEC", 0);
+  if (env_vec == 4) {
+    vec = 4;
+  }
+  int count = 0;
+  const direct::Variant* v = bit_rate == 8 ? direct_variants_8(&count)
+      : bit_rate == 4                      ? direct_variants_4(&count)
+                                           : direct_variants_2(&count);
+  const int cpc = vec * 8 / bit_rate;      // columns per chunk
+  const int nchunks = p.data_bytes / vec;
+  int cpl_max = 0;
+  for (int i = 0; i < count; ++i) {
+    if (v[i].vec == vec && v[i].cpl > cpl_max) {
+      cpl_max = v[i].cpl;
+    }
+  }
+  // Aim at about 16 columns per lane: narrow lane groups amortise the per-row
+  // work that does not scale with D; more than 32 columns do not fit registers.
+  int cpl_target = 16 / cpc < 1 ? 1 : 16 / cpc;
+  cpl_target = cpl_target > cpl_max ? cpl_max : cpl_target;
+  int lpb = 2;
+  while (lpb < 32 && lpb * cpl_target < nchunks) {
+    lpb *= 2;
+  }
+  int cpl = 1;
+  while (lpb * cpl < nchunks) {
+    cpl *= 2;
+  }
+  const int env_lpb = env_int("FBGEMM_B200_LPB", 0);
+  const int env_cpl = env_int("FBGEMM_B200_CPL", 0);
+  if (env_lpb > 0 && env_cpl > 0 && env_lpb * env_cpl >= nchunks) {
+    lpb = env_lpb;
+    cpl = env_cpl;
+  }
+  const direct::Variant* pick = nullptr;
+  for (int i = 0; i < count; ++i) {
+    if (v[i].vec == vec && v[i].lpb == lpb && v[i].cpl == cpl) {
+      pick = &v[i];
+    }
+  }
+  if (!pick) {
+    return cudaErrorNotSupported;
+  }
+  const int64_t bags_per_block = (int64_t)direct::kWarpsPerBlock * (32 / lpb);
+  const int64_t blocks = (p.output_size + bags_per_block - 1) / bags_per_block;
+  if (blocks <= 0 || blocks > 0x7fffffffLL) {
+    return cudaErrorInvalidValue;
+  }
+  pick->fn<<<(unsigned)blocks, direct::kThreads, 0, stream>>>(p);
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_spmdm(const SpmdmParams& p_in, int bit_rate, cudaStream_t stream) {
+  const char* force = std::getenv("FBGEMM_B200_KERNEL");
+  if (!(force && force[0] == 's')) {  // "staged" forces the generic kernel
+    const cudaError_t e = launch_direct(p_in, bit_rate, stream);
+    if (e != cudaErrorNotSupported) {
+      return e;
+    }
+  }
   SpmdmParams p = p_in;
   int count = 0;
   const Variant* v = bit_rate == 8 ? variants<8>(&count) : bit_rate == 4 ? variants<4>(&count) : variants<2>(&count);
