@@ -81,7 +81,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     for src in _sources():
         obj = os.path.join(objdir, os.path.basename(src) + ".o")
         objs.append(obj)
-        cmd = [nvcc, *NVCC_FLAGS, "-c", src, "-o", obj]
+        cmd = [nvcc, *NVCC_FLAGS, *os.environ.get("FBGEMM_B200_EXTRA_NVCC", "").split(), "-c", src, "-o", obj]
         if src.endswith(".cc"):
             cmd.insert(1, "-x")
             cmd.insert(2, "cu")

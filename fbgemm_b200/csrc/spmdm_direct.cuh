@@ -326,8 +326,14 @@ spmdm_direct_kernel(const __grid_constant__ SpmdmParams p) {
   constexpr int GPW = 32 / LPB;                       // bags per warp
   constexpr int CPC = VEC * 8 / BITS;                 // columns per chunk
   constexpr int PAIRS = (VEC / 4) * (16 / BITS);      // fp32x2 pairs per chunk
-  // Rows in flight per bag: bounded by the registers the row data takes.
-  constexpr int UMAX = (CPL * VEC / 4 <= 4) ? 8 : 4;
+  // Rows per step.  Measured on B200: 4 beats 2, 8 and 16 for every row format
+  // (more rows per step cost registers, hence resident warps, and that costs
+  // more than the extra loads in flight per warp bring).
+#ifdef FBGEMM_B200_UMAX
+  constexpr int UMAX = FBGEMM_B200_UMAX;
+#else
+  constexpr int UMAX = 4;
+#endif
   constexpr int OWN = (UMAX + LPB - 1) / LPB;
 
   const int lane = threadIdx.x & 31;
@@ -408,6 +414,15 @@ spmdm_direct_kernel(const __grid_constant__ SpmdmParams p) {
   }
   // The remaining rows, largest power of two first (each such step is full).
   int r = nfull * UMAX;
+  if constexpr (UMAX >= 16) {
+    if (len - r >= 8) {
+      uint32_t id8[(8 + LPB - 1) / LPB];
+      float w8[(8 + LPB - 1) / LPB];
+      fetch_rows<LPB, 8>(p, gl, bag, start + r, r, 8, id8, w8);
+      pool_step<BITS, VEC, LPB, CPL, 8>(chunk_base, sb_base, stride, gmask, lane0, weighted, id8, w8, acc);
+      r += 8;
+    }
+  }
   if constexpr (UMAX >= 8) {
     if (len - r >= 4) {
       uint32_t id4[(4 + LPB - 1) / LPB];
@@ -417,7 +432,7 @@ spmdm_direct_kernel(const __grid_constant__ SpmdmParams p) {
       r += 4;
     }
   }
-  if (len - r >= 2) {
+  if (UMAX >= 4 && len - r >= 2) {
     uint32_t id2[(2 + LPB - 1) / LPB];
     float w2[(2 + LPB - 1) / LPB];
     fetch_rows<LPB, 2>(p, gl, bag, start + r, r, 2, id2, w2);
