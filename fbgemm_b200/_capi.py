@@ -15,6 +15,7 @@ from . import build as _build
 STATUS_SLOTS = 1024
 HOST_LANES = 8
 NOALLOC_MAX_BAGS = 1 << 20
+MAX_PEERS = 8
 OUT_F32 = 0
 OUT_F16 = 1
 
@@ -55,6 +56,8 @@ SIGNATURES = {
     "fbgemm_b200_launch_count": (C.c_uint64, []),
     "fbgemm_b200_spmdm_check_config": (C.c_int, [_cfgp]),
     "fbgemm_b200_spmdm_launch": (C.c_int, [_p, _cfgp, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, C.c_int, _p]),
+    "fbgemm_b200_spmdm_launch_sharded": (C.c_int, [_p, _cfgp, _i64, _i64, _i64, _p, _p, _p, _p, C.POINTER(_p),
+                                                   C.c_int, _i64, C.c_int, _p]),
     "fbgemm_b200_status_read": (C.c_int, [_p, C.c_int, _p, C.POINTER(C.c_int32)]),
     "fbgemm_b200_spmdm": (C.c_int, [_p, _cfgp, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, _p]),
     "fbgemm_b200_spmdm_lengths_noalloc": (C.c_int, [_cfgp, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, _p]),

@@ -196,7 +196,10 @@ int fbgemm_b200::enqueue_lookup(
     const int32_t* cit,
     int32_t* status,
     DeviceBuffer& scan,
-    cudaStream_t stream) {
+    cudaStream_t stream,
+    void* const* peer_out,
+    int num_peers,
+    int64_t bags_per_peer) {
   Derived d;
   int rc = check_config(cfg, &d);
   if (rc) {
@@ -258,7 +261,23 @@ int fbgemm_b200::enqueue_lookup(
   flags |= cfg->normalize_by_lengths ? kNormalize : 0;
   flags |= cit ? kPruned : 0;
   const size_t esize = cfg->out_dtype == FBGEMM_B200_OUT_F16 ? 2 : 4;
-  if (reinterpret_cast<uintptr_t>(out) % 16 == 0 && (d.output_stride * esize) % 16 == 0) {
+  bool out_aligned = (d.output_stride * esize) % 16 == 0;
+  if (num_peers > 0) {
+    if (!peer_out || num_peers > FBGEMM_B200_MAX_PEERS || bags_per_peer <= 0 ||
+        (int64_t)num_peers * bags_per_peer < output_size || cit) {
+      set_error("bad peer output description");
+      return FBGEMM_B200_EINVAL;
+    }
+    p.num_peers = num_peers;
+    p.bags_per_peer = bags_per_peer;
+    for (int i = 0; i < num_peers; ++i) {
+      p.peer_out[i] = peer_out[i];
+      out_aligned = out_aligned && reinterpret_cast<uintptr_t>(peer_out[i]) % 16 == 0;
+    }
+  } else {
+    out_aligned = out_aligned && reinterpret_cast<uintptr_t>(out) % 16 == 0;
+  }
+  if (out_aligned) {
     flags |= kOutVec;
   }
 
@@ -419,6 +438,35 @@ int fbgemm_b200_spmdm_launch(
   return enqueue_lookup(cfg, output_size, index_size, data_size, input, indices, offsets_or_lengths, weights, out,
                         compressed_indices_table, ctx->status + 4 * slot, ctx->scan,
                         static_cast<cudaStream_t>(stream));
+}
+
+int fbgemm_b200_spmdm_launch_sharded(
+    fbgemm_b200_ctx* ctx,
+    const fbgemm_b200_spmdm_config* cfg,
+    int64_t output_size,
+    int64_t index_size,
+    int64_t data_size,
+    const void* input,
+    const void* indices,
+    const void* offsets,
+    const float* weights,
+    void* const* peer_out,
+    int num_peers,
+    int64_t bags_per_peer,
+    int slot,
+    void* stream) {
+  if (!ctx || slot < 0 || slot >= FBGEMM_B200_STATUS_SLOTS) {
+    set_error("bad context or status slot");
+    return FBGEMM_B200_EINVAL;
+  }
+  if (!cfg || !cfg->use_offsets || output_size <= 0 || num_peers <= 0) {
+    set_error("sharded launch needs offsets, at least one bag and at least one peer");
+    return FBGEMM_B200_EINVAL;
+  }
+  DeviceGuard guard(ctx->device);
+  return enqueue_lookup(cfg, output_size, index_size, data_size, input, indices, offsets, weights, nullptr, nullptr,
+                        ctx->status + 4 * slot, ctx->scan, static_cast<cudaStream_t>(stream), peer_out, num_peers,
+                        bags_per_peer);
 }
 
 int fbgemm_b200_status_read(fbgemm_b200_ctx* ctx, int slot, void* stream, int32_t* info) {

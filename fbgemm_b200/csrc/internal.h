@@ -46,7 +46,22 @@ struct SpmdmParams {
   int32_t group_smem;         // shared-memory bytes per bag slot
   int32_t copy_width;         // 16/8/4: cp.async granule; 0: byte-wise path
   uint32_t flags;
+  // Batch-wise redistribution of the pooled rows (table-wise sharding): when
+  // num_peers > 0, bag b is written to peer_out[b / bags_per_peer] at row
+  // b % bags_per_peer instead of `out`.  The pointers may be peer-GPU memory.
+  int32_t num_peers;
+  int64_t bags_per_peer;
+  void* peer_out[FBGEMM_B200_MAX_PEERS];
 };
+
+// Where the pooled row of `bag` goes (byte pointer; esize = bytes per element).
+__device__ __forceinline__ char* output_row(const SpmdmParams& p, int64_t bag, int esize) {
+  if (p.num_peers > 0) {
+    const int64_t d = bag / p.bags_per_peer;
+    return static_cast<char*>(p.peer_out[d]) + (bag - d * p.bags_per_peer) * p.output_stride * esize;
+  }
+  return static_cast<char*>(p.out) + bag * p.output_stride * esize;
+}
 
 // One lookup kernel launch (spmdm_kernels.cu).  Returns cudaSuccess or the
 // launch error; never synchronises.
@@ -90,7 +105,10 @@ int enqueue_lookup(
     const int32_t* cit,
     int32_t* status,
     DeviceBuffer& scan,
-    cudaStream_t stream);
+    cudaStream_t stream,
+    void* const* peer_out = nullptr,
+    int num_peers = 0,
+    int64_t bags_per_peer = 0);
 
 // Process-wide count of kernels launched by this library.
 extern std::atomic<uint64_t> g_launch_count;

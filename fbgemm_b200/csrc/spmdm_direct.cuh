@@ -278,7 +278,7 @@ __device__ __forceinline__ void store_columns(const SpmdmParams& p, int64_t bag,
   }
   const bool full = col0 + CPC <= p.block_size;
   if (p.flags & kOutHalf) {
-    __half* o = reinterpret_cast<__half*>(p.out) + bag * p.output_stride + col0;
+    __half* o = reinterpret_cast<__half*>(output_row(p, bag, 2)) + col0;
     if (full && (p.flags & kOutVec)) {
       uint32_t h[CPC / 2];
 #pragma unroll
@@ -303,7 +303,7 @@ __device__ __forceinline__ void store_columns(const SpmdmParams& p, int64_t bag,
       }
     }
   } else {
-    float* o = reinterpret_cast<float*>(p.out) + bag * p.output_stride + col0;
+    float* o = reinterpret_cast<float*>(output_row(p, bag, 4)) + col0;
     if (full && (p.flags & kOutVec)) {
 #pragma unroll
       for (int i = 0; i < CPC / 4; ++i) {

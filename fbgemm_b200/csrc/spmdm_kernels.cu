@@ -178,7 +178,7 @@ __device__ __forceinline__ void store_chunk(
     const float* v) {
   const bool full = col0 + COLS <= p.block_size;
   if (p.flags & kOutHalf) {
-    __half* o = reinterpret_cast<__half*>(p.out) + bag * p.output_stride + col0;
+    __half* o = reinterpret_cast<__half*>(output_row(p, bag, 2)) + col0;
     if (full && (p.flags & kOutVec)) {
       uint32_t w[COLS / 2];
 #pragma unroll
@@ -203,7 +203,7 @@ __device__ __forceinline__ void store_chunk(
       }
     }
   } else {
-    float* o = reinterpret_cast<float*>(p.out) + bag * p.output_stride + col0;
+    float* o = reinterpret_cast<float*>(output_row(p, bag, 4)) + col0;
     if (full && (p.flags & kOutVec)) {
 #pragma unroll
       for (int i = 0; i < COLS / 4; ++i) {

@@ -1,0 +1,221 @@
+"""Table-wise sharding of a multi-table quantized embedding-bag lookup over the
+GPUs of one box, with the pooled rows redistributed batch-wise.
+
+Every table lives wholly on one GPU.  Each GPU pools the WHOLE (global) batch
+for the tables it owns; the pooled rows then have to reach the GPU that owns
+their slice of the batch: rank g ends up with rows [g*B/G, (g+1)*B/G) of every
+table, columns ordered by owner rank and, within a rank, by table - the layout
+the reference's multi-table caller produces on one host
+(``output + D_start`` with ``output_stride = total_D``,
+fbgemm_gpu/codegen/inference/embedding_forward_quantized_cpu_template.cpp:343-473
+of FBGEMM), cut batch-wise.
+
+Two ways to get them there:
+
+* ``mode="p2p"`` (the product): the lookup kernel itself stores each pooled
+  row into the destination GPU's output buffer over NVLink
+  (``fbgemm_b200_spmdm_launch_sharded``): lookup and all-to-all are one kernel,
+  no staging buffer, no collective call.  The output buffers are symmetric
+  memory (``torch.distributed._symmetric_memory``), which hands every rank the
+  peers' buffer addresses.  Plain peer stores only - no multicast.
+* ``mode="nccl"`` (the baseline): pool into a local ``[B, sum D_local]``
+  buffer, then ``all_to_all_single`` over NCCL and a local copy into the
+  column blocks.
+
+``TableWisePlan`` and ``assemble_columns`` are plain host logic and are tested
+on CPU ranks (gloo).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import dataclasses
+
+import numpy as np
+import torch
+
+from . import _capi
+from .workloads import TableSpec, fused_row_bytes
+
+
+@dataclasses.dataclass
+class TableWisePlan:
+    """Which rank owns which table, and where each table's columns sit in the
+    batch-wise output ``[B/G, total_dim]``."""
+    owner: list[int]            # owner[t]
+    dims: list[int]             # dims[t]
+    world_size: int
+
+    @staticmethod
+    def balanced(costs: list[float], dims: list[int], world_size: int) -> "TableWisePlan":
+        """Greedy longest-processing-time assignment on expected gathered bytes
+        (tables differ in row width and pooling factor, so balancing the table
+        COUNT would not balance the work)."""
+        load = [0.0] * world_size
+        owner = [0] * len(costs)
+        for t in sorted(range(len(costs)), key=lambda i: (-costs[i], i)):
+            r = min(range(world_size), key=lambda i: (load[i], i))
+            owner[t] = r
+            load[r] += costs[t]
+        return TableWisePlan(owner, list(dims), world_size)
+
+    def tables_of(self, rank: int) -> list[int]:
+        return [t for t, o in enumerate(self.owner) if o == rank]
+
+    def local_dim(self, rank: int) -> int:
+        return sum(self.dims[t] for t in self.tables_of(rank))
+
+    @property
+    def total_dim(self) -> int:
+        return sum(self.dims)
+
+    def rank_column_start(self, rank: int) -> int:
+        return sum(self.local_dim(r) for r in range(rank))
+
+    def column_start(self, table: int) -> int:
+        """First column of `table` in the batch-wise output."""
+        r = self.owner[table]
+        start = self.rank_column_start(r)
+        for t in self.tables_of(r):
+            if t == table:
+                return start
+            start += self.dims[t]
+        raise ValueError(table)
+
+
+def expected_cost(spec: TableSpec, bags: int, mean_len: float) -> float:
+    return bags * mean_len * fused_row_bytes(spec.bit_rate, spec.dim)
+
+
+def exchange_pooled(local_out: torch.Tensor, plan: TableWisePlan, rank: int, group=None) -> torch.Tensor:
+    """The baseline redistribution.  ``local_out`` is ``[B, local_dim(rank)]``
+    (all bags, this rank's columns); returns ``[B/G, total_dim]`` (this rank's
+    bags, every rank's columns).  Works on any backend (NCCL on GPUs, gloo on
+    CPU ranks)."""
+    import torch.distributed as dist
+
+    G = plan.world_size
+    B = local_out.shape[0]
+    assert B % G == 0, "the global batch must divide evenly over the ranks"
+    rows = B // G
+    in_splits = [rows * plan.local_dim(rank)] * G
+    out_splits = [rows * plan.local_dim(r) for r in range(G)]
+    recv = torch.empty(sum(out_splits), dtype=local_out.dtype, device=local_out.device)
+    dist.all_to_all_single(recv, local_out.reshape(-1), out_splits, in_splits, group=group)
+    return assemble_columns(recv, plan, rows)
+
+
+def assemble_columns(recv: torch.Tensor, plan: TableWisePlan, rows: int) -> torch.Tensor:
+    """``recv`` holds, rank after rank, the ``[rows, local_dim(r)]`` block that
+    rank r pooled for our bags; lay the blocks side by side."""
+    out = torch.empty((rows, plan.total_dim), dtype=recv.dtype, device=recv.device)
+    at = 0
+    for r in range(plan.world_size):
+        d = plan.local_dim(r)
+        if d:
+            c0 = plan.rank_column_start(r)
+            out[:, c0:c0 + d] = recv[at:at + rows * d].view(rows, d)
+        at += rows * d
+    return out
+
+
+class ShardedLookup:
+    """The tables one rank owns plus the machinery to pool a global batch for
+    them and deliver the rows batch-wise.  One instance per process (one
+    process per GPU)."""
+
+    def __init__(self, specs: list[TableSpec], plan: TableWisePlan, rank: int, global_batch: int,
+                 device: torch.device, out_dtype=torch.float16, mode: str = "p2p", num_buffers: int = 1,
+                 tables: dict[int, torch.Tensor] | None = None, group=None):
+        import torch.distributed as dist
+
+        from . import embedding as E
+        from .workloads import random_table
+
+        assert mode in ("p2p", "nccl")
+        self.specs, self.plan, self.rank, self.device, self.mode = specs, plan, rank, device, mode
+        self.world = plan.world_size
+        assert global_batch % self.world == 0
+        self.B, self.rows = global_batch, global_batch // self.world
+        self.out_dtype = out_dtype
+        self.local = plan.tables_of(rank)
+        self.group = group if group is not None else (dist.group.WORLD if self.world > 1 else None)
+        self.tables = {t: (tables[t] if tables and t in tables else
+                           random_table(specs[t].rows, specs[t].dim, specs[t].bit_rate, device, specs[t].seed))
+                       for t in self.local}
+        np_out = np.float16 if out_dtype == torch.float16 else np.float32
+        self.kernels = {}
+        for t in self.local:
+            s = specs[t]
+            stride = plan.total_dim if mode == "p2p" else max(plan.local_dim(rank), 1)
+            kw = dict(index_dtype=np.int32, offset_dtype=np.int32, out_dtype=np_out, output_stride=stride)
+            self.kernels[t] = (E.GenerateEmbeddingSpMDMWithStrides(s.dim, False, False, **kw) if s.bit_rate == 8 else
+                               E.GenerateEmbeddingSpMDMNBitWithStrides(s.bit_rate, s.dim, False, False, **kw))
+        self.ctx = E.get_context(device.index)
+        esize = 2 if out_dtype == torch.float16 else 4
+        self.num_buffers = num_buffers
+        if mode == "p2p":
+            # Output buffers in symmetric memory: every rank learns the peers' addresses.
+            if self.world > 1:
+                import torch.distributed._symmetric_memory as symm
+
+                self._symm = symm.empty((num_buffers, self.rows, plan.total_dim), dtype=out_dtype, device=device)
+                self._hdl = symm.rendezvous(self._symm, self.group)
+                base = [int(p) for p in self._hdl.buffer_ptrs]
+                self.out = self._symm
+            else:
+                self.out = torch.zeros((num_buffers, self.rows, plan.total_dim), dtype=out_dtype, device=device)
+                base = [self.out.data_ptr()]
+            buf_bytes = self.rows * plan.total_dim * esize
+            # peer pointer arrays per (buffer, table): column offset folded in
+            self._peer_ptrs = {}
+            for b in range(num_buffers):
+                for t in self.local:
+                    col = plan.column_start(t) * esize
+                    arr = (C.c_void_p * self.world)(*[base[r] + b * buf_bytes + col for r in range(self.world)])
+                    self._peer_ptrs[(b, t)] = arr
+        else:
+            self.local_out = torch.zeros((num_buffers, self.B, max(plan.local_dim(rank), 1)), dtype=out_dtype,
+                                         device=device)
+            self.out = torch.zeros((num_buffers, self.rows, plan.total_dim), dtype=out_dtype, device=device)
+
+    def launch(self, batches: dict, buffer: int = 0, slot_base: int = 0, stream=None) -> None:
+        """Enqueue the lookups of every local table for one global batch
+        (``batches[t]`` = workloads.Batch with B bags).  In p2p mode the rows are
+        on their way to their final place when the kernels end; in nccl mode
+        call ``exchange`` afterwards."""
+        lib = _capi.lib()
+        if stream is None:
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+        col = 0
+        for i, t in enumerate(self.local):
+            b, s, k = batches[t], self.specs[t], self.kernels[t]
+            slot = (slot_base + i) % 512
+            if self.mode == "p2p":
+                rc = lib.fbgemm_b200_spmdm_launch_sharded(
+                    self.ctx.handle, C.byref(k.cfg), b.output_size, b.index_size, s.rows,
+                    self.tables[t].data_ptr(), b.indices.data_ptr(), b.offsets.data_ptr(), None,
+                    self._peer_ptrs[(buffer, t)], self.world, self.rows, slot, stream)
+                _capi.check(rc, "fbgemm_b200_spmdm_launch_sharded")
+            else:
+                out = self.local_out[buffer].view(-1)[col:]
+                k.launch(b.output_size, b.index_size, s.rows, self.tables[t], b.indices, b.offsets, None, out,
+                         slot=slot, stream=stream)
+                col += s.dim
+
+    def exchange(self, buffer: int = 0) -> torch.Tensor:
+        """nccl mode: the all-to-all and the column assembly (on the current stream)."""
+        assert self.mode == "nccl"
+        if self.world == 1:
+            self.out[buffer].copy_(self.local_out[buffer][:, :self.plan.total_dim])
+        else:
+            self.out[buffer].copy_(exchange_pooled(self.local_out[buffer], self.plan, self.rank, self.group))
+        return self.out[buffer]
+
+    def barrier(self) -> None:
+        """All ranks' kernels (and therefore their peer stores) are complete."""
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.barrier(group=self.group)
+            torch.cuda.synchronize(self.device)

@@ -134,6 +134,40 @@ FBGEMM_B200_API int fbgemm_b200_spmdm_launch(
     int slot,
     void* stream);
 
+/*
+ * Table-wise sharding over the GPUs of one box: the lookup of a table owned by
+ * this GPU for the whole (global) batch, with the pooled rows written straight
+ * to where the batch-wise layout wants them - bag b goes to row
+ * b % bags_per_peer of peer_out[b / bags_per_peer], which may be a buffer in a
+ * peer GPU's memory (mapped through CUDA IPC / symmetric memory, stores cross
+ * NVLink).  This is the lookup and the all-to-all of the pooled outputs in one
+ * kernel; there is no staging buffer and no separate collective.  The
+ * reference has neither step (its callers loop over tables on one host,
+ * fbgemm_gpu/codegen/inference/embedding_forward_quantized_cpu_template.cpp:343-473);
+ * the layout written is that caller's `output + D_start` with
+ * output_stride = total_D, cut batch-wise.
+ * Each peer_out[i] already includes the column offset of this table;
+ * cfg->output_stride is the row pitch of the destination buffers.  Offsets
+ * flavour only, dense tables only.  The caller orders the peers' reads after
+ * this kernel (stream/event or barrier).  Returns 0 or a negative code.
+ */
+#define FBGEMM_B200_MAX_PEERS 8
+FBGEMM_B200_API int fbgemm_b200_spmdm_launch_sharded(
+    fbgemm_b200_ctx* ctx,
+    const fbgemm_b200_spmdm_config* cfg,
+    int64_t output_size,
+    int64_t index_size,
+    int64_t data_size,
+    const void* input,
+    const void* indices,
+    const void* offsets,
+    const float* weights,
+    void* const* peer_out,
+    int num_peers,
+    int64_t bags_per_peer,
+    int slot,
+    void* stream);
+
 /* Waits for `stream`, reads status slot `slot` into info[4] = {code, bag,
  * position in indices, offending value (low 32 bits)} and clears the slot.
  * Returns 1 if the code is 0 (functor result true), 0 otherwise, negative on

@@ -1,0 +1,99 @@
+"""Host-side logic of the table-wise sharding, on CPU: the placement plan and
+the batch-wise redistribution of pooled rows, the latter run as two gloo ranks
+(the same code runs over NCCL on GPUs)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from fbgemm_b200.sharding import TableWisePlan, assemble_columns, exchange_pooled, expected_cost
+from fbgemm_b200.workloads import TableSpec, config3_tables, config4_tables, fused_row_bytes
+
+
+def test_plan_balances_cost_not_count():
+    specs = config3_tables()
+    assert len(specs) == 64
+    assert {s.bit_rate for s in specs} <= {8, 4, 2} and {s.dim for s in specs} <= {64, 128, 256}
+    assert all(1_000_000 <= s.rows <= 20_000_000 for s in specs)
+    costs = [expected_cost(s, 16384, 30.0) for s in specs]
+    for world in (1, 2, 4, 8):
+        plan = TableWisePlan.balanced(costs, [s.dim for s in specs], world)
+        loads = [sum(costs[t] for t in plan.tables_of(r)) for r in range(world)]
+        assert sum(len(plan.tables_of(r)) for r in range(world)) == 64
+        assert max(loads) <= 1.10 * (sum(costs) / world)          # within 10 % of perfect
+        assert plan.total_dim == sum(s.dim for s in specs)
+        # the columns of all tables tile [0, total_dim) without gaps, grouped by owner rank
+        spans = sorted((plan.column_start(t), plan.column_start(t) + specs[t].dim, plan.owner[t]) for t in range(64))
+        assert spans[0][0] == 0 and spans[-1][1] == plan.total_dim
+        assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+        assert [o for _, _, o in spans] == sorted(o for _, _, o in spans)
+    # deterministic
+    assert TableWisePlan.balanced(costs, [s.dim for s in specs], 8).owner == \
+        TableWisePlan.balanced(costs, [s.dim for s in specs], 8).owner
+
+
+def test_uniform_tables_split_evenly():
+    specs = config4_tables()
+    assert len(specs) == 256 and fused_row_bytes(4, 128) == 68
+    plan = TableWisePlan.balanced([1.0] * 256, [128] * 256, 8)
+    assert [len(plan.tables_of(r)) for r in range(8)] == [32] * 8
+    assert specs[0].rows * 68 * 32 < 180e9   # 32 tables of 2.72 GB fit one B200
+
+
+def test_assemble_columns_single_rank():
+    plan = TableWisePlan([0, 0], [3, 2], 1)
+    recv = torch.arange(4 * 5, dtype=torch.float32)
+    out = assemble_columns(recv, plan, 4)
+    assert torch.equal(out, recv.view(4, 5))
+
+
+def pooled_value(table, bag, col):
+    return table * 1000.0 + bag + col / 64.0
+
+
+def _rank_main(rank, world, port, dims, owner, B, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        plan = TableWisePlan(owner, dims, world)
+        # what this rank's lookups would have produced: all bags, its own tables' columns
+        cols = []
+        for t in plan.tables_of(rank):
+            bag = torch.arange(B, dtype=torch.float32).view(B, 1)
+            col = torch.arange(dims[t], dtype=torch.float32).view(1, -1)
+            cols.append(pooled_value(t, bag, col))
+        local_out = torch.cat(cols, dim=1) if cols else torch.zeros((B, 0))
+        out = exchange_pooled(local_out.contiguous(), plan, rank)
+        rows = B // world
+        want = torch.empty((rows, plan.total_dim))
+        for t in range(len(dims)):
+            c0 = plan.column_start(t)
+            bag = torch.arange(rank * rows, (rank + 1) * rows, dtype=torch.float32).view(rows, 1)
+            col = torch.arange(dims[t], dtype=torch.float32).view(1, -1)
+            want[:, c0:c0 + dims[t]] = pooled_value(t, bag, col)
+        q.put((rank, bool(torch.equal(out, want)), tuple(out.shape)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_batchwise_redistribution_two_gloo_ranks():
+    dims = [4, 8, 2, 6, 4]
+    owner = [1, 0, 1, 0, 1]     # uneven: rank 0 owns 14 columns, rank 1 owns 10
+    world, B = 2, 12
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, dims, owner, B, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert sorted(results) == [(0, True, (6, 24)), (1, True, (6, 24))]
