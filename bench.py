@@ -49,7 +49,7 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=500)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", type=int, default=1, help="index into BASELINE.json configs (0, 1 or 2)")
-    ap.add_argument("--streams", type=int, default=4, help="streams the graph spreads the launches over")
+    ap.add_argument("--streams", type=int, default=16, help="streams the graph spreads the launches over")
     ap.add_argument("--group", type=int, default=1, help="batches concatenated into one call (1 = the config's batch)")
     ap.add_argument("--scale", type=float, default=1.0, help="shrink rows and batch (tests only)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
@@ -281,12 +281,33 @@ def main():
         return 0
 
     kern = w.make_kernel()
-    outs = [torch.zeros(b.output_size * w.dim, dtype=w.out_dtype, device=dev) for b in batches]
+    sharded = None
+    if world > 1:
+        # Table-wise sharding: this rank's table pools the whole batch and the
+        # kernel stores every pooled row straight into the output buffer of the
+        # rank that owns that slice of the batch (peer stores over NVLink):
+        # lookup and all-to-all in one kernel.
+        from fbgemm_b200.sharding import ShardedLookup, TableWisePlan
+
+        assert w.cit is None, "the sharded path covers dense tables"
+        tnp = {torch.int32: np.int32, torch.int64: np.int64}
+        specs = [W.TableSpec(w.rows, w.dim, w.bit_rate, W.SEED + 1000 * r) for r in range(world)]
+        plan = TableWisePlan(list(range(world)), [w.dim] * world, world)
+        sharded = ShardedLookup(specs, plan, rank, bags_per_step, dev, w.out_dtype, mode="p2p",
+                                num_buffers=NUM_BATCHES, tables={rank: w.table}, weighted=w.has_weight,
+                                index_dtype=tnp[w.index_dtype], offset_dtype=tnp[w.offset_dtype])
+        config["redistribution"] = ("pooled rows stored by the lookup kernel into the owning rank's "
+                                    f"[{bags_per_step // world}, {plan.total_dim}] buffer (peer stores, symmetric memory)")
+    else:
+        outs = [torch.zeros(b.output_size * w.dim, dtype=w.out_dtype, device=dev) for b in batches]
 
     def launch(i, stream=None):
         b = batches[i % NUM_BATCHES]
-        kern.launch(b.output_size, b.index_size, w.rows, w.table, b.indices, b.offsets, b.weights,
-                    outs[i % NUM_BATCHES], w.cit, slot=i % 256, stream=stream)
+        if sharded is not None:
+            sharded.launch({rank: b}, buffer=i % NUM_BATCHES, slot_base=i % 256, stream=stream)
+        else:
+            kern.launch(b.output_size, b.index_size, w.rows, w.table, b.indices, b.offsets, b.weights,
+                        outs[i % NUM_BATCHES], w.cit, slot=i % 256, stream=stream)
 
     def barrier():
         if world > 1:
@@ -352,7 +373,7 @@ def main():
 
     # ---- e2e: host buffers through the C ABI -------------------------------------
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and world == 1:
         lanes = 8
         hb = []
         for b in batches:

@@ -704,23 +704,46 @@ int fbgemm_b200_spmdm_host_submit(
   const size_t out_pitch = (size_t)d.output_stride * esize;
   const size_t out_bytes = (size_t)output_size * out_pitch;
 
-  if ((e = reserve(L.h_in, in_bytes)) != cudaSuccess || (e = reserve(L.d_in, in_bytes)) != cudaSuccess ||
-      (e = reserve(L.d_out, out_bytes)) != cudaSuccess) {
+  if ((e = reserve(L.d_in, in_bytes)) != cudaSuccess || (e = reserve(L.d_out, out_bytes)) != cudaSuccess) {
     return fail_cuda(e, "lane staging buffers");
   }
-  uint8_t* h = static_cast<uint8_t*>(L.h_in.ptr);
-  if (idx_bytes) {
-    std::memcpy(h, indices, idx_bytes);
+  uint8_t* di = static_cast<uint8_t*>(L.d_in.ptr);
+  // Page-locked caller buffers go to the device as they are; pageable ones are
+  // first packed into the lane's pinned block so that the copy stays asynchronous.
+  auto pinned = [](const void* ptr) {
+    cudaPointerAttributes a{};
+    const bool yes = ptr && cudaPointerGetAttributes(&a, ptr) == cudaSuccess && a.type == cudaMemoryTypeHost;
+    cudaGetLastError();
+    return yes;
+  };
+  if ((!idx_bytes || pinned(indices)) && pinned(offsets_or_lengths) && (!n_w || pinned(weights))) {
+    e = cudaSuccess;
+    if (idx_bytes) {
+      e = cudaMemcpyAsync(di, indices, idx_bytes, cudaMemcpyHostToDevice, L.stream);
+    }
+    if (e == cudaSuccess) {
+      e = cudaMemcpyAsync(di + off_at, offsets_or_lengths, off_bytes, cudaMemcpyHostToDevice, L.stream);
+    }
+    if (e == cudaSuccess && n_w) {
+      e = cudaMemcpyAsync(di + w_at, weights, n_w * sizeof(float), cudaMemcpyHostToDevice, L.stream);
+    }
+  } else {
+    if ((e = reserve(L.h_in, in_bytes)) != cudaSuccess) {
+      return fail_cuda(e, "lane staging buffers");
+    }
+    uint8_t* h = static_cast<uint8_t*>(L.h_in.ptr);
+    if (idx_bytes) {
+      std::memcpy(h, indices, idx_bytes);
+    }
+    std::memcpy(h + off_at, offsets_or_lengths, off_bytes);
+    if (n_w) {
+      std::memcpy(h + w_at, weights, n_w * sizeof(float));
+    }
+    e = cudaMemcpyAsync(di, h, in_bytes, cudaMemcpyHostToDevice, L.stream);
   }
-  std::memcpy(h + off_at, offsets_or_lengths, off_bytes);
-  if (n_w) {
-    std::memcpy(h + w_at, weights, n_w * sizeof(float));
-  }
-  e = cudaMemcpyAsync(L.d_in.ptr, h, in_bytes, cudaMemcpyHostToDevice, L.stream);
   if (e != cudaSuccess) {
     return fail_cuda(e, "input upload");
   }
-  uint8_t* di = static_cast<uint8_t*>(L.d_in.ptr);
 
   // Status of this lane: the last FBGEMM_B200_HOST_LANES slots of the context.
   const int slot = FBGEMM_B200_STATUS_SLOTS - FBGEMM_B200_HOST_LANES + lane_id;

@@ -169,6 +169,13 @@ static __device__ __noinline__ void report(int32_t* st, int code, int64_t bag, i
 
 constexpr uint32_t kSkipRow = 0xFFFFFFFFu;
 
+// base + row * stride as one 32 x 32 -> 64-bit multiply-add.
+__device__ __forceinline__ const uint8_t* row_address(const uint8_t* base, uint32_t row, uint32_t stride) {
+  unsigned long long a;
+  asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(a) : "r"(row), "r"(stride), "l"(base));
+  return reinterpret_cast<const uint8_t*>(a);
+}
+
 // The per-row work that does not depend on the column - index fetch, range
 // check, pruning map, weight fetch - is done once per row by ONE lane of the
 // bag's group: in a step of U rows, lane gl resolves rows gl, gl+LPB, ...
@@ -235,12 +242,12 @@ __device__ __forceinline__ void pool_step(
 #pragma unroll
   for (int u = 0; u < U; ++u) {
     // a skipped row reads row 0 (always there) and is then pooled with zeros
-    const unsigned long long off = (unsigned long long)(rid[u] == kSkipRow ? 0u : rid[u]) * stride;
+    const uint32_t row = rid[u] == kSkipRow ? 0u : rid[u];
 #pragma unroll
     for (int ci = 0; ci < CPL; ++ci) {
-      d[u][ci].load(chunk_base[ci] + off);
+      d[u][ci].load(row_address(chunk_base[ci], row, stride));
     }
-    sb[u].load(sb_base + off);
+    sb[u].load(row_address(sb_base, row, stride));
   }
   const u64 nm2 = pack2(-8388608.0f, -8388608.0f);
 #pragma unroll

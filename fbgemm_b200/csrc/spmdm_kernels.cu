@@ -23,6 +23,7 @@
 #include <cuda_fp16.h>
 
 #include <cstdlib>
+#include <cstring>
 
 #include "internal.h"
 #include "spmdm_direct.cuh"
@@ -447,9 +448,12 @@ static cudaError_t launch_direct(SpmdmParams p, int bit_rate, cudaStream_t strea
       cpl_max = v[i].cpl;
     }
   }
-  // Aim at about 16 columns per lane: narrow lane groups amortise the per-row
-  // work that does not scale with D; more than 32 columns do not fit registers.
-  int cpl_target = 16 / cpc < 1 ? 1 : 16 / cpc;
+  // Columns per lane: narrow lane groups amortise the per-row work that does
+  // not scale with D, wide ones keep registers (and so resident warps) in
+  // check.  Measured best on B200: 32 columns for 8-bit rows, 16 for 4- and
+  // 2-bit rows (whose unpacking needs more registers per column).
+  const int cols_target = bit_rate == 8 ? 32 : 16;
+  int cpl_target = cols_target / cpc < 1 ? 1 : cols_target / cpc;
   cpl_target = cpl_target > cpl_max ? cpl_max : cpl_target;
   int lpb = 2;
   while (lpb < 32 && lpb * cpl_target < nchunks) {
@@ -486,7 +490,7 @@ static cudaError_t launch_direct(SpmdmParams p, int bit_rate, cudaStream_t strea
 
 cudaError_t launch_spmdm(const SpmdmParams& p_in, int bit_rate, cudaStream_t stream) {
   const char* force = std::getenv("FBGEMM_B200_KERNEL");
-  if (!(force && force[0] == 's')) {  // "staged" forces the generic kernel
+  if (!(force && std::strcmp(force, "staged") == 0)) {  // forces the generic kernel (tuning aid)
     const cudaError_t e = launch_direct(p_in, bit_rate, stream);
     if (e != cudaErrorNotSupported) {
       return e;

@@ -125,7 +125,8 @@ class ShardedLookup:
 
     def __init__(self, specs: list[TableSpec], plan: TableWisePlan, rank: int, global_batch: int,
                  device: torch.device, out_dtype=torch.float16, mode: str = "p2p", num_buffers: int = 1,
-                 tables: dict[int, torch.Tensor] | None = None, group=None):
+                 tables: dict[int, torch.Tensor] | None = None, group=None, weighted: bool = False,
+                 index_dtype=np.int32, offset_dtype=np.int32):
         import torch.distributed as dist
 
         from . import embedding as E
@@ -147,9 +148,9 @@ class ShardedLookup:
         for t in self.local:
             s = specs[t]
             stride = plan.total_dim if mode == "p2p" else max(plan.local_dim(rank), 1)
-            kw = dict(index_dtype=np.int32, offset_dtype=np.int32, out_dtype=np_out, output_stride=stride)
-            self.kernels[t] = (E.GenerateEmbeddingSpMDMWithStrides(s.dim, False, False, **kw) if s.bit_rate == 8 else
-                               E.GenerateEmbeddingSpMDMNBitWithStrides(s.bit_rate, s.dim, False, False, **kw))
+            kw = dict(index_dtype=index_dtype, offset_dtype=offset_dtype, out_dtype=np_out, output_stride=stride)
+            self.kernels[t] = (E.GenerateEmbeddingSpMDMWithStrides(s.dim, weighted, False, **kw) if s.bit_rate == 8
+                               else E.GenerateEmbeddingSpMDMNBitWithStrides(s.bit_rate, s.dim, weighted, False, **kw))
         self.ctx = E.get_context(device.index)
         esize = 2 if out_dtype == torch.float16 else 4
         self.num_buffers = num_buffers
@@ -193,13 +194,14 @@ class ShardedLookup:
             if self.mode == "p2p":
                 rc = lib.fbgemm_b200_spmdm_launch_sharded(
                     self.ctx.handle, C.byref(k.cfg), b.output_size, b.index_size, s.rows,
-                    self.tables[t].data_ptr(), b.indices.data_ptr(), b.offsets.data_ptr(), None,
+                    self.tables[t].data_ptr(), b.indices.data_ptr(), b.offsets.data_ptr(),
+                    b.weights.data_ptr() if (k.cfg.has_weight and b.weights is not None) else None,
                     self._peer_ptrs[(buffer, t)], self.world, self.rows, slot, stream)
                 _capi.check(rc, "fbgemm_b200_spmdm_launch_sharded")
             else:
                 out = self.local_out[buffer].view(-1)[col:]
-                k.launch(b.output_size, b.index_size, s.rows, self.tables[t], b.indices, b.offsets, None, out,
-                         slot=slot, stream=stream)
+                k.launch(b.output_size, b.index_size, s.rows, self.tables[t], b.indices, b.offsets,
+                         b.weights if k.cfg.has_weight else None, out, slot=slot, stream=stream)
                 col += s.dim
 
     def exchange(self, buffer: int = 0) -> torch.Tensor:
