@@ -39,7 +39,14 @@ if ROOT not in sys.path:
 FALLBACK_HBM_GBS = 6650.0
 GRAPH_CHUNK = 500       # steps per captured graph
 NUM_BATCHES = 32        # distinct pre-generated batches the steps rotate over
-ESZ = {"torch.int32": 4, "torch.int64": 8, "torch.float32": 4, "torch.float16": 2}
+# DRAM bytes (read + write) per lookup launch, from ncu captures of the same
+# launch shape: key = (workload, batches per call).
+TRAFFIC_BYTES_PER_LAUNCH = {
+    (1, 1): 13_755_648,             # profiles/spmdm_direct_kernel__workload1_one_batch.md
+    (1, 16): 170_838_016 + 6_931_200,   # profiles/spmdm_direct_kernel__workload1_16batches.md
+    (0, 16): 440_144_128 + 73_972_736,  # profiles/spmdm_direct_kernel__workload0_16batches.md
+    (2, 16): 271_241_472 + 50_875_648,  # profiles/spmdm_direct_kernel__workload2_16batches.md
+}
 
 
 def parse_args():
@@ -438,6 +445,34 @@ def main():
 
     total_launches = F.launch_count() - launches_before
 
+    # ---- the practical ceiling: the same rows fetched with no arithmetic ----------
+    ceiling = None
+    if rank == 0:
+        import ctypes as C
+
+        from fbgemm_b200 import _capi
+        rows_all = torch.cat([(w.cit[b.indices.long()] if w.cit is not None else b.indices).to(torch.int32)
+                              for b in batches])
+        rows_all = rows_all[rows_all >= 0].contiguous()
+        mean_len = max(1, int(round(sum(b.index_size for b in batches) / sum(b.output_size for b in batches))))
+        sink = torch.zeros(1, dtype=torch.int32, device=dev)
+        stream = torch.cuda.current_stream().cuda_stream
+
+        def probe():
+            _capi.check(_capi.lib().fbgemm_b200_probe_row_gather(
+                w.table.data_ptr(), w.row_bytes, w.row_bytes, rows_all.data_ptr(), rows_all.numel(), mean_len,
+                sink.data_ptr(), stream), "probe")
+        for _ in range(3):
+            probe()
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p0.record()
+        for _ in range(10):
+            probe()
+        p1.record()
+        torch.cuda.synchronize()
+        probe_ms = p0.elapsed_time(p1) / 10
+        ceiling = rows_all.numel() * w.row_bytes / (probe_ms * 1e-3) / 1e9
+
     # ---- cpu_baseline (rank 0, one GPU only) ------------------------------------
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -463,8 +498,14 @@ def main():
             "gpu_launches": timed_launches,
             "gpu_launches_whole_run": int(total_launches),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": peak_src,
-                         "per_launch_us": per_launch_us,
+                         "traffic": TRAFFIC_BYTES_PER_LAUNCH.get((args.workload, args.group)),
+                         "traffic_source": "dram__bytes_read+write of one ncu capture of this launch shape "
+                                           "(profiles/spmdm_direct_kernel__workload*_*.md)",
+                         "peak_source": peak_src, "per_launch_us": per_launch_us,
+                         "random_row_gather_ceiling_GBps": ceiling,
+                         "frac_of_gather_ceiling": (achieved / ceiling) if ceiling else None,
+                         "ceiling_note": "fbgemm_b200_probe_row_gather: the same rows read with the same lane "
+                                         "layout and no arithmetic, one launch over all 32 batches",
                          "note": "achieved = gathered-row bytes per launch / (timed region / launches); launches "
                                  "of different streams overlap"},
             "cpu_baseline": cpu,

@@ -67,6 +67,7 @@ SIGNATURES = {
     "fbgemm_b200_spmdm_host_submit": (C.c_int, [_p, C.c_int, _cfgp, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p]),
     "fbgemm_b200_spmdm_host_wait": (C.c_int, [_p, C.c_int]),
     "fbgemm_b200_spmdm_host": (C.c_int, [_p, _cfgp, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p]),
+    "fbgemm_b200_probe_row_gather": (C.c_int, [_p, _i64, C.c_int32, _p, _i64, C.c_int32, _p, _p]),
     "fbgemm_b200_float_to_fused_8bit_rowwise": (C.c_int, [_p, _i64, C.c_int32, _p, _p]),
     "fbgemm_b200_float_to_fused_nbit_rowwise": (C.c_int, [C.c_int32, _p, _i64, C.c_int32, _p, _p]),
 }

@@ -59,10 +59,18 @@ def zipf(n: int, alpha: float, device, seed: int) -> torch.Tensor:
     return out
 
 
-def zipf_indices(n: int, alpha: float, rows: int, device, seed: int, dtype=torch.int64) -> torch.Tensor:
-    """perm[(Zipf(alpha) - 1) mod rows] with a seeded permutation of the rows."""
+def row_permutation(rows: int, device, seed: int) -> torch.Tensor:
+    """The seeded permutation that scatters the hot Zipf ranks over the table."""
+    return torch.randperm(rows, generator=_gen(device, seed), device=device)
+
+
+def zipf_indices(n: int, alpha: float, rows: int, device, seed: int, dtype=torch.int64,
+                 perm: torch.Tensor | None = None) -> torch.Tensor:
+    """perm[(Zipf(alpha) - 1) mod rows]; `perm` is the table's row permutation
+    (one per table, drawn from `seed` if not given)."""
     z = (zipf(n, alpha, device, seed) - 1) % rows
-    perm = torch.randperm(rows, generator=_gen(device, seed + 1), device=device)
+    if perm is None:
+        perm = row_permutation(rows, device, seed + 1)
     return perm[z].to(dtype)
 
 
@@ -169,13 +177,14 @@ def config1(device, scale: float = 1.0, seed: int = SEED) -> Workload:
     U(0,1), weighted sum, fp16 out."""
     rows, dim, B = _scaled(10_000_000, scale, 64), 64, _scaled(4_096, scale, 8)
     table = random_table(rows, dim, 4, device, seed)
+    perm = row_permutation(rows, device, seed + 5)
 
     def make_batch(s):
         g = _gen(device, seed + 1000 + s)
         lengths = torch.randint(0, 65, (B,), generator=g, device=device, dtype=torch.int64)
         off = offsets_from_lengths(lengths, torch.int32)
         n = int(off[-1])
-        idx = zipf_indices(n, 1.05, rows, device, seed + 2000 + s, torch.int32)
+        idx = zipf_indices(n, 1.05, rows, device, seed + 2000 + s, torch.int32, perm)
         w = torch.rand(n, generator=g, device=device, dtype=torch.float32)
         return Batch(idx, off, w, B, n, n)
 
@@ -194,6 +203,7 @@ def config2(device, scale: float = 1.0, seed: int = SEED) -> Workload:
     n_dense = int(keep.sum())
     cit[keep] = torch.arange(n_dense, dtype=torch.int32, device=device)
     table = random_table(max(n_dense, 1), dim, 2, device, seed)
+    perm = row_permutation(rows, device, seed + 5)
 
     def make_batch(s):
         g = _gen(device, seed + 1000 + s)
@@ -201,7 +211,7 @@ def config2(device, scale: float = 1.0, seed: int = SEED) -> Workload:
         lengths = torch.poisson(lam, generator=g).to(torch.int64)
         off = offsets_from_lengths(lengths, torch.int64)
         n = int(off[-1])
-        idx = zipf_indices(n, 1.1, rows, device, seed + 2000 + s, torch.int64)
+        idx = zipf_indices(n, 1.1, rows, device, seed + 2000 + s, torch.int64, perm)
         valid = int((cit[idx] >= 0).sum())
         return Batch(idx, off, None, B, n, valid)
 

@@ -295,6 +295,26 @@ FBGEMM_B200_API int fbgemm_b200_spmdm_host(
     void* out,
     const int32_t* compressed_indices_table);
 
+/* ---- measuring stick ---------------------------------------------------- */
+
+/* Reads n random rows (row_bytes of each, int32 row numbers in `indices`,
+ * rows `stride` bytes apart) with the lookup's lane layout and memory-level
+ * parallelism but no arithmetic: the time it takes is the practical floor for
+ * any gather of such rows on this GPU, which for small unaligned rows is far
+ * from what a streaming copy reaches (DRAM serves 32-byte sectors of 64-byte
+ * atoms).  Benchmarks report the lookup against it.  rows_per_group mimics the
+ * bag length; `sink` is 4 bytes of device memory.  No counterpart in the
+ * reference.  Enqueues one kernel; returns 0 or a negative code. */
+FBGEMM_B200_API int fbgemm_b200_probe_row_gather(
+    const void* table,
+    int64_t stride,
+    int32_t row_bytes,
+    const int32_t* indices,
+    int64_t n,
+    int32_t rows_per_group,
+    void* sink,
+    void* stream);
+
 /* ---- row-wise quantizers, device pointers ------------------------------ */
 
 /* fbgemm::FloatOrHalfToFused8BitRowwiseQuantizedSBFloat<float>
