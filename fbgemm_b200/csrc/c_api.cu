@@ -671,7 +671,7 @@ int fbgemm_b200_spmdm_host_submit(
   const size_t off_bytes = n_off * cfg->offset_bytes;
   size_t n_w = 0;
   if (cfg->has_weight) {
-    if (!weights) {
+    if (!weights && index_size > 0) {
       set_error("has_weight set but weights is null");
       return FBGEMM_B200_EINVAL;
     }

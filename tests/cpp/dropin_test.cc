@@ -1,0 +1,181 @@
+// The C++ generator API used the way a caller of FBGEMM uses it: same template
+// names and functor signatures (FBGEMM_B200_AS_FBGEMM makes them visible as
+// fbgemm::), host vectors in, bool out - and, as in the reference's own tests
+// (test/EmbeddingSpMDM8BitTest.cc:308-334, test/EmbeddingSpMDMNBitTest.cc:396),
+// every element compared for equality with the scalar reference semantics,
+// here the CPU oracle (test infrastructure, linked only into this test).
+#define FBGEMM_B200_AS_FBGEMM
+#include "fbgemm_b200/FbgemmEmbedding.h"
+
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <random>
+#include <stdexcept>
+#include <vector>
+
+extern "C" {
+int oracle_embedding_spmdm_8bit(int64_t, int64_t, int64_t, int64_t, const uint8_t*, const void*, int, const void*, int,
+                                const float*, int, void*, int, int, int, int64_t, int64_t);
+int oracle_embedding_spmdm_nbit(int, int64_t, int64_t, int64_t, int64_t, const uint8_t*, const void*, int, const void*,
+                                int, const float*, int, void*, int, int, int, int64_t, int64_t);
+int oracle_embedding_spmdm_rowwise_sparse(int, int64_t, int64_t, int64_t, int64_t, const uint8_t*, const void*, int,
+                                          const int32_t*, const void*, int, const float*, int, float*, int, int);
+}
+
+static int failures = 0;
+#define CHECK(cond)                                              \
+  do {                                                           \
+    if (!(cond)) {                                               \
+      std::printf("FAILED %s:%d %s\n", __FILE__, __LINE__, #cond); \
+      ++failures;                                                \
+    }                                                            \
+  } while (0)
+
+struct Inputs {
+  std::vector<uint8_t> table;
+  std::vector<int64_t> idx64, off64;
+  std::vector<int32_t> idx32, off32, len32;
+  std::vector<float> weights;
+  int64_t n = 0;
+};
+
+static Inputs make(std::mt19937& g, int bit_rate, int batch, int rows, int dim, int avg_len, int corner) {
+  Inputs in;
+  const int epb = 8 / bit_rate;
+  const int data = (dim + epb - 1) / epb;
+  const int stride = data + (bit_rate == 8 ? 8 : 4);
+  in.table.resize((size_t)rows * stride);
+  for (auto& b : in.table) b = (uint8_t)(g() & 0xff);
+  std::normal_distribution<float> nd;
+  for (int r = 0; r < rows; ++r) {
+    if (bit_rate == 8) {
+      float sb[2] = {nd(g), nd(g)};
+      std::memcpy(&in.table[(size_t)r * stride + data], sb, 8);
+    } else {
+      // fp16 1.0 / 0.5 style values: sign, exponent 13..17, random mantissa
+      for (int k = 0; k < 2; ++k) {
+        uint16_t h = (uint16_t)(((g() & 1) << 15) | ((13 + g() % 5) << 10) | (g() & 0x3ff));
+        std::memcpy(&in.table[(size_t)r * stride + data + 2 * k], &h, 2);
+      }
+    }
+  }
+  in.off64.push_back(0);
+  for (int b = 0; b < batch; ++b) {
+    int len = corner == 1 ? 0 : 1 + (int)(g() % (2 * avg_len));
+    in.off64.push_back(in.off64.back() + len);
+  }
+  in.n = in.off64.back();
+  for (int64_t i = 0; i < in.n; ++i) in.idx64.push_back(g() % rows);
+  if (corner == 2 && in.n > 0) in.idx64[g() % in.n] = rows;  // out of bound
+  for (auto v : in.idx64) in.idx32.push_back((int32_t)v);
+  for (auto v : in.off64) in.off32.push_back((int32_t)v);
+  for (size_t b = 0; b + 1 < in.off64.size(); ++b) in.len32.push_back((int32_t)(in.off64[b + 1] - in.off64[b]));
+  for (int64_t i = 0; i < in.n; ++i) in.weights.push_back(nd(g));
+  return in;
+}
+
+int main() {
+  std::mt19937 g(2024);
+  // --- 8-bit, int64/int64, fp32 out: GenerateEmbeddingSpMDM as in BASELINE config 0 (host pointers)
+  for (int corner = 0; corner < 3; ++corner) {
+    for (int dim : {128, 64, 40, 7}) {
+      const int batch = 33, rows = 900;
+      Inputs in = make(g, 8, batch, rows, dim, 12, corner);
+      for (bool weighted : {false, true}) {
+        auto kernel = fbgemm::GenerateEmbeddingSpMDM<uint8_t, int64_t, int64_t, float>(dim, weighted, /*normalize=*/weighted);
+        std::vector<float> out((size_t)batch * dim, 1.f), ref((size_t)batch * dim, 2.f);
+        const bool ok = kernel(batch, in.n, rows, in.table.data(), in.n ? in.idx64.data() : nullptr, in.off64.data(),
+                               weighted ? in.weights.data() : nullptr, out.data());
+        const int ok_ref = oracle_embedding_spmdm_8bit(dim, batch, in.n, rows, in.table.data(), in.idx64.data(), 8,
+                                                       in.off64.data(), 8, weighted ? in.weights.data() : nullptr,
+                                                       weighted, ref.data(), 0, 0, 1, -1, -1);
+        CHECK(ok == (ok_ref != 0));
+        CHECK(ok == (corner != 2));
+        if (ok) CHECK(std::memcmp(out.data(), ref.data(), out.size() * 4) == 0);
+        fbgemm_b200::InvalidateTable(in.table.data());
+      }
+    }
+  }
+  // --- 4-/2-bit, int32/int32, fp16 out, lengths flavour: GenerateEmbeddingSpMDMNBit
+  for (int bit_rate : {4, 2}) {
+    for (int dim : {64, 128, 36}) {
+      const int batch = 21, rows = 500;
+      Inputs in = make(g, bit_rate, batch, rows, dim, 9, 0);
+      auto kernel = fbgemm::GenerateEmbeddingSpMDMNBit<int32_t, int32_t, uint16_t>(
+          bit_rate, dim, true, false, 16, false, /*use_offsets=*/false);
+      std::vector<uint16_t> out((size_t)batch * dim, 7), ref((size_t)batch * dim, 9);
+      const bool ok = kernel(batch, in.n, rows, in.table.data(), in.idx32.data(), in.len32.data(), in.weights.data(),
+                             out.data());
+      const int ok_ref = oracle_embedding_spmdm_nbit(bit_rate, dim, batch, in.n, rows, in.table.data(), in.idx32.data(), 4,
+                                                     in.len32.data(), 4, in.weights.data(), 0, ref.data(), 1, 0, 0, -1, -1);
+      CHECK(ok && ok_ref);
+      CHECK(std::memcmp(out.data(), ref.data(), out.size() * 2) == 0);
+      fbgemm_b200::InvalidateTable(in.table.data());
+    }
+  }
+  // --- strides: a column slice of a wider output, as the multi-table caller does
+  {
+    const int batch = 19, rows = 300, dim = 64, total = 200, col = 72;
+    Inputs in = make(g, 4, batch, rows, dim, 8, 0);
+    auto kernel = fbgemm::GenerateEmbeddingSpMDMNBitWithStrides<int64_t, int32_t, float, true>(
+        4, dim, false, false, 16, false, true, /*output_stride=*/total, /*input_stride=*/-1, true);
+    std::vector<float> out((size_t)batch * total, 5.f), ref((size_t)batch * total, 5.f);
+    CHECK(kernel(batch, in.n, rows, in.table.data(), in.idx64.data(), in.off32.data(), nullptr, out.data() + col));
+    CHECK(oracle_embedding_spmdm_nbit(4, dim, batch, in.n, rows, in.table.data(), in.idx64.data(), 8, in.off32.data(), 4,
+                                      nullptr, 0, ref.data() + col, 0, 0, 1, total, -1));
+    // the functor wrote `batch` rows starting at out+col; the last row ends at col+dim of that row
+    CHECK(std::memcmp(out.data(), ref.data(), ((size_t)(batch - 1) * total + col + dim) * 4) == 0);
+    fbgemm_b200::InvalidateTable(in.table.data());
+  }
+  // --- pruned table: GenerateEmbeddingSpMDMNBitRowWiseSparse with device pointers
+  {
+    const int batch = 40, rows = 2000, dim = 128, bit_rate = 2;
+    std::vector<int32_t> mapping(rows);
+    int dense = 0;
+    for (auto& m : mapping) m = (g() & 1) ? -1 : dense++;
+    Inputs in = make(g, bit_rate, batch, dense, dim, 15, 0);
+    for (auto& v : in.idx64) v = g() % rows;  // indices address the uncompressed space
+    auto kernel = fbgemm::GenerateEmbeddingSpMDMNBitRowWiseSparse<int64_t, int64_t>(bit_rate, dim, true, true);
+    std::vector<float> ref((size_t)batch * dim), out((size_t)batch * dim);
+    CHECK(oracle_embedding_spmdm_rowwise_sparse(bit_rate, dim, batch, in.n, rows, in.table.data(), in.idx64.data(), 8,
+                                                mapping.data(), in.off64.data(), 8, in.weights.data(), 1, ref.data(), 0,
+                                                1));
+    void *d_table, *d_idx, *d_off, *d_w, *d_out, *d_map;
+    cudaMalloc(&d_table, in.table.size() + 16);
+    cudaMalloc(&d_idx, in.n * 8);
+    cudaMalloc(&d_off, in.off64.size() * 8);
+    cudaMalloc(&d_w, in.n * 4);
+    cudaMalloc(&d_out, out.size() * 4);
+    cudaMalloc(&d_map, rows * 4);
+    cudaMemcpy(d_table, in.table.data(), in.table.size(), cudaMemcpyHostToDevice);
+    cudaMemcpy(d_idx, in.idx64.data(), in.n * 8, cudaMemcpyHostToDevice);
+    cudaMemcpy(d_off, in.off64.data(), in.off64.size() * 8, cudaMemcpyHostToDevice);
+    cudaMemcpy(d_w, in.weights.data(), in.n * 4, cudaMemcpyHostToDevice);
+    cudaMemcpy(d_map, mapping.data(), rows * 4, cudaMemcpyHostToDevice);
+    const bool ok = kernel(batch, in.n, rows, (const uint8_t*)d_table, (const int64_t*)d_idx, (const int64_t*)d_off,
+                           (const float*)d_w, (float*)d_out, (const int32_t*)d_map);
+    cudaMemcpy(out.data(), d_out, out.size() * 4, cudaMemcpyDeviceToHost);
+    CHECK(ok);
+    CHECK(std::memcmp(out.data(), ref.data(), out.size() * 4) == 0);
+  }
+  // --- what the sm_100a path does not provide is refused when the kernel is generated
+  bool threw = false;
+  try {
+    fbgemm::GenerateEmbeddingSpMDMNBit<int32_t, int32_t, float>(3, 64, false, false);
+  } catch (const std::invalid_argument&) {
+    threw = true;
+  }
+  CHECK(threw);
+  threw = false;
+  try {
+    fbgemm::GenerateEmbeddingSpMDMWithStrides<uint8_t, int64_t, int64_t, float>(64, false, false, 16, false, true, -1, -1,
+                                                                                /*scale_bias_last=*/false);
+  } catch (const std::invalid_argument&) {
+    threw = true;
+  }
+  CHECK(threw);
+  std::printf(failures ? "DROPIN_FAILED %d\n" : "DROPIN_OK\n", failures);
+  return failures ? 1 : 0;
+}
