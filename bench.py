@@ -55,10 +55,14 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=20000)
     ap.add_argument("--warmup", type=int, default=500)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", type=int, default=1, help="index into BASELINE.json configs (0, 1 or 2)")
+    ap.add_argument("--workload", type=int, default=1, help="index into BASELINE.json configs (0..4)")
     ap.add_argument("--streams", type=int, default=16, help="streams the graph spreads the launches over")
     ap.add_argument("--group", type=int, default=1, help="batches concatenated into one call (1 = the config's batch)")
-    ap.add_argument("--scale", type=float, default=1.0, help="shrink rows and batch (tests only)")
+    ap.add_argument("--scale", type=float, default=1.0, help="shrink table rows (and, for workloads 0-2, the batch)")
+    ap.add_argument("--tables-scale", type=float, default=1.0, help="workloads 3/4: fraction of the tables")
+    ap.add_argument("--batch-scale", type=float, default=1.0, help="workloads 3/4: fraction of the batch")
+    ap.add_argument("--redistribution", default="p2p", choices=["p2p", "nccl"],
+                    help="workloads 3/4: peer stores from the lookup kernel, or NCCL all-to-all after it")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-pointer leg")
     ap.add_argument("--e2e-steps", type=int, default=2000)
@@ -222,10 +226,135 @@ def time_cpu(workload, batches, host_table, host_cit, threads, max_steps, max_se
     return dt, steps, nbytes, kind, desc
 
 
+# ---- multi-table workloads (BASELINE configs 3 and 4) ------------------------------
+
+def main_multi(args):
+    """Table-wise sharded multi-table lookup: every rank pools the global batch
+    for the tables it owns and the kernels store the pooled rows batch-wise
+    into the owning ranks' buffers.  One step = one global batch over all
+    tables."""
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    import fbgemm_b200 as F
+    from fbgemm_b200 import workloads as W
+    from fbgemm_b200.sharding import ShardedLookup, TableWisePlan, expected_cost
+
+    if args.workload == 3:
+        specs = W.config3_tables(max(world, int(round(64 * args.tables_scale))), args.scale)
+        B, alpha, idt, weighted, name = int(16384 * args.batch_scale), 1.05, torch.int32, False, "mixed 8/4/2-bit"
+        mean_len = 30.0
+        plan = TableWisePlan.balanced([expected_cost(s, B, mean_len) for s in specs], [s.dim for s in specs], world)
+    else:
+        per_gpu = max(1, int(round(32 * args.tables_scale)))
+        specs = W.config4_tables(per_gpu * world, args.scale)
+        B, alpha, idt, weighted, name = int(65536 * args.batch_scale), 1.1, torch.int64, True, "4-bit x128"
+        mean_len = 40.0
+        plan = TableWisePlan.balanced([1.0] * len(specs), [s.dim for s in specs], world)
+    B -= B % world
+    tnp = {torch.int32: np.int32, torch.int64: np.int64}
+    sl = ShardedLookup(specs, plan, rank, B, dev, torch.float16, mode=args.redistribution, num_buffers=2,
+                       weighted=weighted, index_dtype=tnp[idt], offset_dtype=tnp[idt])
+    perms = {t: W.row_permutation(specs[t].rows, dev, specs[t].seed + 5) for t in sl.local}
+    nsets = 2
+    sets = []
+    for sidx in range(nsets):
+        d = {}
+        for t in sl.local:
+            g = torch.Generator(device=dev).manual_seed(specs[t].seed + 77 * sidx)
+            if args.workload == 3:
+                lengths = torch.poisson(torch.full((B,), mean_len, device=dev), generator=g).to(torch.int64)
+            else:
+                lengths = torch.full((B,), int(mean_len), device=dev, dtype=torch.int64)
+            off = W.offsets_from_lengths(lengths, idt)
+            n = int(off[-1])
+            idx = W.zipf_indices(n, alpha, specs[t].rows, dev, specs[t].seed + 1000 + sidx, idt, perms[t])
+            wts = torch.rand(n, generator=g, device=dev) if weighted else None
+            d[t] = W.Batch(idx, off, wts, B, n, n)
+        sets.append(d)
+    del perms
+    bytes_local = float(np.mean([sum(b.index_size * specs[t].row_bytes for t, b in d.items()) for d in sets]))
+    streams = [torch.cuda.Stream(device=dev) for _ in range(4)]
+    handles = [s.cuda_stream for s in streams]
+
+    def step(i):
+        cur = torch.cuda.current_stream()
+        for s in streams:
+            s.wait_stream(cur)
+        sl.launch(sets[i % nsets], buffer=i % 2, slot_base=(i % 4) * 100, streams=handles)
+        for s in streams:
+            cur.wait_stream(s)
+        if args.redistribution == "nccl":
+            sl.exchange(i % 2)
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    sl.barrier()
+    ok = all(F.status_read(s, dev.index)[0] for s in range(400))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        e0.record()
+        for i in range(args.steps):
+            step(i)
+        e1.record()
+        sl.barrier()
+    ms = e0.elapsed_time(e1)
+    ok = ok and all(F.status_read(s, dev.index)[0] for s in range(400))
+    tot = torch.tensor([bytes_local, ms, float(ok)], device=dev, dtype=torch.float64)
+    if world > 1:
+        import torch.distributed as dist
+
+        t_ms = tot[1:2].clone()
+        dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
+        t_b = tot[0:1].clone()
+        dist.all_reduce(t_b, op=dist.ReduceOp.SUM)
+        t_ok = tot[2:3].clone()
+        dist.all_reduce(t_ok, op=dist.ReduceOp.MIN)
+        ms, job_bytes, ok = float(t_ms), float(t_b), bool(t_ok)
+    else:
+        job_bytes = bytes_local
+    sec = ms / 1e3
+    peak, peak_src = measured_peak()
+    value = job_bytes * args.steps / sec / 1e9
+    if rank == 0:
+        print(json.dumps({
+            "metric": "gathered_row_GBps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong" if args.workload == 3 else "weak", "vs_baseline": None,
+            "dtype": "u8/u4/u2->f32 accumulate", "data": "synthetic",
+            "config": {"workload": f"{len(specs)} tables {name}, table-wise over {world} GPU(s), batch {B} per table",
+                       "baseline_config_index": args.workload, "tables": len(specs), "total_dim": plan.total_dim,
+                       "rows_scale": args.scale, "tables_scale": args.tables_scale, "batch_scale": args.batch_scale,
+                       "table_GB_this_rank": round(sum(t.numel() for t in sl.tables.values()) / 1e9, 2),
+                       "redistribution": args.redistribution,
+                       "l2": "tables are far larger than L2; two alternating input sets"},
+            "results_ok": ok, "bags_per_s": len(specs) * B * args.steps / sec,
+            "frac_of_hbm_peak": value / world / peak, "clocks": clocks.summary(),
+            "gpu_launches": len(sl.local) * args.steps,
+            "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s",
+                         "frac": value / world / peak, "traffic": None, "peak_source": peak_src},
+            "e2e": None, "cpu_baseline": None}))
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+    return 0
+
+
 # ---- main -----------------------------------------------------------------------
 
 def main():
     args = parse_args()
+    if args.workload in (3, 4) and args.impl != "reference":
+        return main_multi(args)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -397,26 +397,77 @@ spmdm_direct_kernel(const __grid_constant__ SpmdmParams p) {
     }
   }
 
-  // Full steps of UMAX rows; the indices of step s+1 are fetched before the
-  // arithmetic of step s so that their latency hides behind it.
+  // Full steps of UMAX rows.  The lane that resolves a row works two steps
+  // ahead of the arithmetic so that nothing waits on a load that was only just
+  // issued: while step s is pooled, the pruning-map entries of step s+1 and the
+  // indices and weights of step s+2 are in flight.
   const int nfull = len / UMAX;
-  uint32_t id_cur[OWN];
-  float w_cur[OWN];
-  if (nfull > 0) {
-    fetch_rows<LPB, UMAX>(p, gl, bag, start, 0, UMAX, id_cur, w_cur);
+  const bool idx64 = p.flags & kIdx64;
+  const bool pruned = p.flags & kPruned;
+  const bool positional = p.flags & kPositional;
+  // loads only: raw index and weight of this lane's rows of step s
+  auto issue = [&](int s, long long (&raw)[OWN], float (&w)[OWN]) {
+#pragma unroll
+    for (int j = 0; j < OWN; ++j) {
+      const int u = gl + j * LPB;
+      raw[j] = 0;
+      w[j] = 0.f;
+      if (u < UMAX && s < nfull) {
+        const int64_t pos = start + (int64_t)s * UMAX + u;
+        raw[j] = load_int(p.indices, pos, idx64);
+        if (weighted) {
+          w[j] = __ldg(p.weights + (positional ? (int64_t)(s * UMAX + u) : pos));
+        }
+      }
+    }
+  };
+  // range check; for pruned tables start the load of the map entry (its
+  // value, -1 for a pruned row, is the row id or kSkipRow as it stands)
+  auto resolve = [&](int s, const long long (&raw)[OWN], uint32_t (&id)[OWN]) {
+#pragma unroll
+    for (int j = 0; j < OWN; ++j) {
+      const int u = gl + j * LPB;
+      id[j] = kSkipRow;
+      if (u < UMAX && s < nfull) {
+        if ((unsigned long long)raw[j] >= (unsigned long long)p.data_size) {
+          report(p.status, FBGEMM_B200_STATUS_BAD_INDEX, bag, start + (int64_t)s * UMAX + u, raw[j]);
+        } else if (pruned) {
+          id[j] = (uint32_t)__ldg(p.cit + raw[j]);
+        } else {
+          id[j] = (uint32_t)raw[j];
+        }
+      }
+    }
+  };
+  long long raw_1[OWN], raw_2[OWN];
+  uint32_t id_cur[OWN], id_1[OWN];
+  float w_cur[OWN], w_1[OWN], w_2[OWN];
+  issue(0, raw_1, w_cur);
+  issue(1, raw_2, w_1);
+  resolve(0, raw_1, id_cur);
+#pragma unroll
+  for (int j = 0; j < OWN; ++j) {
+    raw_1[j] = raw_2[j];
   }
 #pragma unroll 1
   for (int s = 0; s < nfull; ++s) {
-    uint32_t id_nxt[OWN];
-    float w_nxt[OWN];
-    if (s + 1 < nfull) {
-      fetch_rows<LPB, UMAX>(p, gl, bag, start + (int64_t)(s + 1) * UMAX, (s + 1) * UMAX, UMAX, id_nxt, w_nxt);
+    issue(s + 2, raw_2, w_2);
+    resolve(s + 1, raw_1, id_1);
+    if (pruned) {
+#pragma unroll
+      for (int j = 0; j < OWN; ++j) {
+        if ((int32_t)id_cur[j] < 0) {
+          id_cur[j] = kSkipRow;  // any negative map entry skips the row
+        }
+      }
     }
     pool_step<BITS, VEC, LPB, CPL, UMAX>(chunk_base, sb_base, stride, gmask, lane0, weighted, id_cur, w_cur, acc);
 #pragma unroll
     for (int j = 0; j < OWN; ++j) {
-      id_cur[j] = id_nxt[j];
-      w_cur[j] = w_nxt[j];
+      id_cur[j] = id_1[j];
+      w_cur[j] = w_1[j];
+      w_1[j] = w_2[j];
+      raw_1[j] = raw_2[j];
     }
   }
   // The remaining rows, largest power of two first (each such step is full).

@@ -179,18 +179,21 @@ class ShardedLookup:
                                          device=device)
             self.out = torch.zeros((num_buffers, self.rows, plan.total_dim), dtype=out_dtype, device=device)
 
-    def launch(self, batches: dict, buffer: int = 0, slot_base: int = 0, stream=None) -> None:
+    def launch(self, batches: dict, buffer: int = 0, slot_base: int = 0, stream=None, streams=None) -> None:
         """Enqueue the lookups of every local table for one global batch
         (``batches[t]`` = workloads.Batch with B bags).  In p2p mode the rows are
         on their way to their final place when the kernels end; in nccl mode
-        call ``exchange`` afterwards."""
+        call ``exchange`` afterwards.  ``streams`` (a list of stream handles)
+        spreads the tables round-robin so that their kernels overlap."""
         lib = _capi.lib()
-        if stream is None:
+        if stream is None and not streams:
             stream = torch.cuda.current_stream(self.device).cuda_stream
         col = 0
         for i, t in enumerate(self.local):
             b, s, k = batches[t], self.specs[t], self.kernels[t]
             slot = (slot_base + i) % 512
+            if streams:
+                stream = streams[i % len(streams)]
             if self.mode == "p2p":
                 rc = lib.fbgemm_b200_spmdm_launch_sharded(
                     self.ctx.handle, C.byref(k.cfg), b.output_size, b.index_size, s.rows,
