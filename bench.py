@@ -509,7 +509,7 @@ def main():
 
     # ---- e2e: host buffers through the C ABI -------------------------------------
     e2e = None
-    if not args.no_e2e and world == 1:
+    if not args.no_e2e:
         lanes = 8
         hb = []
         for b in batches:
@@ -566,7 +566,9 @@ def main():
         e2e = {"value": job_bytes_per_step * steps_e2e / dt / 1e9, "unit": "GB/s",
                "h2d_bytes_per_step": round(h2d), "d2h_bytes_per_step": round(d2h), "steps": steps_e2e,
                "ms_per_step": dt / steps_e2e * 1e3, "bags_per_s": job_bags_per_step * steps_e2e / dt,
-               "path": "fbgemm_b200_spmdm_host_submit/wait, 8 pipelined lanes, pinned host buffers, table resident",
+               "path": "fbgemm_b200_spmdm_host_submit/wait, 8 pipelined lanes, pinned host buffers, table resident"
+                       + ("; every rank calls it on its own table and gets its rows back in its own host buffer "
+                          "(the host-pointer interface has no redistribution step)" if world > 1 else ""),
                "timer": "host perf_counter bracketed by device synchronisation"}
         ctx.unregister_table(host_tbl)
         if w.cit is not None:
