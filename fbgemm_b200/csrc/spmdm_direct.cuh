@@ -369,9 +369,11 @@ spmdm_direct_kernel(const __grid_constant__ SpmdmParams p) {
   const int64_t start = o0 - off_base;
   const int bag_len = (int)(o1 - o0);  // the reference narrows to 32 bits too
   int len = bag_len < 0 ? 0 : bag_len;
-  if (start < 0 || start + len > p.index_size) {
+  // Offsets that step backwards: the reference, which walks the index array
+  // with a running position, ends up past index_size and returns false.
+  if (bag_len < 0 || start < 0 || start + len > p.index_size) {
     if (gl == 0) {
-      report(p.status, FBGEMM_B200_STATUS_BAG_OVERRUN, bag, start, len);
+      report(p.status, FBGEMM_B200_STATUS_BAG_OVERRUN, bag, start, bag_len);
     }
     len = 0;  // never read past the caller's arrays
   }

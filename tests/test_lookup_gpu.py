@@ -8,6 +8,7 @@ enumerated from a seed instead.  The bar is the reference's: EXPECT_EQ on every
 element, i.e. bit-exact fp32 and fp16.
 """
 import itertools
+import os
 
 import numpy as np
 import pytest
@@ -123,6 +124,29 @@ def test_offsets_not_zero_based(gpu_ctx, oracle, bit_rate):
     out = torch.zeros(batch * dim, device="cuda")
     assert kern(batch, n, rows, dev(table), dev(indices), dev(shifted), dev(weights), out) and ok_ref
     np.testing.assert_array_equal(bits(out.cpu().numpy()), bits(ref))
+
+
+@pytest.mark.parametrize("bit_rate", [8, 4])
+def test_offsets_stepping_backwards_return_false(gpu_ctx, oracle, bit_rate):
+    """offsets = [0, 5, 3, 8] with 8 indices: the last offset matches, every
+    bag stays inside the index array, yet the reference (which walks the array
+    with a running position) runs past the end and returns false."""
+    rng = np.random.default_rng(4100 + bit_rate)
+    rows, dim = 300, 32
+    table = random_fused_table(rng, rows, dim, bit_rate)
+    indices = rng.integers(0, rows, 8).astype(np.int64)
+    for odt in (np.int32, np.int64):
+        offsets = np.array([0, 5, 3, 8], dtype=odt)
+        ok_ref, _ = oracle.spmdm(bit_rate, dim, rows, table, indices, offsets, None, False, np.float32)
+        assert not ok_ref
+        kern = make_kernel(bit_rate, dim, False, False, False, True, np.int64, odt, np.float32)
+        out = torch.zeros(3 * dim, device="cuda")
+        assert not kern(3, 8, rows, dev(table), dev(indices), dev(offsets), None, out)
+        os.environ["FBGEMM_B200_KERNEL"] = "staged"
+        try:
+            assert not kern(3, 8, rows, dev(table), dev(indices), dev(offsets), None, out)
+        finally:
+            del os.environ["FBGEMM_B200_KERNEL"]
 
 
 @pytest.mark.parametrize("bit_rate", [8, 4, 2])
