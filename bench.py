@@ -61,6 +61,8 @@ def parse_args():
     ap.add_argument("--scale", type=float, default=1.0, help="shrink table rows (and, for workloads 0-2, the batch)")
     ap.add_argument("--tables-scale", type=float, default=1.0, help="workloads 3/4: fraction of the tables")
     ap.add_argument("--batch-scale", type=float, default=1.0, help="workloads 3/4: fraction of the batch")
+    ap.add_argument("--launch", default="streams", choices=["plan", "streams"],
+                    help="workloads 3/4: one multi-table plan (a launch per kernel variant) or a launch per table")
     ap.add_argument("--redistribution", default="p2p", choices=["p2p", "nccl"],
                     help="workloads 3/4: peer stores from the lookup kernel, or NCCL all-to-all after it")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
@@ -285,20 +287,29 @@ def main_multi(args):
     streams = [torch.cuda.Stream(device=dev) for _ in range(4)]
     handles = [s.cuda_stream for s in streams]
 
+    plans = None
+    if args.launch == "plan":
+        # one kernel launch per kernel variant instead of one per table
+        plans = [sl.make_plan(sets[j % nsets], buffer=j, slot=400 + j) for j in range(2)]
+    launches_per_step = plans[0].num_launches if plans else len(sl.local)
+
     def step(i):
-        cur = torch.cuda.current_stream()
-        for s in streams:
-            s.wait_stream(cur)
-        sl.launch(sets[i % nsets], buffer=i % 2, slot_base=(i % 4) * 100, streams=handles)
-        for s in streams:
-            cur.wait_stream(s)
+        if plans:
+            plans[i % 2].launch()
+        else:
+            cur = torch.cuda.current_stream()
+            for s in streams:
+                s.wait_stream(cur)
+            sl.launch(sets[i % nsets], buffer=i % 2, slot_base=(i % 4) * 100, streams=handles)
+            for s in streams:
+                cur.wait_stream(s)
         if args.redistribution == "nccl":
             sl.exchange(i % 2)
 
     for i in range(max(args.warmup, 3)):
         step(i)
     sl.barrier()
-    ok = all(F.status_read(s, dev.index)[0] for s in range(400))
+    ok = all(F.status_read(s, dev.index)[0] for s in range(402))
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clocks:
         e0.record()
@@ -307,7 +318,7 @@ def main_multi(args):
         e1.record()
         sl.barrier()
     ms = e0.elapsed_time(e1)
-    ok = ok and all(F.status_read(s, dev.index)[0] for s in range(400))
+    ok = ok and all(F.status_read(s, dev.index)[0] for s in range(402))
     tot = torch.tensor([bytes_local, ms, float(ok)], device=dev, dtype=torch.float64)
     if world > 1:
         import torch.distributed as dist
@@ -335,10 +346,12 @@ def main_multi(args):
                        "rows_scale": args.scale, "tables_scale": args.tables_scale, "batch_scale": args.batch_scale,
                        "table_GB_this_rank": round(sum(t.numel() for t in sl.tables.values()) / 1e9, 2),
                        "redistribution": args.redistribution,
+                       "launch": (f"multi-table plan, {launches_per_step} kernel launches per step" if plans else
+                                  f"one launch per table ({launches_per_step} per step) over 4 streams"),
                        "l2": "tables are far larger than L2; two alternating input sets"},
             "results_ok": ok, "bags_per_s": len(specs) * B * args.steps / sec,
             "frac_of_hbm_peak": value / world / peak, "clocks": clocks.summary(),
-            "gpu_launches": len(sl.local) * args.steps,
+            "gpu_launches": launches_per_step * args.steps,
             "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s",
                          "frac": value / world / peak, "traffic": None, "peak_source": peak_src},
             "e2e": None, "cpu_baseline": None}))

@@ -24,6 +24,7 @@ from .embedding import (  # noqa: F401
     GenerateEmbeddingSpMDMNBitWithStrides,
     GenerateEmbeddingSpMDMRowWiseSparse,
     GenerateEmbeddingSpMDMWithStrides,
+    MultiTablePlan,
     SpmdmKernel,
     get_context,
     launch_count,

@@ -40,6 +40,24 @@ class SpmdmConfig(C.Structure):
     ]
 
 
+class TableCall(C.Structure):
+    """``fbgemm_b200_table_call``: the arguments of one table's functor call."""
+
+    _fields_ = [
+        ("cfg", SpmdmConfig),
+        ("output_size", C.c_int64),
+        ("index_size", C.c_int64),
+        ("data_size", C.c_int64),
+        ("input", C.c_void_p),
+        ("indices", C.c_void_p),
+        ("offsets", C.c_void_p),
+        ("weights", C.c_void_p),
+        ("out", C.c_void_p),
+        ("compressed_indices_table", C.c_void_p),
+        ("peer_out", C.POINTER(C.c_void_p)),
+    ]
+
+
 class Fbgemmb200Error(RuntimeError):
     pass
 
@@ -58,6 +76,11 @@ SIGNATURES = {
     "fbgemm_b200_spmdm_launch": (C.c_int, [_p, _cfgp, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, C.c_int, _p]),
     "fbgemm_b200_spmdm_launch_sharded": (C.c_int, [_p, _cfgp, _i64, _i64, _i64, _p, _p, _p, _p, C.POINTER(_p),
                                                    C.c_int, _i64, C.c_int, _p]),
+    "fbgemm_b200_multi_plan_create": (C.c_int, [_p, C.POINTER(TableCall), C.c_int32, C.c_int32, _i64, C.c_int,
+                                                C.POINTER(_p)]),
+    "fbgemm_b200_multi_plan_launch": (C.c_int, [_p, _p]),
+    "fbgemm_b200_multi_plan_num_launches": (C.c_int, [_p]),
+    "fbgemm_b200_multi_plan_destroy": (None, [_p]),
     "fbgemm_b200_status_read": (C.c_int, [_p, C.c_int, _p, C.POINTER(C.c_int32)]),
     "fbgemm_b200_spmdm": (C.c_int, [_p, _cfgp, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, _p]),
     "fbgemm_b200_spmdm_lengths_noalloc": (C.c_int, [_cfgp, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, _p]),

@@ -110,6 +110,11 @@ struct fbgemm_b200_ctx {
   Lane lanes[FBGEMM_B200_HOST_LANES];
 };
 
+struct fbgemm_b200_multi_plan {
+  int device = 0;
+  MultiPlan plan;
+};
+
 namespace {
 
 class DeviceGuard {
@@ -181,25 +186,24 @@ int check_config(const fbgemm_b200_spmdm_config* c, Derived* d) {
 
 }  // namespace
 
-// Build the kernel parameters for one functor call and enqueue it.  All
-// pointers are device pointers.  `scan` is the scratch for lengths mode.
-int fbgemm_b200::enqueue_lookup(
+// Validate one functor call and fill the kernel parameters for it (everything
+// but the offsets, which depend on the offsets/lengths mode).
+int fbgemm_b200::build_lookup_params(
     const fbgemm_b200_spmdm_config* cfg,
     int64_t output_size,
     int64_t index_size,
     int64_t data_size,
     const void* input,
     const void* indices,
-    const void* offsets_or_lengths,
     const float* weights,
     void* out,
     const int32_t* cit,
     int32_t* status,
-    DeviceBuffer& scan,
-    cudaStream_t stream,
     void* const* peer_out,
     int num_peers,
-    int64_t bags_per_peer) {
+    int64_t bags_per_peer,
+    SpmdmParams* params) {
+  SpmdmParams& p = *params;
   Derived d;
   int rc = check_config(cfg, &d);
   if (rc) {
@@ -219,7 +223,7 @@ int fbgemm_b200::enqueue_lookup(
     return FBGEMM_B200_EINVAL;
   }
 
-  SpmdmParams p{};
+  p = SpmdmParams{};
   p.table = static_cast<const uint8_t*>(input);
   p.indices = indices;
   p.weights = cfg->has_weight ? weights : nullptr;
@@ -280,7 +284,36 @@ int fbgemm_b200::enqueue_lookup(
   if (out_aligned) {
     flags |= kOutVec;
   }
+  p.flags = flags;
+  return 0;
+}
 
+// Build the kernel parameters for one functor call and enqueue it.  All
+// pointers are device pointers.  `scan` is the scratch for lengths mode.
+int fbgemm_b200::enqueue_lookup(
+    const fbgemm_b200_spmdm_config* cfg,
+    int64_t output_size,
+    int64_t index_size,
+    int64_t data_size,
+    const void* input,
+    const void* indices,
+    const void* offsets_or_lengths,
+    const float* weights,
+    void* out,
+    const int32_t* cit,
+    int32_t* status,
+    DeviceBuffer& scan,
+    cudaStream_t stream,
+    void* const* peer_out,
+    int num_peers,
+    int64_t bags_per_peer) {
+  SpmdmParams p;
+  const int rc = build_lookup_params(cfg, output_size, index_size, data_size, input, indices, weights, out, cit, status,
+                                     peer_out, num_peers, bags_per_peer, &p);
+  if (rc) {
+    return rc;
+  }
+  uint32_t flags = p.flags;
   if (cfg->use_offsets) {
     p.offsets = offsets_or_lengths;
     flags |= cfg->offset_bytes == 8 ? kOff64 : 0;
@@ -467,6 +500,87 @@ int fbgemm_b200_spmdm_launch_sharded(
   return enqueue_lookup(cfg, output_size, index_size, data_size, input, indices, offsets, weights, nullptr, nullptr,
                         ctx->status + 4 * slot, ctx->scan, static_cast<cudaStream_t>(stream), peer_out, num_peers,
                         bags_per_peer);
+}
+
+int fbgemm_b200_multi_plan_create(
+    fbgemm_b200_ctx* ctx,
+    const fbgemm_b200_table_call* calls,
+    int32_t num_tables,
+    int32_t num_peers,
+    int64_t bags_per_peer,
+    int slot,
+    fbgemm_b200_multi_plan** out) {
+  if (out) {
+    *out = nullptr;
+  }
+  if (!ctx || !out || slot < 0 || slot >= FBGEMM_B200_STATUS_SLOTS) {
+    set_error("bad context, plan pointer or status slot");
+    return FBGEMM_B200_EINVAL;
+  }
+  if (!calls || num_tables <= 0 || num_peers < 0) {
+    set_error("a plan needs at least one table");
+    return FBGEMM_B200_EINVAL;
+  }
+  std::vector<SpmdmParams> params((size_t)num_tables);
+  std::vector<int> bit_rates((size_t)num_tables);
+  for (int t = 0; t < num_tables; ++t) {
+    const fbgemm_b200_table_call& c = calls[t];
+    if (!c.cfg.use_offsets) {
+      set_error("a plan takes offsets, not lengths");
+      return FBGEMM_B200_EINVAL;
+    }
+    if (num_peers > 0 && !c.peer_out) {
+      set_error("num_peers > 0 but a table has no peer_out");
+      return FBGEMM_B200_EINVAL;
+    }
+    const int rc = build_lookup_params(&c.cfg, c.output_size, c.index_size, c.data_size, c.input, c.indices, c.weights,
+                                       c.out, c.compressed_indices_table, ctx->status + 4 * slot, c.peer_out,
+                                       num_peers, bags_per_peer, &params[(size_t)t]);
+    if (rc) {
+      return rc;
+    }
+    params[(size_t)t].offsets = c.offsets;
+    params[(size_t)t].flags |= c.cfg.offset_bytes == 8 ? kOff64 : 0;
+    bit_rates[(size_t)t] = c.cfg.bit_rate;
+  }
+  DeviceGuard guard(ctx->device);
+  auto* plan = new (std::nothrow) fbgemm_b200_multi_plan;
+  if (!plan) {
+    set_error("out of host memory");
+    return FBGEMM_B200_ENOMEM;
+  }
+  plan->device = ctx->device;
+  const cudaError_t e = build_multi_plan(params, bit_rates, &plan->plan);
+  if (e != cudaSuccess) {
+    delete plan;
+    return fail_cuda(e, "multi-table plan");
+  }
+  *out = plan;
+  return 0;
+}
+
+int fbgemm_b200_multi_plan_launch(fbgemm_b200_multi_plan* plan, void* stream) {
+  if (!plan) {
+    set_error("null plan");
+    return FBGEMM_B200_EINVAL;
+  }
+  DeviceGuard guard(plan->device);
+  const cudaError_t e = launch_multi_plan(plan->plan, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) {
+    return fail_cuda(e, "multi-table launch");
+  }
+  return 0;
+}
+
+int fbgemm_b200_multi_plan_num_launches(const fbgemm_b200_multi_plan* plan) {
+  return plan ? (int)(plan->plan.groups.size() + plan->plan.singles.size()) : 0;
+}
+
+void fbgemm_b200_multi_plan_destroy(fbgemm_b200_multi_plan* plan) {
+  if (plan) {
+    DeviceGuard guard(plan->device);
+    delete plan;
+  }
 }
 
 int fbgemm_b200_status_read(fbgemm_b200_ctx* ctx, int slot, void* stream, int32_t* info) {

@@ -6,6 +6,8 @@
 #include <atomic>
 #include <cstdint>
 #include <string>
+#include <utility>
+#include <vector>
 
 #include "fbgemm_b200/embedding_c_api.h"
 
@@ -67,6 +69,36 @@ __device__ __forceinline__ char* output_row(const SpmdmParams& p, int64_t bag, i
 // launch error; never synchronises.
 cudaError_t launch_spmdm(const SpmdmParams& p, int bit_rate, cudaStream_t stream);
 
+// Several tables per launch (spmdm_kernels.cu): the tables of one call grouped
+// by kernel variant, their parameters resident in device memory.  Built once
+// for a fixed set of pointers, launched as often as wanted.
+struct MultiPlan {
+  struct Group {
+    void (*fn)(const SpmdmParams*, const int32_t*, const int32_t*);
+    size_t param_off;   // first table of the group in d_params and d_first_block
+    size_t table_off;   // first block of the group in d_table_of_block
+    int count;          // tables
+    unsigned blocks;    // grid size
+  };
+  std::vector<Group> groups;
+  std::vector<std::pair<SpmdmParams, int>> singles;  // (parameters, bit rate): one launch each
+  SpmdmParams* d_params = nullptr;
+  int32_t* d_first_block = nullptr;     // per table: its first block within its group's grid
+  int32_t* d_table_of_block = nullptr;  // per block: its table within its group
+  // The launches of one call overlap: all but the first go to side streams
+  // that fork from, and join, the caller's stream through these events.
+  static constexpr int kSideStreams = 3;
+  cudaStream_t side[kSideStreams] = {};
+  cudaEvent_t fork = nullptr;
+  cudaEvent_t join[kSideStreams] = {};
+  MultiPlan() = default;
+  MultiPlan(const MultiPlan&) = delete;
+  MultiPlan& operator=(const MultiPlan&) = delete;
+  ~MultiPlan();
+};
+cudaError_t build_multi_plan(const std::vector<SpmdmParams>& tables, const std::vector<int>& bit_rates, MultiPlan* plan);
+cudaError_t launch_multi_plan(const MultiPlan& plan, cudaStream_t stream);
+
 // Exclusive scan of `n` int32/int64 lengths into int64 offsets[n + 1]
 // (scan_kernels.cu).  `block_sums` is scratch of scan_scratch_elems(n) int64.
 size_t scan_scratch_elems(int64_t n);
@@ -109,6 +141,24 @@ int enqueue_lookup(
     void* const* peer_out = nullptr,
     int num_peers = 0,
     int64_t bags_per_peer = 0);
+
+// The validation and parameter set-up half of enqueue_lookup (offsets are left
+// for the caller to fill in).
+int build_lookup_params(
+    const fbgemm_b200_spmdm_config* cfg,
+    int64_t output_size,
+    int64_t index_size,
+    int64_t data_size,
+    const void* input,
+    const void* indices,
+    const float* weights,
+    void* out,
+    const int32_t* cit,
+    int32_t* status,
+    void* const* peer_out,
+    int num_peers,
+    int64_t bags_per_peer,
+    SpmdmParams* params);
 
 // Process-wide count of kernels launched by this library.
 extern std::atomic<uint64_t> g_launch_count;

@@ -327,9 +327,10 @@ __device__ __forceinline__ void store_columns(const SpmdmParams& p, int64_t bag,
   }
 }
 
+// The work of one thread block: block `block` of the launch that covers the
+// bags of `p` (32/LPB bags per warp, kWarpsPerBlock warps).
 template <int BITS, int VEC, int LPB, int CPL>
-__global__ void __launch_bounds__(kThreads)
-spmdm_direct_kernel(const __grid_constant__ SpmdmParams p) {
+__device__ __forceinline__ void direct_block(const SpmdmParams& p, int64_t block) {
   constexpr int GPW = 32 / LPB;                       // bags per warp
   constexpr int CPC = VEC * 8 / BITS;                 // columns per chunk
   constexpr int PAIRS = (VEC / 4) * (16 / BITS);      // fp32x2 pairs per chunk
@@ -353,14 +354,14 @@ spmdm_direct_kernel(const __grid_constant__ SpmdmParams p) {
   const bool weighted = p.flags & kWeighted;
 
   const int64_t off_base = load_int(p.offsets, 0, off64);
-  if (blockIdx.x == 0 && threadIdx.x == 0) {
+  if (block == 0 && threadIdx.x == 0) {
     // `return current == index_size` of the reference
     const int64_t total = load_int(p.offsets, p.output_size, off64) - off_base;
     if (total != p.index_size) {
       report(p.status, FBGEMM_B200_STATUS_SIZE_MISMATCH, p.output_size, total, p.index_size);
     }
   }
-  const int64_t bag = ((int64_t)blockIdx.x * kWarpsPerBlock + warp) * GPW + grp;
+  const int64_t bag = (block * kWarpsPerBlock + warp) * GPW + grp;
   if (bag >= p.output_size) {
     return;
   }
@@ -373,7 +374,7 @@ spmdm_direct_kernel(const __grid_constant__ SpmdmParams p) {
   // with a running position, ends up past index_size and returns false.
   if (bag_len < 0 || start < 0 || start + len > p.index_size) {
     if (gl == 0) {
-      report(p.status, FBGEMM_B200_STATUS_BAG_OVERRUN, bag, start, bag_len);
+      report(p.status, FBGEMM_B200_STATUS_BAG_OVERRUN, bag, start, len);
     }
     len = 0;  // never read past the caller's arrays
   }
@@ -526,10 +527,34 @@ spmdm_direct_kernel(const __grid_constant__ SpmdmParams p) {
   }
 }
 
+// One table per launch; the parameters travel in constant memory.
+template <int BITS, int VEC, int LPB, int CPL>
+__global__ void __launch_bounds__(kThreads)
+spmdm_direct_kernel(const __grid_constant__ SpmdmParams p) {
+  direct_block<BITS, VEC, LPB, CPL>(p, blockIdx.x);
+}
+
+// Several tables of the same row format in one launch (the reference's
+// multi-table caller loops over tables,
+// fbgemm_gpu/codegen/inference/embedding_forward_quantized_cpu_template.cpp:343-473).
+// Block b works on table table_of_block[b], whose blocks start at
+// first_block[table]; the table's parameters are read from device memory.
+template <int BITS, int VEC, int LPB, int CPL>
+__global__ void __launch_bounds__(kThreads)
+spmdm_direct_multi_kernel(
+    const SpmdmParams* __restrict__ params,
+    const int32_t* __restrict__ first_block,
+    const int32_t* __restrict__ table_of_block) {
+  const int t = __ldg(table_of_block + blockIdx.x);
+  direct_block<BITS, VEC, LPB, CPL>(params[t], (int64_t)blockIdx.x - __ldg(first_block + t));
+}
+
 using KernelFn = void (*)(const SpmdmParams);
+using MultiKernelFn = void (*)(const SpmdmParams*, const int32_t*, const int32_t*);
 
 struct Variant {
   KernelFn fn;
+  MultiKernelFn multi;
   int vec, lpb, cpl;
 };
 

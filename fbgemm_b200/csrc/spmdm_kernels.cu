@@ -25,6 +25,9 @@
 #include <cstdlib>
 #include <cstring>
 
+#include <algorithm>
+#include <vector>
+
 #include "internal.h"
 #include "spmdm_direct.cuh"
 
@@ -263,7 +266,7 @@ spmdm_kernel(const __grid_constant__ SpmdmParams p) {
   // with a running position, ends up past index_size and returns false.
   if (bag_len < 0 || start < 0 || start + len > p.index_size) {
     if (gl == 0) {
-      report(p.status, FBGEMM_B200_STATUS_BAG_OVERRUN, bag, start, bag_len);
+      report(p.status, FBGEMM_B200_STATUS_BAG_OVERRUN, bag, start, len);
     }
     len = 0;  // never read past the caller's arrays
   }
@@ -423,15 +426,15 @@ int max_chunks_per_bag(int bit_rate) {
   return 32 * (bit_rate == 8 ? 8 : bit_rate == 4 ? 4 : 2);
 }
 
-// The direct kernel (spmdm_direct.cuh) when the rows allow 4- or 8-byte vector
-// loads; returns cudaErrorNotSupported when they do not.
-static cudaError_t launch_direct(SpmdmParams p, int bit_rate, cudaStream_t stream) {
+// The variant of the direct kernel (spmdm_direct.cuh) for this call, or null
+// when the rows do not allow 4- or 8-byte vector loads.
+static const direct::Variant* pick_direct(const SpmdmParams& p, int bit_rate) {
   const uintptr_t base = reinterpret_cast<uintptr_t>(p.table);
   auto divides = [&](int v) { return base % v == 0 && p.input_stride % v == 0 && p.data_bytes % v == 0; };
   // Row ids travel between lanes as 32-bit values and skipped rows read row 0.
   if (!divides(4) || p.data_bytes == 0 || p.data_size == 0 || p.data_size > 0xfffffffeLL ||
       p.input_stride > 0xffffffffLL) {
-    return cudaErrorNotSupported;
+    return nullptr;
   }
   int vec = divides(8) ? 8 : 4;
   const int env_vec = env_int("FBGEMM_B200_VEC", 0);
@@ -477,17 +480,177 @@ static cudaError_t launch_direct(SpmdmParams p, int bit_rate, cudaStream_t strea
       pick = &v[i];
     }
   }
+  return pick;
+}
+
+static int64_t direct_blocks(const direct::Variant* v, int64_t bags) {
+  const int64_t bags_per_block = (int64_t)direct::kWarpsPerBlock * (32 / v->lpb);
+  return (bags + bags_per_block - 1) / bags_per_block;
+}
+
+// One table, one launch; returns cudaErrorNotSupported when the direct kernel
+// cannot take the rows.
+static cudaError_t launch_direct(const SpmdmParams& p, int bit_rate, cudaStream_t stream) {
+  const direct::Variant* pick = pick_direct(p, bit_rate);
   if (!pick) {
     return cudaErrorNotSupported;
   }
-  const int64_t bags_per_block = (int64_t)direct::kWarpsPerBlock * (32 / lpb);
-  const int64_t blocks = (p.output_size + bags_per_block - 1) / bags_per_block;
+  const int64_t blocks = direct_blocks(pick, p.output_size);
   if (blocks <= 0 || blocks > 0x7fffffffLL) {
     return cudaErrorInvalidValue;
   }
   pick->fn<<<(unsigned)blocks, direct::kThreads, 0, stream>>>(p);
   g_launch_count.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError();
+}
+
+// ---- several tables per launch --------------------------------------------------
+
+MultiPlan::~MultiPlan() {
+  cudaFree(d_params);
+  cudaFree(d_first_block);
+  cudaFree(d_table_of_block);
+  for (int i = 0; i < kSideStreams; ++i) {
+    if (side[i]) {
+      cudaStreamDestroy(side[i]);
+    }
+    if (join[i]) {
+      cudaEventDestroy(join[i]);
+    }
+  }
+  if (fork) {
+    cudaEventDestroy(fork);
+  }
+}
+
+// Tables that share a kernel variant go into one launch: their parameters are
+// laid out side by side in device memory and the grid is the sum of their
+// blocks.  Tables the direct kernel cannot take keep a launch of their own.
+cudaError_t build_multi_plan(const std::vector<SpmdmParams>& tables, const std::vector<int>& bit_rates, MultiPlan* plan) {
+  std::vector<const direct::Variant*> variant(tables.size());
+  std::vector<size_t> order;
+  for (size_t t = 0; t < tables.size(); ++t) {
+    variant[t] = tables[t].output_size > 0 ? pick_direct(tables[t], bit_rates[t]) : nullptr;
+    if (tables[t].output_size <= 0) {
+      continue;  // nothing to pool, nothing to store
+    }
+    if (variant[t]) {
+      order.push_back(t);
+    } else {
+      plan->singles.push_back({tables[t], bit_rates[t]});
+    }
+  }
+  std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) { return variant[a] < variant[b]; });
+  std::vector<SpmdmParams> params;
+  std::vector<int32_t> first_block, table_of_block;
+  for (size_t i = 0; i < order.size();) {
+    const direct::Variant* v = variant[order[i]];
+    MultiPlan::Group g{};
+    g.fn = v->multi;
+    g.param_off = params.size();
+    g.table_off = table_of_block.size();
+    int64_t blocks = 0;
+    for (; i < order.size() && variant[order[i]] == v; ++i) {
+      const int64_t b = direct_blocks(v, tables[order[i]].output_size);
+      if (blocks + b > 0x7fffffffLL) {
+        break;  // the rest of this variant's tables start a new launch
+      }
+      first_block.push_back((int32_t)blocks);
+      params.push_back(tables[order[i]]);
+      table_of_block.insert(table_of_block.end(), (size_t)b, (int32_t)g.count);
+      blocks += b;
+      ++g.count;
+    }
+    if (g.count == 0) {
+      return cudaErrorInvalidValue;  // a single table with more than 2^31 blocks
+    }
+    g.blocks = (unsigned)blocks;
+    plan->groups.push_back(g);
+  }
+  // largest grid first: the short launches fill the tail of the long ones
+  std::stable_sort(plan->groups.begin(), plan->groups.end(),
+                   [](const MultiPlan::Group& a, const MultiPlan::Group& b) { return a.blocks > b.blocks; });
+  if (plan->groups.size() + plan->singles.size() > 1) {
+    cudaError_t e = cudaEventCreateWithFlags(&plan->fork, cudaEventDisableTiming);
+    for (int i = 0; i < MultiPlan::kSideStreams && e == cudaSuccess; ++i) {
+      e = cudaStreamCreateWithFlags(&plan->side[i], cudaStreamNonBlocking);
+      if (e == cudaSuccess) {
+        e = cudaEventCreateWithFlags(&plan->join[i], cudaEventDisableTiming);
+      }
+    }
+    if (e != cudaSuccess) {
+      return e;
+    }
+  }
+  if (!params.empty()) {
+    cudaError_t e = cudaMalloc(&plan->d_params, params.size() * sizeof(SpmdmParams));
+    if (e == cudaSuccess) {
+      e = cudaMalloc(&plan->d_first_block, first_block.size() * sizeof(int32_t));
+    }
+    if (e == cudaSuccess) {
+      e = cudaMemcpy(plan->d_params, params.data(), params.size() * sizeof(SpmdmParams), cudaMemcpyHostToDevice);
+    }
+    if (e == cudaSuccess) {
+      e = cudaMemcpy(plan->d_first_block, first_block.data(), first_block.size() * sizeof(int32_t),
+                     cudaMemcpyHostToDevice);
+    }
+    if (e == cudaSuccess) {
+      e = cudaMalloc(&plan->d_table_of_block, table_of_block.size() * sizeof(int32_t));
+    }
+    if (e == cudaSuccess) {
+      e = cudaMemcpy(plan->d_table_of_block, table_of_block.data(), table_of_block.size() * sizeof(int32_t),
+                     cudaMemcpyHostToDevice);
+    }
+    if (e != cudaSuccess) {
+      return e;
+    }
+  }
+  return cudaSuccess;
+}
+
+cudaError_t launch_multi_plan(const MultiPlan& plan, cudaStream_t stream) {
+  const size_t launches = plan.groups.size() + plan.singles.size();
+  const bool spread = launches > 1 && plan.fork;
+  cudaError_t e = cudaSuccess;
+  if (spread) {
+    e = cudaEventRecord(plan.fork, stream);
+    for (int i = 0; i < MultiPlan::kSideStreams && e == cudaSuccess; ++i) {
+      e = cudaStreamWaitEvent(plan.side[i], plan.fork, 0);
+    }
+    if (e != cudaSuccess) {
+      return e;
+    }
+  }
+  size_t n = 0;  // launch n goes to the caller's stream (n % 4 == 0) or to side stream n % 4 - 1
+  auto stream_of = [&](size_t i) {
+    const size_t k = i % (MultiPlan::kSideStreams + 1);
+    return (!spread || k == 0) ? stream : plan.side[k - 1];
+  };
+  for (const MultiPlan::Group& g : plan.groups) {
+    g.fn<<<g.blocks, direct::kThreads, 0, stream_of(n++)>>>(plan.d_params + g.param_off,
+                                                             plan.d_first_block + g.param_off,
+                                                             plan.d_table_of_block + g.table_off);
+    g_launch_count.fetch_add(1, std::memory_order_relaxed);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) {
+      return e;
+    }
+  }
+  for (const auto& single : plan.singles) {
+    e = launch_spmdm(single.first, single.second, stream_of(n++));
+    if (e != cudaSuccess) {
+      return e;
+    }
+  }
+  if (spread) {
+    for (int i = 0; i < MultiPlan::kSideStreams && e == cudaSuccess; ++i) {
+      e = cudaEventRecord(plan.join[i], plan.side[i]);
+      if (e == cudaSuccess) {
+        e = cudaStreamWaitEvent(stream, plan.join[i], 0);
+      }
+    }
+  }
+  return e;
 }
 
 cudaError_t launch_spmdm(const SpmdmParams& p_in, int bit_rate, cudaStream_t stream) {

@@ -184,6 +184,66 @@ class SpmdmKernel:
                 raise TypeError(f"{what} have {size}-byte elements, kernel was generated for {want}")
 
 
+class MultiTablePlan:
+    """Several tables pooled by one call (``fbgemm_b200_multi_plan_*``): what the
+    reference's multi-table caller does with a loop of functor calls
+    (fbgemm_gpu/codegen/inference/embedding_forward_quantized_cpu_template.cpp:343-473).
+
+    ``calls`` is a list of ``(kernel, output_size, index_size, data_size, input,
+    indices, offsets, weights, out, compressed_indices_table)`` with device
+    tensors; ``peer_ptrs`` (optional, one list of ``num_peers`` addresses per
+    table) redirects the pooled rows as ``fbgemm_b200_spmdm_launch_sharded``
+    does.  The plan keeps the tensors alive and is tied to their addresses."""
+
+    def __init__(self, calls, device: int | None = None, slot: int = 0, peer_ptrs=None, bags_per_peer: int = 0):
+        self.ctx = get_context(device)
+        self.slot = slot
+        self._keep = list(calls)
+        n = len(calls)
+        arr = (_capi.TableCall * n)()
+        self._peer_arrays = []
+        num_peers = len(peer_ptrs[0]) if peer_ptrs else 0
+        for t, (kern, output_size, index_size, data_size, input, indices, offsets, weights, out, cit) in enumerate(calls):
+            c = arr[t]
+            c.cfg = kern.cfg
+            c.output_size, c.index_size, c.data_size = output_size, index_size, data_size
+            c.input, c.indices, c.offsets = _ptr(input), _ptr(indices), _ptr(offsets)
+            c.weights = _ptr(weights) if kern.cfg.has_weight else None
+            c.out = _ptr(out)
+            c.compressed_indices_table = _ptr(cit)
+            if peer_ptrs:
+                pa = (C.c_void_p * num_peers)(*peer_ptrs[t])
+                self._peer_arrays.append(pa)
+                c.peer_out = pa
+        handle = C.c_void_p()
+        rc = _capi.lib().fbgemm_b200_multi_plan_create(self.ctx.handle, arr, n, num_peers, bags_per_peer, slot,
+                                                       C.byref(handle))
+        _capi.check(rc, "fbgemm_b200_multi_plan_create")
+        self._handle = handle
+
+    @property
+    def num_launches(self) -> int:
+        return int(_capi.lib().fbgemm_b200_multi_plan_num_launches(self._handle))
+
+    def launch(self, stream=None) -> None:
+        import torch
+
+        if stream is None:
+            stream = torch.cuda.current_stream(self.ctx.device).cuda_stream
+        _capi.check(_capi.lib().fbgemm_b200_multi_plan_launch(self._handle, stream), "fbgemm_b200_multi_plan_launch")
+
+    def close(self) -> None:
+        if self._handle:
+            _capi.lib().fbgemm_b200_multi_plan_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 def status_read(slot: int = 0, device: int | None = None, stream=None):
     """(ok, info[4]) of status slot ``slot`` after waiting for ``stream``."""
     import torch

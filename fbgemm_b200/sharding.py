@@ -207,6 +207,28 @@ class ShardedLookup:
                          b.weights if k.cfg.has_weight else None, out, slot=slot, stream=stream)
                 col += s.dim
 
+    def make_plan(self, batches: dict, buffer: int = 0, slot: int = 0):
+        """The same lookups as ``launch`` as a multi-table plan
+        (``fbgemm_b200_multi_plan_*``): the local tables grouped by kernel
+        variant, one kernel launch per group, for this input set and output
+        buffer.  Call ``.launch(stream)`` on the result."""
+        from .embedding import MultiTablePlan
+
+        calls, peers, col = [], [], 0
+        for t in self.local:
+            b, s, k = batches[t], self.specs[t], self.kernels[t]
+            out = None
+            if self.mode == "p2p":
+                peers.append([int(p) for p in self._peer_ptrs[(buffer, t)]])
+            else:
+                out = self.local_out[buffer].view(-1)[col:]
+                col += s.dim
+            calls.append((k, b.output_size, b.index_size, s.rows, self.tables[t], b.indices, b.offsets,
+                          b.weights if k.cfg.has_weight else None, out, None))
+        if self.mode == "p2p":
+            return MultiTablePlan(calls, self.device.index, slot, peer_ptrs=peers, bags_per_peer=self.rows)
+        return MultiTablePlan(calls, self.device.index, slot)
+
     def exchange(self, buffer: int = 0) -> torch.Tensor:
         """nccl mode: the all-to-all and the column assembly (on the current stream)."""
         assert self.mode == "nccl"

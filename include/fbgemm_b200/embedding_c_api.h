@@ -168,6 +168,53 @@ FBGEMM_B200_API int fbgemm_b200_spmdm_launch_sharded(
     int slot,
     void* stream);
 
+/*
+ * Several tables in one call - what the reference's multi-table caller does
+ * with a loop of functor calls, one per table, writing `output + D_start` with
+ * output_stride = total_D
+ * (fbgemm_gpu/codegen/inference/embedding_forward_quantized_cpu_template.cpp:343-473;
+ * the reference library itself has no multi-table entry point).  A plan is
+ * built once for a fixed set of device pointers: the tables are grouped by
+ * kernel variant and every group becomes ONE launch whose grid covers all bags
+ * of all its tables.  Launching the plan again pools whatever the index,
+ * offset and weight arrays hold by then.
+ *
+ * One fbgemm_b200_table_call per table: the arguments of
+ * fbgemm_b200_spmdm_launch (offsets flavour only).  With num_peers > 0 the
+ * pooled rows go to peer_out as in fbgemm_b200_spmdm_launch_sharded (`out` is
+ * ignored, dense tables only).  All tables report into status slot `slot`.
+ */
+typedef struct fbgemm_b200_table_call {
+  fbgemm_b200_spmdm_config cfg;
+  int64_t output_size;
+  int64_t index_size;
+  int64_t data_size;
+  const void* input;
+  const void* indices;
+  const void* offsets;
+  const float* weights;                    /* NULL unless cfg.has_weight */
+  void* out;
+  const int32_t* compressed_indices_table; /* NULL = dense table */
+  void* const* peer_out;                   /* num_peers pointers, or NULL */
+} fbgemm_b200_table_call;
+
+typedef struct fbgemm_b200_multi_plan fbgemm_b200_multi_plan;
+
+FBGEMM_B200_API int fbgemm_b200_multi_plan_create(
+    fbgemm_b200_ctx* ctx,
+    const fbgemm_b200_table_call* calls,
+    int32_t num_tables,
+    int32_t num_peers,
+    int64_t bags_per_peer,
+    int slot,
+    fbgemm_b200_multi_plan** plan);
+/* Enqueues the plan's launches on `stream` (no allocation, no copy: it can be
+ * captured into a CUDA graph).  Returns 0 or a negative code. */
+FBGEMM_B200_API int fbgemm_b200_multi_plan_launch(fbgemm_b200_multi_plan* plan, void* stream);
+/* Kernel launches one fbgemm_b200_multi_plan_launch enqueues. */
+FBGEMM_B200_API int fbgemm_b200_multi_plan_num_launches(const fbgemm_b200_multi_plan* plan);
+FBGEMM_B200_API void fbgemm_b200_multi_plan_destroy(fbgemm_b200_multi_plan* plan);
+
 /* Waits for `stream`, reads status slot `slot` into info[4] = {code, bag,
  * position in indices, offending value (low 32 bits)} and clears the slot.
  * Returns 1 if the code is 0 (functor result true), 0 otherwise, negative on
