@@ -37,6 +37,8 @@ class SpmdmConfig(C.Structure):
         ("normalize_by_lengths", C.c_int32),
         ("is_weight_positional", C.c_int32),
         ("use_offsets", C.c_int32),
+        ("scale_bias_first", C.c_int32),
+        ("no_bag", C.c_int32),
     ]
 
 

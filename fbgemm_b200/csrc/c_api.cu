@@ -150,8 +150,14 @@ int check_config(const fbgemm_b200_spmdm_config* c, Derived* d) {
     set_error("index/offset types must be int32 or int64");
     return FBGEMM_B200_EINVAL;
   }
-  if (c->out_dtype != FBGEMM_B200_OUT_F32 && c->out_dtype != FBGEMM_B200_OUT_F16) {
-    set_error("output type must be fp32 or fp16");
+  if (c->out_dtype != FBGEMM_B200_OUT_F32 && c->out_dtype != FBGEMM_B200_OUT_F16 &&
+      c->out_dtype != FBGEMM_B200_OUT_BF16) {
+    set_error("output type must be fp32, fp16 or bf16");
+    return FBGEMM_B200_EINVAL;
+  }
+  if (c->no_bag && c->bit_rate != 8) {
+    // EmbeddingSpMDMNBit_ref: "no_bag is only supported for int4 to int4", a raw row copy
+    set_error("no_bag is provided for 8-bit rows with fp32/fp16/bf16 output");
     return FBGEMM_B200_EINVAL;
   }
   if (c->block_size <= 0 || c->block_size > (1 << 20)) {
@@ -164,7 +170,7 @@ int check_config(const fbgemm_b200_spmdm_config* c, Derived* d) {
     set_error("block_size too large for the sm_100a kernels (1024 columns at most)");
     return FBGEMM_B200_EINVAL;
   }
-  const int sb_bytes = c->bit_rate == 8 ? 8 : 4;
+  const int sb_bytes = (c->bit_rate == 8 && !c->scale_bias_first) ? 8 : 4;
   const int64_t in_stride = c->input_stride == -1 ? data_bytes + sb_bytes : c->input_stride;
   const int64_t out_stride = c->output_stride == -1 ? c->block_size : c->output_stride;
   if (in_stride < data_bytes + sb_bytes) {
@@ -217,6 +223,14 @@ int fbgemm_b200::build_lookup_params(
     set_error("has_weight set but weights is null");
     return FBGEMM_B200_EINVAL;
   }
+  if (cfg->no_bag && (output_size != index_size || cit || cfg->is_weight_positional)) {
+    set_error("no_bag: one index per output row, dense table, no positional weights");
+    return FBGEMM_B200_EINVAL;
+  }
+  if (cit && cfg->scale_bias_first) {
+    set_error("row-wise sparse lookup takes rows with scale, bias last");
+    return FBGEMM_B200_EINVAL;
+  }
   if (cit && (cfg->out_dtype != FBGEMM_B200_OUT_F32 || cfg->output_stride != -1 || cfg->input_stride != -1)) {
     // EmbeddingSpMDMRowWiseSparseKernelSignature: float* out, dense strides.
     set_error("row-wise sparse lookup takes fp32 output and default strides");
@@ -237,8 +251,14 @@ int fbgemm_b200::build_lookup_params(
   p.index_size = index_size;
   p.block_size = (int32_t)cfg->block_size;
   p.data_bytes = d.data_bytes;
-  p.sb_off = (d.data_bytes + 3) & ~3;
   p.row_bytes = d.data_bytes + d.sb_bytes;
+  p.data_row_off = cfg->scale_bias_first ? d.sb_bytes : 0;
+  p.sb_row_off = cfg->scale_bias_first ? 0 : d.data_bytes;
+  // In the shared-memory stage of the generic kernel the payload comes first
+  // and scale,bias sit at the next 4-byte boundary, unless whole rows are
+  // copied as they are (copy_width > 0 below).
+  p.data_off = 0;
+  p.sb_off = (d.data_bytes + 3) & ~3;
   p.pitch = p.sb_off + d.sb_bytes;
 
   // cp.async granule: the widest of 16/8/4 bytes that divides the table
@@ -253,6 +273,10 @@ int fbgemm_b200::build_lookup_params(
       }
     }
   }
+  if (p.copy_width > 0) {
+    p.data_off = p.data_row_off;
+    p.sb_off = p.sb_row_off;
+  }
   if (p.copy_width > 4) {
     p.pitch = (p.pitch + p.copy_width - 1) / p.copy_width * p.copy_width;
   }
@@ -260,11 +284,14 @@ int fbgemm_b200::build_lookup_params(
   uint32_t flags = 0;
   flags |= cfg->index_bytes == 8 ? kIdx64 : 0;
   flags |= cfg->out_dtype == FBGEMM_B200_OUT_F16 ? kOutHalf : 0;
+  flags |= cfg->out_dtype == FBGEMM_B200_OUT_BF16 ? kOutBf16 : 0;
+  flags |= cfg->scale_bias_first ? kSbFirst : 0;
+  flags |= cfg->no_bag ? kNoBag : 0;
   flags |= p.weights ? kWeighted : 0;
   flags |= (p.weights && cfg->is_weight_positional) ? kPositional : 0;
-  flags |= cfg->normalize_by_lengths ? kNormalize : 0;
+  flags |= (cfg->normalize_by_lengths && !cfg->no_bag) ? kNormalize : 0;
   flags |= cit ? kPruned : 0;
-  const size_t esize = cfg->out_dtype == FBGEMM_B200_OUT_F16 ? 2 : 4;
+  const size_t esize = cfg->out_dtype == FBGEMM_B200_OUT_F32 ? 4 : 2;
   bool out_aligned = (d.output_stride * esize) % 16 == 0;
   if (num_peers > 0) {
     if (!peer_out || num_peers > FBGEMM_B200_MAX_PEERS || bags_per_peer <= 0 ||
@@ -314,7 +341,9 @@ int fbgemm_b200::enqueue_lookup(
     return rc;
   }
   uint32_t flags = p.flags;
-  if (cfg->use_offsets) {
+  if (cfg->no_bag) {
+    p.offsets = nullptr;  // bag m is the single index m
+  } else if (cfg->use_offsets) {
     p.offsets = offsets_or_lengths;
     flags |= cfg->offset_bytes == 8 ? kOff64 : 0;
   } else {
@@ -465,7 +494,7 @@ int fbgemm_b200_spmdm_launch(
     return 0;
   }
   std::unique_lock<std::mutex> lock(ctx->mu, std::defer_lock);
-  if (cfg && !cfg->use_offsets) {
+  if (cfg && !cfg->use_offsets && !cfg->no_bag) {
     lock.lock();  // the scan scratch is shared by device-pointer calls
   }
   return enqueue_lookup(cfg, output_size, index_size, data_size, input, indices, offsets_or_lengths, weights, out,
@@ -525,7 +554,7 @@ int fbgemm_b200_multi_plan_create(
   std::vector<int> bit_rates((size_t)num_tables);
   for (int t = 0; t < num_tables; ++t) {
     const fbgemm_b200_table_call& c = calls[t];
-    if (!c.cfg.use_offsets) {
+    if (!c.cfg.use_offsets && !c.cfg.no_bag) {
       set_error("a plan takes offsets, not lengths");
       return FBGEMM_B200_EINVAL;
     }
@@ -539,7 +568,7 @@ int fbgemm_b200_multi_plan_create(
     if (rc) {
       return rc;
     }
-    params[(size_t)t].offsets = c.offsets;
+    params[(size_t)t].offsets = c.cfg.no_bag ? nullptr : c.offsets;
     params[(size_t)t].flags |= c.cfg.offset_bytes == 8 ? kOff64 : 0;
     bit_rates[(size_t)t] = c.cfg.bit_rate;
   }
@@ -724,6 +753,10 @@ int fbgemm_b200_spmdm_host_submit(
     set_error("negative size");
     return FBGEMM_B200_EINVAL;
   }
+  if (cfg->no_bag) {
+    set_error("no_bag is provided for device pointers only");
+    return FBGEMM_B200_EINVAL;
+  }
   DeviceGuard guard(ctx->device);
   Lane& L = ctx->lanes[lane_id];
   if (L.busy) {
@@ -812,7 +845,7 @@ int fbgemm_b200_spmdm_host_submit(
   const size_t off_at = up16(idx_bytes);
   const size_t w_at = off_at + up16(off_bytes);
   const size_t in_bytes = w_at + up16(n_w * sizeof(float));
-  const size_t esize = cfg->out_dtype == FBGEMM_B200_OUT_F16 ? 2 : 4;
+  const size_t esize = cfg->out_dtype == FBGEMM_B200_OUT_F32 ? 4 : 2;
   // The device copy of the output is dense in block_size-wide rows only when
   // the user's rows are; otherwise keep the user's pitch.
   const size_t out_pitch = (size_t)d.output_stride * esize;

@@ -67,12 +67,19 @@ fbgemm_b200_spmdm_config make_config(
     bool is_weight_positional,
     bool use_offsets,
     std::int64_t output_stride,
-    std::int64_t input_stride) {
+    std::int64_t input_stride,
+    bool scale_bias_last = true,
+    bool no_bag = false,
+    bool is_bf16_out = false) {
   fbgemm_b200_spmdm_config c{};
   c.bit_rate = bit_rate;
   c.index_bytes = index_bytes;
   c.offset_bytes = offset_bytes;
-  c.out_dtype = out_dt;
+  // A 16-bit OutType holds bf16 when is_bf16_out is set (convert_from_float_ref,
+  // src/RefImplementations.h:443-453); a float OutType ignores the flag.
+  c.out_dtype = (is_bf16_out && out_dt == FBGEMM_B200_OUT_F16) ? FBGEMM_B200_OUT_BF16 : out_dt;
+  c.scale_bias_first = !scale_bias_last;
+  c.no_bag = no_bag;
   c.block_size = block_size;
   c.output_stride = output_stride;
   c.input_stride = input_stride;
@@ -164,13 +171,13 @@ GenerateEmbeddingSpMDMWithStrides(
     bool is_bf16_out,
     bool is_bf16_in) {
   static_assert(std::is_same<InType, std::uint8_t>::value, "only fused 8-bit rows (InType = uint8_t)");
-  if (!scale_bias_last || no_bag || is_bf16_out || is_bf16_in) {
-    throw std::invalid_argument(
-        "fbgemm_b200: scale_bias_last=false, no_bag and bf16 are not provided by the sm_100a path");
+  if (is_bf16_in) {
+    throw std::invalid_argument("fbgemm_b200: is_bf16_in belongs to unquantized tables, which this path does not take");
   }
   const fbgemm_b200_spmdm_config cfg = make_config(
       8, sizeof(IndexType), sizeof(OffsetType), out_dtype<OutType>(), block_size, has_weight,
-      normalize_by_lengths, is_weight_positional, use_offsets, output_stride, input_stride);
+      normalize_by_lengths, is_weight_positional, use_offsets, output_stride, input_stride, scale_bias_last, no_bag,
+      is_bf16_out);
   return [cfg](
              std::int64_t output_size,
              std::int64_t index_size,
@@ -218,14 +225,14 @@ GenerateEmbeddingSpMDMNBitWithStrides(
   if (input_bit_rate != 2 && input_bit_rate != 4) {
     throw std::invalid_argument("fbgemm_b200: bit_rate must be 2 or 4");
   }
-  if (!scale_bias_last || no_bag || is_bf16_out ||
-      (output_bit_rate != -1 && output_bit_rate != (int)(8 * sizeof(OutType)))) {
-    throw std::invalid_argument(
-        "fbgemm_b200: scale_bias_last=false, no_bag, bf16 and N-bit output are not provided by the sm_100a path");
+  if (no_bag || (output_bit_rate != -1 && output_bit_rate != (int)(8 * sizeof(OutType)))) {
+    // the reference's N-bit no_bag is an int4 -> int4 row copy (src/RefImplementations.cc:1467-1485)
+    throw std::invalid_argument("fbgemm_b200: N-bit no_bag and N-bit output are not provided by the sm_100a path");
   }
   const fbgemm_b200_spmdm_config cfg = make_config(
       input_bit_rate, sizeof(IndexType), sizeof(OffsetType), out_dtype<OutType>(), block_size, has_weight,
-      normalize_by_lengths, is_weight_positional, use_offsets, output_stride, input_stride);
+      normalize_by_lengths, is_weight_positional, use_offsets, output_stride, input_stride, scale_bias_last, false,
+      is_bf16_out);
   return [cfg](
              std::int64_t output_size,
              std::int64_t index_size,

@@ -23,6 +23,9 @@ enum : uint32_t {
   kNormalize = 1u << 5,   // multiply the pooled row by 1/len
   kPruned = 1u << 6,      // indices go through compressed_indices_table
   kOutVec = 1u << 7,      // output rows allow vector stores
+  kSbFirst = 1u << 8,     // fp16 scale,bias at the start of the row; index -1 = pruned row
+  kOutBf16 = 1u << 9,     // bf16 output
+  kNoBag = 1u << 10,      // one index per output row, no offsets
 };
 
 // Everything one lookup launch needs; passed by value to the kernel.
@@ -41,6 +44,9 @@ struct SpmdmParams {
   int64_t index_size;         // indices
   int32_t block_size;         // D
   int32_t data_bytes;         // packed payload bytes per row
+  int32_t data_row_off;       // offset of the payload inside a table row (0, or 4 when scale,bias come first)
+  int32_t sb_row_off;         // offset of scale,bias inside a table row
+  int32_t data_off;           // offset of the payload inside a staged row
   int32_t sb_off;             // offset of scale,bias inside a staged row
   int32_t row_bytes;          // payload + scale,bias bytes actually read
   int32_t pitch;              // bytes between staged rows in shared memory

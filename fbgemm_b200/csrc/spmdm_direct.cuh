@@ -127,29 +127,35 @@ struct Vec<8> {
   }
 };
 
-// Raw scale,bias bits of one row: fp32 pair for 8-bit rows, fp16 pair else.
+// Raw scale,bias bits of one row: an fp32 pair for 8-bit rows with scale,bias
+// last, an fp16 pair otherwise (`half_sb`; always true for 4- and 2-bit rows).
 template <int BITS, int VEC>
 struct ScaleBias {
   uint32_t raw[BITS == 8 ? 2 : 1];
-  __device__ __forceinline__ void load(const uint8_t* p) {
+  __device__ __forceinline__ void load(const uint8_t* p, bool half_sb) {
     if constexpr (BITS != 8) {
       raw[0] = __ldg(reinterpret_cast<const uint32_t*>(p));
-    } else if constexpr (VEC >= 8) {
-      const uint2 v = __ldg(reinterpret_cast<const uint2*>(p));
-      raw[0] = v.x;
-      raw[1] = v.y;
     } else {
-      raw[0] = __ldg(reinterpret_cast<const uint32_t*>(p));
-      raw[1] = __ldg(reinterpret_cast<const uint32_t*>(p + 4));
+      if (half_sb) {
+        raw[0] = __ldg(reinterpret_cast<const uint32_t*>(p));
+        raw[1] = 0;
+      } else if constexpr (VEC >= 8) {
+        const uint2 v = __ldg(reinterpret_cast<const uint2*>(p));
+        raw[0] = v.x;
+        raw[1] = v.y;
+      } else {
+        raw[0] = __ldg(reinterpret_cast<const uint32_t*>(p));
+        raw[1] = __ldg(reinterpret_cast<const uint32_t*>(p + 4));
+      }
     }
   }
-  __device__ __forceinline__ void get(float& scale, float& bias) const {
-    if constexpr (BITS == 8) {
-      scale = __uint_as_float(raw[0]);
-      bias = __uint_as_float(raw[1]);
-    } else {
+  __device__ __forceinline__ void get(float& scale, float& bias, bool half_sb) const {
+    if (BITS != 8 || half_sb) {
       scale = __half2float(__ushort_as_half((unsigned short)(raw[0] & 0xffffu)));
       bias = __half2float(__ushort_as_half((unsigned short)(raw[0] >> 16)));
+    } else {
+      scale = __uint_as_float(raw[0]);
+      bias = __uint_as_float(raw[BITS == 8 ? 1 : 0]);
     }
   }
 };
@@ -202,7 +208,9 @@ __device__ __forceinline__ void fetch_rows(
       const int64_t pos = pos0 + u;
       const int64_t idx = load_int(p.indices, pos, p.flags & kIdx64);
       if ((unsigned long long)idx >= (unsigned long long)p.data_size) {
-        report(p.status, FBGEMM_B200_STATUS_BAD_INDEX, bag, pos, idx);
+        if (!((p.flags & (kSbFirst | kNoBag)) == kSbFirst && idx == -1)) {  // that layout's pruned row: skipped
+          report(p.status, FBGEMM_B200_STATUS_BAD_INDEX, bag, pos, idx);
+        }
       } else if (p.flags & kPruned) {
         const int32_t c = __ldg(p.cit + idx);  // -1: pruned row
         if (c >= 0) {
@@ -227,6 +235,7 @@ __device__ __forceinline__ void pool_step(
     uint32_t stride,
     unsigned gmask,
     int lane0,  // first lane of the group
+    bool half_sb,
     bool weighted,
     const uint32_t (&id_own)[(U + LPB - 1) / LPB],
     const float (&w_own)[(U + LPB - 1) / LPB],
@@ -247,13 +256,13 @@ __device__ __forceinline__ void pool_step(
     for (int ci = 0; ci < CPL; ++ci) {
       d[u][ci].load(row_address(chunk_base[ci], row, stride));
     }
-    sb[u].load(row_address(sb_base, row, stride));
+    sb[u].load(row_address(sb_base, row, stride), half_sb);
   }
   const u64 nm2 = pack2(-8388608.0f, -8388608.0f);
 #pragma unroll
   for (int u = 0; u < U; ++u) {
     float scale, bias;
-    sb[u].get(scale, bias);
+    sb[u].get(scale, bias, half_sb);
     if (weighted) {
       const float w = LPB == 1 ? w_own[u] : __shfl_sync(gmask, w_own[u / LPB], lane0 + (u % LPB));
       scale = __fmul_rn(w, scale);
@@ -275,6 +284,13 @@ __device__ __forceinline__ void pool_step(
   }
 }
 
+// fp32 -> fp16 (round to nearest even, cpu_float2half_rn) or bf16 the way the
+// reference does it: (bits + 0x8000) >> 16 (cpu_float2bfloat16,
+// include/fbgemm/FloatConversion.h:312-315).
+__device__ __forceinline__ uint16_t to_16bit(float v, bool bf16) {
+  return bf16 ? (uint16_t)((__float_as_uint(v) + 0x8000u) >> 16) : __half_as_ushort(__float2half_rn(v));
+}
+
 // Store CPC consecutive columns starting at col0 of output row `bag`.
 template <int CPC>
 __device__ __forceinline__ void store_columns(const SpmdmParams& p, int64_t bag, int col0, const u64* pairs) {
@@ -284,14 +300,14 @@ __device__ __forceinline__ void store_columns(const SpmdmParams& p, int64_t bag,
     unpack2(pairs[i], v[2 * i], v[2 * i + 1]);
   }
   const bool full = col0 + CPC <= p.block_size;
-  if (p.flags & kOutHalf) {
-    __half* o = reinterpret_cast<__half*>(output_row(p, bag, 2)) + col0;
+  if (p.flags & (kOutHalf | kOutBf16)) {
+    const bool bf16 = p.flags & kOutBf16;
+    uint16_t* o = reinterpret_cast<uint16_t*>(output_row(p, bag, 2)) + col0;
     if (full && (p.flags & kOutVec)) {
       uint32_t h[CPC / 2];
 #pragma unroll
       for (int i = 0; i < CPC / 2; ++i) {
-        const __half2 hh = __halves2half2(__float2half_rn(v[2 * i]), __float2half_rn(v[2 * i + 1]));
-        h[i] = *reinterpret_cast<const uint32_t*>(&hh);
+        h[i] = (uint32_t)to_16bit(v[2 * i], bf16) | ((uint32_t)to_16bit(v[2 * i + 1], bf16) << 16);
       }
       if constexpr (CPC == 4) {
         *reinterpret_cast<uint2*>(o) = make_uint2(h[0], h[1]);
@@ -305,7 +321,7 @@ __device__ __forceinline__ void store_columns(const SpmdmParams& p, int64_t bag,
 #pragma unroll
       for (int i = 0; i < CPC; ++i) {
         if (col0 + i < p.block_size) {
-          o[i] = __float2half_rn(v[i]);
+          o[i] = to_16bit(v[i], bf16);
         }
       }
     }
@@ -353,8 +369,9 @@ __device__ __forceinline__ void direct_block(const SpmdmParams& p, int64_t block
   const bool off64 = p.flags & kOff64;
   const bool weighted = p.flags & kWeighted;
 
-  const int64_t off_base = load_int(p.offsets, 0, off64);
-  if (block == 0 && threadIdx.x == 0) {
+  const bool no_bag = p.flags & kNoBag;
+  const int64_t off_base = no_bag ? 0 : load_int(p.offsets, 0, off64);
+  if (block == 0 && threadIdx.x == 0 && !no_bag) {
     // `return current == index_size` of the reference
     const int64_t total = load_int(p.offsets, p.output_size, off64) - off_base;
     if (total != p.index_size) {
@@ -365,8 +382,9 @@ __device__ __forceinline__ void direct_block(const SpmdmParams& p, int64_t block
   if (bag >= p.output_size) {
     return;
   }
-  const int64_t o0 = load_int(p.offsets, bag, off64);
-  const int64_t o1 = load_int(p.offsets, bag + 1, off64);
+  // no_bag: output row m is the single row indices[m]
+  const int64_t o0 = no_bag ? bag : load_int(p.offsets, bag, off64);
+  const int64_t o1 = no_bag ? bag + 1 : load_int(p.offsets, bag + 1, off64);
   const int64_t start = o0 - off_base;
   const int bag_len = (int)(o1 - o0);  // the reference narrows to 32 bits too
   int len = bag_len < 0 ? 0 : bag_len;
@@ -386,9 +404,10 @@ __device__ __forceinline__ void direct_block(const SpmdmParams& p, int64_t block
 #pragma unroll
   for (int ci = 0; ci < CPL; ++ci) {
     const int c = gl + ci * LPB;
-    chunk_base[ci] = p.table + (c < nchunks ? c * VEC : 0);
+    chunk_base[ci] = p.table + p.data_row_off + (c < nchunks ? c * VEC : 0);
   }
-  const uint8_t* sb_base = p.table + p.data_bytes;
+  const uint8_t* sb_base = p.table + p.sb_row_off;
+  const bool half_sb = BITS != 8 || (p.flags & kSbFirst);
   const uint32_t stride = (uint32_t)p.input_stride;
 
   u64 acc[CPL][PAIRS];
@@ -408,6 +427,7 @@ __device__ __forceinline__ void direct_block(const SpmdmParams& p, int64_t block
   const bool idx64 = p.flags & kIdx64;
   const bool pruned = p.flags & kPruned;
   const bool positional = p.flags & kPositional;
+  const bool minus_one_skips = (p.flags & (kSbFirst | kNoBag)) == kSbFirst;  // that layout's pruned row
   // loads only: raw index and weight of this lane's rows of step s
   auto issue = [&](int s, long long (&raw)[OWN], float (&w)[OWN]) {
 #pragma unroll
@@ -433,7 +453,9 @@ __device__ __forceinline__ void direct_block(const SpmdmParams& p, int64_t block
       id[j] = kSkipRow;
       if (u < UMAX && s < nfull) {
         if ((unsigned long long)raw[j] >= (unsigned long long)p.data_size) {
-          report(p.status, FBGEMM_B200_STATUS_BAD_INDEX, bag, start + (int64_t)s * UMAX + u, raw[j]);
+          if (!(minus_one_skips && raw[j] == -1)) {
+            report(p.status, FBGEMM_B200_STATUS_BAD_INDEX, bag, start + (int64_t)s * UMAX + u, raw[j]);
+          }
         } else if (pruned) {
           id[j] = (uint32_t)__ldg(p.cit + raw[j]);
         } else {
@@ -464,7 +486,7 @@ __device__ __forceinline__ void direct_block(const SpmdmParams& p, int64_t block
         }
       }
     }
-    pool_step<BITS, VEC, LPB, CPL, UMAX>(chunk_base, sb_base, stride, gmask, lane0, weighted, id_cur, w_cur, acc);
+    pool_step<BITS, VEC, LPB, CPL, UMAX>(chunk_base, sb_base, stride, gmask, lane0, half_sb, weighted, id_cur, w_cur, acc);
 #pragma unroll
     for (int j = 0; j < OWN; ++j) {
       id_cur[j] = id_1[j];
@@ -480,7 +502,7 @@ __device__ __forceinline__ void direct_block(const SpmdmParams& p, int64_t block
       uint32_t id8[(8 + LPB - 1) / LPB];
       float w8[(8 + LPB - 1) / LPB];
       fetch_rows<LPB, 8>(p, gl, bag, start + r, r, 8, id8, w8);
-      pool_step<BITS, VEC, LPB, CPL, 8>(chunk_base, sb_base, stride, gmask, lane0, weighted, id8, w8, acc);
+      pool_step<BITS, VEC, LPB, CPL, 8>(chunk_base, sb_base, stride, gmask, lane0, half_sb, weighted, id8, w8, acc);
       r += 8;
     }
   }
@@ -489,7 +511,7 @@ __device__ __forceinline__ void direct_block(const SpmdmParams& p, int64_t block
       uint32_t id4[(4 + LPB - 1) / LPB];
       float w4[(4 + LPB - 1) / LPB];
       fetch_rows<LPB, 4>(p, gl, bag, start + r, r, 4, id4, w4);
-      pool_step<BITS, VEC, LPB, CPL, 4>(chunk_base, sb_base, stride, gmask, lane0, weighted, id4, w4, acc);
+      pool_step<BITS, VEC, LPB, CPL, 4>(chunk_base, sb_base, stride, gmask, lane0, half_sb, weighted, id4, w4, acc);
       r += 4;
     }
   }
@@ -497,14 +519,14 @@ __device__ __forceinline__ void direct_block(const SpmdmParams& p, int64_t block
     uint32_t id2[(2 + LPB - 1) / LPB];
     float w2[(2 + LPB - 1) / LPB];
     fetch_rows<LPB, 2>(p, gl, bag, start + r, r, 2, id2, w2);
-    pool_step<BITS, VEC, LPB, CPL, 2>(chunk_base, sb_base, stride, gmask, lane0, weighted, id2, w2, acc);
+    pool_step<BITS, VEC, LPB, CPL, 2>(chunk_base, sb_base, stride, gmask, lane0, half_sb, weighted, id2, w2, acc);
     r += 2;
   }
   if (len - r >= 1) {
     uint32_t id1[1];
     float w1[1];
     fetch_rows<LPB, 1>(p, gl, bag, start + r, r, 1, id1, w1);
-    pool_step<BITS, VEC, LPB, CPL, 1>(chunk_base, sb_base, stride, gmask, lane0, weighted, id1, w1, acc);
+    pool_step<BITS, VEC, LPB, CPL, 1>(chunk_base, sb_base, stride, gmask, lane0, half_sb, weighted, id1, w1, acc);
   }
 
   if ((p.flags & kNormalize) && bag_len != 0) {

@@ -98,7 +98,8 @@ __device__ __forceinline__ void stage_rows(
 }
 
 // Rows whose address, pitch or width is not a multiple of 4 bytes: plain byte
-// loads.  The payload lands at [0, data_bytes), scale,bias at sb_off.
+// loads.  The payload lands at [data_off, data_off + data_bytes), scale,bias
+// at sb_off, wherever they sit in the table row.
 __device__ __forceinline__ void stage_rows_bytewise(
     const SpmdmParams& p,
     uint8_t* s_rows,
@@ -112,7 +113,8 @@ __device__ __forceinline__ void stage_rows_bytewise(
     const int b = k - row * p.row_bytes;
     const long long off = s_off[row];
     if (off >= 0) {
-      const int dst = b < p.data_bytes ? b : p.sb_off + (b - p.data_bytes);
+      const bool payload = b >= p.data_row_off && b < p.data_row_off + p.data_bytes;
+      const int dst = payload ? p.data_off + (b - p.data_row_off) : p.sb_off + (b - p.sb_row_off);
       s_rows[row * p.pitch + dst] = __ldg(p.table + off + b);
     }
   }
@@ -174,6 +176,12 @@ __device__ __forceinline__ void accumulate(float* acc, uint32_t x, float scale, 
   }
 }
 
+// fp32 -> fp16 (round to nearest even) or bf16 as the reference rounds it,
+// (bits + 0x8000) >> 16 (include/fbgemm/FloatConversion.h:312-315).
+__device__ __forceinline__ uint16_t to_16bit(float v, bool bf16) {
+  return bf16 ? (uint16_t)((__float_as_uint(v) + 0x8000u) >> 16) : __half_as_ushort(__float2half_rn(v));
+}
+
 template <int COLS>
 __device__ __forceinline__ void store_chunk(
     const SpmdmParams& p,
@@ -181,14 +189,14 @@ __device__ __forceinline__ void store_chunk(
     int col0,
     const float* v) {
   const bool full = col0 + COLS <= p.block_size;
-  if (p.flags & kOutHalf) {
-    __half* o = reinterpret_cast<__half*>(output_row(p, bag, 2)) + col0;
+  if (p.flags & (kOutHalf | kOutBf16)) {
+    const bool bf16 = p.flags & kOutBf16;
+    uint16_t* o = reinterpret_cast<uint16_t*>(output_row(p, bag, 2)) + col0;
     if (full && (p.flags & kOutVec)) {
       uint32_t w[COLS / 2];
 #pragma unroll
       for (int i = 0; i < COLS / 2; ++i) {
-        const __half2 h = __halves2half2(__float2half_rn(v[2 * i]), __float2half_rn(v[2 * i + 1]));
-        w[i] = *reinterpret_cast<const uint32_t*>(&h);
+        w[i] = (uint32_t)to_16bit(v[2 * i], bf16) | ((uint32_t)to_16bit(v[2 * i + 1], bf16) << 16);
       }
       if constexpr (COLS == 4) {
         *reinterpret_cast<uint2*>(o) = make_uint2(w[0], w[1]);
@@ -202,7 +210,7 @@ __device__ __forceinline__ void store_chunk(
 #pragma unroll
       for (int i = 0; i < COLS; ++i) {
         if (col0 + i < p.block_size) {
-          o[i] = __float2half_rn(v[i]);
+          o[i] = to_16bit(v[i], bf16);
         }
       }
     }
@@ -243,8 +251,10 @@ spmdm_kernel(const __grid_constant__ SpmdmParams p) {
   const bool positional = p.flags & kPositional;
   const bool pruned = p.flags & kPruned;
 
-  const int64_t off_base = load_int(p.offsets, 0, off64);
-  if (blockIdx.x == 0 && threadIdx.x == 0) {
+  const bool no_bag = p.flags & kNoBag;
+  const bool half_sb = BITS != 8 || (p.flags & kSbFirst);
+  const int64_t off_base = no_bag ? 0 : load_int(p.offsets, 0, off64);
+  if (blockIdx.x == 0 && threadIdx.x == 0 && !no_bag) {
     // `return current == index_size` of the reference
     const int64_t total = load_int(p.offsets, p.output_size, off64) - off_base;
     if (total != p.index_size) {
@@ -257,8 +267,9 @@ spmdm_kernel(const __grid_constant__ SpmdmParams p) {
     return;
   }
 
-  const int64_t o0 = load_int(p.offsets, bag, off64);
-  const int64_t o1 = load_int(p.offsets, bag + 1, off64);
+  // no_bag: output row m is the single row indices[m]
+  const int64_t o0 = no_bag ? bag : load_int(p.offsets, bag, off64);
+  const int64_t o1 = no_bag ? bag + 1 : load_int(p.offsets, bag + 1, off64);
   const int64_t start = o0 - off_base;
   const int bag_len = (int)(o1 - o0);  // the reference narrows to 32 bits too
   int len = bag_len < 0 ? 0 : bag_len;
@@ -295,7 +306,9 @@ spmdm_kernel(const __grid_constant__ SpmdmParams p) {
       int64_t idx = load_int(p.indices, pos, idx64);
       long long off = -1;
       if (idx < 0 || idx >= p.data_size) {
-        report(p.status, FBGEMM_B200_STATUS_BAD_INDEX, bag, pos, idx);
+        if (!((p.flags & (kSbFirst | kNoBag)) == kSbFirst && idx == -1)) {  // that layout's pruned row: skipped
+          report(p.status, FBGEMM_B200_STATUS_BAD_INDEX, bag, pos, idx);
+        }
       } else {
         if (pruned) {
           idx = __ldg(p.cit + idx);  // -1: pruned row, contributes nothing
@@ -331,7 +344,7 @@ spmdm_kernel(const __grid_constant__ SpmdmParams p) {
       }
       const uint8_t* srow = s_rows + r * p.pitch;
       float scale, bias;
-      if constexpr (BITS == 8) {
+      if (!half_sb) {
         scale = *reinterpret_cast<const float*>(srow + p.sb_off);
         bias = *reinterpret_cast<const float*>(srow + p.sb_off + 4);
       } else {
@@ -348,7 +361,7 @@ spmdm_kernel(const __grid_constant__ SpmdmParams p) {
       for (int ci = 0; ci < CPL; ++ci) {
         const int c = gl + ci * LPB;
         if (c < nchunks) {
-          const uint32_t x = *reinterpret_cast<const uint32_t*>(srow + 4 * c);
+          const uint32_t x = *reinterpret_cast<const uint32_t*>(srow + p.data_off + 4 * c);
           accumulate<BITS>(acc[ci], x, scale, bias);
         }
       }
@@ -430,7 +443,9 @@ int max_chunks_per_bag(int bit_rate) {
 // when the rows do not allow 4- or 8-byte vector loads.
 static const direct::Variant* pick_direct(const SpmdmParams& p, int bit_rate) {
   const uintptr_t base = reinterpret_cast<uintptr_t>(p.table);
-  auto divides = [&](int v) { return base % v == 0 && p.input_stride % v == 0 && p.data_bytes % v == 0; };
+  auto divides = [&](int v) {
+    return base % 4 == 0 && (base + p.data_row_off) % v == 0 && p.input_stride % v == 0 && p.data_bytes % v == 0;
+  };
   // Row ids travel between lanes as 32-bit values and skipped rows read row 0.
   if (!divides(4) || p.data_bytes == 0 || p.data_size == 0 || p.data_size > 0xfffffffeLL ||
       p.input_stride > 0xffffffffLL) {

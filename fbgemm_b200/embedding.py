@@ -92,7 +92,9 @@ def _out_code(out_dtype) -> int:
         return OUT_F32
     if name in ("float16", "uint16"):
         return OUT_F16
-    raise ValueError(f"OutType must be float32 or float16, got {out_dtype}")
+    if name == "bfloat16":
+        return 2
+    raise ValueError(f"OutType must be float32, float16 or bfloat16, got {out_dtype}")
 
 
 def _is_tensor(x) -> bool:
@@ -257,12 +259,18 @@ def status_read(slot: int = 0, device: int | None = None, stream=None):
 
 
 def _config(bit_rate, block_size, has_weight, normalize_by_lengths, is_weight_positional, use_offsets,
-            output_stride, input_stride, index_dtype, offset_dtype, out_dtype) -> SpmdmConfig:
+            output_stride, input_stride, index_dtype, offset_dtype, out_dtype, scale_bias_last=True, no_bag=False,
+            is_bf16_out=False) -> SpmdmConfig:
+    out_code = _out_code(out_dtype)
+    if is_bf16_out and out_code == 1:
+        out_code = 2  # a 16-bit OutType holds bf16 when is_bf16_out is set
     return SpmdmConfig(
+        scale_bias_first=int(not scale_bias_last),
+        no_bag=int(bool(no_bag)),
         bit_rate=bit_rate,
         index_bytes=_np_itemsize(index_dtype),
         offset_bytes=_np_itemsize(offset_dtype),
-        out_dtype=_out_code(out_dtype),
+        out_dtype=out_code,
         block_size=block_size,
         output_stride=output_stride,
         input_stride=input_stride,
@@ -273,9 +281,9 @@ def _config(bit_rate, block_size, has_weight, normalize_by_lengths, is_weight_po
     )
 
 
-def _reject(scale_bias_last=True, no_bag=False, is_bf16_out=False, is_bf16_in=False):
-    if not scale_bias_last or no_bag or is_bf16_out or is_bf16_in:
-        raise ValueError("scale_bias_last=False, no_bag and bf16 are not provided by the sm_100a path")
+def _reject(no_bag=False, is_bf16_in=False):
+    if no_bag or is_bf16_in:
+        raise ValueError("N-bit no_bag and unquantized (bf16) tables are not provided by the sm_100a path")
 
 
 def GenerateEmbeddingSpMDM(block_size, has_weight, normalize_by_lengths, prefetch=16,
@@ -295,9 +303,10 @@ def GenerateEmbeddingSpMDMWithStrides(block_size, has_weight, normalize_by_lengt
                                       out_dtype=np.float32) -> SpmdmKernel:
     """fbgemm::GenerateEmbeddingSpMDMWithStrides<uint8_t, ...>
     (include/fbgemm/FbgemmEmbedding.h:94-117)."""
-    _reject(scale_bias_last, no_bag, is_bf16_out, is_bf16_in)
+    _reject(False, is_bf16_in)
     return SpmdmKernel(_config(8, block_size, has_weight, normalize_by_lengths, is_weight_positional, use_offsets,
-                               output_stride, input_stride, index_dtype, offset_dtype, out_dtype), False)
+                               output_stride, input_stride, index_dtype, offset_dtype, out_dtype, scale_bias_last,
+                               no_bag, is_bf16_out), False)
 
 
 def GenerateEmbeddingSpMDMNBit(bit_rate, block_size, has_weight, normalize_by_lengths, prefetch=16,
@@ -320,11 +329,12 @@ def GenerateEmbeddingSpMDMNBitWithStrides(input_bit_rate, block_size, has_weight
     (include/fbgemm/FbgemmEmbedding.h:149-174)."""
     if input_bit_rate not in (2, 4):
         raise ValueError("bit_rate must be 2 or 4")  # src/EmbeddingSpMDMNBit.cc:999-1001
-    _reject(scale_bias_last, no_bag, is_bf16_out)
+    _reject(no_bag)  # the reference's N-bit no_bag is an int4 -> int4 row copy
     if output_bit_rate not in (-1, 8 * (2 if _out_code(out_dtype) == OUT_F16 else 4)):
         raise ValueError("N-bit output is not provided by the sm_100a path")
     return SpmdmKernel(_config(input_bit_rate, block_size, has_weight, normalize_by_lengths, is_weight_positional,
-                               use_offsets, output_stride, input_stride, index_dtype, offset_dtype, out_dtype), False)
+                               use_offsets, output_stride, input_stride, index_dtype, offset_dtype, out_dtype,
+                               scale_bias_last, False, is_bf16_out), False)
 
 
 def GenerateEmbeddingSpMDMRowWiseSparse(block_size, has_weight, normalize_by_lengths, prefetch=16,

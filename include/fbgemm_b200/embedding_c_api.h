@@ -43,6 +43,9 @@ extern "C" {
 /* Output element types (OutType of the reference generators). */
 #define FBGEMM_B200_OUT_F32 0
 #define FBGEMM_B200_OUT_F16 1
+#define FBGEMM_B200_OUT_BF16 2 /* is_bf16_out = true with a 16-bit OutType:
+                                  (bits + 0x8000) >> 16, as cpu_float2bfloat16,
+                                  include/fbgemm/FloatConversion.h:312-315 */
 
 /* Why a lookup returned 0 (first word of the status record). */
 #define FBGEMM_B200_STATUS_OK 0
@@ -66,7 +69,8 @@ typedef struct fbgemm_b200_ctx fbgemm_b200_ctx;
  */
 typedef struct fbgemm_b200_spmdm_config {
   int32_t bit_rate;     /* 8: rows of uint8 + fp32 scale,bias; 4 or 2: packed
-                           little-endian within the byte + fp16 scale,bias   */
+                           little-endian within the byte + fp16 scale,bias
+                           (see scale_bias_first for the other row layout)   */
   int32_t index_bytes;  /* sizeof(IndexType): 4 or 8                         */
   int32_t offset_bytes; /* sizeof(OffsetType): 4 or 8                        */
   int32_t out_dtype;    /* FBGEMM_B200_OUT_F32 / _F16                        */
@@ -77,6 +81,17 @@ typedef struct fbgemm_b200_spmdm_config {
   int32_t normalize_by_lengths;
   int32_t is_weight_positional;
   int32_t use_offsets;  /* 1: offsets[output_size+1]; 0: lengths[output_size]*/
+  int32_t scale_bias_first; /* 1 = the generators' scale_bias_last = false, the
+                           row layout of table-batched embeddings: fp16 scale
+                           and bias (4 bytes) at the START of the row, for
+                           8-bit rows too, and an index of -1 is a pruned row
+                           that is skipped (src/RefImplementations.cc:1223-1229,
+                           :1299-1303, :1316-1324).  0 = scale, bias last.   */
+  int32_t no_bag;       /* 1 = the generators' no_bag = true: output row m is
+                           the dequantized row indices[m] (times weights[m]),
+                           output_size rows, no offsets, no normalisation
+                           (src/RefImplementations.cc:1235-1288); 8-bit rows,
+                           fp32 / fp16 / bf16 output                         */
 } fbgemm_b200_spmdm_config;
 
 /* ---- context ----------------------------------------------------------- */

@@ -95,6 +95,36 @@ class _Lookups:
             ok = self._fn(self.prefix + "_embedding_spmdm", [_int] + _LOOKUP_ARGS)(bit_rate, *common)
         return bool(ok), out
 
+    def spmdm_ex(self, bit_rate, block_size, data_size, table, indices, offsets_or_lengths=None,
+                 weights=None, normalize_by_lengths=False, out_kind="f32",
+                 is_weight_positional=False, use_offsets=True, output_stride=-1,
+                 input_stride=-1, scale_bias_last=True, no_bag=False, output_size=None,
+                 index_size=None):
+        """The lookup with every generator option: ``out_kind`` "f32", "f16" or
+        "bf16" (16-bit results come back as uint16 bit patterns),
+        ``scale_bias_last=False`` for rows with fp16 scale, bias first and -1
+        as a pruned index, ``no_bag`` for one output row per index."""
+        indices = np.ascontiguousarray(indices)
+        if index_size is None:
+            index_size = len(indices)
+        if no_bag:
+            offsets_or_lengths = np.zeros(1, dtype=indices.dtype)
+            if output_size is None:
+                output_size = index_size
+        offsets_or_lengths = np.ascontiguousarray(offsets_or_lengths)
+        if output_size is None:
+            output_size = len(offsets_or_lengths) - (1 if use_offsets else 0)
+        ostride = block_size if output_stride == -1 else output_stride
+        kind = {"f32": 0, "f16": 1, "bf16": 2}[out_kind]
+        out = np.zeros(max(output_size, 1) * ostride, dtype=np.float32 if kind == 0 else np.uint16)
+        f = self._fn(self.prefix + "_embedding_spmdm_ex", [_int] + _LOOKUP_ARGS + [_int, _int])
+        ok = f(bit_rate, block_size, output_size, index_size, data_size, _ptr(table),
+               _ptr(indices), indices.dtype.itemsize, _ptr(offsets_or_lengths),
+               offsets_or_lengths.dtype.itemsize, _ptr(weights), int(normalize_by_lengths),
+               _ptr(out), kind, int(is_weight_positional), int(use_offsets), output_stride,
+               input_stride, int(scale_bias_last), int(no_bag))
+        return bool(ok), out
+
     def spmdm_rowwise_sparse(self, bit_rate, block_size, uncompressed_data_size, table,
                              indices, compressed_indices_table, offsets_or_lengths,
                              weights=None, normalize_by_lengths=False,

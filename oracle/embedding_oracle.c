@@ -309,6 +309,138 @@ done:
 }
 
 /* ------------------------------------------------------------------------- */
+/* The same two lookups with the generators' remaining options:               */
+/*  - scale_bias_last = 0: the row layout of table-batched embeddings - fp16  */
+/*    scale and bias at the START of the row (for 8-bit rows too), payload    */
+/*    after them, and an index of -1 is a pruned row: skipped, but it still   */
+/*    consumes its index / weight slot (RefImplementations.cc:1223-1229,      */
+/*    :1299-1303, :1316-1333 for 8-bit; :1496-1501, :1506-1523 for N-bit);    */
+/*  - out_kind 2: bf16 output, (bits + 0x8000) >> 16 (cpu_float2bfloat16,     */
+/*    include/fbgemm/FloatConversion.h:312-315), with 0 = fp32, 1 = fp16;     */
+/*  - no_bag = 1 (8-bit rows only): output row m is the dequantized row       */
+/*    indices[m] times weights[m]; no offsets, no normalisation, and no -1    */
+/*    skipping (:1235-1288).                                                  */
+/* ------------------------------------------------------------------------- */
+static inline void store_out_kind(void* out, int64_t i, float v, int out_kind) {
+  if (out_kind == 2) {
+    uint32_t b;
+    memcpy(&b, &v, sizeof(b));
+    ((uint16_t*)out)[i] = (uint16_t)((b + (1u << 15)) >> 16);
+  } else {
+    store_out(out, i, v, out_kind == 1);
+  }
+}
+
+ORACLE_API int oracle_embedding_spmdm_ex(
+    int bit_rate, /* 8, 4 or 2 */
+    int64_t block_size,
+    int64_t output_size,
+    int64_t index_size,
+    int64_t data_size,
+    const uint8_t* input,
+    const void* indices,
+    int index_bytes,
+    const void* offsets_or_lengths,
+    int offset_bytes,
+    const float* weights,
+    int normalize_by_lengths,
+    void* out,
+    int out_kind,
+    int is_weight_positional,
+    int use_offsets,
+    int64_t output_stride,
+    int64_t input_stride,
+    int scale_bias_last,
+    int no_bag) {
+  if (bit_rate != 8 && bit_rate != 4 && bit_rate != 2) {
+    return 0;
+  }
+  const int epb = 8 / bit_rate;
+  const int64_t data_bytes = (block_size + epb - 1) / epb;
+  const int half_sb = bit_rate != 8 || !scale_bias_last;
+  const int64_t sb_bytes = half_sb ? 4 : 8;
+  const int64_t data_at = scale_bias_last ? 0 : sb_bytes;
+  const int64_t sb_at = scale_bias_last ? data_bytes : 0;
+  const unsigned mask = (1u << bit_rate) - 1u;
+  if (output_stride == -1) {
+    output_stride = block_size;
+  }
+  if (input_stride == -1) {
+    input_stride = data_bytes + sb_bytes;
+  }
+  if (no_bag && bit_rate != 8) {
+    return 0; /* N-bit no_bag is an int4 -> int4 row copy, not restated here */
+  }
+  float* buf = (float*)malloc(sizeof(float) * (size_t)(block_size > 0 ? block_size : 1));
+  int64_t current = 0;
+  int64_t out_base = 0;
+  int ok = 1;
+  for (int64_t m = 0; m < output_size; ++m) {
+    memset(buf, 0, sizeof(float) * (size_t)block_size);
+    int len = 1;
+    if (!no_bag) {
+      len = use_offsets
+          ? (int)(load_int(offsets_or_lengths, m + 1, offset_bytes) - load_int(offsets_or_lengths, m, offset_bytes))
+          : (int)load_int(offsets_or_lengths, m, offset_bytes);
+      if (current + len > index_size) {
+        ok = 0;
+        goto done;
+      }
+    }
+    for (int i = 0; i < len; ++i, ++current) {
+      const int64_t idx = load_int(indices, current, index_bytes);
+      if (!no_bag && !scale_bias_last && idx == -1) {
+        continue; /* pruned row of a table-batched embedding */
+      }
+      if (idx < 0 || idx >= data_size) {
+        ok = 0;
+        goto done;
+      }
+      const uint8_t* row = input + input_stride * idx;
+      float s, b;
+      if (half_sb) {
+        uint16_t sb[2];
+        memcpy(sb, row + sb_at, sizeof(sb));
+        s = oracle_half_to_float(sb[0]);
+        b = oracle_half_to_float(sb[1]);
+      } else {
+        float sb[2];
+        memcpy(sb, row + sb_at, sizeof(sb));
+        s = sb[0];
+        b = sb[1];
+      }
+      float weight = 1.0f;
+      if (weights) {
+        weight = weights[no_bag ? m : (is_weight_positional ? i : current)];
+      }
+      const float scale = weight * s;
+      const float bias = weight * b;
+      for (int64_t j = 0; j < block_size; ++j) {
+        unsigned q = row[data_at + j / epb];
+        q >>= (unsigned)(j % epb) * (unsigned)bit_rate;
+        q &= mask;
+        const float t = buf[j] + bias;
+        buf[j] = fmaf(scale, (float)q, t);
+      }
+    }
+    if (!no_bag && normalize_by_lengths && len) {
+      const float inv = 1.f / (float)len;
+      for (int64_t j = 0; j < block_size; ++j) {
+        buf[j] *= inv;
+      }
+    }
+    for (int64_t j = 0; j < block_size; ++j) {
+      store_out_kind(out, out_base + j, buf[j], out_kind);
+    }
+    out_base += output_stride;
+  }
+  ok = no_bag ? 1 : (current == index_size);
+done:
+  free(buf);
+  return ok;
+}
+
+/* ------------------------------------------------------------------------- */
 /* Pruned (row-wise sparse) pooled lookup: indices address an uncompressed    */
 /* row space and go through compressed_indices_table; -1 there means the row  */
 /* was pruned: it contributes nothing but still consumes its index/weight     */

@@ -18,6 +18,7 @@
  */
 #include <cstdint>
 #include <functional>
+#include <type_traits>
 #include <vector>
 
 #include "fbgemm/FbgemmEmbedding.h"
@@ -127,6 +128,59 @@ int ref_embedding_spmdm_nbit(
         normalize_by_lengths != 0, static_cast<float*>(out),
         is_weight_positional != 0, use_offsets != 0, output_stride,
         input_stride);
+  });
+}
+
+// The same two reference functions with their remaining arguments exposed:
+// scale_bias_last, no_bag (8-bit only) and is_bf16_out.  out_kind: 0 = float,
+// 1 = fp16, 2 = bf16 (OutType uint16_t in both 16-bit cases).
+int ref_embedding_spmdm_ex(
+    int bit_rate,
+    std::int64_t block_size,
+    std::int64_t output_size,
+    std::int64_t index_size,
+    std::int64_t data_size,
+    const std::uint8_t* input,
+    const void* indices,
+    int index_bytes,
+    const void* offsets_or_lengths,
+    int offset_bytes,
+    const float* weights,
+    int normalize_by_lengths,
+    void* out,
+    int out_kind,
+    int is_weight_positional,
+    int use_offsets,
+    std::int64_t output_stride,
+    std::int64_t input_stride,
+    int scale_bias_last,
+    int no_bag) {
+  return dispatch_idx_off(index_bytes, offset_bytes, [&](auto i, auto o) {
+    using I = decltype(i);
+    using O = decltype(o);
+    auto run = [&](auto* typed_out) {
+      using Out = std::remove_pointer_t<decltype(typed_out)>;
+      if (bit_rate == 8) {
+        return (int)fbgemm::EmbeddingSpMDM_ref<std::uint8_t, I, O, Out>(
+            block_size, output_size, index_size, data_size, input,
+            static_cast<const I*>(indices),
+            static_cast<const O*>(offsets_or_lengths), weights,
+            normalize_by_lengths != 0, typed_out, is_weight_positional != 0,
+            use_offsets != 0, output_stride, input_stride,
+            scale_bias_last != 0, no_bag != 0, out_kind == 2, false);
+      }
+      return (int)fbgemm::EmbeddingSpMDMNBit_ref<I, O, Out>(
+          bit_rate, block_size, output_size, index_size, data_size, input,
+          static_cast<const I*>(indices),
+          static_cast<const O*>(offsets_or_lengths), weights,
+          normalize_by_lengths != 0, typed_out, is_weight_positional != 0,
+          use_offsets != 0, output_stride, input_stride, scale_bias_last != 0,
+          out_kind == 2, no_bag != 0, -1);
+    };
+    if (out_kind == 0) {
+      return run(static_cast<float*>(out));
+    }
+    return run(static_cast<std::uint16_t*>(out));
   });
 }
 

@@ -169,9 +169,9 @@ int main() {
   }
   CHECK(threw);
   threw = false;
-  try {
-    fbgemm::GenerateEmbeddingSpMDMWithStrides<uint8_t, int64_t, int64_t, float>(64, false, false, 16, false, true, -1, -1,
-                                                                                /*scale_bias_last=*/false);
+  try {  // the reference's N-bit no_bag is an int4 -> int4 row copy
+    fbgemm::GenerateEmbeddingSpMDMNBitWithStrides<int64_t, int64_t, float>(4, 64, false, false, 16, false, true, -1, -1,
+                                                                           true, false, /*no_bag=*/true);
   } catch (const std::invalid_argument&) {
     threw = true;
   }

@@ -1,0 +1,89 @@
+"""Generates tests/golden/lookup_ex_golden.npz from the REFERENCE's own code:
+the lookups with the generators' remaining options - rows with fp16 scale,
+bias FIRST and -1 as a pruned index (scale_bias_last = false, the layout of
+table-batched embeddings), bf16 output, padded rows, and no_bag.
+
+    python tests/golden/make_golden_ex.py
+
+Outputs come from fbgemm::EmbeddingSpMDM_ref / EmbeddingSpMDMNBit_ref compiled
+from the reference tree into oracle/_ref/libfbgemm_ref.so (oracle/Makefile).
+The fixture pins the CPU oracle (tests/test_oracle.py) and the CUDA kernels
+(tests/test_golden_gpu.py); it travels with the repository, the reference
+tree does not.
+"""
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+from helpers import lengths_indices_weights, random_fused_table  # noqa: E402
+from oracle import checker  # noqa: E402
+
+KINDS = ("f32", "f16", "bf16")
+
+
+def main():
+    if not os.path.exists(checker.REF_SO):
+        checker.build(("ref",))
+    ref = checker.Reference()
+    assert ref.available
+    rng = np.random.default_rng(20260202)
+    out = {}
+    n = 0
+    # (bit_rate, batch, rows, dim, avg_len, row stride or None)
+    shapes = [(8, 9, 300, 128, 14, None), (8, 6, 200, 40, 8, 48), (4, 10, 400, 64, 20, None), (4, 5, 150, 86, 7, 48),
+              (2, 8, 300, 128, 18, None), (2, 4, 90, 36, 6, 16)]
+    for bit_rate, batch, rows, dim, avg_len, stride in shapes:
+        for variant in range(3):
+            sb_last = variant == 2            # two cases of the new layout, one of the old with bf16 output
+            kind = KINDS[(variant + 2) % 3] if not sb_last else "bf16"
+            weighted = variant != 1
+            normalize = variant == 1
+            idt = (np.int32, np.int64)[variant % 2]
+            table = random_fused_table(rng, rows, dim, bit_rate, None if sb_last else stride, not sb_last)
+            _, offsets, indices, weights, cnt = lengths_indices_weights(rng, batch, rows, avg_len, idt, idt)
+            if not sb_last:
+                indices[rng.integers(0, cnt, max(1, cnt // 5))] = -1   # pruned rows
+            ok, res = ref.spmdm_ex(bit_rate, dim, rows, table, indices, offsets, weights if weighted else None,
+                                   normalize, kind, False, True, -1, table.shape[1], sb_last, False)
+            assert ok
+            k = f"ex{n}_"
+            out[k + "meta"] = np.array([bit_rate, batch, rows, dim, int(weighted), int(normalize), int(sb_last), 0,
+                                        KINDS.index(kind)], dtype=np.int64)
+            out[k + "table"] = table
+            out[k + "indices"] = indices
+            out[k + "offsets"] = offsets
+            out[k + "weights"] = weights
+            out[k + "out"] = res[:batch * dim]
+            n += 1
+    # no_bag, 8-bit rows, both layouts
+    for sb_last, kind, weighted, rows, dim, count in [(True, "f32", False, 120, 64, 33), (False, "f16", True, 80, 40, 21),
+                                                      (True, "bf16", True, 60, 128, 17)]:
+        table = random_fused_table(rng, rows, dim, 8, None, not sb_last)
+        indices = rng.integers(0, rows, count).astype(np.int64)
+        weights = rng.standard_normal(count).astype(np.float32)
+        ok, res = ref.spmdm_ex(8, dim, rows, table, indices, None, weights if weighted else None, True, kind, False, True,
+                               -1, -1, sb_last, True)
+        assert ok
+        k = f"ex{n}_"
+        out[k + "meta"] = np.array([8, count, rows, dim, int(weighted), 1, int(sb_last), 1, KINDS.index(kind)],
+                                   dtype=np.int64)
+        out[k + "table"] = table
+        out[k + "indices"] = indices
+        out[k + "offsets"] = np.zeros(1, dtype=np.int64)
+        out[k + "weights"] = weights
+        out[k + "out"] = res[:count * dim]
+        n += 1
+    out["n_ex"] = np.array(n)
+    path = os.path.join(HERE, "lookup_ex_golden.npz")
+    np.savez_compressed(path, **out)
+    print(path, os.path.getsize(path), "bytes;", n, "cases")
+
+
+if __name__ == "__main__":
+    main()

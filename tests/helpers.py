@@ -17,22 +17,26 @@ def row_bytes(bit_rate, dim):
     return (dim + epb - 1) // epb + (8 if bit_rate == 8 else 4)
 
 
-def random_fused_table(rng, rows, dim, bit_rate, stride=None):
+def random_fused_table(rng, rows, dim, bit_rate, stride=None, scale_bias_first=False):
     """Rows as the reference tests build them: small random payload values and
     N(0,1) scale/bias (test/EmbeddingSpMDM8BitTest.cc:120-154,
     test/EmbeddingSpMDMNBitTest.cc:137-166) - not quantizer output, so every
-    payload bit pattern and awkward scales occur."""
+    payload bit pattern and awkward scales occur.  ``scale_bias_first`` builds
+    the table-batched layout (the generators' scale_bias_last = false): fp16
+    scale and bias in the first four bytes of the row, for 8-bit rows too."""
     epb = 8 // bit_rate
     data_bytes = (dim + epb - 1) // epb
-    rb = row_bytes(bit_rate, dim)
-    stride = stride or rb
+    half_sb = bit_rate != 8 or scale_bias_first
+    sb_bytes = 4 if half_sb else 8
+    stride = stride or data_bytes + sb_bytes
+    data_at, sb_at = (sb_bytes, 0) if scale_bias_first else (0, data_bytes)
     t = np.zeros((rows, stride), dtype=np.uint8)
-    t[:, :data_bytes] = rng.integers(0, 256, (rows, data_bytes), dtype=np.uint8)
+    t[:, data_at:data_at + data_bytes] = rng.integers(0, 256, (rows, data_bytes), dtype=np.uint8)
     sb = rng.standard_normal((rows, 2)).astype(np.float32)
-    if bit_rate == 8:
-        t[:, data_bytes:data_bytes + 8] = sb.view(np.uint8).reshape(rows, 8)
+    if half_sb:
+        t[:, sb_at:sb_at + 4] = sb.astype(np.float16).view(np.uint8).reshape(rows, 4)
     else:
-        t[:, data_bytes:data_bytes + 4] = sb.astype(np.float16).view(np.uint8).reshape(rows, 4)
+        t[:, sb_at:sb_at + 8] = sb.view(np.uint8).reshape(rows, 8)
     return t
 
 

@@ -40,10 +40,11 @@ def test_every_declared_entry_point_is_exported_and_bound():
 
 
 def test_config_struct_layout_matches_header():
-    # 4 x int32, 3 x int64, 4 x int32 with natural alignment
-    assert C.sizeof(_capi.SpmdmConfig) == 16 + 24 + 16
+    # 4 x int32, 3 x int64, 6 x int32 with natural alignment
+    assert C.sizeof(_capi.SpmdmConfig) == 16 + 24 + 24
     assert _capi.SpmdmConfig.block_size.offset == 16
     assert _capi.SpmdmConfig.has_weight.offset == 40
+    assert _capi.SpmdmConfig.no_bag.offset == 60
 
 
 def cfg(**kw):
@@ -57,6 +58,7 @@ def cfg(**kw):
     dict(bit_rate=3), dict(bit_rate=16), dict(index_bytes=2), dict(offset_bytes=16), dict(out_dtype=5),
     dict(block_size=0), dict(block_size=-4), dict(block_size=4096), dict(input_stride=10),
     dict(output_stride=8), dict(bit_rate=4, block_size=64, input_stride=35),
+    dict(bit_rate=4, no_bag=1), dict(scale_bias_first=1, input_stride=67),
 ])
 def test_check_config_rejects(bad):
     assert _capi.lib().fbgemm_b200_spmdm_check_config(C.byref(cfg(**bad))) == _capi.EINVAL
@@ -66,6 +68,7 @@ def test_check_config_rejects(bad):
 @pytest.mark.parametrize("good", [
     dict(), dict(bit_rate=4, block_size=64, out_dtype=1), dict(bit_rate=2, block_size=1024),
     dict(block_size=1024), dict(block_size=7, input_stride=20, output_stride=9), dict(bit_rate=4, block_size=1),
+    dict(scale_bias_first=1, input_stride=68), dict(out_dtype=2, no_bag=1), dict(bit_rate=2, scale_bias_first=1),
 ])
 def test_check_config_accepts(good):
     assert _capi.lib().fbgemm_b200_spmdm_check_config(C.byref(cfg(**good))) == 0
@@ -74,12 +77,16 @@ def test_check_config_accepts(good):
 def test_generators_mirror_reference_argument_checks():
     with pytest.raises(ValueError):
         F.GenerateEmbeddingSpMDMNBit(3, 64, False, False)          # bit_rate must be 2 or 4
-    with pytest.raises(ValueError):
-        F.GenerateEmbeddingSpMDMWithStrides(64, False, False, scale_bias_last=False)
-    with pytest.raises(ValueError):
-        F.GenerateEmbeddingSpMDM(64, False, False, is_bf16_out=True)
-    with pytest.raises(ValueError):
+    with pytest.raises(ValueError):   # the reference's N-bit no_bag is an int4 -> int4 row copy: not provided
         F.GenerateEmbeddingSpMDMNBitWithStrides(4, 64, False, False, no_bag=True)
+    with pytest.raises(ValueError):   # is_bf16_in belongs to unquantized tables
+        F.GenerateEmbeddingSpMDM(64, False, False, is_bf16_in=True)
+    # the table-batched row layout, bf16 output and 8-bit no_bag are carried in the config
+    k = F.GenerateEmbeddingSpMDMWithStrides(64, False, False, scale_bias_last=False, no_bag=True, is_bf16_out=True,
+                                            out_dtype=np.uint16)
+    assert (k.cfg.scale_bias_first, k.cfg.no_bag, k.cfg.out_dtype) == (1, 1, 2)
+    k = F.GenerateEmbeddingSpMDMNBitWithStrides(2, 64, False, False, scale_bias_last=False, out_dtype=np.float16)
+    assert (k.cfg.scale_bias_first, k.cfg.no_bag, k.cfg.out_dtype) == (1, 0, 1)
     with pytest.raises(Exception):
         F.GenerateEmbeddingSpMDM(64, False, False, out_dtype=np.int8)
     k = F.GenerateEmbeddingSpMDMNBit(4, 64, True, False, index_dtype=np.int32, offset_dtype=np.int32,

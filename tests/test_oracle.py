@@ -112,6 +112,31 @@ def test_oracle_matches_reference_fixtures(oracle, golden):
     np.testing.assert_array_equal(rw, golden["remap_out_weights"])
 
 
+KINDS = ("f32", "f16", "bf16")
+
+
+def run_ex_fixture(lookups, ex, i):
+    """One case of lookup_ex_golden.npz through `lookups.spmdm_ex`; returns (ok, got, want)."""
+    k = f"ex{i}_"
+    bit_rate, count, rows, dim, weighted, normalize, sb_last, no_bag, kind = (int(v) for v in ex[k + "meta"])
+    table = ex[k + "table"]
+    ok, got = lookups.spmdm_ex(bit_rate, dim, rows, table, ex[k + "indices"], None if no_bag else ex[k + "offsets"],
+                               ex[k + "weights"] if weighted else None, bool(normalize), KINDS[kind], False, True, -1,
+                               table.shape[1], bool(sb_last), bool(no_bag))
+    return ok, got[:count * dim], ex[k + "out"]
+
+
+def test_oracle_ex_matches_reference_fixtures(oracle):
+    """Rows with scale, bias first and -1 as a pruned index, bf16 output,
+    padded rows, no_bag: fixtures made by the reference's own functions."""
+    ex = np.load(os.path.join(os.path.dirname(GOLDEN), "lookup_ex_golden.npz"))
+    assert int(ex["n_ex"]) >= 20
+    for i in range(int(ex["n_ex"])):
+        ok, got, want = run_ex_fixture(oracle, ex, i)
+        assert ok
+        np.testing.assert_array_equal(bits(got), bits(want))
+
+
 # ---- live against the reference's own code ------------------------------------------
 
 @pytest.mark.parametrize("bit_rate", [8, 4, 2])
@@ -173,3 +198,42 @@ def test_reference_jit_matches_oracle(oracle):
                           out_dt)
             assert a[0] and b[0]
             np.testing.assert_array_equal(bits(a[1]), bits(b[1]))
+
+
+@pytest.mark.parametrize("bit_rate", [8, 4, 2])
+def test_oracle_ex_matches_reference_live(oracle, reference, bit_rate):
+    rng = np.random.default_rng(140 + bit_rate)
+    for shape_i, (batch, rows, dim, avg_len) in enumerate(REFERENCE_SHAPES[2:12]):
+        for sb_last in (True, False):
+            for corner in (None, "oob", "unmatched-"):
+                idt = (np.int32, np.int64)[shape_i % 2]
+                table = random_fused_table(rng, rows, dim, bit_rate, None, not sb_last)
+                lengths, offsets, indices, weights, n = lengths_indices_weights(rng, batch, rows, avg_len, idt, idt, corner)
+                if corner is None:
+                    indices[rng.integers(0, n, max(1, n // 6))] = -1  # pruned when scale, bias come first; else an error
+                for kind, weighted, normalize, use_offsets in (("f32", False, True, True), ("bf16", True, False, False),
+                                                               ("f16", True, True, True)):
+                    ol = offsets if use_offsets else lengths
+                    args = (bit_rate, dim, rows, table, indices, ol, weights if weighted else None, normalize, kind,
+                            False, use_offsets, -1, -1, sb_last, False)
+                    a = oracle.spmdm_ex(*args, output_size=batch, index_size=n)
+                    b = reference.spmdm_ex(*args, output_size=batch, index_size=n)
+                    assert a[0] == b[0] == (corner is None and not sb_last)
+                    if a[0]:
+                        np.testing.assert_array_equal(bits(a[1]), bits(b[1]))
+        if bit_rate == 8:
+            for sb_last in (True, False):
+                table = random_fused_table(rng, rows, dim, 8, None, not sb_last)
+                indices = rng.integers(0, rows, 3 * batch).astype(np.int64)
+                weights = rng.standard_normal(3 * batch).astype(np.float32)
+                for kind, weighted in (("f32", True), ("f16", False), ("bf16", True)):
+                    args = (8, dim, rows, table, indices, None, weights if weighted else None, True, kind, False, True,
+                            -1, -1, sb_last, True)
+                    a, b = oracle.spmdm_ex(*args), reference.spmdm_ex(*args)
+                    assert a[0] and b[0]
+                    np.testing.assert_array_equal(bits(a[1]), bits(b[1]))
+                indices[5] = rows
+                assert not oracle.spmdm_ex(8, dim, rows, table, indices, None, None, False, "f32", False, True, -1, -1,
+                                           sb_last, True)[0]
+                assert not reference.spmdm_ex(8, dim, rows, table, indices, None, None, False, "f32", False, True, -1, -1,
+                                              sb_last, True)[0]
