@@ -26,6 +26,7 @@ from .embedding import (  # noqa: F401
     GenerateEmbeddingSpMDMWithStrides,
     MultiTablePlan,
     SpmdmKernel,
+    compressed_indices_remap,
     get_context,
     launch_count,
     status_read,

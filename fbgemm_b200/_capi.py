@@ -39,6 +39,8 @@ class SpmdmConfig(C.Structure):
         ("use_offsets", C.c_int32),
         ("scale_bias_first", C.c_int32),
         ("no_bag", C.c_int32),
+        ("absolute_offsets", C.c_int32),
+        ("reserved_", C.c_int32),
     ]
 
 
@@ -86,6 +88,8 @@ SIGNATURES = {
     "fbgemm_b200_status_read": (C.c_int, [_p, C.c_int, _p, C.POINTER(C.c_int32)]),
     "fbgemm_b200_spmdm": (C.c_int, [_p, _cfgp, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, _p]),
     "fbgemm_b200_spmdm_lengths_noalloc": (C.c_int, [_cfgp, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, _p]),
+    "fbgemm_b200_compressed_indices_remap": (C.c_int, [_p, C.c_int32, _p, C.c_int32, _i64, _p, _i64, _p, _p, _p, _p,
+                                                       _p, _p]),
     "fbgemm_b200_table_register": (C.c_int, [_p, _p, C.c_size_t]),
     "fbgemm_b200_table_unregister": (C.c_int, [_p, _p]),
     "fbgemm_b200_table_device_ptr": (_p, [_p, _p]),

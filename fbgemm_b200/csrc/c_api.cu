@@ -155,6 +155,10 @@ int check_config(const fbgemm_b200_spmdm_config* c, Derived* d) {
     set_error("output type must be fp32, fp16 or bf16");
     return FBGEMM_B200_EINVAL;
   }
+  if (c->absolute_offsets && (!c->use_offsets || c->no_bag || c->is_weight_positional)) {
+    set_error("absolute_offsets goes with use_offsets, bags and per-index weights");
+    return FBGEMM_B200_EINVAL;
+  }
   if (c->no_bag && c->bit_rate != 8) {
     // EmbeddingSpMDMNBit_ref: "no_bag is only supported for int4 to int4", a raw row copy
     set_error("no_bag is provided for 8-bit rows with fp32/fp16/bf16 output");
@@ -287,6 +291,7 @@ int fbgemm_b200::build_lookup_params(
   flags |= cfg->out_dtype == FBGEMM_B200_OUT_BF16 ? kOutBf16 : 0;
   flags |= cfg->scale_bias_first ? kSbFirst : 0;
   flags |= cfg->no_bag ? kNoBag : 0;
+  flags |= cfg->absolute_offsets ? kAbsOffsets : 0;
   flags |= p.weights ? kWeighted : 0;
   flags |= (p.weights && cfg->is_weight_positional) ? kPositional : 0;
   flags |= (cfg->normalize_by_lengths && !cfg->no_bag) ? kNormalize : 0;
@@ -668,6 +673,47 @@ int fbgemm_b200_spmdm(
   return fbgemm_b200_status_read(ctx, 0, stream, nullptr);
 }
 
+int fbgemm_b200_compressed_indices_remap(
+    fbgemm_b200_ctx* ctx,
+    int32_t offsets_len,
+    const void* indices,
+    int32_t index_bytes,
+    int64_t index_size,
+    const int32_t* compressed_indices_mapping,
+    int64_t mapping_size,
+    const void* offsets,
+    const float* weights,
+    void* out_indices,
+    void* out_offsets,
+    float* out_weights,
+    void* stream) {
+  if (!ctx) {
+    set_error("null context");
+    return FBGEMM_B200_EINVAL;
+  }
+  if (offsets_len < 1 || (index_bytes != 4 && index_bytes != 8) || index_size < 0 || mapping_size < 0 || !offsets ||
+      !out_offsets || (index_size > 0 && (!indices || !out_indices || !compressed_indices_mapping)) ||
+      (weights && !out_weights)) {
+    set_error("compressed_indices_remap: bad argument");
+    return FBGEMM_B200_EINVAL;
+  }
+  DeviceGuard guard(ctx->device);
+  // The scratch and the status slot (the last one) are the context's: one remap at a time.
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  cudaError_t e = reserve(ctx->scan, remap_scratch_bytes(index_size));
+  if (e != cudaSuccess) {
+    return fail_cuda(e, "scratch for the index remap");
+  }
+  const int slot = FBGEMM_B200_STATUS_SLOTS - 1;
+  e = launch_compressed_indices_remap(offsets_len, indices, index_bytes, index_size, compressed_indices_mapping,
+                                      mapping_size, offsets, weights, out_indices, out_offsets, out_weights,
+                                      ctx->status + 4 * slot, ctx->scan.ptr, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) {
+    return fail_cuda(e, "index remap launch");
+  }
+  return fbgemm_b200_status_read(ctx, slot, stream, nullptr);
+}
+
 /* ---- table registry ----------------------------------------------------- */
 
 int fbgemm_b200_table_register(fbgemm_b200_ctx* ctx, const void* host_ptr, size_t bytes) {
@@ -753,8 +799,8 @@ int fbgemm_b200_spmdm_host_submit(
     set_error("negative size");
     return FBGEMM_B200_EINVAL;
   }
-  if (cfg->no_bag) {
-    set_error("no_bag is provided for device pointers only");
+  if (cfg->no_bag || cfg->absolute_offsets) {
+    set_error("no_bag and absolute_offsets are provided for device pointers only");
     return FBGEMM_B200_EINVAL;
   }
   DeviceGuard guard(ctx->device);

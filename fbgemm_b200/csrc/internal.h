@@ -26,6 +26,7 @@ enum : uint32_t {
   kSbFirst = 1u << 8,     // fp16 scale,bias at the start of the row; index -1 = pruned row
   kOutBf16 = 1u << 9,     // bf16 output
   kNoBag = 1u << 10,      // one index per output row, no offsets
+  kAbsOffsets = 1u << 11, // offsets index the whole index array (no rebasing, no final size check)
 };
 
 // Everything one lookup launch needs; passed by value to the kernel.
@@ -114,6 +115,26 @@ cudaError_t launch_length_scan(
     int64_t n,
     int64_t* offsets,
     int64_t* block_sums,
+    cudaStream_t stream);
+
+// compressed_indices_remap (remap_kernels.cu).  `scratch` holds
+// remap_scratch_bytes(index_size) bytes; out-of-range indices are recorded in
+// `status` and dropped.
+size_t remap_scratch_bytes(int64_t index_size);
+cudaError_t launch_compressed_indices_remap(
+    int32_t offsets_len,
+    const void* indices,
+    int index_bytes,
+    int64_t index_size,
+    const int32_t* mapping,
+    int64_t mapping_size,
+    const void* offsets,
+    const float* weights,
+    void* out_indices,
+    void* out_offsets,
+    float* out_weights,
+    int32_t* status,
+    void* scratch,
     cudaStream_t stream);
 
 // Row-wise quantizers (quantize_kernels.cu).

@@ -370,8 +370,10 @@ __device__ __forceinline__ void direct_block(const SpmdmParams& p, int64_t block
   const bool weighted = p.flags & kWeighted;
 
   const bool no_bag = p.flags & kNoBag;
-  const int64_t off_base = no_bag ? 0 : load_int(p.offsets, 0, off64);
-  if (block == 0 && threadIdx.x == 0 && !no_bag) {
+  // rebasing to offsets[0] (the functor's convention) unless the offsets are absolute
+  const bool rebase = !(p.flags & (kNoBag | kAbsOffsets));
+  const int64_t off_base = rebase ? load_int(p.offsets, 0, off64) : 0;
+  if (block == 0 && threadIdx.x == 0 && rebase) {
     // `return current == index_size` of the reference
     const int64_t total = load_int(p.offsets, p.output_size, off64) - off_base;
     if (total != p.index_size) {

@@ -253,8 +253,10 @@ spmdm_kernel(const __grid_constant__ SpmdmParams p) {
 
   const bool no_bag = p.flags & kNoBag;
   const bool half_sb = BITS != 8 || (p.flags & kSbFirst);
-  const int64_t off_base = no_bag ? 0 : load_int(p.offsets, 0, off64);
-  if (blockIdx.x == 0 && threadIdx.x == 0 && !no_bag) {
+  // rebasing to offsets[0] (the functor's convention) unless the offsets are absolute
+  const bool rebase = !(p.flags & (kNoBag | kAbsOffsets));
+  const int64_t off_base = rebase ? load_int(p.offsets, 0, off64) : 0;
+  if (blockIdx.x == 0 && threadIdx.x == 0 && rebase) {
     // `return current == index_size` of the reference
     const int64_t total = load_int(p.offsets, p.output_size, off64) - off_base;
     if (total != p.index_size) {

@@ -394,3 +394,23 @@ def FloatToFusedNBitRowwiseQuantizedSBHalf(bit_rate, x, out=None):
         _capi.check(_capi.lib().fbgemm_b200_float_to_fused_nbit_rowwise(
             bit_rate, x.data_ptr(), rows, cols, out.data_ptr(), stream), "N-bit quantizer")
     return out
+
+
+def compressed_indices_remap(indices, compressed_indices_mapping, offsets, weights=None):
+    """fbgemm::compressed_indices_remap (include/fbgemm/FbgemmEmbedding.h:393-401)
+    on CUDA tensors: returns ``(ok, out_indices, out_offsets, out_weights)``
+    where ``out_offsets[-1]`` entries of ``out_indices`` / ``out_weights`` are
+    valid.  ``ok`` is False when an index lay outside the map."""
+    import torch
+
+    assert indices.is_cuda and indices.dtype == offsets.dtype and indices.dtype in (torch.int32, torch.int64)
+    assert compressed_indices_mapping.dtype == torch.int32
+    ctx = get_context(indices.device.index)
+    out_indices = torch.empty_like(indices)
+    out_offsets = torch.empty_like(offsets)
+    out_weights = torch.empty_like(weights) if weights is not None else None
+    rc = _capi.lib().fbgemm_b200_compressed_indices_remap(
+        ctx.handle, offsets.numel(), _ptr(indices), indices.element_size(), indices.numel(),
+        _ptr(compressed_indices_mapping), compressed_indices_mapping.numel(), _ptr(offsets), _ptr(weights),
+        _ptr(out_indices), _ptr(out_offsets), _ptr(out_weights), torch.cuda.current_stream(ctx.device).cuda_stream)
+    return bool(_capi.check(rc, "fbgemm_b200_compressed_indices_remap")), out_indices, out_offsets, out_weights

@@ -1,0 +1,175 @@
+"""Table-batched quantized embedding lookup on the GPU: the caller that sits
+above the generators in the reference,
+``int_nbit_split_embedding_codegen_forward_{unweighted,weighted}_cpu``
+(fbgemm_gpu/codegen/inference/embedding_forward_quantized_cpu_template.cpp:205-520
+of FBGEMM).  Same arguments, same result; the tensors live in HBM.
+
+The reference walks the tables on host threads and calls one generated kernel
+per table with ``output + D_start``, ``output_stride = total_D`` and the slice
+``offsets[t*B : (t+1)*B + 1]`` of the ``T*B + 1`` offsets.  Here every table is
+one launch of the same lookup kernel with *absolute* offsets (the kernel is
+given the whole index array and the slice of offsets, so nothing has to be
+read back to the host to find where a table's indices start), all launches
+enqueued without a synchronisation; or, for callers whose input buffers keep
+their addresses, one multi-table plan that is built once and replayed.
+
+Rows are INT8 / INT4 / INT2 with fp16 scale and bias *first* (the layout of
+table-batched embeddings, ``scale_bias_last = False``), or scale and bias last
+(fp32 pair for INT8) when ``scale_bias_last = True``; each row padded to
+``row_alignment`` bytes.  An index of -1 is a pruned row.  Output FP32, FP16
+or BF16 of shape ``[B, total_D]``.  Unquantized (FP32/FP16/FP8) tables and
+INT8/INT4 output belong to other kernels of the reference and are refused.
+"""
+from __future__ import annotations
+
+import enum
+
+import numpy as np
+import torch
+
+from . import embedding as E
+
+
+class SparseType(enum.IntEnum):
+    """fbgemm_gpu/include/fbgemm_gpu/embedding_common.h:20-32."""
+    FP32 = 0
+    FP16 = 1
+    INT8 = 2
+    INT4 = 3
+    INT2 = 4
+    BF16 = 5
+    FP8 = 6
+
+
+class PoolingMode(enum.IntEnum):
+    """fbgemm_gpu/include/fbgemm_gpu/embedding_common.h:34."""
+    SUM = 0
+    MEAN = 1
+    NONE = 2
+
+
+_BITS = {SparseType.INT8: 8, SparseType.INT4: 4, SparseType.INT2: 2}
+_OUT = {SparseType.FP32: torch.float32, SparseType.FP16: torch.float16, SparseType.BF16: torch.bfloat16}
+
+
+def padded_row_size_in_bytes(dim: int, weight_ty: SparseType, row_alignment: int, scale_bias_bytes: int = 4) -> int:
+    """nbit::padded_row_size_in_bytes (embedding_common.h:189-225) for the quantized types."""
+    bits = _BITS[SparseType(weight_ty)]
+    unpadded = dim * bits // 8 + scale_bias_bytes
+    return (unpadded + row_alignment - 1) // row_alignment * row_alignment
+
+
+def _host(x, dtype):
+    if isinstance(x, torch.Tensor):
+        return x.detach().cpu().numpy().astype(dtype)
+    return np.asarray(x, dtype=dtype)
+
+
+class IntNBitTableBatchedEmbeddingBags:
+    """The tables of one table-batched operator and what does not change from
+    call to call (row sizes, row counts, kernels)."""
+
+    def __init__(self, dev_weights: torch.Tensor, weights_offsets, weights_tys, D_offsets, total_D: int,
+                 pooling_mode: int = PoolingMode.SUM, row_alignment: int = 1, output_dtype: int = SparseType.FP16,
+                 scale_bias_last: bool = False, weighted: bool = False, index_dtype=torch.int32):
+        assert dev_weights.is_cuda and dev_weights.dtype == torch.uint8 and dev_weights.is_contiguous()
+        self.dev_weights = dev_weights
+        self.device = dev_weights.device
+        self.weights_offsets = _host(weights_offsets, np.int64)
+        self.weights_tys = [SparseType(int(t)) for t in _host(weights_tys, np.int64)]
+        self.D_offsets = _host(D_offsets, np.int64)
+        self.T = len(self.D_offsets) - 1
+        self.total_D = int(total_D)
+        if PoolingMode(pooling_mode) == PoolingMode.NONE:
+            raise ValueError("PoolingMode.NONE (sequence output) is the reference's nobag operator, not this one")
+        self.normalize = PoolingMode(pooling_mode) == PoolingMode.MEAN
+        if SparseType(output_dtype) not in _OUT:
+            raise ValueError("output_dtype must be FP32, FP16 or BF16 (INT8/INT4 output is the nobag operator's)")
+        self.out_dtype = _OUT[SparseType(output_dtype)]
+        self.weighted = bool(weighted)
+        self.index_dtype = index_dtype
+        np_idx = np.int32 if index_dtype == torch.int32 else np.int64
+        # num_rows per table from the sorted unique physical offsets, as the reference derives it (:330-342, :369-381)
+        physical = sorted(set(int(o) for o in self.weights_offsets))
+        self.kernels, self.rows, self.tables = [], [], []
+        for t in range(self.T):
+            ty = self.weights_tys[t]
+            if ty not in _BITS:
+                raise ValueError(f"table {t}: weight type {ty.name} is not a quantized row format of this path")
+            D = int(self.D_offsets[t + 1] - self.D_offsets[t])
+            sb_bytes = 8 if (ty == SparseType.INT8 and scale_bias_last) else 4
+            D_bytes = padded_row_size_in_bytes(D, ty, row_alignment, sb_bytes)
+            start = int(self.weights_offsets[t])
+            nxt = [o for o in physical if o > start]
+            end = nxt[0] if nxt else dev_weights.numel()
+            self.rows.append((end - start) // D_bytes)
+            self.tables.append(dev_weights[start:end])
+            kw = dict(index_dtype=np_idx, offset_dtype=np_idx,
+                      out_dtype={torch.float32: np.float32, torch.float16: np.float16,
+                                 torch.bfloat16: np.uint16}[self.out_dtype])
+            bf16 = self.out_dtype == torch.bfloat16
+            if ty == SparseType.INT8:
+                k = E.GenerateEmbeddingSpMDMWithStrides(D, self.weighted, self.normalize, 16, False, True, self.total_D,
+                                                        D_bytes, scale_bias_last, False, bf16, **kw)
+            else:
+                k = E.GenerateEmbeddingSpMDMNBitWithStrides(_BITS[ty], D, self.weighted, self.normalize, 16, False, True,
+                                                            self.total_D, D_bytes, scale_bias_last, bf16, **kw)
+            k.cfg.absolute_offsets = 1
+            self.kernels.append(k)
+        self._streams = [torch.cuda.Stream(device=self.device) for _ in range(4)]
+        self._plans: dict = {}
+
+    def _calls(self, B, indices, offsets, indice_weights, output):
+        flat = output.view(-1)
+        n = indices.numel()
+        calls = []
+        for t in range(self.T):
+            calls.append((self.kernels[t], B, n, self.rows[t], self.tables[t], indices, offsets[t * B:],
+                          indice_weights if self.weighted else None, flat[int(self.D_offsets[t]):], None))
+        return calls
+
+    def forward(self, indices: torch.Tensor, offsets: torch.Tensor, indice_weights: torch.Tensor | None = None,
+                output: torch.Tensor | None = None, slot: int = 0, use_plan: bool = False) -> torch.Tensor:
+        """``offsets`` has ``T*B + 1`` entries, table after table; returns
+        ``[B, total_D]``.  Asynchronous on torch's current stream; a bad index
+        or offsets shows in status slot ``slot`` (``fbgemm_b200.status_read``)."""
+        assert indices.dtype == offsets.dtype == self.index_dtype and indices.is_cuda and offsets.is_cuda
+        assert (offsets.numel() - 1) % self.T == 0
+        B = (offsets.numel() - 1) // self.T
+        if self.weighted:
+            assert indice_weights is not None and indice_weights.dtype == torch.float32
+        if output is None:
+            output = torch.zeros((B, self.total_D), dtype=self.out_dtype, device=self.device)
+        if B == 0:
+            return output
+        calls = self._calls(B, indices, offsets, indice_weights, output)
+        if use_plan:
+            key = (indices.data_ptr(), offsets.data_ptr(), indice_weights.data_ptr() if self.weighted else 0,
+                   output.data_ptr(), B, indices.numel(), slot)
+            plan = self._plans.get(key)
+            if plan is None:
+                plan = self._plans[key] = E.MultiTablePlan(calls, self.device.index, slot)
+            plan.launch()
+            return output
+        cur = torch.cuda.current_stream(self.device)
+        for s in self._streams:
+            s.wait_stream(cur)
+        for t, (k, b, n, rows, table, idx, off, w, out, _) in enumerate(calls):
+            k.launch(b, n, rows, table, idx, off, w, out, slot=slot,
+                     stream=self._streams[t % len(self._streams)].cuda_stream)
+        for s in self._streams:
+            cur.wait_stream(s)
+        return output
+
+
+def int_nbit_split_embedding_codegen_forward(dev_weights, weights_offsets, weights_tys, D_offsets, total_D, indices,
+                                             offsets, pooling_mode, row_alignment, indice_weights=None,
+                                             output_dtype=SparseType.FP16, scale_bias_last=False):
+    """One call with the reference operator's arguments (the placement, UVM
+    and FP8 arguments, which select other storage or other kernels, left out).
+    Builds the per-table kernels every time; keep an
+    ``IntNBitTableBatchedEmbeddingBags`` to amortise that."""
+    op = IntNBitTableBatchedEmbeddingBags(dev_weights, weights_offsets, weights_tys, D_offsets, total_D, pooling_mode,
+                                          row_alignment, output_dtype, scale_bias_last, indice_weights is not None,
+                                          indices.dtype)
+    return op.forward(indices, offsets, indice_weights)

@@ -92,6 +92,17 @@ typedef struct fbgemm_b200_spmdm_config {
                            output_size rows, no offsets, no normalisation
                            (src/RefImplementations.cc:1235-1288); 8-bit rows,
                            fp32 / fp16 / bf16 output                         */
+  int32_t absolute_offsets; /* 1 = offsets index the caller's WHOLE index (and
+                           weight) array: bag m covers indices[offsets[m] ..
+                           offsets[m+1]) with `indices` not advanced to the
+                           table's first index, index_size = length of the
+                           whole array, and the final check "sum of lengths ==
+                           index_size" does not apply.  This is how one table of
+                           a table-batched call (offsets of shape T*B+1,
+                           fbgemm_gpu/codegen/inference/embedding_forward_quantized_cpu_template.cpp:381-387)
+                           is pooled without reading offsets[t*B] on the host.
+                           Offsets flavour only.  0 = the functor's convention */
+  int32_t reserved_;    /* keeps the struct a multiple of 8 bytes; set to 0   */
 } fbgemm_b200_spmdm_config;
 
 /* ---- context ----------------------------------------------------------- */
@@ -304,6 +315,35 @@ FBGEMM_B200_API int fbgemm_b200_spmdm_lengths_noalloc(
  * offsets/lengths, weights and the output travel through pinned staging
  * buffers on every call.
  */
+
+/*
+ * fbgemm::compressed_indices_remap<IndexType> (include/fbgemm/FbgemmEmbedding.h:393-401,
+ * src/EmbeddingSpMDM.cc:1714-1770; scalar form src/RefImplementations.cc:2308-2333):
+ * the other way to use a pruned table - rewrite (indices, offsets, weights)
+ * so that pruned rows disappear and the rest address the compressed table,
+ * then run a plain lookup.  Device pointers; offsets share the index type, as
+ * in the reference.  Two arguments the reference does not have, because a
+ * GPU must not follow a wild index and sizes its grid on the host:
+ * index_size = entries in `indices` (at least offsets[offsets_len-1]) and
+ * mapping_size = entries in the map.  out_indices / out_weights need room for
+ * index_size entries, out_offsets for offsets_len.  Waits for `stream`.
+ * Returns 1, or 0 if an index lay outside the map (that entry is dropped),
+ * or a negative code.  One remap at a time per context.
+ */
+FBGEMM_B200_API int fbgemm_b200_compressed_indices_remap(
+    fbgemm_b200_ctx* ctx,
+    int32_t offsets_len,
+    const void* indices,
+    int32_t index_bytes,
+    int64_t index_size,
+    const int32_t* compressed_indices_mapping,
+    int64_t mapping_size,
+    const void* offsets,
+    const float* weights, /* NULL: no per-sample weights */
+    void* out_indices,
+    void* out_offsets,
+    float* out_weights,
+    void* stream);
 
 /* Copy `bytes` of a fused-row table (or of a compressed_indices_table) to the
  * device and remember it under its host address.  Registering the same

@@ -40,8 +40,8 @@ def test_every_declared_entry_point_is_exported_and_bound():
 
 
 def test_config_struct_layout_matches_header():
-    # 4 x int32, 3 x int64, 6 x int32 with natural alignment
-    assert C.sizeof(_capi.SpmdmConfig) == 16 + 24 + 24
+    # 4 x int32, 3 x int64, 8 x int32 with natural alignment
+    assert C.sizeof(_capi.SpmdmConfig) == 16 + 24 + 32
     assert _capi.SpmdmConfig.block_size.offset == 16
     assert _capi.SpmdmConfig.has_weight.offset == 40
     assert _capi.SpmdmConfig.no_bag.offset == 60
@@ -58,7 +58,7 @@ def cfg(**kw):
     dict(bit_rate=3), dict(bit_rate=16), dict(index_bytes=2), dict(offset_bytes=16), dict(out_dtype=5),
     dict(block_size=0), dict(block_size=-4), dict(block_size=4096), dict(input_stride=10),
     dict(output_stride=8), dict(bit_rate=4, block_size=64, input_stride=35),
-    dict(bit_rate=4, no_bag=1), dict(scale_bias_first=1, input_stride=67),
+    dict(bit_rate=4, no_bag=1), dict(scale_bias_first=1, input_stride=67), dict(absolute_offsets=1, use_offsets=0),
 ])
 def test_check_config_rejects(bad):
     assert _capi.lib().fbgemm_b200_spmdm_check_config(C.byref(cfg(**bad))) == _capi.EINVAL
