@@ -43,9 +43,9 @@ NUM_BATCHES = 32        # distinct pre-generated batches the steps rotate over
 # launch shape: key = (workload, batches per call).
 TRAFFIC_BYTES_PER_LAUNCH = {
     (1, 1): 13_755_648,             # profiles/spmdm_direct_kernel__workload1_one_batch.md
-    (1, 16): 170_838_016 + 6_931_200,   # profiles/spmdm_direct_kernel__workload1_16batches.md
-    (0, 16): 440_144_128 + 73_972_736,  # profiles/spmdm_direct_kernel__workload0_16batches.md
-    (2, 16): 271_241_472 + 50_875_648,  # profiles/spmdm_direct_kernel__workload2_16batches.md
+    (1, 16): 171_206_400 + 8_106_496,   # profiles/spmdm_direct_kernel__workload1_16batches.md
+    (0, 16): 438_344_192 + 71_286_528,  # profiles/spmdm_direct_kernel__workload0_16batches.md
+    (2, 16): 234_103_040 + 49_501_952,  # profiles/spmdm_direct_kernel__workload2_16batches.md
 }
 
 
