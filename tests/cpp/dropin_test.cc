@@ -22,6 +22,8 @@ int oracle_embedding_spmdm_nbit(int, int64_t, int64_t, int64_t, int64_t, const u
                                 int, const float*, int, void*, int, int, int, int64_t, int64_t);
 int oracle_embedding_spmdm_rowwise_sparse(int, int64_t, int64_t, int64_t, int64_t, const uint8_t*, const void*, int,
                                           const int32_t*, const void*, int, const float*, int, float*, int, int);
+int oracle_embedding_spmdm_ex(int, int64_t, int64_t, int64_t, int64_t, const uint8_t*, const void*, int, const void*, int,
+                              const float*, int, void*, int, int, int, int64_t, int64_t, int, int);
 }
 
 static int failures = 0;
@@ -159,6 +161,38 @@ int main() {
     cudaMemcpy(out.data(), d_out, out.size() * 4, cudaMemcpyDeviceToHost);
     CHECK(ok);
     CHECK(std::memcmp(out.data(), ref.data(), out.size() * 4) == 0);
+  }
+  // --- the row layout of table-batched embeddings: fp16 scale, bias FIRST (scale_bias_last = false), rows padded
+  //     to 16 bytes, -1 = pruned index, bf16 output (is_bf16_out with a 16-bit OutType), host pointers
+  for (int bit_rate : {8, 4}) {
+    const int batch = 27, rows = 400, dim = 64;
+    const int data = dim * bit_rate / 8, stride = (data + 4 + 15) / 16 * 16;
+    Inputs in = make(g, 4, batch, rows, dim, 10, 0);  // indices, offsets, weights; the table is rebuilt below
+    in.table.assign((size_t)rows * stride, 0);
+    for (int r = 0; r < rows; ++r) {
+      for (int k = 0; k < 2; ++k) {
+        uint16_t h = (uint16_t)(((g() & 1) << 15) | ((13 + g() % 5) << 10) | (g() & 0x3ff));
+        std::memcpy(&in.table[(size_t)r * stride + 2 * k], &h, 2);
+      }
+      for (int b = 0; b < data; ++b) in.table[(size_t)r * stride + 4 + b] = (uint8_t)(g() & 0xff);
+    }
+    for (int64_t i = 0; i < in.n; i += 7) in.idx64[i] = -1;
+    std::vector<uint16_t> out((size_t)batch * dim, 7), ref((size_t)batch * dim, 9);
+    bool ok;
+    if (bit_rate == 8) {
+      auto kernel = fbgemm::GenerateEmbeddingSpMDMWithStrides<uint8_t, int64_t, int64_t, uint16_t>(
+          dim, true, true, 16, false, true, -1, stride, /*scale_bias_last=*/false, /*no_bag=*/false, /*is_bf16_out=*/true);
+      ok = kernel(batch, in.n, rows, in.table.data(), in.idx64.data(), in.off64.data(), in.weights.data(), out.data());
+    } else {
+      auto kernel = fbgemm::GenerateEmbeddingSpMDMNBitWithStrides<int64_t, int64_t, uint16_t>(
+          4, dim, true, true, 16, false, true, -1, stride, /*scale_bias_last=*/false, /*is_bf16_out=*/true);
+      ok = kernel(batch, in.n, rows, in.table.data(), in.idx64.data(), in.off64.data(), in.weights.data(), out.data());
+    }
+    CHECK(ok);
+    CHECK(oracle_embedding_spmdm_ex(bit_rate, dim, batch, in.n, rows, in.table.data(), in.idx64.data(), 8, in.off64.data(),
+                                    8, in.weights.data(), 1, ref.data(), /*bf16*/ 2, 0, 1, -1, stride, 0, 0));
+    CHECK(std::memcmp(out.data(), ref.data(), out.size() * 2) == 0);
+    fbgemm_b200::InvalidateTable(in.table.data());
   }
   // --- what the sm_100a path does not provide is refused when the kernel is generated
   bool threw = false;
