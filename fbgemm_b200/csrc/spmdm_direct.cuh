@@ -551,6 +551,253 @@ __device__ __forceinline__ void direct_block(const SpmdmParams& p, int64_t block
   }
 }
 
+// U rows whose ids (none skipped) every lane of the group already holds: the
+// registers they occupy while in flight, all row loads issued together, and
+// the rows pooled in order with weights given as fp32 bit patterns.
+template <int BITS, int VEC, int CPL, int U>
+struct KnownRows {
+  Vec<VEC> d[U][CPL];
+  ScaleBias<BITS, VEC> sb[U];
+
+  __device__ __forceinline__ void load(const uint8_t* const (&chunk_base)[CPL], const uint8_t* sb_base, uint32_t stride,
+                                       bool half_sb, const uint2* entry) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t row = entry[u].x;
+#pragma unroll
+      for (int ci = 0; ci < CPL; ++ci) {
+        d[u][ci].load(row_address(chunk_base[ci], row, stride));
+      }
+      sb[u].load(row_address(sb_base, row, stride), half_sb);
+    }
+  }
+
+  __device__ __forceinline__ void pool(bool half_sb, bool weighted, const uint2* entry,
+                                       u64 (&acc)[CPL][(VEC / 4) * (16 / BITS)]) const {
+    constexpr int PAIRS_PER_WORD = 16 / BITS;
+    const u64 nm2 = pack2(-8388608.0f, -8388608.0f);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float scale, bias;
+      sb[u].get(scale, bias, half_sb);
+      if (weighted) {
+        const float w = __uint_as_float(entry[u].y);
+        scale = __fmul_rn(w, scale);
+        bias = __fmul_rn(w, bias);
+      }
+      const u64 s2 = pack2(scale, scale);
+      const u64 b2 = pack2(bias, bias);
+#pragma unroll
+      for (int ci = 0; ci < CPL; ++ci) {
+#pragma unroll
+        for (int wd = 0; wd < VEC / 4; ++wd) {
+          accumulate_word<BITS>(&acc[ci][wd * PAIRS_PER_WORD], d[u][ci].w[wd], s2, b2, nm2);
+        }
+      }
+    }
+  }
+};
+
+// The block's work for tables in which many indices are pruned (row-wise
+// sparse tables): a skipped row costs the arithmetic of a real one in
+// direct_block, because the lanes of a warp move together.  Here a group first
+// walks a stretch of its bag's indices (a queue length at a time), resolves them
+// through the pruning map and writes the rows that remain, with their weights,
+// in order into a small queue in shared memory; then it pools the queue four
+// rows at a time.  Only rows that exist reach the arithmetic.
+// Queue entries per lane group: 8 KB of shared memory per block whatever the
+// group width (fewer, wider groups get longer queues), 128 entries at most.
+#ifndef FBGEMM_B200_QUEUE_BYTES
+#define FBGEMM_B200_QUEUE_BYTES 8192
+#endif
+__host__ __device__ constexpr int queue_entries(int groups_per_warp) {
+  const int q = FBGEMM_B200_QUEUE_BYTES / (kWarpsPerBlock * groups_per_warp * 8);
+  return q > 128 ? 128 : q;
+}
+
+template <int BITS, int VEC, int LPB, int CPL>
+__device__ __forceinline__ void direct_block_compact(const SpmdmParams& p, int64_t block) {
+  constexpr int GPW = 32 / LPB;
+  constexpr int CPC = VEC * 8 / BITS;
+  constexpr int PAIRS = (VEC / 4) * (16 / BITS);
+  constexpr int kQueue = queue_entries(GPW);
+  // rows of the next step in flight during the arithmetic: only where a row is
+  // at most two words per lane, or the extra registers cost resident warps
+#ifdef FBGEMM_B200_COMPACT_PREFETCH
+  constexpr bool kPrefetch = FBGEMM_B200_COMPACT_PREFETCH != 0;
+#else
+  constexpr bool kPrefetch = CPL * (VEC / 4) <= 2;
+#endif
+  __shared__ uint2 queue_s[kWarpsPerBlock * GPW][kQueue];
+
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int grp = lane / LPB;
+  const int gl = lane % LPB;
+  const int lane0 = grp * LPB;
+  const unsigned gmask = LPB == 32 ? 0xffffffffu : (((1u << LPB) - 1u) << lane0);
+  const bool off64 = p.flags & kOff64;
+  const bool idx64 = p.flags & kIdx64;
+  const bool weighted = p.flags & kWeighted;
+  const bool positional = p.flags & kPositional;
+  const bool pruned = p.flags & kPruned;
+  const bool minus_one_skips = (p.flags & (kSbFirst | kNoBag)) == kSbFirst;
+  const bool half_sb = BITS != 8 || (p.flags & kSbFirst);
+  uint2* queue = queue_s[warp * GPW + grp];
+
+  const bool rebase = !(p.flags & (kNoBag | kAbsOffsets));
+  const int64_t off_base = rebase ? load_int(p.offsets, 0, off64) : 0;
+  if (block == 0 && threadIdx.x == 0 && rebase) {
+    const int64_t total = load_int(p.offsets, p.output_size, off64) - off_base;
+    if (total != p.index_size) {
+      report(p.status, FBGEMM_B200_STATUS_SIZE_MISMATCH, p.output_size, total, p.index_size);
+    }
+  }
+  const int64_t bag = (block * kWarpsPerBlock + warp) * GPW + grp;
+  if (bag >= p.output_size) {
+    return;
+  }
+  // no_bag: output row m is the single row indices[m] (there are no offsets)
+  const bool no_bag = p.flags & kNoBag;
+  const int64_t o0 = no_bag ? bag : load_int(p.offsets, bag, off64);
+  const int64_t o1 = no_bag ? bag + 1 : load_int(p.offsets, bag + 1, off64);
+  const int64_t start = o0 - off_base;
+  const int bag_len = (int)(o1 - o0);
+  int len = bag_len < 0 ? 0 : bag_len;
+  if (bag_len < 0 || start < 0 || start + len > p.index_size) {
+    if (gl == 0) {
+      report(p.status, FBGEMM_B200_STATUS_BAG_OVERRUN, bag, start, len);
+    }
+    len = 0;
+  }
+
+  const int nchunks = p.data_bytes / VEC;
+  const uint8_t* chunk_base[CPL];
+#pragma unroll
+  for (int ci = 0; ci < CPL; ++ci) {
+    const int c = gl + ci * LPB;
+    chunk_base[ci] = p.table + p.data_row_off + (c < nchunks ? c * VEC : 0);
+  }
+  const uint8_t* sb_base = p.table + p.sb_row_off;
+  const uint32_t stride = (uint32_t)p.input_stride;
+
+  u64 acc[CPL][PAIRS];
+#pragma unroll
+  for (int ci = 0; ci < CPL; ++ci) {
+#pragma unroll
+    for (int j = 0; j < PAIRS; ++j) {
+      acc[ci][j] = 0ull;
+    }
+  }
+
+  for (int c0 = 0; c0 < len; c0 += kQueue) {
+    const int nc = min(kQueue, len - c0);
+    // 1. resolve: lane gl takes candidates gl, gl + LPB, ...; the index of
+    // round k+2 and the map entry of round k+1 are in flight while round k is
+    // compacted into the queue.
+    const int rounds = (nc + LPB - 1) / LPB;
+    auto fetch_index = [&](int k) -> long long {
+      const int c = k * LPB + gl;
+      return c < nc ? load_int(p.indices, start + c0 + c, idx64) : -2;
+    };
+    // row id after the range check and the pruning map; negative = nothing to pool
+    auto resolve = [&](int k, long long raw) -> int32_t {
+      const int c = k * LPB + gl;
+      if (c >= nc) {
+        return -1;
+      }
+      if ((unsigned long long)raw >= (unsigned long long)p.data_size) {
+        if (!(minus_one_skips && raw == -1)) {
+          report(p.status, FBGEMM_B200_STATUS_BAD_INDEX, bag, start + c0 + c, raw);
+        }
+        return -1;
+      }
+      return pruned ? __ldg(p.cit + raw) : (int32_t)raw;
+    };
+    long long raw_1 = fetch_index(1);
+    int32_t id_0 = resolve(0, fetch_index(0));
+    int count = 0;
+    for (int k = 0; k < rounds; ++k) {
+      const long long raw_2 = fetch_index(k + 2);
+      const int32_t id_1 = resolve(k + 1, raw_1);
+      const int c = k * LPB + gl;
+      float w = 0.f;
+      if (weighted && c < nc) {
+        w = __ldg(p.weights + (positional ? (int64_t)(c0 + c) : start + c0 + c));
+      }
+      const bool keep = id_0 >= 0;
+      const unsigned kept = (__ballot_sync(gmask, keep) >> lane0) & (LPB == 32 ? 0xffffffffu : ((1u << LPB) - 1u));
+      if (keep) {
+        queue[count + __popc(kept & ((1u << gl) - 1u))] = make_uint2((uint32_t)id_0, __float_as_uint(w));
+      }
+      count += __popc(kept);
+      id_0 = id_1;
+      raw_1 = raw_2;
+    }
+    __syncwarp(gmask);
+    // 2. pool the queue in order, four rows at a time.  The ids of every step
+    // are known, so (where the registers allow) the rows of the next step are
+    // requested before the current ones are pooled.
+    const int nfull = count / 4;
+    if constexpr (kPrefetch) {
+      KnownRows<BITS, VEC, CPL, 4> a, b;
+      if (nfull > 0) {
+        a.load(chunk_base, sb_base, stride, half_sb, queue);
+      }
+      for (int s = 0; s < nfull; s += 2) {
+        if (s + 1 < nfull) {
+          b.load(chunk_base, sb_base, stride, half_sb, queue + 4 * (s + 1));
+        }
+        a.pool(half_sb, weighted, queue + 4 * s, acc);
+        if (s + 1 < nfull) {
+          if (s + 2 < nfull) {
+            a.load(chunk_base, sb_base, stride, half_sb, queue + 4 * (s + 2));
+          }
+          b.pool(half_sb, weighted, queue + 4 * (s + 1), acc);
+        }
+      }
+    } else {
+      for (int s = 0; s < nfull; ++s) {
+        KnownRows<BITS, VEC, CPL, 4> a;
+        a.load(chunk_base, sb_base, stride, half_sb, queue + 4 * s);
+        a.pool(half_sb, weighted, queue + 4 * s, acc);
+      }
+    }
+    int r = 4 * nfull;
+    if (count - r >= 2) {
+      KnownRows<BITS, VEC, CPL, 2> t;
+      t.load(chunk_base, sb_base, stride, half_sb, queue + r);
+      t.pool(half_sb, weighted, queue + r, acc);
+      r += 2;
+    }
+    if (count - r >= 1) {
+      KnownRows<BITS, VEC, CPL, 1> t;
+      t.load(chunk_base, sb_base, stride, half_sb, queue + r);
+      t.pool(half_sb, weighted, queue + r, acc);
+    }
+    __syncwarp(gmask);  // the queue is rewritten by the next stretch
+  }
+
+  if ((p.flags & kNormalize) && bag_len != 0) {
+    const float inv = __fdiv_rn(1.f, (float)bag_len);
+    const u64 inv2 = pack2(inv, inv);
+#pragma unroll
+    for (int ci = 0; ci < CPL; ++ci) {
+#pragma unroll
+      for (int j = 0; j < PAIRS; ++j) {
+        acc[ci][j] = mul2(acc[ci][j], inv2);
+      }
+    }
+  }
+#pragma unroll
+  for (int ci = 0; ci < CPL; ++ci) {
+    const int c = gl + ci * LPB;
+    if (c < nchunks) {
+      store_columns<CPC>(p, bag, c * CPC, acc[ci]);
+    }
+  }
+}
+
 // One table per launch; the parameters travel in constant memory.
 template <int BITS, int VEC, int LPB, int CPL>
 __global__ void __launch_bounds__(kThreads)
@@ -573,12 +820,20 @@ spmdm_direct_multi_kernel(
   direct_block<BITS, VEC, LPB, CPL>(params[t], (int64_t)blockIdx.x - __ldg(first_block + t));
 }
 
+// One table per launch, rows compacted before they are pooled (pruned tables).
+template <int BITS, int VEC, int LPB, int CPL>
+__global__ void __launch_bounds__(kThreads)
+spmdm_direct_compact_kernel(const __grid_constant__ SpmdmParams p) {
+  direct_block_compact<BITS, VEC, LPB, CPL>(p, blockIdx.x);
+}
+
 using KernelFn = void (*)(const SpmdmParams);
 using MultiKernelFn = void (*)(const SpmdmParams*, const int32_t*, const int32_t*);
 
 struct Variant {
   KernelFn fn;
   MultiKernelFn multi;
+  KernelFn compact;
   int vec, lpb, cpl;
 };
 

@@ -516,7 +516,10 @@ static cudaError_t launch_direct(const SpmdmParams& p, int bit_rate, cudaStream_
   if (blocks <= 0 || blocks > 0x7fffffffLL) {
     return cudaErrorInvalidValue;
   }
-  pick->fn<<<(unsigned)blocks, direct::kThreads, 0, stream>>>(p);
+  // Row-wise sparse tables: compact the rows that remain before pooling them
+  // (FBGEMM_B200_COMPACT=0/1 overrides, a tuning aid).
+  const int compact = env_int("FBGEMM_B200_COMPACT", (p.flags & kPruned) ? 1 : 0);
+  (compact ? pick->compact : pick->fn)<<<(unsigned)blocks, direct::kThreads, 0, stream>>>(p);
   g_launch_count.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError();
 }
