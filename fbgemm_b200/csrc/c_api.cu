@@ -901,25 +901,24 @@ int fbgemm_b200_spmdm_host_submit(
     return fail_cuda(e, "lane staging buffers");
   }
   uint8_t* di = static_cast<uint8_t*>(L.d_in.ptr);
-  // Page-locked caller buffers go to the device as they are; pageable ones are
-  // first packed into the lane's pinned block so that the copy stays asynchronous.
-  auto pinned = [](const void* ptr) {
+  // Page-locked caller buffers are read by the GPU where they lie: ONE small
+  // kernel streams indices, offsets and weights into the lane's device block
+  // with wide coalesced loads (three DMA copies of this size spend more time
+  // starting than moving data).  Pageable buffers are first packed into the
+  // lane's pinned block so that the copy stays asynchronous.
+  auto device_view = [](const void* ptr) -> const void* {
     cudaPointerAttributes a{};
     const bool yes = ptr && cudaPointerGetAttributes(&a, ptr) == cudaSuccess && a.type == cudaMemoryTypeHost;
     cudaGetLastError();
-    return yes;
+    return yes ? a.devicePointer : nullptr;
   };
-  if ((!idx_bytes || pinned(indices)) && pinned(offsets_or_lengths) && (!n_w || pinned(weights))) {
-    e = cudaSuccess;
-    if (idx_bytes) {
-      e = cudaMemcpyAsync(di, indices, idx_bytes, cudaMemcpyHostToDevice, L.stream);
-    }
-    if (e == cudaSuccess) {
-      e = cudaMemcpyAsync(di + off_at, offsets_or_lengths, off_bytes, cudaMemcpyHostToDevice, L.stream);
-    }
-    if (e == cudaSuccess && n_w) {
-      e = cudaMemcpyAsync(di + w_at, weights, n_w * sizeof(float), cudaMemcpyHostToDevice, L.stream);
-    }
+  const void* v_idx = idx_bytes ? device_view(indices) : nullptr;
+  const void* v_off = device_view(offsets_or_lengths);
+  const void* v_w = n_w ? device_view(weights) : nullptr;
+  if ((!idx_bytes || v_idx) && v_off && (!n_w || v_w)) {
+    const StageSegment seg[3] = {
+        {v_idx, di, idx_bytes}, {v_off, di + off_at, off_bytes}, {v_w, di + w_at, n_w * sizeof(float)}};
+    e = launch_stage_inputs(seg, L.stream);
   } else {
     if ((e = reserve(L.h_in, in_bytes)) != cudaSuccess) {
       return fail_cuda(e, "lane staging buffers");

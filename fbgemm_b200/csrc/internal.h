@@ -137,6 +137,16 @@ cudaError_t launch_compressed_indices_remap(
     void* scratch,
     cudaStream_t stream);
 
+// One contiguous piece of a call's inputs, from page-locked host memory (the
+// address the GPU sees it at) to device memory; three of them per launch
+// (stage_kernels.cu).  Empty segments have bytes = 0.
+struct StageSegment {
+  const void* src;
+  void* dst;
+  size_t bytes;
+};
+cudaError_t launch_stage_inputs(const StageSegment (&seg)[3], cudaStream_t stream);
+
 // Row-wise quantizers (quantize_kernels.cu).
 cudaError_t launch_quantize_8bit(const float* in, int64_t rows, int cols, uint8_t* out, cudaStream_t s);
 cudaError_t launch_quantize_nbit(int bit_rate, const float* in, int64_t rows, int cols, uint8_t* out, cudaStream_t s);
