@@ -25,6 +25,16 @@
 //  * Integer -> float: each byte / nibble / crumb is planted with one prmt in
 //    the mantissa of 2^23 and 2^23 is subtracted (packed as well).
 //
+// Three kernels share that block-level code:
+//   spmdm_direct_kernel          one table per launch, parameters in constant
+//                                memory;
+//   spmdm_direct_multi_kernel    several tables of one row format per launch,
+//                                each block finding its table in an index array;
+//   spmdm_direct_compact_kernel  row-wise sparse tables: the rows that survive
+//                                the pruning map are first compacted into a
+//                                shared-memory queue, so that only rows that
+//                                exist reach the arithmetic.
+//
 // Requirements (checked by the dispatcher): table address, row pitch and
 // payload width are multiples of VEC (4 or 8 bytes).  Everything else takes
 // the staged kernel.
