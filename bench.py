@@ -45,7 +45,7 @@ TRAFFIC_BYTES_PER_LAUNCH = {
     (1, 1): 13_755_648,             # profiles/spmdm_direct_kernel__workload1_one_batch.md
     (1, 16): 171_206_400 + 8_106_496,   # profiles/spmdm_direct_kernel__workload1_16batches.md
     (0, 16): 438_344_192 + 71_286_528,  # profiles/spmdm_direct_kernel__workload0_16batches.md
-    (2, 16): 234_103_040 + 49_501_952,  # profiles/spmdm_direct_kernel__workload2_16batches.md
+    (2, 16): 233_486_336 + 49_955_840,  # profiles/spmdm_direct_compact_kernel__workload2_16batches.md
 }
 
 
@@ -644,7 +644,7 @@ def main():
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": TRAFFIC_BYTES_PER_LAUNCH.get((args.workload, args.group)),
                          "traffic_source": "dram__bytes_read+write of one ncu capture of this launch shape "
-                                           "(profiles/spmdm_direct_kernel__workload*_*.md)",
+                                           "(profiles/spmdm_direct*_kernel__workload*_*.md)",
                          "peak_source": peak_src, "per_launch_us": per_launch_us,
                          "random_row_gather_ceiling_GBps": ceiling,
                          "frac_of_gather_ceiling": (achieved / ceiling) if ceiling else None,

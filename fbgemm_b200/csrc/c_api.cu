@@ -915,10 +915,26 @@ int fbgemm_b200_spmdm_host_submit(
   const void* v_idx = idx_bytes ? device_view(indices) : nullptr;
   const void* v_off = device_view(offsets_or_lengths);
   const void* v_w = n_w ? device_view(weights) : nullptr;
-  if ((!idx_bytes || v_idx) && v_off && (!n_w || v_w)) {
+  // The kernel's reads slow a concurrent device-to-host DMA down (measured:
+  // 88 -> 104 us per step where 4.2 MB of output leave per 2 MB of input), so
+  // it is used only where the upload is the larger transfer; otherwise the
+  // three pieces go up as DMA copies.
+  const bool all_pinned = (!idx_bytes || v_idx) && v_off && (!n_w || v_w);
+  if (all_pinned && in_bytes > out_bytes) {
     const StageSegment seg[3] = {
         {v_idx, di, idx_bytes}, {v_off, di + off_at, off_bytes}, {v_w, di + w_at, n_w * sizeof(float)}};
     e = launch_stage_inputs(seg, L.stream);
+  } else if (all_pinned) {
+    e = cudaSuccess;
+    if (idx_bytes) {
+      e = cudaMemcpyAsync(di, indices, idx_bytes, cudaMemcpyHostToDevice, L.stream);
+    }
+    if (e == cudaSuccess) {
+      e = cudaMemcpyAsync(di + off_at, offsets_or_lengths, off_bytes, cudaMemcpyHostToDevice, L.stream);
+    }
+    if (e == cudaSuccess && n_w) {
+      e = cudaMemcpyAsync(di + w_at, weights, n_w * sizeof(float), cudaMemcpyHostToDevice, L.stream);
+    }
   } else {
     if ((e = reserve(L.h_in, in_bytes)) != cudaSuccess) {
       return fail_cuda(e, "lane staging buffers");
