@@ -125,6 +125,36 @@ class _Lookups:
                input_stride, int(scale_bias_last), int(no_bag))
         return bool(ok), out
 
+    def spmdm_plain(self, in_kind, block_size, data_size, table, indices, offsets_or_lengths=None,
+                    weights=None, normalize_by_lengths=False, out_kind="f32",
+                    is_weight_positional=False, use_offsets=True, output_stride=-1,
+                    input_stride=-1, scale_bias_last=True, no_bag=False, exponent_bits=4,
+                    exponent_bias=7, output_size=None, index_size=None):
+        """Lookup on a table that is not row-wise quantized.  ``in_kind`` "f32",
+        "f16", "bf16" (``table`` holds uint16 bit patterns) or "fp8" (uint8);
+        ``input_stride`` in elements."""
+        indices = np.ascontiguousarray(indices)
+        if index_size is None:
+            index_size = len(indices)
+        if no_bag:
+            offsets_or_lengths = np.zeros(1, dtype=indices.dtype)
+            if output_size is None:
+                output_size = index_size
+        offsets_or_lengths = np.ascontiguousarray(offsets_or_lengths)
+        if output_size is None:
+            output_size = len(offsets_or_lengths) - (1 if use_offsets else 0)
+        ostride = block_size if output_stride == -1 else output_stride
+        kind = {"f32": 0, "f16": 1, "bf16": 2}[out_kind]
+        ik = {"f32": 1, "f16": 2, "bf16": 3, "fp8": 4}[in_kind]
+        out = np.zeros(max(output_size, 1) * ostride, dtype=np.float32 if kind == 0 else np.uint16)
+        f = self._fn(self.prefix + "_embedding_spmdm_plain", [_int] + _LOOKUP_ARGS + [_int, _int, _int, _int])
+        ok = f(ik, block_size, output_size, index_size, data_size, _ptr(table), _ptr(indices),
+               indices.dtype.itemsize, _ptr(offsets_or_lengths), offsets_or_lengths.dtype.itemsize,
+               _ptr(weights), int(normalize_by_lengths), _ptr(out), kind, int(is_weight_positional),
+               int(use_offsets), output_stride, input_stride, int(scale_bias_last), int(no_bag),
+               exponent_bits, exponent_bias)
+        return bool(ok), out
+
     def spmdm_rowwise_sparse(self, bit_rate, block_size, uncompressed_data_size, table,
                              indices, compressed_indices_table, offsets_or_lengths,
                              weights=None, normalize_by_lengths=False,

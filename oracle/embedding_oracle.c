@@ -441,6 +441,117 @@ done:
 }
 
 /* ------------------------------------------------------------------------- */
+/* Pooled lookup on tables that are NOT row-wise quantized: fp32, fp16, bf16  */
+/* rows (EmbeddingSpMDM_ref<float | float16>, the non-uint8 branch,           */
+/* src/RefImplementations.cc:1347-1424) and FP8 rows (EmbeddingSpMDMFP8_ref,  */
+/* :1543-1615, conversion Float8ToFloat_ref :184-215).  One rounding per row  */
+/* and column: buf[j] = fma(w, float(row[j]), buf[j]).                        */
+/* in_kind: 1 fp32, 2 fp16, 3 bf16, 4 fp8.  input_stride counts ELEMENTS, as  */
+/* the reference's does.  scale_bias_last = 0 only makes -1 a pruned index    */
+/* (not for fp8, whose reference has no such argument).                       */
+/* ------------------------------------------------------------------------- */
+static float oracle_fp8_to_float(uint8_t v, int exponent_bits, int exponent_bias) {
+  const uint32_t sign = ((uint32_t)(v & 0x80)) << 24;
+  float f = bits_f32(((uint32_t)(v & 0x7F)) << (24 - (8 - exponent_bits)));
+  const float multiplier = bits_f32((uint32_t)(127 + (127 - exponent_bias)) << 23); /* 2^(127-bias) */
+  f *= multiplier;
+  return bits_f32(f32_bits(f) | sign);
+}
+
+ORACLE_API int oracle_embedding_spmdm_plain(
+    int in_kind,
+    int64_t block_size,
+    int64_t output_size,
+    int64_t index_size,
+    int64_t data_size,
+    const void* input,
+    const void* indices,
+    int index_bytes,
+    const void* offsets_or_lengths,
+    int offset_bytes,
+    const float* weights,
+    int normalize_by_lengths,
+    void* out,
+    int out_kind,
+    int is_weight_positional,
+    int use_offsets,
+    int64_t output_stride,
+    int64_t input_stride,
+    int scale_bias_last,
+    int no_bag,
+    int exponent_bits,
+    int exponent_bias) {
+  if (in_kind < 1 || in_kind > 4 || (no_bag && in_kind == 4)) {
+    return 0;
+  }
+  if (output_stride == -1) {
+    output_stride = block_size;
+  }
+  if (input_stride == -1) {
+    input_stride = block_size;
+  }
+  float* buf = (float*)malloc(sizeof(float) * (size_t)(block_size > 0 ? block_size : 1));
+  int64_t current = 0;
+  int64_t out_base = 0;
+  int ok = 1;
+  for (int64_t m = 0; m < output_size; ++m) {
+    memset(buf, 0, sizeof(float) * (size_t)block_size);
+    int len = 1;
+    if (!no_bag) {
+      len = use_offsets
+          ? (int)(load_int(offsets_or_lengths, m + 1, offset_bytes) - load_int(offsets_or_lengths, m, offset_bytes))
+          : (int)load_int(offsets_or_lengths, m, offset_bytes);
+      if (current + len > index_size) {
+        ok = 0;
+        goto done;
+      }
+    }
+    for (int i = 0; i < len; ++i, ++current) {
+      const int64_t idx = load_int(indices, current, index_bytes);
+      if (!no_bag && in_kind != 4 && !scale_bias_last && idx == -1) {
+        continue;
+      }
+      if (idx < 0 || idx >= data_size) {
+        ok = 0;
+        goto done;
+      }
+      float w = 1.f;
+      if (weights) {
+        w = weights[no_bag ? m : (is_weight_positional ? i : current)];
+      }
+      for (int64_t j = 0; j < block_size; ++j) {
+        const int64_t at = input_stride * idx + j;
+        float x;
+        if (in_kind == 1) {
+          x = ((const float*)input)[at];
+        } else if (in_kind == 2) {
+          x = oracle_half_to_float(((const uint16_t*)input)[at]);
+        } else if (in_kind == 3) {
+          x = bits_f32(((uint32_t)((const uint16_t*)input)[at]) << 16);
+        } else {
+          x = oracle_fp8_to_float(((const uint8_t*)input)[at], exponent_bits, exponent_bias);
+        }
+        buf[j] = fmaf(w, x, buf[j]);
+      }
+    }
+    if (!no_bag && normalize_by_lengths && len) {
+      const float inv = 1.f / (float)len;
+      for (int64_t j = 0; j < block_size; ++j) {
+        buf[j] *= inv;
+      }
+    }
+    for (int64_t j = 0; j < block_size; ++j) {
+      store_out_kind(out, out_base + j, buf[j], out_kind);
+    }
+    out_base += output_stride;
+  }
+  ok = no_bag ? 1 : (current == index_size);
+done:
+  free(buf);
+  return ok;
+}
+
+/* ------------------------------------------------------------------------- */
 /* Pruned (row-wise sparse) pooled lookup: indices address an uncompressed    */
 /* row space and go through compressed_indices_table; -1 there means the row  */
 /* was pruned: it contributes nothing but still consumes its index/weight     */

@@ -184,6 +184,79 @@ int ref_embedding_spmdm_ex(
   });
 }
 
+// Tables that are not row-wise quantized: fbgemm::EmbeddingSpMDM_ref<float>
+// (in_kind 1), <float16> (2), <uint16_t> with is_bf16_in (3) and
+// fbgemm::EmbeddingSpMDMFP8_ref (4).  input_stride in elements.
+int ref_embedding_spmdm_plain(
+    int in_kind,
+    std::int64_t block_size,
+    std::int64_t output_size,
+    std::int64_t index_size,
+    std::int64_t data_size,
+    const void* input,
+    const void* indices,
+    int index_bytes,
+    const void* offsets_or_lengths,
+    int offset_bytes,
+    const float* weights,
+    int normalize_by_lengths,
+    void* out,
+    int out_kind,
+    int is_weight_positional,
+    int use_offsets,
+    std::int64_t output_stride,
+    std::int64_t input_stride,
+    int scale_bias_last,
+    int no_bag,
+    int exponent_bits,
+    int exponent_bias) {
+  return dispatch_idx_off(index_bytes, offset_bytes, [&](auto i, auto o) {
+    using I = decltype(i);
+    using O = decltype(o);
+    auto run = [&](auto* typed_out) {
+      using Out = std::remove_pointer_t<decltype(typed_out)>;
+      const I* idx = static_cast<const I*>(indices);
+      const O* off = static_cast<const O*>(offsets_or_lengths);
+      if (in_kind == 1) {
+        return (int)fbgemm::EmbeddingSpMDM_ref<float, I, O, Out>(
+            block_size, output_size, index_size, data_size,
+            static_cast<const float*>(input), idx, off, weights,
+            normalize_by_lengths != 0, typed_out, is_weight_positional != 0,
+            use_offsets != 0, output_stride, input_stride,
+            scale_bias_last != 0, no_bag != 0, out_kind == 2, false);
+      }
+      if (in_kind == 2) {
+        return (int)fbgemm::EmbeddingSpMDM_ref<float16, I, O, Out>(
+            block_size, output_size, index_size, data_size,
+            static_cast<const float16*>(input), idx, off, weights,
+            normalize_by_lengths != 0, typed_out, is_weight_positional != 0,
+            use_offsets != 0, output_stride, input_stride,
+            scale_bias_last != 0, no_bag != 0, out_kind == 2, false);
+      }
+      if (in_kind == 3) {
+        // 16-bit storage whose meaning is_bf16_in selects (InType uint16_t;
+        // the float16 struct is always fp16, src/RefImplementations.h:428-440)
+        return (int)fbgemm::EmbeddingSpMDM_ref<std::uint16_t, I, O, Out>(
+            block_size, output_size, index_size, data_size,
+            static_cast<const std::uint16_t*>(input), idx, off, weights,
+            normalize_by_lengths != 0, typed_out, is_weight_positional != 0,
+            use_offsets != 0, output_stride, input_stride,
+            scale_bias_last != 0, no_bag != 0, out_kind == 2, true);
+      }
+      return (int)fbgemm::EmbeddingSpMDMFP8_ref<I, O, Out>(
+          block_size, output_size, index_size, data_size,
+          static_cast<const std::uint8_t*>(input), idx, off, weights,
+          normalize_by_lengths != 0, typed_out, is_weight_positional != 0,
+          use_offsets != 0, output_stride, input_stride, exponent_bits,
+          exponent_bias, out_kind == 2);
+    };
+    if (out_kind == 0) {
+      return run(static_cast<float*>(out));
+    }
+    return run(static_cast<std::uint16_t*>(out));
+  });
+}
+
 // fbgemm::EmbeddingSpMDMRowWiseSparse_ref<uint8_t> (:1617) for bit_rate 8,
 // fbgemm::EmbeddingSpMDMNBitRowWiseSparse_ref (:1746) for 4 and 2.
 int ref_embedding_spmdm_rowwise_sparse(

@@ -1,11 +1,13 @@
 """Generates tests/golden/lookup_ex_golden.npz from the REFERENCE's own code:
 the lookups with the generators' remaining options - rows with fp16 scale,
 bias FIRST and -1 as a pruned index (scale_bias_last = false, the layout of
-table-batched embeddings), bf16 output, padded rows, and no_bag.
+table-batched embeddings), bf16 output, padded rows, and no_bag - and the
+lookups on tables that are not row-wise quantized (fp32, fp16, bf16, fp8 rows).
 
     python tests/golden/make_golden_ex.py
 
-Outputs come from fbgemm::EmbeddingSpMDM_ref / EmbeddingSpMDMNBit_ref compiled
+Outputs come from fbgemm::EmbeddingSpMDM_ref / EmbeddingSpMDMNBit_ref /
+EmbeddingSpMDMFP8_ref compiled
 from the reference tree into oracle/_ref/libfbgemm_ref.so (oracle/Makefile).
 The fixture pins the CPU oracle (tests/test_oracle.py) and the CUDA kernels
 (tests/test_golden_gpu.py); it travels with the repository, the reference
@@ -21,7 +23,7 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
-from helpers import lengths_indices_weights, random_fused_table  # noqa: E402
+from helpers import lengths_indices_weights, random_fused_table, random_plain_table  # noqa: E402
 from oracle import checker  # noqa: E402
 
 KINDS = ("f32", "f16", "bf16")
@@ -80,9 +82,48 @@ def main():
         out[k + "out"] = res[:count * dim]
         n += 1
     out["n_ex"] = np.array(n)
+    # tables that are not row-wise quantized: fp32 / fp16 / bf16 / fp8 rows
+    m = 0
+    for in_kind, batch, rows, dim, avg_len, stride, kind, weighted, normalize, sb_last, no_bag in [
+            ("f32", 9, 200, 64, 10, None, "f32", True, False, True, False),
+            ("f32", 6, 100, 7, 5, 12, "bf16", False, True, False, False),
+            ("f16", 8, 300, 128, 12, None, "f16", True, True, True, False),
+            ("f16", 5, 80, 40, 6, 48, "f32", False, False, False, False),
+            ("bf16", 7, 150, 64, 9, None, "bf16", True, False, True, False),
+            ("fp8", 8, 250, 128, 11, None, "f32", True, False, True, False),
+            ("fp8", 5, 90, 36, 7, 40, "f16", False, True, True, False),
+            ("f32", 0, 120, 32, 0, None, "f16", True, False, True, True),
+            ("f16", 0, 70, 96, 0, None, "f32", False, False, True, True)]:
+        table = random_plain_table(rng, rows, dim, in_kind, stride)
+        if no_bag:
+            cnt = 25
+            indices = rng.integers(0, rows, cnt).astype(np.int64)
+            offsets = np.zeros(1, dtype=np.int64)
+            weights = rng.standard_normal(cnt).astype(np.float32)
+            batch = cnt
+        else:
+            _, offsets, indices, weights, cnt = lengths_indices_weights(rng, batch, rows, avg_len, np.int32, np.int32)
+            if not sb_last:
+                indices[rng.integers(0, cnt, max(1, cnt // 5))] = -1
+        ebits, ebias = (5, 15) if (in_kind == "fp8" and m % 2) else (4, 7)
+        ok, res = ref.spmdm_plain(in_kind, dim, rows, table, indices, None if no_bag else offsets,
+                                  weights if weighted else None, normalize, kind, False, True, -1, table.shape[1],
+                                  sb_last, no_bag, ebits, ebias)
+        assert ok
+        k = f"plain{m}_"
+        out[k + "meta"] = np.array([("f32", "f16", "bf16", "fp8").index(in_kind), batch, rows, dim, int(weighted),
+                                    int(normalize), int(sb_last), int(no_bag), KINDS.index(kind), ebits, ebias],
+                                   dtype=np.int64)
+        out[k + "table"] = table
+        out[k + "indices"] = indices
+        out[k + "offsets"] = offsets
+        out[k + "weights"] = weights
+        out[k + "out"] = res[:batch * dim]
+        m += 1
+    out["n_plain"] = np.array(m)
     path = os.path.join(HERE, "lookup_ex_golden.npz")
     np.savez_compressed(path, **out)
-    print(path, os.path.getsize(path), "bytes;", n, "cases")
+    print(path, os.path.getsize(path), "bytes;", n, "quantized-row cases,", m, "plain-row cases")
 
 
 if __name__ == "__main__":

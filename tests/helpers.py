@@ -66,3 +66,20 @@ def mapping_table(rng, rows, sparsity):
     m = np.full(rows, -1, dtype=np.int32)
     m[~pruned] = np.arange(int((~pruned).sum()), dtype=np.int32)
     return m, int((~pruned).sum())
+
+
+def random_plain_table(rng, rows, dim, in_kind, stride=None):
+    """A table that is not row-wise quantized, [rows, stride] elements:
+    "f32" float32, "f16"/"bf16" uint16 bit patterns of N(0,1) values (plus a few
+    subnormals and zeros), "fp8" every uint8 pattern."""
+    stride = stride or dim
+    x = rng.standard_normal((rows, stride)).astype(np.float32)
+    x[rng.integers(0, rows, 3), rng.integers(0, stride, 3)] = 0.0
+    if in_kind == "f32":
+        return x
+    if in_kind == "f16":
+        x[0, 0] = 3e-7  # a half subnormal
+        return x.astype(np.float16).view(np.uint16)
+    if in_kind == "bf16":
+        return (x.view(np.uint32) >> 16).astype(np.uint16)
+    return rng.integers(0, 256, (rows, stride), dtype=np.uint8)

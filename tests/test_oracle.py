@@ -8,7 +8,8 @@ import numpy as np
 import pytest
 
 from conftest import bits
-from helpers import REFERENCE_SHAPES, lengths_indices_weights, mapping_table, random_fused_table
+from helpers import (REFERENCE_SHAPES, lengths_indices_weights, mapping_table, random_fused_table,
+                     random_plain_table)
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "lookup_golden.npz")
 
@@ -137,6 +138,30 @@ def test_oracle_ex_matches_reference_fixtures(oracle):
         np.testing.assert_array_equal(bits(got), bits(want))
 
 
+IN_KINDS = ("f32", "f16", "bf16", "fp8")
+
+
+def run_plain_fixture(lookups, ex, i):
+    """One plain-row case of lookup_ex_golden.npz through `lookups.spmdm_plain`."""
+    k = f"plain{i}_"
+    in_kind, count, rows, dim, weighted, normalize, sb_last, no_bag, kind, ebits, ebias = (int(v) for v in ex[k + "meta"])
+    table = ex[k + "table"]
+    ok, got = lookups.spmdm_plain(IN_KINDS[in_kind], dim, rows, table, ex[k + "indices"],
+                                  None if no_bag else ex[k + "offsets"], ex[k + "weights"] if weighted else None,
+                                  bool(normalize), KINDS[kind], False, True, -1, table.shape[1], bool(sb_last),
+                                  bool(no_bag), ebits, ebias)
+    return ok, got[:count * dim], ex[k + "out"]
+
+
+def test_oracle_plain_rows_match_reference_fixtures(oracle):
+    ex = np.load(os.path.join(os.path.dirname(GOLDEN), "lookup_ex_golden.npz"))
+    assert int(ex["n_plain"]) >= 9
+    for i in range(int(ex["n_plain"])):
+        ok, got, want = run_plain_fixture(oracle, ex, i)
+        assert ok
+        np.testing.assert_array_equal(bits(got), bits(want))
+
+
 # ---- live against the reference's own code ------------------------------------------
 
 @pytest.mark.parametrize("bit_rate", [8, 4, 2])
@@ -237,3 +262,35 @@ def test_oracle_ex_matches_reference_live(oracle, reference, bit_rate):
                                            sb_last, True)[0]
                 assert not reference.spmdm_ex(8, dim, rows, table, indices, None, None, False, "f32", False, True, -1, -1,
                                               sb_last, True)[0]
+
+
+@pytest.mark.parametrize("in_kind", IN_KINDS)
+def test_oracle_plain_rows_match_reference_live(oracle, reference, in_kind):
+    rng = np.random.default_rng(240 + IN_KINDS.index(in_kind))
+    for shape_i, (batch, rows, dim, avg_len) in enumerate(REFERENCE_SHAPES[2:14]):
+        for corner in (None, "oob"):
+            idt = (np.int32, np.int64)[shape_i % 2]
+            sb_last = shape_i % 3 != 0
+            table = random_plain_table(rng, rows, dim, in_kind)
+            lengths, offsets, indices, weights, n = lengths_indices_weights(rng, batch, rows, avg_len, idt, idt, corner)
+            if corner is None and not sb_last and in_kind != "fp8":
+                indices[rng.integers(0, n, max(1, n // 6))] = -1
+            ebits, ebias = ((4, 7), (5, 15))[shape_i % 2]
+            for kind, weighted, normalize, use_offsets in (("f32", False, True, True), ("bf16", True, False, False),
+                                                           ("f16", True, True, True)):
+                ol = offsets if use_offsets else lengths
+                args = (in_kind, dim, rows, table, indices, ol, weights if weighted else None, normalize, kind, False,
+                        use_offsets, -1, -1, sb_last, False, ebits, ebias)
+                a = oracle.spmdm_plain(*args, output_size=batch, index_size=n)
+                b = reference.spmdm_plain(*args, output_size=batch, index_size=n)
+                assert a[0] == b[0] == (corner is None)
+                if a[0]:
+                    np.testing.assert_array_equal(bits(a[1]), bits(b[1]))
+        if in_kind != "fp8":
+            table = random_plain_table(rng, rows, dim, in_kind)
+            indices = rng.integers(0, rows, 2 * batch).astype(np.int64)
+            weights = rng.standard_normal(2 * batch).astype(np.float32)
+            args = (in_kind, dim, rows, table, indices, None, weights, True, "f16", False, True, -1, -1, True, True)
+            a, b = oracle.spmdm_plain(*args), reference.spmdm_plain(*args)
+            assert a[0] and b[0]
+            np.testing.assert_array_equal(bits(a[1]), bits(b[1]))
