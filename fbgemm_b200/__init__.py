@@ -19,6 +19,7 @@ from .embedding import (  # noqa: F401
     FloatToFused8BitRowwiseQuantizedSBFloat,
     FloatToFusedNBitRowwiseQuantizedSBHalf,
     GenerateEmbeddingSpMDM,
+    GenerateEmbeddingSpMDMFP8WithStrides,
     GenerateEmbeddingSpMDMNBit,
     GenerateEmbeddingSpMDMNBitRowWiseSparse,
     GenerateEmbeddingSpMDMNBitWithStrides,

@@ -40,7 +40,9 @@ class SpmdmConfig(C.Structure):
         ("scale_bias_first", C.c_int32),
         ("no_bag", C.c_int32),
         ("absolute_offsets", C.c_int32),
-        ("reserved_", C.c_int32),
+        ("in_dtype", C.c_int32),
+        ("fp8_exponent_bits", C.c_int32),
+        ("fp8_exponent_bias", C.c_int32),
     ]
 
 

@@ -142,7 +142,7 @@ int check_config(const fbgemm_b200_spmdm_config* c, Derived* d) {
     set_error("null config");
     return FBGEMM_B200_EINVAL;
   }
-  if (c->bit_rate != 8 && c->bit_rate != 4 && c->bit_rate != 2) {
+  if (c->in_dtype == FBGEMM_B200_IN_QUANTIZED && c->bit_rate != 8 && c->bit_rate != 4 && c->bit_rate != 2) {
     set_error("bit_rate must be 8, 4 or 2");
     return FBGEMM_B200_EINVAL;
   }
@@ -159,7 +159,7 @@ int check_config(const fbgemm_b200_spmdm_config* c, Derived* d) {
     set_error("absolute_offsets goes with use_offsets, bags and per-index weights");
     return FBGEMM_B200_EINVAL;
   }
-  if (c->no_bag && c->bit_rate != 8) {
+  if (c->no_bag && c->bit_rate != 8 && c->in_dtype == FBGEMM_B200_IN_QUANTIZED) {
     // EmbeddingSpMDMNBit_ref: "no_bag is only supported for int4 to int4", a raw row copy
     set_error("no_bag is provided for 8-bit rows with fp32/fp16/bf16 output");
     return FBGEMM_B200_EINVAL;
@@ -168,17 +168,29 @@ int check_config(const fbgemm_b200_spmdm_config* c, Derived* d) {
     set_error("block_size out of range");
     return FBGEMM_B200_EINVAL;
   }
-  const int epb = 8 / c->bit_rate;
-  const int64_t data_bytes = (c->block_size + epb - 1) / epb;
-  if ((data_bytes + 3) / 4 > max_chunks_per_bag(c->bit_rate)) {
+  const bool plain = c->in_dtype != FBGEMM_B200_IN_QUANTIZED;
+  if (c->in_dtype < 0 || c->in_dtype > FBGEMM_B200_IN_FP8) {
+    set_error("unknown in_dtype");
+    return FBGEMM_B200_EINVAL;
+  }
+  if (c->in_dtype == FBGEMM_B200_IN_FP8 &&
+      (c->fp8_exponent_bits < 1 || c->fp8_exponent_bits > 7 || c->fp8_exponent_bias < 0 || c->fp8_exponent_bias > 253 ||
+       c->no_bag || c->scale_bias_first)) {
+    set_error("FP8 rows: exponent_bits 1..7, exponent_bias 0..253, bags only");
+    return FBGEMM_B200_EINVAL;
+  }
+  const int ebytes = c->in_dtype == FBGEMM_B200_IN_F32 ? 4 : (c->in_dtype == FBGEMM_B200_IN_FP8 ? 1 : 2);
+  const int epb = plain ? 1 : 8 / c->bit_rate;
+  const int64_t data_bytes = plain ? c->block_size * ebytes : (c->block_size + epb - 1) / epb;
+  if (!plain && (data_bytes + 3) / 4 > max_chunks_per_bag(c->bit_rate)) {
     set_error("block_size too large for the sm_100a kernels (1024 columns at most)");
     return FBGEMM_B200_EINVAL;
   }
-  const int sb_bytes = (c->bit_rate == 8 && !c->scale_bias_first) ? 8 : 4;
+  const int sb_bytes = plain ? 0 : ((c->bit_rate == 8 && !c->scale_bias_first) ? 8 : 4);
   const int64_t in_stride = c->input_stride == -1 ? data_bytes + sb_bytes : c->input_stride;
   const int64_t out_stride = c->output_stride == -1 ? c->block_size : c->output_stride;
-  if (in_stride < data_bytes + sb_bytes) {
-    set_error("input_stride smaller than a fused row");
+  if (in_stride < data_bytes + sb_bytes || (plain && in_stride % ebytes != 0)) {
+    set_error("input_stride smaller than a row (or not a whole number of elements)");
     return FBGEMM_B200_EINVAL;
   }
   if (out_stride < c->block_size) {
@@ -254,6 +266,16 @@ int fbgemm_b200::build_lookup_params(
   p.output_size = output_size;
   p.index_size = index_size;
   p.block_size = (int32_t)cfg->block_size;
+  p.in_kind = cfg->in_dtype;
+  p.fp8_exponent_bits = cfg->fp8_exponent_bits;
+  p.fp8_exponent_bias = cfg->fp8_exponent_bias;
+  if (cfg->in_dtype != FBGEMM_B200_IN_QUANTIZED) {
+    const int ebytes = cfg->in_dtype == FBGEMM_B200_IN_F32 ? 4 : (cfg->in_dtype == FBGEMM_B200_IN_FP8 ? 1 : 2);
+    if (cit || reinterpret_cast<uintptr_t>(input) % ebytes != 0) {
+      set_error("unquantized tables: no pruning map, and the table must be aligned to its element type");
+      return FBGEMM_B200_EINVAL;
+    }
+  }
   p.data_bytes = d.data_bytes;
   p.row_bytes = d.data_bytes + d.sb_bytes;
   p.data_row_off = cfg->scale_bias_first ? d.sb_bytes : 0;

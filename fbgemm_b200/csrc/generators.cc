@@ -70,7 +70,10 @@ fbgemm_b200_spmdm_config make_config(
     std::int64_t input_stride,
     bool scale_bias_last = true,
     bool no_bag = false,
-    bool is_bf16_out = false) {
+    bool is_bf16_out = false,
+    int in = FBGEMM_B200_IN_QUANTIZED,
+    int fp8_exponent_bits = 0,
+    int fp8_exponent_bias = 0) {
   fbgemm_b200_spmdm_config c{};
   c.bit_rate = bit_rate;
   c.index_bytes = index_bytes;
@@ -80,6 +83,9 @@ fbgemm_b200_spmdm_config make_config(
   c.out_dtype = (is_bf16_out && out_dt == FBGEMM_B200_OUT_F16) ? FBGEMM_B200_OUT_BF16 : out_dt;
   c.scale_bias_first = !scale_bias_last;
   c.no_bag = no_bag;
+  c.in_dtype = in;
+  c.fp8_exponent_bits = fp8_exponent_bits;
+  c.fp8_exponent_bias = fp8_exponent_bias;
   c.block_size = block_size;
   c.output_stride = output_stride;
   c.input_stride = input_stride;
@@ -155,6 +161,27 @@ void InvalidateTable(const void* host_table, int device) {
   fbgemm_b200_table_unregister(GetContext(device), host_table);
 }
 
+// InType of the 8-bit generator: the fused quantized row (uint8_t) or a table
+// that is not quantized (float, float16, or 16-bit storage that is_bf16_in
+// makes bf16 - convert_to_float_ref, src/RefImplementations.h:428-440).
+template <typename InType>
+int in_dtype(bool is_bf16_in) {
+  static_assert(
+      std::is_same<InType, std::uint8_t>::value || std::is_same<InType, float>::value ||
+          std::is_same<InType, float16>::value || std::is_same<InType, std::uint16_t>::value,
+      "InType must be uint8_t, float, float16 or uint16_t");
+  if (std::is_same<InType, std::uint8_t>::value) {
+    if (is_bf16_in) {
+      throw std::invalid_argument("fbgemm_b200: is_bf16_in belongs to 16-bit tables");
+    }
+    return FBGEMM_B200_IN_QUANTIZED;
+  }
+  if (std::is_same<InType, float>::value) {
+    return FBGEMM_B200_IN_F32;
+  }
+  return (std::is_same<InType, std::uint16_t>::value && is_bf16_in) ? FBGEMM_B200_IN_BF16 : FBGEMM_B200_IN_F16;
+}
+
 template <typename InType, typename IndexType, typename OffsetType, typename OutType, bool THREAD_LOCAL>
 typename EmbeddingSpMDMKernelSignature<InType, IndexType, OffsetType, OutType>::Type
 GenerateEmbeddingSpMDMWithStrides(
@@ -170,14 +197,13 @@ GenerateEmbeddingSpMDMWithStrides(
     bool no_bag,
     bool is_bf16_out,
     bool is_bf16_in) {
-  static_assert(std::is_same<InType, std::uint8_t>::value, "only fused 8-bit rows (InType = uint8_t)");
-  if (is_bf16_in) {
-    throw std::invalid_argument("fbgemm_b200: is_bf16_in belongs to unquantized tables, which this path does not take");
-  }
+  const int in = in_dtype<InType>(is_bf16_in);
+  // the reference counts input_stride in elements of InType, the C ABI in bytes
+  const std::int64_t stride_bytes = input_stride == -1 ? -1 : input_stride * (std::int64_t)sizeof(InType);
   const fbgemm_b200_spmdm_config cfg = make_config(
       8, sizeof(IndexType), sizeof(OffsetType), out_dtype<OutType>(), block_size, has_weight,
-      normalize_by_lengths, is_weight_positional, use_offsets, output_stride, input_stride, scale_bias_last, no_bag,
-      is_bf16_out);
+      normalize_by_lengths, is_weight_positional, use_offsets, output_stride, stride_bytes, scale_bias_last, no_bag,
+      is_bf16_out, in);
   return [cfg](
              std::int64_t output_size,
              std::int64_t index_size,
@@ -188,6 +214,38 @@ GenerateEmbeddingSpMDMWithStrides(
              const float* weights,
              OutType* out) {
     return call(cfg, output_size, index_size, data_size, input, indices, offsets_or_lengths, weights, out, nullptr);
+  };
+}
+
+template <typename IndexType, typename OffsetType, typename OutType>
+typename EmbeddingSpMDMKernelSignature<std::uint8_t, IndexType, OffsetType, OutType>::Type
+GenerateEmbeddingSpMDMFP8WithStrides(
+    const std::int64_t block_size,
+    bool normalize_by_lengths,
+    bool is_weight_positional,
+    bool use_offsets,
+    std::int64_t output_stride,
+    std::int64_t input_stride,
+    int exponent_bits,
+    int exponent_bias,
+    bool is_bf16_out) {
+  fbgemm_b200_spmdm_config plain = make_config(
+      8, sizeof(IndexType), sizeof(OffsetType), out_dtype<OutType>(), block_size, false, normalize_by_lengths,
+      is_weight_positional, use_offsets, output_stride, input_stride, true, false, is_bf16_out, FBGEMM_B200_IN_FP8,
+      exponent_bits, exponent_bias);
+  fbgemm_b200_spmdm_config weighted = plain;
+  weighted.has_weight = 1;
+  return [plain, weighted](
+             std::int64_t output_size,
+             std::int64_t index_size,
+             std::int64_t data_size,
+             const std::uint8_t* input,
+             const IndexType* indices,
+             const OffsetType* offsets_or_lengths,
+             const float* weights,
+             OutType* out) {
+    return call(weights ? weighted : plain, output_size, index_size, data_size, input, indices, offsets_or_lengths,
+                weights, out, nullptr);
   };
 }
 
@@ -330,13 +388,24 @@ GenerateEmbeddingSpMDMNBitRowWiseSparse(
 
 // ---- explicit instantiations -------------------------------------------------
 
-#define INST_8BIT(IDX, OFF, OUT, TL)                                                                           \
-  template FBGEMM_B200_API typename EmbeddingSpMDMKernelSignature<std::uint8_t, IDX, OFF, OUT>::Type           \
-  GenerateEmbeddingSpMDM<std::uint8_t, IDX, OFF, OUT, TL>(                                                     \
-      const std::int64_t, bool, bool, int, bool, bool, bool, bool);                                            \
-  template FBGEMM_B200_API typename EmbeddingSpMDMKernelSignature<std::uint8_t, IDX, OFF, OUT>::Type           \
-  GenerateEmbeddingSpMDMWithStrides<std::uint8_t, IDX, OFF, OUT, TL>(                                          \
+#define INST_IN(IN, IDX, OFF, OUT, TL)                                                               \
+  template FBGEMM_B200_API typename EmbeddingSpMDMKernelSignature<IN, IDX, OFF, OUT>::Type           \
+  GenerateEmbeddingSpMDM<IN, IDX, OFF, OUT, TL>(                                                     \
+      const std::int64_t, bool, bool, int, bool, bool, bool, bool);                                  \
+  template FBGEMM_B200_API typename EmbeddingSpMDMKernelSignature<IN, IDX, OFF, OUT>::Type           \
+  GenerateEmbeddingSpMDMWithStrides<IN, IDX, OFF, OUT, TL>(                                          \
       const std::int64_t, bool, bool, int, bool, bool, std::int64_t, std::int64_t, bool, bool, bool, bool);
+
+#define INST_8BIT(IDX, OFF, OUT, TL)        \
+  INST_IN(std::uint8_t, IDX, OFF, OUT, TL)  \
+  INST_IN(float, IDX, OFF, OUT, TL)         \
+  INST_IN(float16, IDX, OFF, OUT, TL)       \
+  INST_IN(std::uint16_t, IDX, OFF, OUT, TL)
+
+#define INST_FP8(IDX, OFF, OUT)                                                                      \
+  template FBGEMM_B200_API typename EmbeddingSpMDMKernelSignature<std::uint8_t, IDX, OFF, OUT>::Type \
+  GenerateEmbeddingSpMDMFP8WithStrides<IDX, OFF, OUT>(                                               \
+      const std::int64_t, bool, bool, bool, std::int64_t, std::int64_t, int, int, bool);
 
 #define INST_NBIT(IDX, OFF, OUT)                                                                               \
   template FBGEMM_B200_API typename EmbeddingSpMDMKernelSignature<std::uint8_t, IDX, OFF, OUT>::Type           \
@@ -366,6 +435,9 @@ GenerateEmbeddingSpMDMNBitRowWiseSparse(
   INST_NBIT(IDX, OFF, float)               \
   INST_NBIT(IDX, OFF, std::uint16_t)       \
   INST_NBIT(IDX, OFF, float16)             \
+  INST_FP8(IDX, OFF, float)                \
+  INST_FP8(IDX, OFF, std::uint16_t)        \
+  INST_FP8(IDX, OFF, float16)              \
   INST_SPARSE(IDX, OFF)
 
 INST_OUT(std::int32_t, std::int32_t)

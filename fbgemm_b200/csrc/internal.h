@@ -55,6 +55,11 @@ struct SpmdmParams {
   int32_t group_smem;         // shared-memory bytes per bag slot
   int32_t copy_width;         // 16/8/4: cp.async granule; 0: byte-wise path
   uint32_t flags;
+  // Tables that are not row-wise quantized (plain_kernels.cu): 0 = quantized,
+  // else FBGEMM_B200_IN_F32 / _F16 / _BF16 / _FP8 and the FP8 format.
+  int32_t in_kind;
+  int32_t fp8_exponent_bits;
+  int32_t fp8_exponent_bias;
   // Batch-wise redistribution of the pooled rows (table-wise sharding): when
   // num_peers > 0, bag b is written to peer_out[b / bags_per_peer] at row
   // b % bags_per_peer instead of `out`.  The pointers may be peer-GPU memory.
@@ -105,6 +110,9 @@ struct MultiPlan {
 };
 cudaError_t build_multi_plan(const std::vector<SpmdmParams>& tables, const std::vector<int>& bit_rates, MultiPlan* plan);
 cudaError_t launch_multi_plan(const MultiPlan& plan, cudaStream_t stream);
+
+// The lookup on a table that is not row-wise quantized (plain_kernels.cu).
+cudaError_t launch_plain_rows(const SpmdmParams& p, cudaStream_t stream);
 
 // Exclusive scan of `n` int32/int64 lengths into int64 offsets[n + 1]
 // (scan_kernels.cu).  `block_sums` is scratch of scan_scratch_elems(n) int64.

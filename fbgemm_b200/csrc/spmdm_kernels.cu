@@ -444,6 +444,9 @@ int max_chunks_per_bag(int bit_rate) {
 // The variant of the direct kernel (spmdm_direct.cuh) for this call, or null
 // when the rows do not allow 4- or 8-byte vector loads.
 static const direct::Variant* pick_direct(const SpmdmParams& p, int bit_rate) {
+  if (p.in_kind != 0) {
+    return nullptr;  // not a quantized row format
+  }
   const uintptr_t base = reinterpret_cast<uintptr_t>(p.table);
   auto divides = [&](int v) {
     return base % 4 == 0 && (base + p.data_row_off) % v == 0 && p.input_stride % v == 0 && p.data_bytes % v == 0;
@@ -674,6 +677,9 @@ cudaError_t launch_multi_plan(const MultiPlan& plan, cudaStream_t stream) {
 }
 
 cudaError_t launch_spmdm(const SpmdmParams& p_in, int bit_rate, cudaStream_t stream) {
+  if (p_in.in_kind != 0) {
+    return launch_plain_rows(p_in, stream);
+  }
   const char* force = std::getenv("FBGEMM_B200_KERNEL");
   if (!(force && std::strcmp(force, "staged") == 0)) {  // forces the generic kernel (tuning aid)
     const cudaError_t e = launch_direct(p_in, bit_rate, stream);

@@ -281,32 +281,91 @@ def _config(bit_rate, block_size, has_weight, normalize_by_lengths, is_weight_po
     )
 
 
-def _reject(no_bag=False, is_bf16_in=False):
-    if no_bag or is_bf16_in:
-        raise ValueError("N-bit no_bag and unquantized (bf16) tables are not provided by the sm_100a path")
+def _reject(no_bag=False):
+    if no_bag:
+        raise ValueError("N-bit no_bag (an int4 -> int4 row copy) is not provided by the sm_100a path")
+
+
+def _in_code(in_dtype, is_bf16_in) -> tuple[int, int]:
+    """(FBGEMM_B200_IN_* code, element bytes) of the generators' InType:
+    uint8 = fused 8-bit rows, float32, float16, or uint16 / bfloat16 storage
+    (bf16 when is_bf16_in, as convert_to_float_ref reads it)."""
+    try:
+        name = np.dtype(in_dtype).name
+    except TypeError:
+        name = str(in_dtype).rsplit(".", 1)[-1]
+    if name == "uint8":
+        if is_bf16_in:
+            raise ValueError("is_bf16_in belongs to 16-bit tables")
+        return 0, 1
+    if name == "float32":
+        return 1, 4
+    if name == "bfloat16" or (name == "uint16" and is_bf16_in):
+        return 3, 2
+    if name in ("float16", "uint16"):
+        return 2, 2
+    raise ValueError(f"InType must be uint8, float32, float16 or bfloat16, got {in_dtype}")
 
 
 def GenerateEmbeddingSpMDM(block_size, has_weight, normalize_by_lengths, prefetch=16,
                            is_weight_positional=False, use_offsets=True, is_bf16_out=False, is_bf16_in=False, *,
-                           index_dtype=np.int64, offset_dtype=np.int32, out_dtype=np.float32) -> SpmdmKernel:
-    """fbgemm::GenerateEmbeddingSpMDM<uint8_t, Index, Offset, Out>
-    (include/fbgemm/FbgemmEmbedding.h:65-84): 8-bit rows + fp32 scale, bias."""
+                           index_dtype=np.int64, offset_dtype=np.int32, out_dtype=np.float32,
+                           in_dtype=np.uint8) -> SpmdmKernel:
+    """fbgemm::GenerateEmbeddingSpMDM<InType, Index, Offset, Out>
+    (include/fbgemm/FbgemmEmbedding.h:65-84): InType uint8_t = 8-bit rows +
+    fp32 scale, bias; float / float16 / uint16_t = tables that are not quantized."""
     return GenerateEmbeddingSpMDMWithStrides(
         block_size, has_weight, normalize_by_lengths, prefetch, is_weight_positional, use_offsets, -1, -1, True,
-        False, is_bf16_out, is_bf16_in, index_dtype=index_dtype, offset_dtype=offset_dtype, out_dtype=out_dtype)
+        False, is_bf16_out, is_bf16_in, index_dtype=index_dtype, offset_dtype=offset_dtype, out_dtype=out_dtype,
+        in_dtype=in_dtype)
 
 
 def GenerateEmbeddingSpMDMWithStrides(block_size, has_weight, normalize_by_lengths, prefetch=16,
                                       is_weight_positional=False, use_offsets=True, output_stride=-1,
                                       input_stride=-1, scale_bias_last=True, no_bag=False, is_bf16_out=False,
                                       is_bf16_in=False, *, index_dtype=np.int64, offset_dtype=np.int32,
-                                      out_dtype=np.float32) -> SpmdmKernel:
-    """fbgemm::GenerateEmbeddingSpMDMWithStrides<uint8_t, ...>
-    (include/fbgemm/FbgemmEmbedding.h:94-117)."""
-    _reject(False, is_bf16_in)
-    return SpmdmKernel(_config(8, block_size, has_weight, normalize_by_lengths, is_weight_positional, use_offsets,
-                               output_stride, input_stride, index_dtype, offset_dtype, out_dtype, scale_bias_last,
-                               no_bag, is_bf16_out), False)
+                                      out_dtype=np.float32, in_dtype=np.uint8) -> SpmdmKernel:
+    """fbgemm::GenerateEmbeddingSpMDMWithStrides<InType, ...>
+    (include/fbgemm/FbgemmEmbedding.h:94-117).  ``input_stride`` counts
+    elements of InType, as the reference's does."""
+    code, ebytes = _in_code(in_dtype, is_bf16_in)
+    stride_bytes = input_stride if input_stride == -1 else input_stride * ebytes
+    cfg = _config(8, block_size, has_weight, normalize_by_lengths, is_weight_positional, use_offsets, output_stride,
+                  stride_bytes, index_dtype, offset_dtype, out_dtype, scale_bias_last, no_bag, is_bf16_out)
+    cfg.in_dtype = code
+    return SpmdmKernel(cfg, False)
+
+
+class _Fp8Kernel:
+    """The functor of GenerateEmbeddingSpMDMFP8WithStrides: whether the rows are
+    weighted is decided by the call (weights null or not), not by the generator."""
+
+    def __init__(self, make):
+        self._k = {False: make(False), True: make(True)}
+        self.cfg = self._k[False].cfg
+
+    def __call__(self, output_size, index_size, data_size, input, indices, offsets_or_lengths, weights, out):
+        return self._k[weights is not None](output_size, index_size, data_size, input, indices, offsets_or_lengths,
+                                            weights, out)
+
+    def launch(self, output_size, index_size, data_size, input, indices, offsets_or_lengths, weights, out, **kw):
+        return self._k[weights is not None].launch(output_size, index_size, data_size, input, indices,
+                                                   offsets_or_lengths, weights, out, **kw)
+
+
+def GenerateEmbeddingSpMDMFP8WithStrides(block_size, normalize_by_lengths, is_weight_positional=False,
+                                         use_offsets=True, output_stride=-1, input_stride=-1, exponent_bits=4,
+                                         exponent_bias=7, is_bf16_out=False, *, index_dtype=np.int64,
+                                         offset_dtype=np.int32, out_dtype=np.float32) -> _Fp8Kernel:
+    """fbgemm::GenerateEmbeddingSpMDMFP8WithStrides (include/fbgemm/FbgemmEmbedding.h:185-203):
+    rows of FP8 values, no scale or bias."""
+    def make(weighted):
+        cfg = _config(8, block_size, weighted, normalize_by_lengths, is_weight_positional, use_offsets, output_stride,
+                      input_stride, index_dtype, offset_dtype, out_dtype, True, False, is_bf16_out)
+        cfg.in_dtype = 4
+        cfg.fp8_exponent_bits, cfg.fp8_exponent_bias = exponent_bits, exponent_bias
+        return SpmdmKernel(cfg, False)
+    return _Fp8Kernel(make)
 
 
 def GenerateEmbeddingSpMDMNBit(bit_rate, block_size, has_weight, normalize_by_lengths, prefetch=16,

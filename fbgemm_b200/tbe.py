@@ -15,10 +15,11 @@ their addresses, one multi-table plan that is built once and replayed.
 
 Rows are INT8 / INT4 / INT2 with fp16 scale and bias *first* (the layout of
 table-batched embeddings, ``scale_bias_last = False``), or scale and bias last
-(fp32 pair for INT8) when ``scale_bias_last = True``; each row padded to
-``row_alignment`` bytes.  An index of -1 is a pruned row.  Output FP32, FP16
-or BF16 of shape ``[B, total_D]``.  Unquantized (FP32/FP16/FP8) tables and
-INT8/INT4 output belong to other kernels of the reference and are refused.
+(fp32 pair for INT8) when ``scale_bias_last = True``, or FP32 / FP16 / FP8
+values without scale and bias; each row padded to ``row_alignment`` bytes.  An
+index of -1 is a pruned row (not for FP8, as in the reference).  Output FP32,
+FP16 or BF16 of shape ``[B, total_D]``; INT8/INT4 output belongs to the
+reference's nobag operator and is refused.
 """
 from __future__ import annotations
 
@@ -49,13 +50,17 @@ class PoolingMode(enum.IntEnum):
 
 
 _BITS = {SparseType.INT8: 8, SparseType.INT4: 4, SparseType.INT2: 2}
+_PLAIN_BYTES = {SparseType.FP32: 4, SparseType.FP16: 2, SparseType.FP8: 1}
 _OUT = {SparseType.FP32: torch.float32, SparseType.FP16: torch.float16, SparseType.BF16: torch.bfloat16}
 
 
 def padded_row_size_in_bytes(dim: int, weight_ty: SparseType, row_alignment: int, scale_bias_bytes: int = 4) -> int:
-    """nbit::padded_row_size_in_bytes (embedding_common.h:189-225) for the quantized types."""
-    bits = _BITS[SparseType(weight_ty)]
-    unpadded = dim * bits // 8 + scale_bias_bytes
+    """nbit::padded_row_size_in_bytes (embedding_common.h:189-225)."""
+    weight_ty = SparseType(weight_ty)
+    if weight_ty in _PLAIN_BYTES:
+        unpadded = dim * _PLAIN_BYTES[weight_ty]
+    else:
+        unpadded = dim * _BITS[weight_ty] // 8 + scale_bias_bytes
     return (unpadded + row_alignment - 1) // row_alignment * row_alignment
 
 
@@ -71,7 +76,8 @@ class IntNBitTableBatchedEmbeddingBags:
 
     def __init__(self, dev_weights: torch.Tensor, weights_offsets, weights_tys, D_offsets, total_D: int,
                  pooling_mode: int = PoolingMode.SUM, row_alignment: int = 1, output_dtype: int = SparseType.FP16,
-                 scale_bias_last: bool = False, weighted: bool = False, index_dtype=torch.int32):
+                 scale_bias_last: bool = False, weighted: bool = False, index_dtype=torch.int32,
+                 fp8_exponent_bits: int = 4, fp8_exponent_bias: int = 7):
         assert dev_weights.is_cuda and dev_weights.dtype == torch.uint8 and dev_weights.is_contiguous()
         self.dev_weights = dev_weights
         self.device = dev_weights.device
@@ -94,8 +100,8 @@ class IntNBitTableBatchedEmbeddingBags:
         self.kernels, self.rows, self.tables = [], [], []
         for t in range(self.T):
             ty = self.weights_tys[t]
-            if ty not in _BITS:
-                raise ValueError(f"table {t}: weight type {ty.name} is not a quantized row format of this path")
+            if ty not in _BITS and ty not in _PLAIN_BYTES:
+                raise ValueError(f"table {t}: weight type {ty.name} is not a row format of this path")
             D = int(self.D_offsets[t + 1] - self.D_offsets[t])
             sb_bytes = 8 if (ty == SparseType.INT8 and scale_bias_last) else 4
             D_bytes = padded_row_size_in_bytes(D, ty, row_alignment, sb_bytes)
@@ -111,6 +117,15 @@ class IntNBitTableBatchedEmbeddingBags:
             if ty == SparseType.INT8:
                 k = E.GenerateEmbeddingSpMDMWithStrides(D, self.weighted, self.normalize, 16, False, True, self.total_D,
                                                         D_bytes, scale_bias_last, False, bf16, **kw)
+            elif ty in (SparseType.FP32, SparseType.FP16):
+                eb = _PLAIN_BYTES[ty]
+                k = E.GenerateEmbeddingSpMDMWithStrides(
+                    D, self.weighted, self.normalize, 16, False, True, self.total_D, D_bytes // eb, scale_bias_last,
+                    False, bf16, in_dtype=np.float32 if ty == SparseType.FP32 else np.float16, **kw)
+            elif ty == SparseType.FP8:
+                k = E.GenerateEmbeddingSpMDMFP8WithStrides(D, self.normalize, False, True, self.total_D, D_bytes,
+                                                           fp8_exponent_bits, fp8_exponent_bias, bf16, **kw)
+                k = k._k[self.weighted]
             else:
                 k = E.GenerateEmbeddingSpMDMNBitWithStrides(_BITS[ty], D, self.weighted, self.normalize, 16, False, True,
                                                             self.total_D, D_bytes, scale_bias_last, bf16, **kw)

@@ -20,11 +20,13 @@
  *     and the per-call arrays travel through pinned staging buffers.
  *
  * Differences from the reference, all reported at generation time by
- * std::invalid_argument: only InType = uint8_t (the fused quantized rows) is
- * provided; bf16 output, no_bag and scale_bias_last = false are not;
- * block_size is limited to 1024.  `prefetch` and THREAD_LOCAL are accepted and
- * ignored.  There is no CPU fallback: without an sm_100 device the generators
- * throw std::runtime_error.
+ * std::invalid_argument: N-bit no_bag (an int4 -> int4 row copy), 8-bit output
+ * and the row-wise sparse form of unquantized tables are not provided;
+ * block_size of quantized rows is limited to 1024; host pointers do not take
+ * no_bag.  InType uint8_t (fused 8-bit rows), float, float16 and uint16_t
+ * (fp16 or, with is_bf16_in, bf16 storage) are instantiated.  `prefetch` and
+ * THREAD_LOCAL are accepted and ignored.  There is no CPU fallback: without an
+ * sm_100 device the generators throw std::runtime_error.
  */
 #pragma once
 
@@ -132,6 +134,21 @@ GenerateEmbeddingSpMDMNBitWithStrides(
     const bool is_bf16_out = false,
     const bool no_bag = false,
     int output_bit_rate = -1);
+
+/* include/fbgemm/FbgemmEmbedding.h:185-203: rows of FP8 values, no scale or
+ * bias; the functor pools with weights whenever its `weights` is not null. */
+template <typename IndexType, typename OffsetType = std::int32_t, typename OutType = float>
+FBGEMM_B200_API typename EmbeddingSpMDMKernelSignature<std::uint8_t, IndexType, OffsetType, OutType>::Type
+GenerateEmbeddingSpMDMFP8WithStrides(
+    const std::int64_t block_size,
+    bool normalize_by_lengths,
+    bool is_weight_positional = false,
+    bool use_offsets = true,
+    std::int64_t output_stride = -1,
+    std::int64_t input_stride = -1,
+    int exponent_bits = 4,
+    int exponent_bias = 7,
+    bool is_bf16_out = false);
 
 /* include/fbgemm/FbgemmEmbedding.h:205-222 */
 template <typename InType, typename IndexType, typename OffsetType = std::int32_t>

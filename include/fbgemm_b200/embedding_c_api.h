@@ -47,6 +47,13 @@ extern "C" {
                                   (bits + 0x8000) >> 16, as cpu_float2bfloat16,
                                   include/fbgemm/FloatConversion.h:312-315 */
 
+/* Input row types (InType of the reference generators). */
+#define FBGEMM_B200_IN_QUANTIZED 0
+#define FBGEMM_B200_IN_F32 1
+#define FBGEMM_B200_IN_F16 2
+#define FBGEMM_B200_IN_BF16 3
+#define FBGEMM_B200_IN_FP8 4
+
 /* Why a lookup returned 0 (first word of the status record). */
 #define FBGEMM_B200_STATUS_OK 0
 #define FBGEMM_B200_STATUS_BAD_INDEX 1   /* idx < 0 || idx >= data_size      */
@@ -102,7 +109,17 @@ typedef struct fbgemm_b200_spmdm_config {
                            fbgemm_gpu/codegen/inference/embedding_forward_quantized_cpu_template.cpp:381-387)
                            is pooled without reading offsets[t*B] on the host.
                            Offsets flavour only.  0 = the functor's convention */
-  int32_t reserved_;    /* keeps the struct a multiple of 8 bytes; set to 0   */
+  int32_t in_dtype;     /* FBGEMM_B200_IN_QUANTIZED (0): fused row-wise quantized
+                           rows, bit_rate applies.  Otherwise the table is not
+                           quantized - InType float / float16 / uint16_t of
+                           GenerateEmbeddingSpMDM[WithStrides] or the rows of
+                           GenerateEmbeddingSpMDMFP8WithStrides
+                           (include/fbgemm/FbgemmEmbedding.h:65-117,185-203):
+                           _F32, _F16, _BF16 (is_bf16_in), _FP8.  bit_rate is
+                           ignored, there is no scale or bias, and
+                           scale_bias_first only makes -1 a pruned index       */
+  int32_t fp8_exponent_bits; /* FP8 rows only (the generator's exponent_bits)  */
+  int32_t fp8_exponent_bias; /* FP8 rows only (the generator's exponent_bias)  */
 } fbgemm_b200_spmdm_config;
 
 /* ---- context ----------------------------------------------------------- */

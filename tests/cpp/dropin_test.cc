@@ -24,6 +24,8 @@ int oracle_embedding_spmdm_rowwise_sparse(int, int64_t, int64_t, int64_t, int64_
                                           const int32_t*, const void*, int, const float*, int, float*, int, int);
 int oracle_embedding_spmdm_ex(int, int64_t, int64_t, int64_t, int64_t, const uint8_t*, const void*, int, const void*, int,
                               const float*, int, void*, int, int, int, int64_t, int64_t, int, int);
+int oracle_embedding_spmdm_plain(int, int64_t, int64_t, int64_t, int64_t, const void*, const void*, int, const void*, int,
+                                 const float*, int, void*, int, int, int, int64_t, int64_t, int, int, int, int);
 }
 
 static int failures = 0;
@@ -193,6 +195,34 @@ int main() {
                                     8, in.weights.data(), 1, ref.data(), /*bf16*/ 2, 0, 1, -1, stride, 0, 0));
     CHECK(std::memcmp(out.data(), ref.data(), out.size() * 2) == 0);
     fbgemm_b200::InvalidateTable(in.table.data());
+  }
+  // --- tables that are not quantized: InType float (padded rows) and FP8 rows, host pointers
+  {
+    const int batch = 23, rows = 300, dim = 40, stride = 44;
+    Inputs in = make(g, 4, batch, rows, dim, 9, 0);
+    std::vector<float> table((size_t)rows * stride);
+    std::normal_distribution<float> nd;
+    for (auto& v : table) v = nd(g);
+    auto kernel = fbgemm::GenerateEmbeddingSpMDMWithStrides<float, int64_t, int32_t, float>(
+        dim, true, true, 16, false, true, -1, /*input_stride (elements)=*/stride);
+    std::vector<float> out((size_t)batch * dim, 1.f), ref((size_t)batch * dim, 2.f);
+    CHECK(kernel(batch, in.n, rows, table.data(), in.idx64.data(), in.off32.data(), in.weights.data(), out.data()));
+    CHECK(oracle_embedding_spmdm_plain(1, dim, batch, in.n, rows, table.data(), in.idx64.data(), 8, in.off32.data(), 4,
+                                       in.weights.data(), 1, ref.data(), 0, 0, 1, -1, stride, 1, 0, 4, 7));
+    CHECK(std::memcmp(out.data(), ref.data(), out.size() * 4) == 0);
+    fbgemm_b200::InvalidateTable(table.data());
+
+    std::vector<uint8_t> fp8((size_t)rows * 64);
+    for (auto& b : fp8) b = (uint8_t)(g() & 0xff);
+    auto k8 = fbgemm::GenerateEmbeddingSpMDMFP8WithStrides<int64_t, int32_t, uint16_t>(64, false, false, true, -1, -1, 5, 15);
+    std::vector<uint16_t> o8((size_t)batch * 64, 1), r8((size_t)batch * 64, 2);
+    for (const float* w : {(const float*)nullptr, (const float*)in.weights.data()}) {
+      CHECK(k8(batch, in.n, rows, fp8.data(), in.idx64.data(), in.off32.data(), w, o8.data()));
+      CHECK(oracle_embedding_spmdm_plain(4, 64, batch, in.n, rows, fp8.data(), in.idx64.data(), 8, in.off32.data(), 4, w, 0,
+                                         r8.data(), 1, 0, 1, -1, -1, 1, 0, 5, 15));
+      CHECK(std::memcmp(o8.data(), r8.data(), o8.size() * 2) == 0);
+    }
+    fbgemm_b200::InvalidateTable(fp8.data());
   }
   // --- what the sm_100a path does not provide is refused when the kernel is generated
   bool threw = false;

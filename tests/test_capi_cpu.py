@@ -40,8 +40,8 @@ def test_every_declared_entry_point_is_exported_and_bound():
 
 
 def test_config_struct_layout_matches_header():
-    # 4 x int32, 3 x int64, 8 x int32 with natural alignment
-    assert C.sizeof(_capi.SpmdmConfig) == 16 + 24 + 32
+    # 4 x int32, 3 x int64, 10 x int32 with natural alignment
+    assert C.sizeof(_capi.SpmdmConfig) == 16 + 24 + 40
     assert _capi.SpmdmConfig.block_size.offset == 16
     assert _capi.SpmdmConfig.has_weight.offset == 40
     assert _capi.SpmdmConfig.no_bag.offset == 60
@@ -58,7 +58,8 @@ def cfg(**kw):
     dict(bit_rate=3), dict(bit_rate=16), dict(index_bytes=2), dict(offset_bytes=16), dict(out_dtype=5),
     dict(block_size=0), dict(block_size=-4), dict(block_size=4096), dict(input_stride=10),
     dict(output_stride=8), dict(bit_rate=4, block_size=64, input_stride=35),
-    dict(bit_rate=4, no_bag=1), dict(scale_bias_first=1, input_stride=67), dict(absolute_offsets=1, use_offsets=0),
+    dict(bit_rate=4, no_bag=1), dict(scale_bias_first=1, input_stride=67), dict(absolute_offsets=1, use_offsets=0), dict(in_dtype=9), dict(in_dtype=4, fp8_exponent_bits=0),
+    dict(in_dtype=2, input_stride=127),
 ])
 def test_check_config_rejects(bad):
     assert _capi.lib().fbgemm_b200_spmdm_check_config(C.byref(cfg(**bad))) == _capi.EINVAL
@@ -68,7 +69,8 @@ def test_check_config_rejects(bad):
 @pytest.mark.parametrize("good", [
     dict(), dict(bit_rate=4, block_size=64, out_dtype=1), dict(bit_rate=2, block_size=1024),
     dict(block_size=1024), dict(block_size=7, input_stride=20, output_stride=9), dict(bit_rate=4, block_size=1),
-    dict(scale_bias_first=1, input_stride=68), dict(out_dtype=2, no_bag=1), dict(bit_rate=2, scale_bias_first=1),
+    dict(scale_bias_first=1, input_stride=68), dict(out_dtype=2, no_bag=1), dict(bit_rate=2, scale_bias_first=1), dict(in_dtype=1, bit_rate=0, block_size=4000),
+    dict(in_dtype=4, fp8_exponent_bits=4, fp8_exponent_bias=7), dict(in_dtype=3, no_bag=1, input_stride=256),
 ])
 def test_check_config_accepts(good):
     assert _capi.lib().fbgemm_b200_spmdm_check_config(C.byref(cfg(**good))) == 0
@@ -79,8 +81,12 @@ def test_generators_mirror_reference_argument_checks():
         F.GenerateEmbeddingSpMDMNBit(3, 64, False, False)          # bit_rate must be 2 or 4
     with pytest.raises(ValueError):   # the reference's N-bit no_bag is an int4 -> int4 row copy: not provided
         F.GenerateEmbeddingSpMDMNBitWithStrides(4, 64, False, False, no_bag=True)
-    with pytest.raises(ValueError):   # is_bf16_in belongs to unquantized tables
+    with pytest.raises(ValueError):   # is_bf16_in belongs to 16-bit tables
         F.GenerateEmbeddingSpMDM(64, False, False, is_bf16_in=True)
+    k = F.GenerateEmbeddingSpMDMWithStrides(64, False, False, input_stride=80, in_dtype=np.float16)
+    assert (k.cfg.in_dtype, k.cfg.input_stride) == (2, 160)   # the reference counts the stride in elements
+    assert F.GenerateEmbeddingSpMDM(64, False, False, is_bf16_in=True, in_dtype=np.uint16).cfg.in_dtype == 3
+    assert F.GenerateEmbeddingSpMDMFP8WithStrides(64, False, exponent_bits=5, exponent_bias=15).cfg.fp8_exponent_bits == 5
     # the table-batched row layout, bf16 output and 8-bit no_bag are carried in the config
     k = F.GenerateEmbeddingSpMDMWithStrides(64, False, False, scale_bias_last=False, no_bag=True, is_bf16_out=True,
                                             out_dtype=np.uint16)

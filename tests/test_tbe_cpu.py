@@ -20,12 +20,14 @@ def test_enumerations_match_the_reference():
     (128, tbe.SparseType.INT2, 16, 4, 48),    # 32 + 4 = 36 -> 48
     (64, tbe.SparseType.INT2, 1, 4, 20),
     (24, tbe.SparseType.INT8, 16, 4, 32),
+    (64, tbe.SparseType.FP16, 16, 4, 128),
 ])
 def test_padded_row_size(dim, ty, align, sb, want):
     # nbit::padded_row_size_in_bytes, embedding_common.h:189-225
     assert tbe.padded_row_size_in_bytes(dim, ty, align, sb) == want
 
 
-def test_unquantized_types_are_refused():
-    with pytest.raises(KeyError):
-        tbe.padded_row_size_in_bytes(64, tbe.SparseType.FP16, 16)
+def test_row_sizes_of_unquantized_types():
+    assert tbe.padded_row_size_in_bytes(64, tbe.SparseType.FP16, 16) == 128
+    assert tbe.padded_row_size_in_bytes(30, tbe.SparseType.FP32, 16) == 128
+    assert tbe.padded_row_size_in_bytes(36, tbe.SparseType.FP8, 16) == 48

@@ -11,12 +11,13 @@ import torch
 import fbgemm_b200 as F
 from fbgemm_b200 import tbe
 from conftest import bits
-from helpers import random_fused_table
+from helpers import random_fused_table, random_plain_table
 
 pytestmark = pytest.mark.gpu
 
 KIND = {tbe.SparseType.FP32: "f32", tbe.SparseType.FP16: "f16", tbe.SparseType.BF16: "bf16"}
 BITS = {tbe.SparseType.INT8: 8, tbe.SparseType.INT4: 4, tbe.SparseType.INT2: 2}
+PLAIN = {tbe.SparseType.FP32: "f32", tbe.SparseType.FP16: "f16", tbe.SparseType.FP8: "fp8"}
 
 
 def build_op_inputs(rng, tys, dims, rows, B, mean_len, row_alignment, scale_bias_last, idt):
@@ -26,7 +27,12 @@ def build_op_inputs(rng, tys, dims, rows, B, mean_len, row_alignment, scale_bias
     for ty, D, R in zip(tys, dims, rows):
         sb = 8 if (ty == tbe.SparseType.INT8 and scale_bias_last) else 4
         stride = tbe.padded_row_size_in_bytes(D, ty, row_alignment, sb)
-        t = random_fused_table(rng, R, D, BITS[ty], stride, not scale_bias_last)
+        if ty in PLAIN:
+            eb = {"f32": 4, "f16": 2, "fp8": 1}[PLAIN[ty]]
+            t = random_plain_table(rng, R, D, PLAIN[ty], stride // eb)
+            t = t.view(np.uint8).reshape(R, stride)
+        else:
+            t = random_fused_table(rng, R, D, BITS[ty], stride, not scale_bias_last)
         tables.append(t)
         offs_w.append(at)
         blob.append(t.reshape(-1))
@@ -94,3 +100,33 @@ def test_function_form_and_bad_index(gpu_ctx, oracle):
                                                  torch.from_numpy(offsets).cuda(), tbe.PoolingMode.SUM, 16)
     ok, info = F.status_read(0)
     assert not ok and info[0] == 1 and info[2] == hi - 1 and info[3] == 50
+
+
+def test_operator_with_unquantized_and_fp8_tables(gpu_ctx, oracle):
+    rng = np.random.default_rng(8300)
+    tys = [tbe.SparseType.FP16, tbe.SparseType.INT4, tbe.SparseType.FP32, tbe.SparseType.FP8]
+    dims, rows, B = [64, 64, 24, 36], [300, 200, 100, 150], 11
+    tables, blob, w_off, D_off, offsets, indices, weights = build_op_inputs(rng, tys, dims, rows, B, 7, 16, True, np.int32)
+    total_D = int(D_off[-1])
+    op = tbe.IntNBitTableBatchedEmbeddingBags(torch.from_numpy(blob).cuda(), w_off, np.array([int(t) for t in tys], np.uint8),
+                                              D_off, total_D, tbe.PoolingMode.SUM, 16, tbe.SparseType.FP32, True, True,
+                                              torch.int32, 5, 15)
+    out = op.forward(*(torch.from_numpy(a).cuda() for a in (indices, offsets, weights)), slot=22)
+    ok, info = F.status_read(22)
+    assert ok, info
+    got = out.cpu().numpy().view(np.uint32)
+    for t, ty in enumerate(tys):
+        lo, hi = int(offsets[t * B]), int(offsets[(t + 1) * B])
+        if ty in PLAIN:
+            eb = {"f32": 4, "f16": 2, "fp8": 1}[PLAIN[ty]]
+            view = tables[t].reshape(-1).view({4: np.float32, 2: np.uint16, 1: np.uint8}[eb])
+            ok_ref, ref = oracle.spmdm_plain(PLAIN[ty], dims[t], rows[t], view, indices[lo:hi], offsets[t * B:(t + 1) * B + 1],
+                                             weights[lo:hi], False, "f32", False, True, -1, tables[t].shape[1] // eb, True,
+                                             False, 5, 15)
+        else:
+            ok_ref, ref = oracle.spmdm_ex(BITS[ty], dims[t], rows[t], tables[t], indices[lo:hi],
+                                          offsets[t * B:(t + 1) * B + 1], weights[lo:hi], False, "f32", False, True, -1,
+                                          tables[t].shape[1], True, False)
+        assert ok_ref
+        np.testing.assert_array_equal(np.ascontiguousarray(got[:, D_off[t]:D_off[t + 1]]).reshape(-1), bits(ref),
+                                      err_msg=f"table {t}")
