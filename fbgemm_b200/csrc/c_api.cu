@@ -1,6 +1,7 @@
 // The C ABI of libfbgemm_b200.so: context, status slots, table registry,
 // device-pointer and host-pointer functor calls.  See
 // include/fbgemm_b200/embedding_c_api.h for the contract of each entry point.
+#include <algorithm>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -151,15 +152,22 @@ int check_config(const fbgemm_b200_spmdm_config* c, Derived* d) {
     return FBGEMM_B200_EINVAL;
   }
   if (c->out_dtype != FBGEMM_B200_OUT_F32 && c->out_dtype != FBGEMM_B200_OUT_F16 &&
-      c->out_dtype != FBGEMM_B200_OUT_BF16) {
-    set_error("output type must be fp32, fp16 or bf16");
+      c->out_dtype != FBGEMM_B200_OUT_BF16 && c->out_dtype != FBGEMM_B200_OUT_U8) {
+    set_error("output type must be fp32, fp16, bf16 or (no_bag) u8");
+    return FBGEMM_B200_EINVAL;
+  }
+  if (c->out_dtype == FBGEMM_B200_OUT_U8 &&
+      (!c->no_bag || c->in_dtype != FBGEMM_B200_IN_QUANTIZED || (c->bit_rate != 8 && c->bit_rate != 4) ||
+       c->scale_bias_first)) {
+    set_error("8-bit output is the no_bag row copy of 8-bit or 4-bit rows");
     return FBGEMM_B200_EINVAL;
   }
   if (c->absolute_offsets && (!c->use_offsets || c->no_bag || c->is_weight_positional)) {
     set_error("absolute_offsets goes with use_offsets, bags and per-index weights");
     return FBGEMM_B200_EINVAL;
   }
-  if (c->no_bag && c->bit_rate != 8 && c->in_dtype == FBGEMM_B200_IN_QUANTIZED) {
+  if (c->no_bag && c->bit_rate != 8 && c->in_dtype == FBGEMM_B200_IN_QUANTIZED &&
+      c->out_dtype != FBGEMM_B200_OUT_U8) {
     // EmbeddingSpMDMNBit_ref: "no_bag is only supported for int4 to int4", a raw row copy
     set_error("no_bag is provided for 8-bit rows with fp32/fp16/bf16 output");
     return FBGEMM_B200_EINVAL;
@@ -193,8 +201,12 @@ int check_config(const fbgemm_b200_spmdm_config* c, Derived* d) {
     set_error("input_stride smaller than a row (or not a whole number of elements)");
     return FBGEMM_B200_EINVAL;
   }
-  if (out_stride < c->block_size) {
+  if (out_stride < c->block_size && c->out_dtype != FBGEMM_B200_OUT_U8) {
     set_error("output_stride smaller than block_size");
+    return FBGEMM_B200_EINVAL;
+  }
+  if (out_stride <= 0) {
+    set_error("output_stride must be positive");
     return FBGEMM_B200_EINVAL;
   }
   if (d) {
@@ -361,6 +373,26 @@ int fbgemm_b200::enqueue_lookup(
     void* const* peer_out,
     int num_peers,
     int64_t bags_per_peer) {
+  if (cfg && cfg->out_dtype == FBGEMM_B200_OUT_U8) {
+    Derived d;
+    const int rc = check_config(cfg, &d);
+    if (rc) {
+      return rc;
+    }
+    if (output_size < 0 || data_size < 0 || cit || num_peers > 0 || (output_size > 0 && (!input || !indices || !out))) {
+      set_error("row copy: dense table, device pointers, no peers");
+      return FBGEMM_B200_EINVAL;
+    }
+    if (output_size == 0) {
+      return 0;
+    }
+    const int64_t width = cfg->bit_rate == 8 ? std::min(d.output_stride, d.input_stride) : d.input_stride;
+    const int64_t pitch = cfg->bit_rate == 8 ? d.output_stride : d.input_stride;
+    const cudaError_t e = launch_rows_copy(static_cast<const uint8_t*>(input), indices, cfg->index_bytes, output_size,
+                                           data_size, d.input_stride, static_cast<uint8_t*>(out), pitch, width, status,
+                                           stream);
+    return e == cudaSuccess ? 0 : fail_cuda(e, "row copy launch");
+  }
   SpmdmParams p;
   const int rc = build_lookup_params(cfg, output_size, index_size, data_size, input, indices, weights, out, cit, status,
                                      peer_out, num_peers, bags_per_peer, &p);

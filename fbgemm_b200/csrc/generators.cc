@@ -51,9 +51,11 @@ template <typename OutType>
 constexpr int out_dtype() {
   static_assert(
       std::is_same<OutType, float>::value || std::is_same<OutType, std::uint16_t>::value ||
-          std::is_same<OutType, float16>::value,
-      "OutType must be float, uint16_t (fp16 bits) or float16");
-  return std::is_same<OutType, float>::value ? FBGEMM_B200_OUT_F32 : FBGEMM_B200_OUT_F16;
+          std::is_same<OutType, float16>::value || std::is_same<OutType, std::uint8_t>::value,
+      "OutType must be float, uint16_t (fp16 bits), float16 or (no_bag) uint8_t");
+  return std::is_same<OutType, float>::value ? FBGEMM_B200_OUT_F32
+      : std::is_same<OutType, std::uint8_t>::value ? FBGEMM_B200_OUT_U8
+                                                   : FBGEMM_B200_OUT_F16;
 }
 
 fbgemm_b200_spmdm_config make_config(
@@ -283,13 +285,20 @@ GenerateEmbeddingSpMDMNBitWithStrides(
   if (input_bit_rate != 2 && input_bit_rate != 4) {
     throw std::invalid_argument("fbgemm_b200: bit_rate must be 2 or 4");
   }
-  if (no_bag || (output_bit_rate != -1 && output_bit_rate != (int)(8 * sizeof(OutType)))) {
-    // the reference's N-bit no_bag is an int4 -> int4 row copy (src/RefImplementations.cc:1467-1485)
-    throw std::invalid_argument("fbgemm_b200: N-bit no_bag and N-bit output are not provided by the sm_100a path");
+  if (no_bag) {
+    // the reference's N-bit no_bag is the int4 -> int4 sequence lookup, a byte copy of the rows
+    // (src/RefImplementations.cc:1467-1485)
+    if (input_bit_rate != 4 || output_bit_rate != 4 || !std::is_same<OutType, std::uint8_t>::value) {
+      throw std::invalid_argument("fbgemm_b200: no_bag is only supported for int4 to int4");
+    }
+  } else if (
+      std::is_same<OutType, std::uint8_t>::value ||
+      (output_bit_rate != -1 && output_bit_rate != (int)(8 * sizeof(OutType)))) {
+    throw std::invalid_argument("fbgemm_b200: N-bit output is provided for no_bag only");
   }
   const fbgemm_b200_spmdm_config cfg = make_config(
       input_bit_rate, sizeof(IndexType), sizeof(OffsetType), out_dtype<OutType>(), block_size, has_weight,
-      normalize_by_lengths, is_weight_positional, use_offsets, output_stride, input_stride, scale_bias_last, false,
+      normalize_by_lengths, is_weight_positional, use_offsets, output_stride, input_stride, scale_bias_last, no_bag,
       is_bf16_out);
   return [cfg](
              std::int64_t output_size,
@@ -435,6 +444,9 @@ GenerateEmbeddingSpMDMNBitRowWiseSparse(
   INST_NBIT(IDX, OFF, float)               \
   INST_NBIT(IDX, OFF, std::uint16_t)       \
   INST_NBIT(IDX, OFF, float16)             \
+  INST_NBIT(IDX, OFF, std::uint8_t)        \
+  INST_IN(std::uint8_t, IDX, OFF, std::uint8_t, false) \
+  INST_IN(std::uint8_t, IDX, OFF, std::uint8_t, true)  \
   INST_FP8(IDX, OFF, float)                \
   INST_FP8(IDX, OFF, std::uint16_t)        \
   INST_FP8(IDX, OFF, float16)              \

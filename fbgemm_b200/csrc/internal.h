@@ -114,6 +114,20 @@ cudaError_t launch_multi_plan(const MultiPlan& plan, cudaStream_t stream);
 // The lookup on a table that is not row-wise quantized (plain_kernels.cu).
 cudaError_t launch_plain_rows(const SpmdmParams& p, cudaStream_t stream);
 
+// no_bag with 8-bit output: byte copies of the indexed rows (plain_kernels.cu).
+cudaError_t launch_rows_copy(
+    const uint8_t* table,
+    const void* indices,
+    int index_bytes,
+    int64_t rows_out,
+    int64_t data_size,
+    int64_t input_stride,
+    uint8_t* out,
+    int64_t out_pitch,
+    int64_t width,
+    int32_t* status,
+    cudaStream_t stream);
+
 // Exclusive scan of `n` int32/int64 lengths into int64 offsets[n + 1]
 // (scan_kernels.cu).  `block_sums` is scratch of scan_scratch_elems(n) int64.
 size_t scan_scratch_elems(int64_t n);

@@ -202,7 +202,47 @@ __global__ void __launch_bounds__(kThreads) plain_rows_kernel(const __grid_const
   }
 }
 
-using PlainFn = void (*)(const SpmdmParams);
+// no_bag with 8-bit output: output row m is a byte copy of table row
+// indices[m] (src/RefImplementations.cc:1235-1254 for 8-bit rows, :1467-1485
+// for 4-bit rows).  One warp per row; 4-byte words when everything is aligned.
+__global__ void __launch_bounds__(kThreads) rows_copy_kernel(
+    const uint8_t* __restrict__ table,
+    const void* __restrict__ indices,
+    int idx64,
+    int64_t rows_out,
+    int64_t data_size,
+    int64_t input_stride,
+    uint8_t* __restrict__ out,
+    int64_t out_pitch,
+    int64_t width,
+    int wordwise,
+    int32_t* status) {
+  const int lane = threadIdx.x & 31;
+  const int64_t m = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
+  if (m >= rows_out) {
+    return;
+  }
+  const int64_t idx = load_int(indices, m, idx64 != 0);
+  if (idx < 0 || idx >= data_size) {
+    if (lane == 0) {
+      report(status, FBGEMM_B200_STATUS_BAD_INDEX, m, m, idx);
+    }
+    return;
+  }
+  const uint8_t* src = table + idx * input_stride;
+  uint8_t* dst = out + m * out_pitch;
+  if (wordwise) {
+    for (int64_t i = lane; i < width / 4; i += 32) {
+      reinterpret_cast<uint32_t*>(dst)[i] = __ldg(reinterpret_cast<const uint32_t*>(src) + i);
+    }
+  } else {
+    for (int64_t i = lane; i < width; i += 32) {
+      dst[i] = __ldg(src + i);
+    }
+  }
+}
+
+using PlainFn = void (*)(const SpmdmParams);using PlainFn = void (*)(const SpmdmParams);
 
 template <bool WORD>
 PlainFn pick(int kind) {
@@ -229,6 +269,30 @@ cudaError_t launch_plain_rows(const SpmdmParams& p, cudaStream_t stream) {
   }
   PlainFn fn = word ? pick<true>(p.in_kind) : pick<false>(p.in_kind);
   fn<<<dim3((unsigned)blocks, (unsigned)tiles), kThreads, 0, stream>>>(p);
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rows_copy(
+    const uint8_t* table,
+    const void* indices,
+    int index_bytes,
+    int64_t rows_out,
+    int64_t data_size,
+    int64_t input_stride,
+    uint8_t* out,
+    int64_t out_pitch,
+    int64_t width,
+    int32_t* status,
+    cudaStream_t stream) {
+  const int64_t blocks = (rows_out + kWarps - 1) / kWarps;
+  if (blocks <= 0 || blocks > 0x7fffffffLL) {
+    return cudaErrorInvalidValue;
+  }
+  const uintptr_t a = reinterpret_cast<uintptr_t>(table), b = reinterpret_cast<uintptr_t>(out);
+  const int wordwise = ((a | b | (uintptr_t)input_stride | (uintptr_t)out_pitch | (uintptr_t)width) & 3) == 0;
+  rows_copy_kernel<<<(unsigned)blocks, kThreads, 0, stream>>>(
+      table, indices, index_bytes == 8, rows_out, data_size, input_stride, out, out_pitch, width, wordwise, status);
   g_launch_count.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError();
 }

@@ -94,7 +94,9 @@ def _out_code(out_dtype) -> int:
         return OUT_F16
     if name == "bfloat16":
         return 2
-    raise ValueError(f"OutType must be float32, float16 or bfloat16, got {out_dtype}")
+    if name == "uint8":
+        return 3  # no_bag only: byte copies of the indexed rows
+    raise ValueError(f"OutType must be float32, float16, bfloat16 or (no_bag) uint8, got {out_dtype}")
 
 
 def _is_tensor(x) -> bool:
@@ -281,11 +283,6 @@ def _config(bit_rate, block_size, has_weight, normalize_by_lengths, is_weight_po
     )
 
 
-def _reject(no_bag=False):
-    if no_bag:
-        raise ValueError("N-bit no_bag (an int4 -> int4 row copy) is not provided by the sm_100a path")
-
-
 def _in_code(in_dtype, is_bf16_in) -> tuple[int, int]:
     """(FBGEMM_B200_IN_* code, element bytes) of the generators' InType:
     uint8 = fused 8-bit rows, float32, float16, or uint16 / bfloat16 storage
@@ -388,12 +385,16 @@ def GenerateEmbeddingSpMDMNBitWithStrides(input_bit_rate, block_size, has_weight
     (include/fbgemm/FbgemmEmbedding.h:149-174)."""
     if input_bit_rate not in (2, 4):
         raise ValueError("bit_rate must be 2 or 4")  # src/EmbeddingSpMDMNBit.cc:999-1001
-    _reject(no_bag)  # the reference's N-bit no_bag is an int4 -> int4 row copy
-    if output_bit_rate not in (-1, 8 * (2 if _out_code(out_dtype) == OUT_F16 else 4)):
-        raise ValueError("N-bit output is not provided by the sm_100a path")
+    if no_bag:
+        # the reference's N-bit no_bag is the int4 -> int4 sequence lookup: a byte copy of the rows
+        # (src/RefImplementations.cc:1467-1485)
+        if input_bit_rate != 4 or output_bit_rate != 4 or _out_code(out_dtype) != 3:
+            raise ValueError("no_bag is only supported for int4 to int4 (uint8 OutType, output_bit_rate = 4)")
+    elif output_bit_rate not in (-1, 8 * {0: 4, 1: 2, 2: 2, 3: 1}[_out_code(out_dtype)]) or _out_code(out_dtype) == 3:
+        raise ValueError("N-bit output is provided for no_bag only")
     return SpmdmKernel(_config(input_bit_rate, block_size, has_weight, normalize_by_lengths, is_weight_positional,
                                use_offsets, output_stride, input_stride, index_dtype, offset_dtype, out_dtype,
-                               scale_bias_last, False, is_bf16_out), False)
+                               scale_bias_last, no_bag, is_bf16_out), False)
 
 
 def GenerateEmbeddingSpMDMRowWiseSparse(block_size, has_weight, normalize_by_lengths, prefetch=16,

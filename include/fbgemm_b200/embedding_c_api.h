@@ -47,6 +47,15 @@ extern "C" {
                                   (bits + 0x8000) >> 16, as cpu_float2bfloat16,
                                   include/fbgemm/FloatConversion.h:312-315 */
 
+#define FBGEMM_B200_OUT_U8 3   /* no_bag only: output row m is a byte copy of
+                                  table row indices[m].  8-bit rows: the first
+                                  min(output_stride, input_stride) bytes, output
+                                  rows output_stride bytes apart; 4-bit rows
+                                  (the reference's int4 -> int4 sequence
+                                  lookup): input_stride bytes, rows input_stride
+                                  apart (src/RefImplementations.cc:1235-1254,
+                                  :1467-1485)                                  */
+
 /* Input row types (InType of the reference generators). */
 #define FBGEMM_B200_IN_QUANTIZED 0
 #define FBGEMM_B200_IN_F32 1

@@ -155,6 +155,23 @@ class _Lookups:
                exponent_bits, exponent_bias)
         return bool(ok), out
 
+    def rows_copy(self, bit_rate, block_size, data_size, table, indices, output_stride, input_stride):
+        """no_bag with 8-bit output: byte copies of the indexed rows.  Returns
+        (ok, out[len(indices), pitch]) with pitch = output_stride (8-bit rows) or
+        input_stride (4-bit rows)."""
+        indices = np.ascontiguousarray(indices)
+        pitch = output_stride if bit_rate == 8 else input_stride
+        out = np.zeros((max(len(indices), 1), pitch), dtype=np.uint8)
+        if self.prefix == "oracle":
+            f = self._fn("oracle_embedding_rows_copy", [_int, _i64, _i64, _p, _p, _int, _p, _i64, _i64])
+            ok = f(bit_rate, len(indices), data_size, _ptr(table), _ptr(indices), indices.dtype.itemsize, _ptr(out),
+                   output_stride, input_stride)
+        else:
+            f = self._fn("ref_embedding_rows_copy", [_int, _i64, _i64, _i64, _p, _p, _int, _p, _i64, _i64])
+            ok = f(bit_rate, block_size, len(indices), data_size, _ptr(table), _ptr(indices), indices.dtype.itemsize,
+                   _ptr(out), output_stride, input_stride)
+        return bool(ok), out
+
     def spmdm_rowwise_sparse(self, bit_rate, block_size, uncompressed_data_size, table,
                              indices, compressed_indices_table, offsets_or_lengths,
                              weights=None, normalize_by_lengths=False,

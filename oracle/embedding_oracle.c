@@ -552,6 +552,41 @@ done:
 }
 
 /* ------------------------------------------------------------------------- */
+/* no_bag with 8-bit output: output row m is a byte copy of table row          */
+/* indices[m] - no arithmetic.  bit_rate 8: min(output_stride, input_stride)   */
+/* bytes per row, rows output_stride apart (EmbeddingSpMDM_ref<uint8_t, ...,   */
+/* uint8_t>, src/RefImplementations.cc:1235-1254).  bit_rate 4: input_stride   */
+/* bytes per row, rows input_stride apart (EmbeddingSpMDMNBit_ref, int4 to     */
+/* int4 only, :1467-1485; that loop lets idx == data_size through - one row    */
+/* past the table - which this restatement refuses like any other index out    */
+/* of range).                                                                  */
+/* ------------------------------------------------------------------------- */
+ORACLE_API int oracle_embedding_rows_copy(
+    int bit_rate,
+    int64_t output_size,
+    int64_t data_size,
+    const uint8_t* input,
+    const void* indices,
+    int index_bytes,
+    uint8_t* out,
+    int64_t output_stride,
+    int64_t input_stride) {
+  if (bit_rate != 8 && bit_rate != 4) {
+    return 0;
+  }
+  const int64_t width = bit_rate == 8 ? (output_stride < input_stride ? output_stride : input_stride) : input_stride;
+  const int64_t pitch = bit_rate == 8 ? output_stride : input_stride;
+  for (int64_t m = 0; m < output_size; ++m) {
+    const int64_t idx = load_int(indices, m, index_bytes);
+    if (idx < 0 || idx >= data_size) {
+      return 0;
+    }
+    memcpy(out + m * pitch, input + input_stride * idx, (size_t)width);
+  }
+  return 1;
+}
+
+/* ------------------------------------------------------------------------- */
 /* Pruned (row-wise sparse) pooled lookup: indices address an uncompressed    */
 /* row space and go through compressed_indices_table; -1 there means the row  */
 /* was pruned: it contributes nothing but still consumes its index/weight     */

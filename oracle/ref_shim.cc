@@ -257,6 +257,37 @@ int ref_embedding_spmdm_plain(
   });
 }
 
+// no_bag with 8-bit output: the reference's row copies.  bit_rate 8:
+// EmbeddingSpMDM_ref<uint8_t, I, I, uint8_t>(no_bag = true); bit_rate 4:
+// EmbeddingSpMDMNBit_ref<I, I, uint8_t>(4, ..., no_bag = true, output_bit_rate = 4).
+int ref_embedding_rows_copy(
+    int bit_rate,
+    std::int64_t block_size,
+    std::int64_t output_size,
+    std::int64_t data_size,
+    const std::uint8_t* input,
+    const void* indices,
+    int index_bytes,
+    std::uint8_t* out,
+    std::int64_t output_stride,
+    std::int64_t input_stride) {
+  return dispatch_idx_off(index_bytes, index_bytes, [&](auto i, auto o) {
+    using I = decltype(i);
+    using O = decltype(o);
+    const O dummy_offsets[1] = {0};
+    if (bit_rate == 8) {
+      return (int)fbgemm::EmbeddingSpMDM_ref<std::uint8_t, I, O, std::uint8_t>(
+          block_size, output_size, output_size, data_size, input,
+          static_cast<const I*>(indices), dummy_offsets, nullptr, false, out,
+          false, true, output_stride, input_stride, true, true, false, false);
+    }
+    return (int)fbgemm::EmbeddingSpMDMNBit_ref<I, O, std::uint8_t>(
+        bit_rate, block_size, output_size, output_size, data_size, input,
+        static_cast<const I*>(indices), dummy_offsets, nullptr, false, out,
+        false, true, output_stride, input_stride, true, false, true, 4);
+  });
+}
+
 // fbgemm::EmbeddingSpMDMRowWiseSparse_ref<uint8_t> (:1617) for bit_rate 8,
 // fbgemm::EmbeddingSpMDMNBitRowWiseSparse_ref (:1746) for 4 and 2.
 int ref_embedding_spmdm_rowwise_sparse(

@@ -233,7 +233,7 @@ int main() {
   }
   CHECK(threw);
   threw = false;
-  try {  // the reference's N-bit no_bag is an int4 -> int4 row copy
+  try {  // the reference's N-bit no_bag is int4 -> int4 only
     fbgemm::GenerateEmbeddingSpMDMNBitWithStrides<int64_t, int64_t, float>(4, 64, false, false, 16, false, true, -1, -1,
                                                                            true, false, /*no_bag=*/true);
   } catch (const std::invalid_argument&) {

@@ -58,7 +58,7 @@ def cfg(**kw):
     dict(bit_rate=3), dict(bit_rate=16), dict(index_bytes=2), dict(offset_bytes=16), dict(out_dtype=5),
     dict(block_size=0), dict(block_size=-4), dict(block_size=4096), dict(input_stride=10),
     dict(output_stride=8), dict(bit_rate=4, block_size=64, input_stride=35),
-    dict(bit_rate=4, no_bag=1), dict(scale_bias_first=1, input_stride=67), dict(absolute_offsets=1, use_offsets=0), dict(in_dtype=9), dict(in_dtype=4, fp8_exponent_bits=0),
+    dict(bit_rate=4, no_bag=1), dict(scale_bias_first=1, input_stride=67), dict(out_dtype=3), dict(bit_rate=2, no_bag=1, out_dtype=3), dict(absolute_offsets=1, use_offsets=0), dict(in_dtype=9), dict(in_dtype=4, fp8_exponent_bits=0),
     dict(in_dtype=2, input_stride=127),
 ])
 def test_check_config_rejects(bad):
@@ -69,7 +69,7 @@ def test_check_config_rejects(bad):
 @pytest.mark.parametrize("good", [
     dict(), dict(bit_rate=4, block_size=64, out_dtype=1), dict(bit_rate=2, block_size=1024),
     dict(block_size=1024), dict(block_size=7, input_stride=20, output_stride=9), dict(bit_rate=4, block_size=1),
-    dict(scale_bias_first=1, input_stride=68), dict(out_dtype=2, no_bag=1), dict(bit_rate=2, scale_bias_first=1), dict(in_dtype=1, bit_rate=0, block_size=4000),
+    dict(scale_bias_first=1, input_stride=68), dict(out_dtype=2, no_bag=1), dict(bit_rate=2, scale_bias_first=1), dict(out_dtype=3, no_bag=1), dict(bit_rate=4, out_dtype=3, no_bag=1), dict(in_dtype=1, bit_rate=0, block_size=4000),
     dict(in_dtype=4, fp8_exponent_bits=4, fp8_exponent_bias=7), dict(in_dtype=3, no_bag=1, input_stride=256),
 ])
 def test_check_config_accepts(good):
@@ -79,8 +79,10 @@ def test_check_config_accepts(good):
 def test_generators_mirror_reference_argument_checks():
     with pytest.raises(ValueError):
         F.GenerateEmbeddingSpMDMNBit(3, 64, False, False)          # bit_rate must be 2 or 4
-    with pytest.raises(ValueError):   # the reference's N-bit no_bag is an int4 -> int4 row copy: not provided
+    with pytest.raises(ValueError):   # the reference's N-bit no_bag is int4 -> int4 only
         F.GenerateEmbeddingSpMDMNBitWithStrides(4, 64, False, False, no_bag=True)
+    k = F.GenerateEmbeddingSpMDMNBitWithStrides(4, 64, False, False, no_bag=True, output_bit_rate=4, out_dtype=np.uint8)
+    assert (k.cfg.no_bag, k.cfg.out_dtype) == (1, 3)
     with pytest.raises(ValueError):   # is_bf16_in belongs to 16-bit tables
         F.GenerateEmbeddingSpMDM(64, False, False, is_bf16_in=True)
     k = F.GenerateEmbeddingSpMDMWithStrides(64, False, False, input_stride=80, in_dtype=np.float16)

@@ -110,3 +110,31 @@ def test_no_bag(gpu_ctx, oracle, sb_last):
                                    True)[0]
         kern = generate(8, dim, False, False, True, idt, idt, kind, sb_last, True)
         assert not kern(count, count, rows, dev(table), dev(indices), None, None, out)
+
+
+def test_no_bag_with_8bit_output_copies_rows(gpu_ctx, oracle):
+    """The reference's sequence lookups with 8-bit output are byte copies of the
+    indexed rows (src/RefImplementations.cc:1235-1254, :1467-1485)."""
+    rng = np.random.default_rng(5200)
+    for bit_rate, dim, ostride, istride, idt in ((8, 64, 72, 72, np.int64), (8, 64, 68, 80, np.int32), (8, 40, 64, 48, np.int64),
+                                                 (8, 37, 45, 45, np.int32), (4, 64, 36, 36, np.int64), (4, 128, 68, 80, np.int32)):
+        rows, count = 90, 300
+        table = random_fused_table(rng, rows, dim, bit_rate, istride)
+        indices = rng.integers(0, rows, count).astype(idt)
+        ok_ref, ref = oracle.rows_copy(bit_rate, dim, rows, table, indices, ostride, istride)
+        if bit_rate == 8:
+            kern = F.GenerateEmbeddingSpMDMWithStrides(dim, False, False, 16, False, True, ostride, istride, True, True,
+                                                       index_dtype=idt, offset_dtype=idt, out_dtype=np.uint8)
+        else:
+            kern = F.GenerateEmbeddingSpMDMNBitWithStrides(4, dim, False, False, 16, False, True, ostride, istride, True,
+                                                           False, True, 4, index_dtype=idt, offset_dtype=idt,
+                                                           out_dtype=np.uint8)
+        pitch = ref.shape[1]
+        out = torch.zeros(count * pitch + 5, dtype=torch.uint8, device="cuda")
+        assert kern(count, count, rows, dev(table), dev(indices), None, None, out) and ok_ref
+        got = out.cpu().numpy()
+        width = min(ostride, istride) if bit_rate == 8 else istride
+        np.testing.assert_array_equal(got[:count * pitch].reshape(count, pitch)[:, :width], ref[:, :width])
+        assert (got[count * pitch:] == 0).all()
+        indices[7] = rows
+        assert not kern(count, count, rows, dev(table), dev(indices), None, None, out)
