@@ -193,23 +193,34 @@ def cpu_runner(workload, host_table, host_cit):
 
 
 def time_cpu(workload, batches, host_table, host_cit, threads, max_steps, max_seconds):
-    """Run whole batches, each split over `threads` host threads, until
-    max_steps batches or max_seconds have passed.  Returns (seconds, steps,
-    gathered bytes, kind, desc)."""
+    """Run whole batches, each split over `threads` host threads (contiguous
+    bag ranges, one functor call each - how the reference's callers and
+    benchmarks parallelise this single-threaded kernel), until max_steps
+    batches or max_seconds have passed.  Returns (seconds, steps, gathered
+    bytes, kind, desc).  With the reference's JIT kernels the split runs on
+    OpenMP threads inside the checker library; otherwise on a Python pool."""
     from concurrent.futures import ThreadPoolExecutor
 
     from fbgemm_b200.workloads import algorithmic_bytes
+    from oracle import checker
 
     call, kind, desc = cpu_runner(workload, host_table, host_cit)
+    jit = checker.ReferenceJit()
+    out_dt = np.float16 if (str(workload.out_dtype) == "torch.float16" and host_cit is None) else np.float32
     host_batches = []
     for b in batches:
         host_batches.append({
             "indices": b.indices.cpu().numpy(), "offsets": b.offsets.cpu().numpy(),
             "weights": b.weights.cpu().numpy() if b.weights is not None else None,
-            "B": b.output_size, "bytes": algorithmic_bytes(workload, b)})
-    pool = ThreadPoolExecutor(max_workers=threads)
+            "B": b.output_size, "bytes": algorithmic_bytes(workload, b),
+            "out": np.zeros(b.output_size * workload.dim, dtype=out_dt)})
+    pool = None if jit.available else ThreadPoolExecutor(max_workers=threads)
 
     def run_batch(hb):
+        if jit.available:
+            return jit.batch_parallel(workload.bit_rate, workload.dim, workload.rows, host_table, hb["indices"],
+                                      hb["offsets"], hb["weights"], workload.normalize_by_lengths, hb["out"], threads,
+                                      host_cit)
         B = hb["B"]
         cuts = [B * t // threads for t in range(threads + 1)]
         futs = [pool.submit(call, hb, cuts[t], cuts[t + 1]) for t in range(threads) if cuts[t + 1] > cuts[t]]
@@ -224,8 +235,9 @@ def time_cpu(workload, batches, host_table, host_cit, threads, max_steps, max_se
         steps += 1
         nbytes += hb["bytes"]
     dt = time.perf_counter() - t0
-    pool.shutdown()
-    return dt, steps, nbytes, kind, desc
+    if pool:
+        pool.shutdown()
+    return dt, steps, nbytes, kind, desc + ("; OpenMP threads over contiguous bag ranges" if jit.available else "")
 
 
 # ---- multi-table workloads (BASELINE configs 3 and 4) ------------------------------
@@ -335,6 +347,25 @@ def main_multi(args):
     sec = ms / 1e3
     peak, peak_src = measured_peak()
     value = job_bytes * args.steps / sec / 1e9
+    # cpu_baseline (one GPU only): the reference's CPU kernels on a sample of this rank's tables - the whole set does
+    # not fit a host (config 4) or would take minutes (config 3), so a few tables stand for the rest
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        import types
+
+        threads = os.cpu_count() or 1
+        sample = sl.local[:: max(1, len(sl.local) // 3)][:3]
+        tot_b, tot_t, kind, desc = 0, 0.0, "", ""
+        for t in sample:
+            wl = types.SimpleNamespace(bit_rate=specs[t].bit_rate, dim=specs[t].dim, rows=specs[t].rows,
+                                       row_bytes=specs[t].row_bytes, out_dtype=torch.float16,
+                                       normalize_by_lengths=False)
+            dt, steps, nbytes, kind, desc = time_cpu(wl, [sets[0][t]], sl.tables[t].cpu().numpy(), None, threads, 3,
+                                                     args.cpu_seconds)
+            tot_b, tot_t = tot_b + nbytes, tot_t + dt
+        cpu = {"value": tot_b / tot_t / 1e9, "unit": "GB/s", "cores": threads, "kind": kind,
+               "sample": f"tables {sample} of {len(specs)} (their whole batches, up to 3 passes each), every batch split "
+                         f"over {threads} host threads; {desc}; extrapolates to the whole table set by gathered bytes"}
     if rank == 0:
         print(json.dumps({
             "metric": "gathered_row_GBps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
@@ -354,7 +385,7 @@ def main_multi(args):
             "gpu_launches": launches_per_step * args.steps,
             "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s",
                          "frac": value / world / peak, "traffic": None, "peak_source": peak_src},
-            "e2e": None, "cpu_baseline": None}))
+            "e2e": None, "cpu_baseline": cpu}))
     if world > 1:
         import torch.distributed as dist
 
@@ -490,17 +521,36 @@ def main():
     torch.cuda.synchronize()
 
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(replays + 1)]
     barrier()
     with ClockSampler(local_rank) as clocks:
         e0.record()
-        for _ in range(replays):
+        marks[0].record()
+        for r in range(replays):
             graph.replay()
+            marks[r + 1].record()   # between replays: spread of the per-step time over the run
         for i in range(rest):
             launch(i)
         e1.record()
         torch.cuda.synchronize()
     barrier()
     ms = e0.elapsed_time(e1)
+    per_step_us = sorted(marks[r].elapsed_time(marks[r + 1]) * 1e3 / chunk for r in range(replays))
+
+    def pct(q):
+        return per_step_us[min(len(per_step_us) - 1, int(q * len(per_step_us)))] if per_step_us else None
+
+    # one call alone on an idle GPU (launch to completion), median of 20
+    lat = []
+    for i in range(20):
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        launch(i)
+        b.record()
+        torch.cuda.synchronize()
+        lat.append(a.elapsed_time(b) * 1e3)
+    single_call_us = sorted(lat)[len(lat) // 2]
     ok = all(F.status_read(s)[0] for s in range(256))
     timed_launches = replays * chunk + rest
     if world > 1:
@@ -624,9 +674,12 @@ def main():
         host_table = w.table.cpu().numpy()
         host_cit = w.cit.cpu().numpy() if w.cit is not None else None
         dt, steps, nbytes, kind, desc = time_cpu(w, batches, host_table, host_cit, threads, 10 ** 9, args.cpu_seconds)
+        dt1, steps1, nbytes1, _, _ = time_cpu(w, batches, host_table, host_cit, 1, 10 ** 9, min(3.0, args.cpu_seconds))
         cpu = {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": kind,
                "sample": f"{steps} whole batches in {dt:.1f} s, each split over {threads} host threads; {desc}",
-               "bags_per_s": bags_per_step * steps / dt}
+               "bags_per_s": bags_per_step * steps / dt,
+               "one_thread": {"value": nbytes1 / dt1 / 1e9, "unit": "GB/s",
+                              "sample": f"{steps1} whole batches in {dt1:.1f} s on one thread"}}
 
     if rank == 0:
         line = {
@@ -634,6 +687,8 @@ def main():
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": f"u{w.bit_rate}->f32 accumulate", "data": "synthetic",
             "config": config, "results_ok": bool(ok),
+            "us_per_step_p10_p50_p90": [pct(0.1), pct(0.5), pct(0.9)],
+            "single_call_latency_us": single_call_us,
             "bags_per_s": job_bags_per_step * args.steps / sec,
             "all_bytes_GBps": all_bytes_per_step * world * args.steps / sec / 1e9,
             "frac_of_hbm_peak": value / world / peak,

@@ -306,3 +306,15 @@ class ReferenceJit(_Lookups):
         lib = _load(JIT_SO)
         self.available = lib is not None
         super().__init__(lib, "jit", has_8bit_entry=False)
+
+    def batch_parallel(self, bit_rate, block_size, data_size, table, indices, offsets, weights, normalize_by_lengths,
+                       out, threads, compressed_indices_table=None):
+        """One whole batch split into ``threads`` contiguous bag ranges, one
+        OpenMP thread each (how the reference's callers parallelise the
+        kernel).  ``out`` is a preallocated float32/float16 array."""
+        f = self._fn("jit_embedding_spmdm_batch_parallel",
+                     [_int, _i64, _i64, _i64, _p, _p, _int, _p, _int, _p, _int, _p, _int, _p, _int])
+        return bool(f(bit_rate, block_size, len(offsets) - 1, data_size, _ptr(table), _ptr(indices),
+                      indices.dtype.itemsize, _ptr(offsets), offsets.dtype.itemsize, _ptr(weights),
+                      int(normalize_by_lengths), _ptr(out), int(out.dtype == np.float16),
+                      _ptr(compressed_indices_table), threads))

@@ -172,4 +172,67 @@ int jit_embedding_spmdm_rowwise_sparse(
   });
 }
 
+// One whole batch split into `threads` contiguous bag ranges, one OpenMP thread
+// each - how the reference's callers and benchmarks parallelise this kernel
+// (fbgemm_gpu/codegen/inference/embedding_forward_quantized_cpu_template.cpp:67-72,
+// bench/EmbeddingSpMDM8BitBenchmark.cc:394-396): the kernel itself is
+// single-threaded.  Offsets flavour; every range is one functor call on a
+// slice (offsets need not start at zero).  compressed_indices_table may be
+// null.  Returns 1 if every range returned true.
+int jit_embedding_spmdm_batch_parallel(
+    int bit_rate,
+    std::int64_t block_size,
+    std::int64_t output_size,
+    std::int64_t data_size,
+    const std::uint8_t* input,
+    const void* indices,
+    int index_bytes,
+    const void* offsets,
+    int offset_bytes,
+    const float* weights,
+    int normalize_by_lengths,
+    void* out,
+    int out_is_half,
+    const std::int32_t* compressed_indices_table,
+    int threads) {
+  if (threads < 1) {
+    threads = 1;
+  }
+  auto off_at = [&](std::int64_t m) -> std::int64_t {
+    return offset_bytes == 8 ? static_cast<const std::int64_t*>(offsets)[m]
+                             : static_cast<const std::int32_t*>(offsets)[m];
+  };
+  const std::int64_t base = off_at(0);
+  int all_ok = 1;
+#pragma omp parallel for num_threads(threads) schedule(static, 1) reduction(&& : all_ok)
+  for (int t = 0; t < threads; ++t) {
+    const std::int64_t lo = output_size * t / threads;
+    const std::int64_t hi = output_size * (t + 1) / threads;
+    if (hi <= lo) {
+      continue;
+    }
+    const std::int64_t i0 = off_at(lo) - base;
+    const std::int64_t n = off_at(hi) - off_at(lo);
+    const char* idx = static_cast<const char*>(indices) + i0 * index_bytes;
+    const char* off = static_cast<const char*>(offsets) + lo * offset_bytes;
+    const float* w = weights ? weights + i0 : nullptr;
+    const std::size_t esize = out_is_half ? 2 : 4;
+    char* o = static_cast<char*>(out) + (std::size_t)lo * block_size * esize;
+    int ok;
+    if (compressed_indices_table) {
+      ok = jit_embedding_spmdm_rowwise_sparse(
+          bit_rate, block_size, hi - lo, n, data_size, input, idx, index_bytes,
+          compressed_indices_table, off, offset_bytes, w, normalize_by_lengths,
+          reinterpret_cast<float*>(o), 0, 1);
+    } else {
+      ok = jit_embedding_spmdm(
+          bit_rate, block_size, hi - lo, n, data_size, input, idx, index_bytes,
+          off, offset_bytes, w, normalize_by_lengths, o, out_is_half, 0, 1, -1,
+          -1);
+    }
+    all_ok = all_ok && ok == 1;
+  }
+  return all_ok;
+}
+
 } // extern "C"

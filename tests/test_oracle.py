@@ -223,6 +223,11 @@ def test_reference_jit_matches_oracle(oracle):
                           out_dt)
             assert a[0] and b[0]
             np.testing.assert_array_equal(bits(a[1]), bits(b[1]))
+            # the benchmark's CPU leg: the same batch split over OpenMP threads by bag ranges
+            par = np.zeros_like(a[1])
+            assert jit.batch_parallel(bit_rate, dim, rows, table, indices, offsets, weights if weighted else None,
+                                      normalize, par, 3)
+            np.testing.assert_array_equal(bits(par), bits(a[1]))
 
 
 @pytest.mark.parametrize("bit_rate", [8, 4, 2])
