@@ -497,7 +497,6 @@ def main():
         torch.cuda.synchronize()
 
     # ---- value: device-resident inputs ------------------------------------
-    launches_before = F.launch_count()
     for i in range(max(args.warmup, 3)):
         launch(i)
     torch.cuda.synchronize()
@@ -637,8 +636,6 @@ def main():
         if w.cit is not None:
             ctx.unregister_table(host_cit)
 
-    total_launches = F.launch_count() - launches_before
-
     # ---- the practical ceiling: the same rows fetched with no arithmetic ----------
     ceiling = None
     if rank == 0:
@@ -695,7 +692,6 @@ def main():
             "clocks": clocks.summary(),
             "e2e": e2e,
             "gpu_launches": timed_launches,
-            "gpu_launches_whole_run": int(total_launches),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": TRAFFIC_BYTES_PER_LAUNCH.get((args.workload, args.group)),
                          "traffic_source": "dram__bytes_read+write of one ncu capture of this launch shape "
