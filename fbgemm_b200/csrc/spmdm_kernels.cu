@@ -480,7 +480,9 @@ static const direct::Variant* pick_direct(const SpmdmParams& p, int bit_rate) {
   const int cols_target = bit_rate == 8 ? 32 : 16;
   int cpl_target = cols_target / cpc < 1 ? 1 : cols_target / cpc;
   cpl_target = cpl_target > cpl_max ? cpl_max : cpl_target;
-  int lpb = 2;
+  // At least 4 lanes per bag: with 2 (sixteen bags per warp) an 8-bit D=64
+  // table measured 32 us per 16384-bag call against 25.5 us with 4.
+  int lpb = 4;
   while (lpb < 32 && lpb * cpl_target < nchunks) {
     lpb *= 2;
   }
