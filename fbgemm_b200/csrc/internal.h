@@ -81,22 +81,29 @@ __device__ __forceinline__ char* output_row(const SpmdmParams& p, int64_t bag, i
 // launch error; never synchronises.
 cudaError_t launch_spmdm(const SpmdmParams& p, int bit_rate, cudaStream_t stream);
 
-// Several tables per launch (spmdm_kernels.cu): the tables of one call grouped
-// by kernel variant, their parameters resident in device memory.  Built once
-// for a fixed set of pointers, launched as often as wanted.
+// The argument of one multi-table launch: up to kMultiTables tables of the
+// same kernel variant, passed by value so that, like the single-table
+// kernel's, their parameters live in constant memory.  Table t owns the blocks
+// [first_block[t], first_block[t + 1]).
+constexpr int kMultiTables = 16;
+struct MultiArgs {
+  int32_t count;
+  int32_t first_block[kMultiTables + 1];
+  SpmdmParams t[kMultiTables];
+};
+static_assert(sizeof(MultiArgs) <= 4096, "one kernel argument, within the classic 4 KB of parameter space");
+
+// Several tables per call (spmdm_kernels.cu): the tables grouped by kernel
+// variant, each group cut into launches of up to kMultiTables tables.  Built
+// once for a fixed set of pointers, launched as often as wanted.
 struct MultiPlan {
-  struct Group {
-    void (*fn)(const SpmdmParams*, const int32_t*, const int32_t*);
-    size_t param_off;   // first table of the group in d_params and d_first_block
-    size_t table_off;   // first block of the group in d_table_of_block
-    int count;          // tables
+  struct Launch {
+    void (*fn)(const MultiArgs);
     unsigned blocks;    // grid size
+    MultiArgs args;
   };
-  std::vector<Group> groups;
+  std::vector<Launch> groups;
   std::vector<std::pair<SpmdmParams, int>> singles;  // (parameters, bit rate): one launch each
-  SpmdmParams* d_params = nullptr;
-  int32_t* d_first_block = nullptr;     // per table: its first block within its group's grid
-  int32_t* d_table_of_block = nullptr;  // per block: its table within its group
   // The launches of one call overlap: all but the first go to side streams
   // that fork from, and join, the caller's stream through these events.
   static constexpr int kSideStreams = 3;

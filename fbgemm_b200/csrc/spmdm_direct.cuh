@@ -818,16 +818,18 @@ spmdm_direct_kernel(const __grid_constant__ SpmdmParams p) {
 // Several tables of the same row format in one launch (the reference's
 // multi-table caller loops over tables,
 // fbgemm_gpu/codegen/inference/embedding_forward_quantized_cpu_template.cpp:343-473).
-// Block b works on table table_of_block[b], whose blocks start at
-// first_block[table]; the table's parameters are read from device memory.
+// The tables' parameters arrive by value, i.e. in constant memory as in the
+// single-table kernel; a block finds its table by comparing its index with
+// the tables' first blocks (at most kMultiTables - 1 uniform comparisons).
 template <int BITS, int VEC, int LPB, int CPL>
 __global__ void __launch_bounds__(kThreads)
-spmdm_direct_multi_kernel(
-    const SpmdmParams* __restrict__ params,
-    const int32_t* __restrict__ first_block,
-    const int32_t* __restrict__ table_of_block) {
-  const int t = __ldg(table_of_block + blockIdx.x);
-  direct_block<BITS, VEC, LPB, CPL>(params[t], (int64_t)blockIdx.x - __ldg(first_block + t));
+spmdm_direct_multi_kernel(const __grid_constant__ MultiArgs a) {
+  int t = 0;
+#pragma unroll
+  for (int i = 1; i < kMultiTables; ++i) {
+    t += (i < a.count && blockIdx.x >= (unsigned)a.first_block[i]) ? 1 : 0;
+  }
+  direct_block<BITS, VEC, LPB, CPL>(a.t[t], (int64_t)blockIdx.x - a.first_block[t]);
 }
 
 // One table per launch, rows compacted before they are pooled (pruned tables).
@@ -838,7 +840,7 @@ spmdm_direct_compact_kernel(const __grid_constant__ SpmdmParams p) {
 }
 
 using KernelFn = void (*)(const SpmdmParams);
-using MultiKernelFn = void (*)(const SpmdmParams*, const int32_t*, const int32_t*);
+using MultiKernelFn = void (*)(const MultiArgs);
 
 struct Variant {
   KernelFn fn;

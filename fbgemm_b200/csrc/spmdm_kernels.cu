@@ -532,9 +532,6 @@ static cudaError_t launch_direct(const SpmdmParams& p, int bit_rate, cudaStream_
 // ---- several tables per launch --------------------------------------------------
 
 MultiPlan::~MultiPlan() {
-  cudaFree(d_params);
-  cudaFree(d_first_block);
-  cudaFree(d_table_of_block);
   for (int i = 0; i < kSideStreams; ++i) {
     if (side[i]) {
       cudaStreamDestroy(side[i]);
@@ -548,9 +545,10 @@ MultiPlan::~MultiPlan() {
   }
 }
 
-// Tables that share a kernel variant go into one launch: their parameters are
-// laid out side by side in device memory and the grid is the sum of their
-// blocks.  Tables the direct kernel cannot take keep a launch of their own.
+// Tables that share a kernel variant go into one launch (up to kMultiTables of
+// them): their parameters travel as the kernel's argument and the grid is the
+// sum of their blocks.  Tables the direct kernel cannot take keep a launch of
+// their own.
 cudaError_t build_multi_plan(const std::vector<SpmdmParams>& tables, const std::vector<int>& bit_rates, MultiPlan* plan) {
   std::vector<const direct::Variant*> variant(tables.size());
   std::vector<size_t> order;
@@ -566,35 +564,32 @@ cudaError_t build_multi_plan(const std::vector<SpmdmParams>& tables, const std::
     }
   }
   std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) { return variant[a] < variant[b]; });
-  std::vector<SpmdmParams> params;
-  std::vector<int32_t> first_block, table_of_block;
   for (size_t i = 0; i < order.size();) {
     const direct::Variant* v = variant[order[i]];
-    MultiPlan::Group g{};
+    plan->groups.emplace_back();
+    MultiPlan::Launch& g = plan->groups.back();
     g.fn = v->multi;
-    g.param_off = params.size();
-    g.table_off = table_of_block.size();
+    g.args = MultiArgs{};
     int64_t blocks = 0;
-    for (; i < order.size() && variant[order[i]] == v; ++i) {
+    for (; i < order.size() && variant[order[i]] == v && g.args.count < kMultiTables; ++i) {
       const int64_t b = direct_blocks(v, tables[order[i]].output_size);
       if (blocks + b > 0x7fffffffLL) {
         break;  // the rest of this variant's tables start a new launch
       }
-      first_block.push_back((int32_t)blocks);
-      params.push_back(tables[order[i]]);
-      table_of_block.insert(table_of_block.end(), (size_t)b, (int32_t)g.count);
+      g.args.first_block[g.args.count] = (int32_t)blocks;
+      g.args.t[g.args.count] = tables[order[i]];
       blocks += b;
-      ++g.count;
+      ++g.args.count;
     }
-    if (g.count == 0) {
+    if (g.args.count == 0) {
       return cudaErrorInvalidValue;  // a single table with more than 2^31 blocks
     }
+    g.args.first_block[g.args.count] = (int32_t)blocks;
     g.blocks = (unsigned)blocks;
-    plan->groups.push_back(g);
   }
   // largest grid first: the short launches fill the tail of the long ones
   std::stable_sort(plan->groups.begin(), plan->groups.end(),
-                   [](const MultiPlan::Group& a, const MultiPlan::Group& b) { return a.blocks > b.blocks; });
+                   [](const MultiPlan::Launch& a, const MultiPlan::Launch& b) { return a.blocks > b.blocks; });
   if (plan->groups.size() + plan->singles.size() > 1) {
     cudaError_t e = cudaEventCreateWithFlags(&plan->fork, cudaEventDisableTiming);
     for (int i = 0; i < MultiPlan::kSideStreams && e == cudaSuccess; ++i) {
@@ -602,29 +597,6 @@ cudaError_t build_multi_plan(const std::vector<SpmdmParams>& tables, const std::
       if (e == cudaSuccess) {
         e = cudaEventCreateWithFlags(&plan->join[i], cudaEventDisableTiming);
       }
-    }
-    if (e != cudaSuccess) {
-      return e;
-    }
-  }
-  if (!params.empty()) {
-    cudaError_t e = cudaMalloc(&plan->d_params, params.size() * sizeof(SpmdmParams));
-    if (e == cudaSuccess) {
-      e = cudaMalloc(&plan->d_first_block, first_block.size() * sizeof(int32_t));
-    }
-    if (e == cudaSuccess) {
-      e = cudaMemcpy(plan->d_params, params.data(), params.size() * sizeof(SpmdmParams), cudaMemcpyHostToDevice);
-    }
-    if (e == cudaSuccess) {
-      e = cudaMemcpy(plan->d_first_block, first_block.data(), first_block.size() * sizeof(int32_t),
-                     cudaMemcpyHostToDevice);
-    }
-    if (e == cudaSuccess) {
-      e = cudaMalloc(&plan->d_table_of_block, table_of_block.size() * sizeof(int32_t));
-    }
-    if (e == cudaSuccess) {
-      e = cudaMemcpy(plan->d_table_of_block, table_of_block.data(), table_of_block.size() * sizeof(int32_t),
-                     cudaMemcpyHostToDevice);
     }
     if (e != cudaSuccess) {
       return e;
@@ -651,10 +623,8 @@ cudaError_t launch_multi_plan(const MultiPlan& plan, cudaStream_t stream) {
     const size_t k = i % (MultiPlan::kSideStreams + 1);
     return (!spread || k == 0) ? stream : plan.side[k - 1];
   };
-  for (const MultiPlan::Group& g : plan.groups) {
-    g.fn<<<g.blocks, direct::kThreads, 0, stream_of(n++)>>>(plan.d_params + g.param_off,
-                                                             plan.d_first_block + g.param_off,
-                                                             plan.d_table_of_block + g.table_off);
+  for (const MultiPlan::Launch& g : plan.groups) {
+    g.fn<<<g.blocks, direct::kThreads, 0, stream_of(n++)>>>(g.args);
     g_launch_count.fetch_add(1, std::memory_order_relaxed);
     e = cudaGetLastError();
     if (e != cudaSuccess) {
