@@ -183,8 +183,6 @@ static __device__ __noinline__ void report(int32_t* st, int code, int64_t bag, i
   }
 }
 
-constexpr uint32_t kSkipRow = 0xFFFFFFFFu;
-
 // base + row * stride as one 32 x 32 -> 64-bit multiply-add.
 __device__ __forceinline__ const uint8_t* row_address(const uint8_t* base, uint32_t row, uint32_t stride) {
   unsigned long long a;
@@ -193,11 +191,13 @@ __device__ __forceinline__ const uint8_t* row_address(const uint8_t* base, uint3
 }
 
 // The per-row work that does not depend on the column - index fetch, range
-// check, pruning map, weight fetch - is done once per row by ONE lane of the
-// bag's group: in a step of U rows, lane gl resolves rows gl, gl+LPB, ...
-// The results reach the other lanes of the group by shuffle in pool_step.
-// id = row to read (after pruning), or kSkipRow for a row that contributes
-// nothing (pruned, out of range, or beyond the `nvalid` rows of a short step).
+// check, weight fetch - is done once per row by ONE lane of the bag's group:
+// in a step of U rows, lane gl resolves rows gl, gl+LPB, ...  The results
+// reach the other lanes of the group by shuffle in pool_step.  This kernel
+// sees dense tables only (tables with a pruning map, or whose layout makes -1
+// a pruned index, take direct_block_compact), so every index names a row to
+// pool; an index out of range is reported and replaced by row 0 - the call
+// returns false and its output is unspecified, as with the reference.
 template <int LPB, int U>
 __device__ __forceinline__ void fetch_rows(
     const SpmdmParams& p,
@@ -205,27 +205,19 @@ __device__ __forceinline__ void fetch_rows(
     int64_t bag,
     int64_t pos0,
     int r0,
-    int nvalid,
     uint32_t (&id)[(U + LPB - 1) / LPB],
     float (&w)[(U + LPB - 1) / LPB]) {
   constexpr int OWN = (U + LPB - 1) / LPB;
 #pragma unroll
   for (int j = 0; j < OWN; ++j) {
     const int u = gl + j * LPB;
-    id[j] = kSkipRow;
+    id[j] = 0u;
     w[j] = 0.f;
-    if (u < nvalid) {
+    if (u < U) {
       const int64_t pos = pos0 + u;
       const int64_t idx = load_int(p.indices, pos, p.flags & kIdx64);
       if ((unsigned long long)idx >= (unsigned long long)p.data_size) {
-        if (!((p.flags & (kSbFirst | kNoBag)) == kSbFirst && idx == -1)) {  // that layout's pruned row: skipped
-          report(p.status, FBGEMM_B200_STATUS_BAD_INDEX, bag, pos, idx);
-        }
-      } else if (p.flags & kPruned) {
-        const int32_t c = __ldg(p.cit + idx);  // -1: pruned row
-        if (c >= 0) {
-          id[j] = (uint32_t)c;
-        }
+        report(p.status, FBGEMM_B200_STATUS_BAD_INDEX, bag, pos, idx);
       } else {
         id[j] = (uint32_t)idx;
       }
@@ -260,13 +252,11 @@ __device__ __forceinline__ void pool_step(
   ScaleBias<BITS, VEC> sb[U];
 #pragma unroll
   for (int u = 0; u < U; ++u) {
-    // a skipped row reads row 0 (always there) and is then pooled with zeros
-    const uint32_t row = rid[u] == kSkipRow ? 0u : rid[u];
 #pragma unroll
     for (int ci = 0; ci < CPL; ++ci) {
-      d[u][ci].load(row_address(chunk_base[ci], row, stride));
+      d[u][ci].load(row_address(chunk_base[ci], rid[u], stride));
     }
-    sb[u].load(row_address(sb_base, row, stride), half_sb);
+    sb[u].load(row_address(sb_base, rid[u], stride), half_sb);
   }
   const u64 nm2 = pack2(-8388608.0f, -8388608.0f);
 #pragma unroll
@@ -278,10 +268,6 @@ __device__ __forceinline__ void pool_step(
       scale = __fmul_rn(w, scale);
       bias = __fmul_rn(w, bias);
     }
-    // scale = bias = 0 leaves every accumulator unchanged: acc + 0 = acc and
-    // 0 * q = 0 for the finite q that prmt makes of any bit pattern.
-    scale = rid[u] == kSkipRow ? 0.f : scale;
-    bias = rid[u] == kSkipRow ? 0.f : bias;
     const u64 s2 = pack2(scale, scale);
     const u64 b2 = pack2(bias, bias);
 #pragma unroll
@@ -433,13 +419,11 @@ __device__ __forceinline__ void direct_block(const SpmdmParams& p, int64_t block
 
   // Full steps of UMAX rows.  The lane that resolves a row works two steps
   // ahead of the arithmetic so that nothing waits on a load that was only just
-  // issued: while step s is pooled, the pruning-map entries of step s+1 and the
-  // indices and weights of step s+2 are in flight.
+  // issued: while step s is pooled, the indices and weights of step s+2 are in
+  // flight and those of step s+1 have landed.
   const int nfull = len / UMAX;
   const bool idx64 = p.flags & kIdx64;
-  const bool pruned = p.flags & kPruned;
   const bool positional = p.flags & kPositional;
-  const bool minus_one_skips = (p.flags & (kSbFirst | kNoBag)) == kSbFirst;  // that layout's pruned row
   // loads only: raw index and weight of this lane's rows of step s
   auto issue = [&](int s, long long (&raw)[OWN], float (&w)[OWN]) {
 #pragma unroll
@@ -456,20 +440,15 @@ __device__ __forceinline__ void direct_block(const SpmdmParams& p, int64_t block
       }
     }
   };
-  // range check; for pruned tables start the load of the map entry (its
-  // value, -1 for a pruned row, is the row id or kSkipRow as it stands)
+  // range check (an index out of range is reported and row 0 pooled in its place)
   auto resolve = [&](int s, const long long (&raw)[OWN], uint32_t (&id)[OWN]) {
 #pragma unroll
     for (int j = 0; j < OWN; ++j) {
       const int u = gl + j * LPB;
-      id[j] = kSkipRow;
+      id[j] = 0u;
       if (u < UMAX && s < nfull) {
         if ((unsigned long long)raw[j] >= (unsigned long long)p.data_size) {
-          if (!(minus_one_skips && raw[j] == -1)) {
-            report(p.status, FBGEMM_B200_STATUS_BAD_INDEX, bag, start + (int64_t)s * UMAX + u, raw[j]);
-          }
-        } else if (pruned) {
-          id[j] = (uint32_t)__ldg(p.cit + raw[j]);
+          report(p.status, FBGEMM_B200_STATUS_BAD_INDEX, bag, start + (int64_t)s * UMAX + u, raw[j]);
         } else {
           id[j] = (uint32_t)raw[j];
         }
@@ -490,14 +469,6 @@ __device__ __forceinline__ void direct_block(const SpmdmParams& p, int64_t block
   for (int s = 0; s < nfull; ++s) {
     issue(s + 2, raw_2, w_2);
     resolve(s + 1, raw_1, id_1);
-    if (pruned) {
-#pragma unroll
-      for (int j = 0; j < OWN; ++j) {
-        if ((int32_t)id_cur[j] < 0) {
-          id_cur[j] = kSkipRow;  // any negative map entry skips the row
-        }
-      }
-    }
     pool_step<BITS, VEC, LPB, CPL, UMAX>(chunk_base, sb_base, stride, gmask, lane0, half_sb, weighted, id_cur, w_cur, acc);
 #pragma unroll
     for (int j = 0; j < OWN; ++j) {
@@ -513,7 +484,7 @@ __device__ __forceinline__ void direct_block(const SpmdmParams& p, int64_t block
     if (len - r >= 8) {
       uint32_t id8[(8 + LPB - 1) / LPB];
       float w8[(8 + LPB - 1) / LPB];
-      fetch_rows<LPB, 8>(p, gl, bag, start + r, r, 8, id8, w8);
+      fetch_rows<LPB, 8>(p, gl, bag, start + r, r, id8, w8);
       pool_step<BITS, VEC, LPB, CPL, 8>(chunk_base, sb_base, stride, gmask, lane0, half_sb, weighted, id8, w8, acc);
       r += 8;
     }
@@ -522,7 +493,7 @@ __device__ __forceinline__ void direct_block(const SpmdmParams& p, int64_t block
     if (len - r >= 4) {
       uint32_t id4[(4 + LPB - 1) / LPB];
       float w4[(4 + LPB - 1) / LPB];
-      fetch_rows<LPB, 4>(p, gl, bag, start + r, r, 4, id4, w4);
+      fetch_rows<LPB, 4>(p, gl, bag, start + r, r, id4, w4);
       pool_step<BITS, VEC, LPB, CPL, 4>(chunk_base, sb_base, stride, gmask, lane0, half_sb, weighted, id4, w4, acc);
       r += 4;
     }
@@ -530,14 +501,14 @@ __device__ __forceinline__ void direct_block(const SpmdmParams& p, int64_t block
   if (UMAX >= 4 && len - r >= 2) {
     uint32_t id2[(2 + LPB - 1) / LPB];
     float w2[(2 + LPB - 1) / LPB];
-    fetch_rows<LPB, 2>(p, gl, bag, start + r, r, 2, id2, w2);
+    fetch_rows<LPB, 2>(p, gl, bag, start + r, r, id2, w2);
     pool_step<BITS, VEC, LPB, CPL, 2>(chunk_base, sb_base, stride, gmask, lane0, half_sb, weighted, id2, w2, acc);
     r += 2;
   }
   if (len - r >= 1) {
     uint32_t id1[1];
     float w1[1];
-    fetch_rows<LPB, 1>(p, gl, bag, start + r, r, 1, id1, w1);
+    fetch_rows<LPB, 1>(p, gl, bag, start + r, r, id1, w1);
     pool_step<BITS, VEC, LPB, CPL, 1>(chunk_base, sb_base, stride, gmask, lane0, half_sb, weighted, id1, w1, acc);
   }
 
@@ -608,9 +579,10 @@ struct KnownRows {
   }
 };
 
-// The block's work for tables in which many indices are pruned (row-wise
-// sparse tables): a skipped row costs the arithmetic of a real one in
-// direct_block, because the lanes of a warp move together.  Here a group first
+// The block's work for tables in which an index may name no row: row-wise
+// sparse tables (a pruning map) and the table-batched layout (-1 = pruned).
+// Pooling such a row with zeros would cost the arithmetic of a real one,
+// because the lanes of a warp move together.  Here a group first
 // walks a stretch of its bag's indices (a queue length at a time), resolves them
 // through the pruning map and writes the rows that remain, with their weights,
 // in order into a small queue in shared memory; then it pools the queue four
@@ -839,6 +811,18 @@ spmdm_direct_compact_kernel(const __grid_constant__ SpmdmParams p) {
   direct_block_compact<BITS, VEC, LPB, CPL>(p, blockIdx.x);
 }
 
+// Several such tables in one launch (see spmdm_direct_multi_kernel).
+template <int BITS, int VEC, int LPB, int CPL>
+__global__ void __launch_bounds__(kThreads)
+spmdm_direct_compact_multi_kernel(const __grid_constant__ MultiArgs a) {
+  int t = 0;
+#pragma unroll
+  for (int i = 1; i < kMultiTables; ++i) {
+    t += (i < a.count && blockIdx.x >= (unsigned)a.first_block[i]) ? 1 : 0;
+  }
+  direct_block_compact<BITS, VEC, LPB, CPL>(a.t[t], (int64_t)blockIdx.x - a.first_block[t]);
+}
+
 using KernelFn = void (*)(const SpmdmParams);
 using MultiKernelFn = void (*)(const MultiArgs);
 
@@ -846,6 +830,7 @@ struct Variant {
   KernelFn fn;
   MultiKernelFn multi;
   KernelFn compact;
+  MultiKernelFn compact_multi;
   int vec, lpb, cpl;
 };
 

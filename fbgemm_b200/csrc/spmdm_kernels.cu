@@ -521,9 +521,11 @@ static cudaError_t launch_direct(const SpmdmParams& p, int bit_rate, cudaStream_
   if (blocks <= 0 || blocks > 0x7fffffffLL) {
     return cudaErrorInvalidValue;
   }
-  // Row-wise sparse tables: compact the rows that remain before pooling them
-  // (FBGEMM_B200_COMPACT=0/1 overrides, a tuning aid).
-  const int compact = env_int("FBGEMM_B200_COMPACT", (p.flags & kPruned) ? 1 : 0);
+  // Tables in which an index may name no row (a pruning map, or the layout in
+  // which -1 is a pruned index) take the compacting kernel; the plain one has
+  // no notion of a skipped row.  FBGEMM_B200_COMPACT=1 sends dense tables there
+  // too (a tuning aid).
+  const bool compact = (p.flags & (kPruned | kSbFirst)) || env_int("FBGEMM_B200_COMPACT", 0) == 1;
   (compact ? pick->compact : pick->fn)<<<(unsigned)blocks, direct::kThreads, 0, stream>>>(p);
   g_launch_count.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError();
@@ -563,15 +565,19 @@ cudaError_t build_multi_plan(const std::vector<SpmdmParams>& tables, const std::
       plan->singles.push_back({tables[t], bit_rates[t]});
     }
   }
-  std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) { return variant[a] < variant[b]; });
+  auto may_skip = [&](size_t t) { return (tables[t].flags & (kPruned | kSbFirst)) != 0; };
+  std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) {
+    return variant[a] != variant[b] ? variant[a] < variant[b] : may_skip(a) < may_skip(b);
+  });
   for (size_t i = 0; i < order.size();) {
     const direct::Variant* v = variant[order[i]];
+    const bool skip = may_skip(order[i]);
     plan->groups.emplace_back();
     MultiPlan::Launch& g = plan->groups.back();
-    g.fn = v->multi;
+    g.fn = skip ? v->compact_multi : v->multi;
     g.args = MultiArgs{};
     int64_t blocks = 0;
-    for (; i < order.size() && variant[order[i]] == v && g.args.count < kMultiTables; ++i) {
+    for (; i < order.size() && variant[order[i]] == v && may_skip(order[i]) == skip && g.args.count < kMultiTables; ++i) {
       const int64_t b = direct_blocks(v, tables[order[i]].output_size);
       if (blocks + b > 0x7fffffffLL) {
         break;  // the rest of this variant's tables start a new launch
