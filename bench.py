@@ -42,9 +42,9 @@ NUM_BATCHES = 32        # distinct pre-generated batches the steps rotate over
 # DRAM bytes (read + write) per lookup launch, from ncu captures of the same
 # launch shape: key = (workload, batches per call).
 TRAFFIC_BYTES_PER_LAUNCH = {
-    (1, 1): 13_755_648,             # profiles/spmdm_direct_kernel__workload1_one_batch.md
-    (1, 16): 171_206_400 + 8_106_496,   # profiles/spmdm_direct_kernel__workload1_16batches.md
-    (0, 16): 438_344_192 + 71_286_528,  # profiles/spmdm_direct_kernel__workload0_16batches.md
+    (1, 1): 13_766_144,             # profiles/spmdm_direct_kernel__workload1_one_batch.md
+    (1, 16): 171_163_904 + 7_316_992,   # profiles/spmdm_direct_kernel__workload1_16batches.md
+    (0, 16): 438_465_024 + 71_525_888,  # profiles/spmdm_direct_kernel__workload0_16batches.md
     (2, 16): 233_486_336 + 49_955_840,  # profiles/spmdm_direct_compact_kernel__workload2_16batches.md
 }
 
