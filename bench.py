@@ -55,7 +55,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=20000)
     ap.add_argument("--warmup", type=int, default=500)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", type=int, default=1, help="index into BASELINE.json configs (0..4)")
+    ap.add_argument("--workload", type=int, default=1, help="which benchmark configuration (0..4): 8-bit, 4-bit (default), pruned 2-bit, 64 mixed tables, 256 large tables")
     ap.add_argument("--streams", type=int, default=16, help="streams the graph spreads the launches over")
     ap.add_argument("--group", type=int, default=1, help="batches concatenated into one call (1 = the config's batch)")
     ap.add_argument("--scale", type=float, default=1.0, help="shrink table rows (and, for workloads 0-2, the batch)")
@@ -240,7 +240,7 @@ def time_cpu(workload, batches, host_table, host_cit, threads, max_steps, max_se
     return dt, steps, nbytes, kind, desc + ("; OpenMP threads over contiguous bag ranges" if jit.available else "")
 
 
-# ---- multi-table workloads (BASELINE configs 3 and 4) ------------------------------
+# ---- multi-table workloads (configurations 3 and 4) ----------------------------------
 
 def main_multi(args):
     """Table-wise sharded multi-table lookup: every rank pools the global batch

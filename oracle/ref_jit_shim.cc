@@ -1,5 +1,5 @@
 /*
- * TEST / BASELINE INFRASTRUCTURE - NOT PART OF THE PRODUCT.
+ * TEST AND CPU-BASELINE INFRASTRUCTURE - NOT PART OF THE PRODUCT.
  *
  * The reference's fast CPU path for the quantized embedding bag is x86 code
  * that FBGEMM emits at run time with asmjit (src/EmbeddingSpMDM.cc:161-968,

@@ -82,7 +82,7 @@ static Inputs make(std::mt19937& g, int bit_rate, int batch, int rows, int dim, 
 
 int main() {
   std::mt19937 g(2024);
-  // --- 8-bit, int64/int64, fp32 out: GenerateEmbeddingSpMDM as in BASELINE config 0 (host pointers)
+  // --- 8-bit, int64/int64, fp32 out: GenerateEmbeddingSpMDM as the 8-bit benchmark configuration calls it (host pointers)
   for (int corner = 0; corner < 3; ++corner) {
     for (int dim : {128, 64, 40, 7}) {
       const int batch = 33, rows = 900;
