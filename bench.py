@@ -24,6 +24,7 @@ same line shape with ``"impl": "reference"``.
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import sys
@@ -257,7 +258,7 @@ def main_multi(args):
     if world > 1:
         import torch.distributed as dist
 
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(minutes=5))  # a lost rank ends the run
     import fbgemm_b200 as F
     from fbgemm_b200 import workloads as W
     from fbgemm_b200.sharding import ShardedLookup, TableWisePlan, expected_cost
@@ -417,7 +418,7 @@ def main():
         import torch.distributed as dist
 
         if args.impl != "reference":
-            dist.init_process_group("nccl", device_id=dev)
+            dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(minutes=5))  # a lost rank ends the run
 
     import fbgemm_b200 as F
     from fbgemm_b200 import workloads as W

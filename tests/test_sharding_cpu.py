@@ -97,3 +97,44 @@ def test_batchwise_redistribution_two_gloo_ranks():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert sorted(results) == [(0, True, (6, 24)), (1, True, (6, 24))]
+
+
+def _rank_that_may_leave(rank, world, port, leaver, q):
+    """Rank `leaver` raises before the redistribution (a failure made on the
+    host); the others must see their exchange fail within the process group's
+    short timeout instead of waiting for ever."""
+    import datetime
+    import time
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    plan = TableWisePlan([0, 1], [4, 4], world)
+    local_out = torch.full((8, 4), float(rank))
+    t0 = time.monotonic()
+    try:
+        if rank == leaver:
+            raise RuntimeError("this rank's lookup failed")       # never joins the exchange
+        exchange_pooled(local_out, plan, rank)
+        q.put((rank, "completed", time.monotonic() - t0))
+    except RuntimeError as e:
+        kind = "left" if "lookup failed" in str(e) else "exchange failed"
+        q.put((rank, kind, time.monotonic() - t0))
+    # no destroy_process_group: the survivor's group is broken, the leaver just exits
+
+
+def test_a_rank_that_leaves_is_detected_by_the_others():
+    world = 2
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_rank_that_may_leave, args=(r, world, port, 1, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict((r, (kind, dt)) for r, kind, dt in (q.get(timeout=120) for _ in procs))
+    for p in procs:
+        p.join(timeout=60)
+    assert results[1][0] == "left"
+    assert results[0][0] == "exchange failed", results      # detected, not hung
+    assert results[0][1] < 60
