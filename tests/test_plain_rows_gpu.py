@@ -57,7 +57,7 @@ def test_reference_shapes(gpu_ctx, oracle, in_kind):
         stride = dim + (shape_i % 3)   # padded rows; odd strides take the element-wise kernel
         table = random_plain_table(rng, rows, dim, in_kind, stride)
         ebits, ebias = ((4, 7), (5, 15))[shape_i % 2]
-        for corner in (None, "oob"):
+        for corner in (None, "oob", "empty"):
             lengths, offsets, indices, weights, n = lengths_indices_weights(rng, batch, rows, avg_len, idt, odt, corner)
             if corner is None and not sb_last:
                 indices[rng.integers(0, n, max(1, n // 5))] = -1
@@ -68,8 +68,9 @@ def test_reference_shapes(gpu_ctx, oracle, in_kind):
             kern = generate(in_kind, dim, weighted, normalize, use_offsets, idt, odt, kind, sb_last, False, stride, ebits,
                             ebias)
             out = torch.ones(batch * dim + 6, dtype=TORCH_KIND[kind], device="cuda")
-            ok = kern(batch, n, rows, dev(table), dev(indices), dev(ol), dev(weights) if weighted else None, out)
-            assert ok == ok_ref == (corner is None)
+            ok = kern(batch, n, rows, dev(table), dev(indices) if n else None, dev(ol),
+                      dev(weights) if weighted and n else None, out)
+            assert ok == ok_ref == (corner != "oob")
             assert (out[batch * dim:].float().cpu().numpy() == 1).all(), "wrote past the output"
             if ok:
                 np.testing.assert_array_equal(out_bits(out)[:batch * dim], bits(ref[:batch * dim]), err_msg=str(shape_i))
