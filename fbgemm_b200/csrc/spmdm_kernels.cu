@@ -7,7 +7,14 @@
 //
 //     acc[j] = fma(w*scale, q[j], acc[j] + w*bias)    rows in index order
 //
-// Scheduling.  A bag is owned by a group of LPB lanes (8, 16 or a full warp,
+// This file holds (1) the staged kernel, which takes every shape and option,
+// (2) the dispatcher that sends a lookup to one of the register-resident
+// direct kernels (spmdm_direct.cuh; dense or compacting) when a variant fits
+// the row width, else to the staged kernel, and (3) the multi-table plans that
+// put up to 16 tables of the same variant into one launch.
+//
+// Scheduling of the staged kernel.  A bag is owned by a group of LPB lanes (8,
+// 16 or a full warp,
 // chosen from the row width), so a warp pools 4, 2 or 1 bags at once and the
 // rows of one bag are accumulated strictly in order (no cross-lane reduction:
 // that would change the rounding).  What IS parallel inside a bag is the
