@@ -92,6 +92,12 @@ SIGNATURES = {
     "fbgemm_b200_spmdm_lengths_noalloc": (C.c_int, [_cfgp, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, _p]),
     "fbgemm_b200_compressed_indices_remap": (C.c_int, [_p, C.c_int32, _p, C.c_int32, _i64, _p, _i64, _p, _p, _p, _p,
                                                        _p, _p]),
+    "fbgemm_b200_pruned_hashmap_lookup": (C.c_int, [_p, C.c_int32, C.c_int32, _p, _p, C.c_int32, _i64, _p, C.c_int32,
+                                                    _p, _p, C.c_int32, _p]),
+    "fbgemm_b200_pruned_array_lookup": (C.c_int, [_p, C.c_int32, C.c_int32, _p, _p, C.c_int32, _i64, _p, C.c_int32,
+                                                  _p, _p, C.c_int32, _p]),
+    "fbgemm_b200_pruned_hashmap_insert_host": (C.c_int, [C.c_int32, C.c_int32, _p, _p, _p, C.c_int32, _p, C.c_int32,
+                                                         _p]),
     "fbgemm_b200_table_register": (C.c_int, [_p, _p, C.c_size_t]),
     "fbgemm_b200_table_unregister": (C.c_int, [_p, _p]),
     "fbgemm_b200_table_device_ptr": (_p, [_p, _p]),

@@ -6,6 +6,7 @@
 #include <mutex>
 #include <new>
 #include <unordered_map>
+#include <type_traits>
 #include <vector>
 
 #include "internal.h"
@@ -429,6 +430,104 @@ int fbgemm_b200::enqueue_lookup(
   return 0;
 }
 
+namespace {
+
+int pruned_lookup(
+    bool hashmap,
+    fbgemm_b200_ctx* ctx,
+    int32_t T,
+    int32_t B,
+    const void* indices,
+    const void* offsets,
+    int32_t index_bytes,
+    int64_t index_size,
+    const void* map,
+    int32_t map_bytes,
+    const int64_t* map_offsets,
+    void* dense_indices,
+    int32_t slot,
+    void* stream) {
+  const char* what = hashmap ? "pruned_hashmap_lookup: bad argument" : "pruned_array_lookup: bad argument";
+  if (!ctx || slot < 0 || slot >= FBGEMM_B200_STATUS_SLOTS) {
+    set_error("bad context or status slot");
+    return FBGEMM_B200_EINVAL;
+  }
+  const size_t map_align = hashmap ? 2 * (size_t)map_bytes : (size_t)map_bytes;
+  if (T < 1 || B < 1 || (index_bytes != 4 && index_bytes != 8) || (map_bytes != 4 && map_bytes != 8) ||
+      index_size < 0 || !offsets || !map_offsets || (index_size > 0 && (!indices || !dense_indices)) ||
+      reinterpret_cast<uintptr_t>(map) % map_align != 0) {
+    set_error(what);
+    return FBGEMM_B200_EINVAL;
+  }
+  DeviceGuard guard(ctx->device);
+  const cudaError_t e =
+      launch_pruned_lookup(hashmap, T, B, indices, offsets, index_bytes, index_size, map, map_bytes, map_offsets,
+                           dense_indices, ctx->status + 4 * slot, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) {
+    return fail_cuda(e, "pruned index lookup launch");
+  }
+  return 0;
+}
+
+template <typename Index, typename Hash>
+bool hashmap_insert(
+    int32_t T,
+    int32_t B,
+    const Index* indices,
+    const Index* dense,
+    const Index* offsets,
+    Hash* table,
+    const int64_t* table_offsets) {
+  using Unsigned = typename std::make_unsigned<Index>::type;
+  bool ok = true;
+  for (int32_t t = 0; t < T; ++t) {
+    const int64_t first = table_offsets[t];
+    const uint64_t capacity = (uint64_t)(table_offsets[t + 1] - first);
+    if (capacity == 0) {
+      continue;
+    }
+    Hash* slots = table + 2 * first;
+    for (int64_t k = offsets[(int64_t)t * B]; k < (int64_t)offsets[(int64_t)(t + 1) * B]; ++k) {
+      if (dense[k] == -1) {
+        continue;
+      }
+      const Unsigned key = (Unsigned)indices[k];
+      uint64_t h;
+      if (sizeof(Index) == 8) {
+        uint64_t x = (uint64_t)key;
+        x ^= x >> 33;
+        x *= 0xff51afd7ed558ccdULL;
+        x ^= x >> 33;
+        x *= 0xc4ceb9fe1a85ec53ULL;
+        x ^= x >> 33;
+        h = x;
+      } else {
+        uint32_t x = (uint32_t)key;
+        x ^= x >> 16;
+        x *= 0x85ebca6bu;
+        x ^= x >> 13;
+        x *= 0xc2b2ae35u;
+        x ^= x >> 16;
+        h = x;
+      }
+      uint64_t slot = h % capacity, tried = 0;
+      while (tried < capacity && slots[2 * slot] != -1 && (int64_t)slots[2 * slot] != (int64_t)indices[k]) {
+        slot = slot + 1 == capacity ? 0 : slot + 1;
+        ++tried;
+      }
+      if (tried == capacity) {
+        ok = false;
+        continue;
+      }
+      slots[2 * slot] = (Hash)indices[k];
+      slots[2 * slot + 1] = (Hash)dense[k];
+    }
+  }
+  return ok;
+}
+
+}  // namespace
+
 extern "C" {
 
 int fbgemm_b200_ctx_create(int device, fbgemm_b200_ctx** out) {
@@ -766,6 +865,82 @@ int fbgemm_b200_compressed_indices_remap(
     return fail_cuda(e, "index remap launch");
   }
   return fbgemm_b200_status_read(ctx, slot, stream, nullptr);
+}
+
+int fbgemm_b200_pruned_hashmap_lookup(
+    fbgemm_b200_ctx* ctx,
+    int32_t T,
+    int32_t B,
+    const void* indices,
+    const void* offsets,
+    int32_t index_bytes,
+    int64_t index_size,
+    const void* hash_table,
+    int32_t hash_bytes,
+    const int64_t* hash_table_offsets,
+    void* dense_indices,
+    int32_t slot,
+    void* stream) {
+  return pruned_lookup(true, ctx, T, B, indices, offsets, index_bytes, index_size, hash_table, hash_bytes,
+                       hash_table_offsets, dense_indices, slot, stream);
+}
+
+int fbgemm_b200_pruned_array_lookup(
+    fbgemm_b200_ctx* ctx,
+    int32_t T,
+    int32_t B,
+    const void* indices,
+    const void* offsets,
+    int32_t index_bytes,
+    int64_t index_size,
+    const void* remappings,
+    int32_t remap_bytes,
+    const int64_t* remappings_offsets,
+    void* dense_indices,
+    int32_t slot,
+    void* stream) {
+  return pruned_lookup(false, ctx, T, B, indices, offsets, index_bytes, index_size, remappings, remap_bytes,
+                       remappings_offsets, dense_indices, slot, stream);
+}
+
+int fbgemm_b200_pruned_hashmap_insert_host(
+    int32_t T,
+    int32_t B,
+    const void* indices,
+    const void* dense_indices,
+    const void* offsets,
+    int32_t index_bytes,
+    void* hash_table,
+    int32_t hash_bytes,
+    const int64_t* hash_table_offsets) {
+  if (T < 1 || B < 1 || !offsets || !hash_table_offsets || (index_bytes != 4 && index_bytes != 8) ||
+      (hash_bytes != 4 && hash_bytes != 8)) {
+    set_error("pruned_hashmap_insert: bad argument");
+    return FBGEMM_B200_EINVAL;
+  }
+  // Empty inputs may come as null pointers (an empty tensor has no storage).
+  const int64_t last = (int64_t)T * B;
+  const int64_t covered = index_bytes == 8 ? static_cast<const int64_t*>(offsets)[last]
+                                           : (int64_t) static_cast<const int32_t*>(offsets)[last];
+  if ((covered > 0 && (!indices || !dense_indices)) || (hash_table_offsets[T] > 0 && !hash_table)) {
+    set_error("pruned_hashmap_insert: null indices or hash table");
+    return FBGEMM_B200_EINVAL;
+  }
+  bool ok;
+  if (index_bytes == 8 && hash_bytes == 8) {
+    ok = hashmap_insert(T, B, static_cast<const int64_t*>(indices), static_cast<const int64_t*>(dense_indices),
+                        static_cast<const int64_t*>(offsets), static_cast<int64_t*>(hash_table), hash_table_offsets);
+  } else if (index_bytes == 8) {
+    ok = hashmap_insert(T, B, static_cast<const int64_t*>(indices), static_cast<const int64_t*>(dense_indices),
+                        static_cast<const int64_t*>(offsets), static_cast<int32_t*>(hash_table), hash_table_offsets);
+  } else if (hash_bytes == 8) {
+    ok = hashmap_insert(T, B, static_cast<const int32_t*>(indices), static_cast<const int32_t*>(dense_indices),
+                        static_cast<const int32_t*>(offsets), static_cast<int64_t*>(hash_table), hash_table_offsets);
+  } else {
+    ok = hashmap_insert(T, B, static_cast<const int32_t*>(indices), static_cast<const int32_t*>(dense_indices),
+                        static_cast<const int32_t*>(offsets), static_cast<int32_t*>(hash_table), hash_table_offsets);
+  }
+  return ok ? 1 : 0;
 }
 
 /* ---- table registry ----------------------------------------------------- */

@@ -166,6 +166,24 @@ cudaError_t launch_compressed_indices_remap(
     void* scratch,
     cudaStream_t stream);
 
+// Sparse -> dense index remapping of table-batched pruned tables through a
+// per-table hash map (hashmap = true; map is [.][2] integers) or a per-table
+// array (pruned_lookup_kernels.cu).  One launch, nothing allocated.
+cudaError_t launch_pruned_lookup(
+    bool hashmap,
+    int32_t T,
+    int32_t B,
+    const void* indices,
+    const void* offsets,
+    int index_bytes,
+    int64_t index_size,
+    const void* map,
+    int map_bytes,
+    const int64_t* map_offsets,
+    void* dense_indices,
+    int32_t* status,
+    cudaStream_t stream);
+
 // One contiguous piece of a call's inputs, from page-locked host memory (the
 // address the GPU sees it at) to device memory; three of them per launch
 // (stage_kernels.cu).  Empty segments have bytes = 0.

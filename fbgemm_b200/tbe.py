@@ -188,3 +188,70 @@ def int_nbit_split_embedding_codegen_forward(dev_weights, weights_offsets, weigh
                                           row_alignment, output_dtype, scale_bias_last, indice_weights is not None,
                                           indices.dtype)
     return op.forward(indices, offsets, indice_weights)
+
+
+def _index_tensors(indices, offsets):
+    assert indices.is_cuda and offsets.is_cuda and indices.dtype == offsets.dtype
+    assert indices.dtype in (torch.int32, torch.int64) and indices.is_contiguous() and offsets.is_contiguous()
+
+
+def _pruned_lookup(fn_name, indices, offsets, mapping, mapping_offsets, slot):
+    _index_tensors(indices, offsets)
+    assert mapping.is_cuda and mapping.is_contiguous() and mapping.dtype in (torch.int32, torch.int64)
+    assert mapping_offsets.is_cuda and mapping_offsets.dtype == torch.int64 and mapping_offsets.is_contiguous()
+    T = mapping_offsets.numel() - 1
+    assert T > 0 and (offsets.numel() - 1) % T == 0
+    B = (offsets.numel() - 1) // T
+    if B <= 0:
+        raise ValueError("B must be positive")
+    ctx = E.get_context(indices.device.index)
+    dense = torch.empty_like(indices)
+    fn = getattr(E._capi.lib(), fn_name)
+    rc = fn(ctx.handle, T, B, E._ptr(indices), E._ptr(offsets), indices.element_size(), indices.numel(),
+            E._ptr(mapping), mapping.element_size(), E._ptr(mapping_offsets), E._ptr(dense), slot,
+            torch.cuda.current_stream(indices.device).cuda_stream)
+    E._capi.check(rc, fn_name)
+    return dense
+
+
+def pruned_hashmap_lookup(indices: torch.Tensor, offsets: torch.Tensor, hash_table: torch.Tensor,
+                          hash_table_offsets: torch.Tensor, slot: int = 0) -> torch.Tensor:
+    """``torch.ops.fbgemm.pruned_hashmap_lookup`` of the reference
+    (embedding_forward_quantized_cpu_template.cpp:524-601) on CUDA tensors:
+    the dense index of every index of a table-batched call, -1 for pruned
+    rows; tables whose hash table is empty keep their indices.  Asynchronous
+    on torch's current stream."""
+    assert hash_table.dim() == 2 and hash_table.shape[1] == 2
+    return _pruned_lookup("fbgemm_b200_pruned_hashmap_lookup", indices, offsets, hash_table, hash_table_offsets, slot)
+
+
+def pruned_array_lookup(indices: torch.Tensor, offsets: torch.Tensor, index_remappings: torch.Tensor,
+                        index_remappings_offsets: torch.Tensor, slot: int = 0) -> torch.Tensor:
+    """``torch.ops.fbgemm.pruned_array_lookup`` (same file, :605-659) on CUDA
+    tensors.  An index outside its table's remapping array gives -1 and shows
+    in status slot ``slot`` (``fbgemm_b200.status_read``)."""
+    assert index_remappings.dim() == 1
+    return _pruned_lookup("fbgemm_b200_pruned_array_lookup", indices, offsets, index_remappings,
+                          index_remappings_offsets, slot)
+
+
+def pruned_hashmap_insert(indices: torch.Tensor, dense_indices: torch.Tensor, offsets: torch.Tensor,
+                          hash_table: torch.Tensor, hash_table_offsets: torch.Tensor) -> bool:
+    """``torch.ops.fbgemm.pruned_hashmap_insert`` (same file, :124-204): host
+    tensors, ``hash_table`` filled in place (start from -1 everywhere); move it
+    to the GPU afterwards, as the reference's own GPU module does.  Returns
+    False if a table had no free slot left for a key."""
+    for x in (indices, dense_indices, offsets, hash_table, hash_table_offsets):
+        assert not x.is_cuda and x.is_contiguous()
+    assert indices.dtype == offsets.dtype == dense_indices.dtype and indices.dtype in (torch.int32, torch.int64)
+    assert hash_table.dim() == 2 and hash_table.shape[1] == 2 and hash_table.dtype in (torch.int32, torch.int64)
+    assert hash_table_offsets.dtype == torch.int64
+    T = hash_table_offsets.numel() - 1
+    assert T > 0 and (offsets.numel() - 1) % T == 0
+    B = (offsets.numel() - 1) // T
+    if B <= 0:
+        raise ValueError("B must be positive")
+    rc = E._capi.lib().fbgemm_b200_pruned_hashmap_insert_host(
+        T, B, indices.data_ptr(), dense_indices.data_ptr(), offsets.data_ptr(), indices.element_size(),
+        hash_table.data_ptr(), hash_table.element_size(), hash_table_offsets.data_ptr())
+    return bool(E._capi.check(rc, "fbgemm_b200_pruned_hashmap_insert_host"))

@@ -332,15 +332,7 @@ FBGEMM_B200_API int fbgemm_b200_spmdm_lengths_noalloc(
     const int32_t* compressed_indices_table,
     void* stream);
 
-/* ---- pooled lookup, host pointers -------------------------------------- */
-
-/*
- * The reference functor is called with host pointers.  A caller that keeps
- * its buffers in host memory registers each table once (the table then lives
- * in HBM) and afterwards passes the same host address as `input`; indices,
- * offsets/lengths, weights and the output travel through pinned staging
- * buffers on every call.
- */
+/* ---- index remapping ahead of the lookup --------------------------------- */
 
 /*
  * fbgemm::compressed_indices_remap<IndexType> (include/fbgemm/FbgemmEmbedding.h:393-401,
@@ -370,6 +362,95 @@ FBGEMM_B200_API int fbgemm_b200_compressed_indices_remap(
     void* out_offsets,
     float* out_weights,
     void* stream);
+
+/*
+ * Index remapping of table-batched pruned tables (the step a table-batched
+ * caller runs before the lookup when rows were pruned):
+ *   pruned_hashmap_lookup_{un}weighted_cpu and pruned_array_lookup_cpu,
+ *   fbgemm_gpu/codegen/inference/embedding_forward_quantized_cpu_template.cpp:524-601, :605-659
+ *   (GPU forms: embedding_forward_quantized_split_lookup.cu:20-160).
+ * `offsets` holds T*B+1 entries, table after table; position k of `indices`
+ * belongs to the table t with offsets[t*B] <= k < offsets[(t+1)*B].
+ *
+ * hashmap: hash_table is [sum of capacities][2] integers of hash_bytes (4 or
+ * 8) each, (sparse index, dense index), sparse index -1 = empty slot; table t
+ * owns slots [hash_table_offsets[t], hash_table_offsets[t+1]).  The index is
+ * hashed in its own width with the MurmurHash3 finaliser (:102-120), reduced
+ * modulo the capacity and probed linearly; dense_indices[k] is the dense
+ * index, or -1 when an empty slot is met first (a pruned row).  A table of
+ * capacity 0 is not pruned: its indices are copied.  Unlike the reference,
+ * whose probe loop has no end on a full table that lacks the key, a probe
+ * sequence stops after `capacity` slots with -1.
+ *
+ * array: remappings is one array of remap_bytes-wide integers; table t owns
+ * [remappings_offsets[t], remappings_offsets[t+1]) and dense_indices[k] =
+ * remappings[start_t + indices[k]]; capacity 0 copies the indices.  An index
+ * outside its table's array (the reference reads out of bounds) gives -1 and
+ * a return value of 0.
+ *
+ * All pointers are device pointers; hash_table_offsets / remappings_offsets
+ * are int64[T+1].  index_size = entries in `indices` and `dense_indices`;
+ * positions the offsets do not cover are left untouched.  Asynchronous on
+ * `stream`; a bad index shows in status slot `slot`.  Returns 0 or a negative
+ * code.
+ */
+FBGEMM_B200_API int fbgemm_b200_pruned_hashmap_lookup(
+    fbgemm_b200_ctx* ctx,
+    int32_t T,
+    int32_t B,
+    const void* indices,
+    const void* offsets,
+    int32_t index_bytes,
+    int64_t index_size,
+    const void* hash_table,
+    int32_t hash_bytes,
+    const int64_t* hash_table_offsets,
+    void* dense_indices,
+    int32_t slot,
+    void* stream);
+
+FBGEMM_B200_API int fbgemm_b200_pruned_array_lookup(
+    fbgemm_b200_ctx* ctx,
+    int32_t T,
+    int32_t B,
+    const void* indices,
+    const void* offsets,
+    int32_t index_bytes,
+    int64_t index_size,
+    const void* remappings,
+    int32_t remap_bytes,
+    const int64_t* remappings_offsets,
+    void* dense_indices,
+    int32_t slot,
+    void* stream);
+
+/*
+ * pruned_hashmap_insert_{un}weighted_cpu (same file, :124-204): fills the
+ * hash table at model-load time.  HOST pointers and host code, as in the
+ * reference (whose GPU module also inserts on the CPU and then moves the
+ * table); positions whose dense index is -1 are not inserted.  Returns 1, or
+ * 0 if a table was full (the reference would not return), or a negative code.
+ */
+FBGEMM_B200_API int fbgemm_b200_pruned_hashmap_insert_host(
+    int32_t T,
+    int32_t B,
+    const void* indices,
+    const void* dense_indices,
+    const void* offsets,
+    int32_t index_bytes,
+    void* hash_table,
+    int32_t hash_bytes,
+    const int64_t* hash_table_offsets);
+
+/* ---- pooled lookup, host pointers -------------------------------------- */
+
+/*
+ * The reference functor is called with host pointers.  A caller that keeps
+ * its buffers in host memory registers each table once (the table then lives
+ * in HBM) and afterwards passes the same host address as `input`; indices,
+ * offsets/lengths, weights and the output travel through pinned staging
+ * buffers on every call.
+ */
 
 /* Copy `bytes` of a fused-row table (or of a compressed_indices_table) to the
  * device and remember it under its host address.  Registering the same

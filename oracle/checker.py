@@ -235,6 +235,42 @@ class Oracle(_Lookups):
         n = int(out_o[-1])
         return out_i[:n], out_o, (out_w[:n] if out_w is not None else None)
 
+    def pruned_hash(self, key, index_bytes):
+        f = self._fn("oracle_pruned_hash", [C.c_uint64, _int], C.c_uint64)
+        return int(f(int(key) & (2 ** 64 - 1), index_bytes))
+
+    def pruned_hashmap_insert(self, T, B, indices, dense_indices, offsets, hash_table, hash_table_offsets):
+        """Inserts in place into ``hash_table`` ([capacity, 2], int32 or int64, -1 = empty)."""
+        indices = np.ascontiguousarray(indices)
+        dense_indices = np.ascontiguousarray(dense_indices, dtype=indices.dtype)
+        offsets = np.ascontiguousarray(offsets, dtype=indices.dtype)
+        hto = np.ascontiguousarray(hash_table_offsets, dtype=np.int64)
+        assert hash_table.flags.c_contiguous and hash_table.shape[1] == 2
+        f = self._fn("oracle_pruned_hashmap_insert", [_i64, _i64, _p, _p, _p, _int, _p, _int, _p], _int)
+        return bool(f(T, B, _ptr(indices), _ptr(dense_indices), _ptr(offsets), indices.dtype.itemsize,
+                      _ptr(hash_table), hash_table.dtype.itemsize, _ptr(hto)))
+
+    def pruned_hashmap_lookup(self, T, B, indices, offsets, hash_table, hash_table_offsets):
+        indices = np.ascontiguousarray(indices)
+        offsets = np.ascontiguousarray(offsets, dtype=indices.dtype)
+        hto = np.ascontiguousarray(hash_table_offsets, dtype=np.int64)
+        out = np.full_like(indices, -7)
+        f = self._fn("oracle_pruned_hashmap_lookup", [_i64, _i64, _p, _p, _int, _p, _int, _p, _p], None)
+        f(T, B, _ptr(indices), _ptr(offsets), indices.dtype.itemsize, _ptr(hash_table), hash_table.dtype.itemsize,
+          _ptr(hto), _ptr(out))
+        return out
+
+    def pruned_array_lookup(self, T, B, indices, offsets, remappings, remappings_offsets):
+        indices = np.ascontiguousarray(indices)
+        offsets = np.ascontiguousarray(offsets, dtype=indices.dtype)
+        ro = np.ascontiguousarray(remappings_offsets, dtype=np.int64)
+        remappings = np.ascontiguousarray(remappings)
+        out = np.full_like(indices, -7)
+        f = self._fn("oracle_pruned_array_lookup", [_i64, _i64, _p, _p, _int, _p, _int, _p, _p], _int)
+        ok = bool(f(T, B, _ptr(indices), _ptr(offsets), indices.dtype.itemsize, _ptr(remappings),
+                    remappings.dtype.itemsize, _ptr(ro), _ptr(out)))
+        return ok, out
+
     def float_to_half(self, f):
         return int(self.lib.oracle_float_to_half_rn(float(f)))
 

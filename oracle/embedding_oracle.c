@@ -810,3 +810,155 @@ ORACLE_API void oracle_compressed_indices_remap(
     }
   }
 }
+
+/* ------------------------------------------------------------------------- */
+/* Index remapping of table-batched pruned tables, before the lookup.         */
+/* Restates fbgemm_gpu/codegen/inference/embedding_forward_quantized_cpu_     */
+/* template.cpp: pruned_hash_function :102-120 (the MurmurHash3 32- and       */
+/* 64-bit finalisers), pruned_hashmap_insert_*_cpu :124-204,                  */
+/* pruned_hashmap_lookup_*_cpu :524-601 and pruned_array_lookup_cpu :605-659. */
+/*                                                                            */
+/* Parity status of THIS block: UNPINNED against reference output.  The       */
+/* functions live in a Jinja template over ATen tensors, which cannot be      */
+/* compiled from its own sources here, and the reference holds no golden      */
+/* vectors for them; they are checked by the property the reference's own     */
+/* test uses (fbgemm_gpu/test/tbe/utils/split_embeddings_utils_test.py:       */
+/* 476-620: insert, then every inserted index looks up its dense index and    */
+/* any other index looks up -1) and by the published MurmurHash3 finalisers.  */
+/*                                                                            */
+/* One deliberate difference: the reference probes `while (true)`, which      */
+/* never ends on a full table that lacks the key; here a probe sequence ends  */
+/* after `capacity` slots (lookup: -1; insert: returns 0).                    */
+/* ------------------------------------------------------------------------- */
+
+static inline uint32_t pruned_hash32(uint32_t h) {
+  h ^= h >> 16;
+  h *= 0x85ebca6bu;
+  h ^= h >> 13;
+  h *= 0xc2b2ae35u;
+  h ^= h >> 16;
+  return h;
+}
+
+static inline uint64_t pruned_hash64(uint64_t k) {
+  k ^= k >> 33;
+  k *= 0xff51afd7ed558ccdULL;
+  k ^= k >> 33;
+  k *= 0xc4ceb9fe1a85ec53ULL;
+  k ^= k >> 33;
+  return k;
+}
+
+ORACLE_API uint64_t oracle_pruned_hash(uint64_t key, int index_bytes) {
+  return index_bytes == 8 ? pruned_hash64(key) : (uint64_t)pruned_hash32((uint32_t)key);
+}
+
+static inline void store_int(void* p, int64_t i, int64_t v, int width) {
+  if (width == 8) {
+    ((int64_t*)p)[i] = v;
+  } else {
+    ((int32_t*)p)[i] = (int32_t)v;
+  }
+}
+
+static inline uint64_t first_slot(int64_t idx, int index_bytes, int64_t capacity) {
+  /* the index is hashed in its own width (static_cast<uidx_t>(idx), :176,:573) */
+  const uint64_t h = index_bytes == 8 ? pruned_hash64((uint64_t)idx) : (uint64_t)pruned_hash32((uint32_t)idx);
+  return h % (uint64_t)capacity;
+}
+
+/* hash_table: [sum(capacity)][2] of hash_bytes-wide integers, (-1,-1) = empty. */
+ORACLE_API int oracle_pruned_hashmap_insert(
+    int64_t T, int64_t B, const void* indices, const void* dense_indices, const void* offsets, int index_bytes,
+    void* hash_table, int hash_bytes, const int64_t* hash_table_offsets) {
+  int ok = 1;
+  for (int64_t t = 0; t < T; ++t) {
+    const int64_t table_start = hash_table_offsets[t];
+    const int64_t capacity = hash_table_offsets[t + 1] - table_start;
+    if (capacity == 0) {
+      continue;
+    }
+    const int64_t lo = load_int(offsets, t * B, index_bytes), hi = load_int(offsets, (t + 1) * B, index_bytes);
+    for (int64_t k = lo; k < hi; ++k) {
+      const int64_t idx = load_int(indices, k, index_bytes);
+      const int64_t dense = load_int(dense_indices, k, index_bytes);
+      if (dense == -1) {
+        continue; /* a pruned row is not inserted (:171-174) */
+      }
+      uint64_t slot = first_slot(idx, index_bytes, capacity);
+      int64_t probes = 0;
+      for (; probes < capacity; ++probes) {
+        const int64_t at = table_start + (int64_t)slot;
+        const int64_t key = load_int(hash_table, 2 * at, hash_bytes);
+        if (key == -1 || key == idx) {
+          store_int(hash_table, 2 * at, idx, hash_bytes);
+          store_int(hash_table, 2 * at + 1, dense, hash_bytes);
+          break;
+        }
+        slot = (slot + 1) % (uint64_t)capacity;
+      }
+      if (probes == capacity) {
+        ok = 0;
+      }
+    }
+  }
+  return ok;
+}
+
+ORACLE_API void oracle_pruned_hashmap_lookup(
+    int64_t T, int64_t B, const void* indices, const void* offsets, int index_bytes, const void* hash_table,
+    int hash_bytes, const int64_t* hash_table_offsets, void* dense_indices) {
+  for (int64_t t = 0; t < T; ++t) {
+    const int64_t table_start = hash_table_offsets[t];
+    const int64_t capacity = hash_table_offsets[t + 1] - table_start;
+    const int64_t lo = load_int(offsets, t * B, index_bytes), hi = load_int(offsets, (t + 1) * B, index_bytes);
+    for (int64_t k = lo; k < hi; ++k) {
+      const int64_t idx = load_int(indices, k, index_bytes);
+      if (capacity == 0) {
+        store_int(dense_indices, k, idx, index_bytes); /* table without pruning (:565-569) */
+        continue;
+      }
+      uint64_t slot = first_slot(idx, index_bytes, capacity);
+      int64_t found = -1;
+      for (int64_t probes = 0; probes < capacity; ++probes) {
+        const int64_t at = table_start + (int64_t)slot;
+        const int64_t key = load_int(hash_table, 2 * at, hash_bytes);
+        if (key == -1) {
+          break;
+        }
+        if (key == idx) {
+          found = load_int(hash_table, 2 * at + 1, hash_bytes);
+          break;
+        }
+        slot = (slot + 1) % (uint64_t)capacity;
+      }
+      store_int(dense_indices, k, found, index_bytes);
+    }
+  }
+}
+
+/* Returns 0 if an index falls outside its table's remapping array (the
+ * reference reads out of bounds there and leaves it to a bounds checker,
+ * split_embeddings_utils_test.py:612-614); such a position gets -1. */
+ORACLE_API int oracle_pruned_array_lookup(
+    int64_t T, int64_t B, const void* indices, const void* offsets, int index_bytes, const void* remappings,
+    int remap_bytes, const int64_t* remappings_offsets, void* dense_indices) {
+  int ok = 1;
+  for (int64_t t = 0; t < T; ++t) {
+    const int64_t start = remappings_offsets[t];
+    const int64_t capacity = remappings_offsets[t + 1] - start;
+    const int64_t lo = load_int(offsets, t * B, index_bytes), hi = load_int(offsets, (t + 1) * B, index_bytes);
+    for (int64_t k = lo; k < hi; ++k) {
+      const int64_t idx = load_int(indices, k, index_bytes);
+      if (capacity <= 0) {
+        store_int(dense_indices, k, idx, index_bytes);
+      } else if (idx < 0 || idx >= capacity) {
+        ok = 0;
+        store_int(dense_indices, k, -1, index_bytes);
+      } else {
+        store_int(dense_indices, k, load_int(remappings, start + idx, remap_bytes), index_bytes);
+      }
+    }
+  }
+  return ok;
+}
