@@ -903,6 +903,57 @@ int fbgemm_b200_pruned_array_lookup(
                        remappings_offsets, dense_indices, slot, stream);
 }
 
+int fbgemm_b200_sequence_lookup(
+    fbgemm_b200_ctx* ctx,
+    const void* dev_weights,
+    const fbgemm_b200_sequence_table* tables,
+    int32_t T,
+    int32_t B,
+    int32_t D,
+    const void* indices,
+    const void* offsets,
+    int32_t index_bytes,
+    int64_t index_size,
+    void* out,
+    int32_t out_dtype,
+    int64_t out_row_bytes,
+    int32_t scale_bias_last,
+    int32_t fp8_exponent_bits,
+    int32_t fp8_exponent_bias,
+    int32_t slot,
+    void* stream) {
+  if (!ctx || slot < 0 || slot >= FBGEMM_B200_STATUS_SLOTS) {
+    set_error("bad context or status slot");
+    return FBGEMM_B200_EINVAL;
+  }
+  int64_t min_row = 0;
+  switch (out_dtype) {
+    case FBGEMM_B200_OUT_F32: min_row = 4 * (int64_t)D; break;
+    case FBGEMM_B200_OUT_F16:
+    case FBGEMM_B200_OUT_BF16: min_row = 2 * (int64_t)D; break;
+    case FBGEMM_B200_OUT_U8:
+    case FBGEMM_B200_OUT_INT4: min_row = 1; break;
+    default: min_row = -1;
+  }
+  const int64_t elem = out_dtype == FBGEMM_B200_OUT_F32 ? 4 : (out_dtype <= FBGEMM_B200_OUT_BF16 ? 2 : 1);
+  if (T < 1 || B < 1 || D < 1 || min_row < 0 || out_row_bytes < min_row || out_row_bytes % elem != 0 ||
+      (index_bytes != 4 && index_bytes != 8) || index_size < 0 || !offsets || !tables ||
+      (index_size > 0 && (!indices || !out || !dev_weights)) || reinterpret_cast<uintptr_t>(out) % elem != 0 ||
+      fp8_exponent_bits < 0 || fp8_exponent_bits > 7 || fp8_exponent_bias < 0 || fp8_exponent_bias > 253) {
+    set_error("sequence_lookup: bad argument");
+    return FBGEMM_B200_EINVAL;
+  }
+  DeviceGuard guard(ctx->device);
+  const cudaError_t e = launch_sequence_lookup(
+      static_cast<const uint8_t*>(dev_weights), tables, T, B, D, indices, offsets, index_bytes, index_size, out,
+      out_dtype, out_row_bytes, scale_bias_last != 0, fp8_exponent_bits, fp8_exponent_bias, ctx->status + 4 * slot,
+      static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) {
+    return fail_cuda(e, "sequence lookup launch");
+  }
+  return 0;
+}
+
 int fbgemm_b200_pruned_hashmap_insert_host(
     int32_t T,
     int32_t B,

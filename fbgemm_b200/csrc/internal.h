@@ -184,6 +184,28 @@ cudaError_t launch_pruned_lookup(
     int32_t* status,
     cudaStream_t stream);
 
+// Sequence ("nobag") lookup over the tables of a table-batched call
+// (sequence_kernels.cu): one output row per index position, one launch.
+using SequenceTable = fbgemm_b200_sequence_table;
+cudaError_t launch_sequence_lookup(
+    const uint8_t* weights,
+    const SequenceTable* tables,
+    int32_t T,
+    int32_t B,
+    int32_t D,
+    const void* indices,
+    const void* offsets,
+    int index_bytes,
+    int64_t index_size,
+    void* out,
+    int out_kind,
+    int64_t out_row_bytes,
+    bool scale_bias_last,
+    int fp8_exponent_bits,
+    int fp8_exponent_bias,
+    int32_t* status,
+    cudaStream_t stream);
+
 // One contiguous piece of a call's inputs, from page-locked host memory (the
 // address the GPU sees it at) to device memory; three of them per launch
 // (stage_kernels.cu).  Empty segments have bytes = 0.

@@ -16,6 +16,7 @@
 // The reference's probe loop has no end on a full table that lacks the key;
 // here it stops after `capacity` slots with -1, so no launch can spin.
 #include "internal.h"
+#include "position_tables.cuh"
 
 namespace fbgemm_b200 {
 
@@ -23,7 +24,6 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kPerThread = 4;
-constexpr int kSharedStarts = 2048;  // table starts staged per block (16 KB)
 
 __device__ __forceinline__ int64_t load_int(const void* p, int64_t i, bool is64) {
   return is64 ? (int64_t)__ldg(reinterpret_cast<const long long*>(p) + i)
@@ -78,51 +78,10 @@ __device__ __forceinline__ void report(const PrunedArgs& a, int code, int64_t ta
   }
 }
 
-// Stage the table starts offsets[t*B], t = 0..T, clamped to the index array.
-// Returns the pointer the bisection reads (shared memory, or null = global).
-__device__ __forceinline__ const int64_t* stage_starts(const PrunedArgs& a, int64_t* smem) {
-  if (a.T + 1 > kSharedStarts) {
-    return nullptr;
-  }
-  for (int t = threadIdx.x; t <= a.T; t += kThreads) {
-    int64_t v = load_int(a.offsets, (int64_t)t * a.B, a.index64);
-    smem[t] = v < 0 ? 0 : (v > a.index_size ? a.index_size : v);
-  }
-  __syncthreads();
-  return smem;
-}
-
-__device__ __forceinline__ int64_t start_of(const PrunedArgs& a, const int64_t* starts, int t) {
-  if (starts) {
-    return starts[t];
-  }
-  const int64_t v = load_int(a.offsets, (int64_t)t * a.B, a.index64);
-  return v < 0 ? 0 : (v > a.index_size ? a.index_size : v);
-}
-
-// The table of position k: the last t in [0, T) with start(t) <= k, provided
-// k < start(T); -1 if no table covers k.  (With offsets that step backwards
-// the answer is some table - never an access outside the arrays.)
-__device__ __forceinline__ int table_of(const PrunedArgs& a, const int64_t* starts, int64_t k) {
-  if (k < start_of(a, starts, 0) || k >= start_of(a, starts, a.T)) {
-    return -1;
-  }
-  int lo = 0, hi = a.T;  // start(lo) <= k < start(hi)
-  while (hi - lo > 1) {
-    const int mid = (lo + hi) >> 1;
-    if (start_of(a, starts, mid) <= k) {
-      lo = mid;
-    } else {
-      hi = mid;
-    }
-  }
-  return lo;
-}
-
 template <bool HASH>
 __global__ void __launch_bounds__(kThreads) pruned_lookup_kernel(const PrunedArgs a) {
   __shared__ int64_t starts_s[kSharedStarts];
-  const int64_t* starts = stage_starts(a, starts_s);
+  const int64_t* starts = stage_table_starts(a, starts_s);
   const int64_t base = ((int64_t)blockIdx.x * kPerThread) * kThreads + threadIdx.x;
 #pragma unroll
   for (int i = 0; i < kPerThread; ++i) {

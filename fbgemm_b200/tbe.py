@@ -255,3 +255,127 @@ def pruned_hashmap_insert(indices: torch.Tensor, dense_indices: torch.Tensor, of
         T, B, indices.data_ptr(), dense_indices.data_ptr(), offsets.data_ptr(), indices.element_size(),
         hash_table.data_ptr(), hash_table.element_size(), hash_table_offsets.data_ptr())
     return bool(E._capi.check(rc, "fbgemm_b200_pruned_hashmap_insert_host"))
+
+
+_SEQ_TABLE = np.dtype([("weight_offset", np.int64), ("rows", np.int64), ("row_bytes", np.int32), ("type", np.int32)])
+_SEQ_OUT = {SparseType.FP32: (0, torch.float32), SparseType.FP16: (1, torch.float16),
+            SparseType.BF16: (2, torch.bfloat16), SparseType.INT8: (3, torch.uint8), SparseType.INT4: (4, torch.uint8)}
+
+
+class IntNBitSequenceEmbedding:
+    """The sequence ("nobag", ``PoolingMode.NONE``) form of the table-batched
+    operator, ``int_nbit_split_embedding_nobag_codegen_forward_unweighted_cpu``
+    of the reference (embedding_forward_quantized_cpu_template.cpp:206-520):
+    one output row per index, all tables of width ``D``.  Holds the table
+    descriptors on the device; ``forward`` is one kernel launch."""
+
+    def __init__(self, dev_weights: torch.Tensor, weights_offsets, weights_tys, D: int, row_alignment: int = 1,
+                 output_dtype: int = SparseType.FP16, scale_bias_last: bool = False, fp8_exponent_bits: int = 4,
+                 fp8_exponent_bias: int = 7):
+        assert dev_weights.is_cuda and dev_weights.dtype == torch.uint8 and dev_weights.is_contiguous()
+        self.dev_weights = dev_weights
+        self.device = dev_weights.device
+        self.D = int(D)
+        offs = _host(weights_offsets, np.int64)
+        tys = [SparseType(int(t)) for t in _host(weights_tys, np.int64)]
+        self.T = len(offs)
+        out_ty = SparseType(output_dtype)
+        if out_ty not in _SEQ_OUT:
+            raise ValueError("output_dtype must be FP32, FP16, BF16, INT8 or INT4")
+        self.out_code, self.out_dtype = _SEQ_OUT[out_ty]
+        # output row: D columns, plus the 4 bytes of fp16 scale and bias for INT8 / INT4 rows (:284-291)
+        if out_ty == SparseType.INT8:
+            self.out_cols = self.D + 4
+        elif out_ty == SparseType.INT4:
+            self.out_cols = (self.D + 8 + 1) // 2
+        else:
+            self.out_cols = self.D
+        self.out_row_bytes = self.out_cols * torch.empty((), dtype=self.out_dtype).element_size()
+        self.scale_bias_last = bool(scale_bias_last)
+        self.fp8 = (int(fp8_exponent_bits), int(fp8_exponent_bias))
+        physical = sorted(set(int(o) for o in offs))
+        desc = np.zeros(self.T, dtype=_SEQ_TABLE)
+        self.rows = []
+        for t in range(self.T):
+            ty = tys[t]
+            if ty not in _BITS and ty not in _PLAIN_BYTES:
+                raise ValueError(f"table {t}: weight type {ty.name} is not a row format of this path")
+            if out_ty == SparseType.INT8 and ty != SparseType.INT8:
+                raise ValueError("int8 output is only supported for int8 weights")
+            if out_ty == SparseType.INT4 and ty != SparseType.INT4:
+                raise ValueError("int4 output is only supported for int4 weights")
+            sb_bytes = 8 if (ty == SparseType.INT8 and scale_bias_last) else 4
+            row_bytes = padded_row_size_in_bytes(self.D, ty, row_alignment, sb_bytes)
+            if out_ty == SparseType.INT4 and row_bytes != self.out_row_bytes:
+                raise ValueError("int4 output needs table rows of (D + 8 + 1) / 2 bytes (row_alignment 1)")
+            start = int(offs[t])
+            nxt = [o for o in physical if o > start]
+            end = nxt[0] if nxt else dev_weights.numel()
+            desc[t] = (start, (end - start) // row_bytes, row_bytes, int(ty))
+            self.rows.append((end - start) // row_bytes)
+        self._desc = torch.from_numpy(desc.view(np.uint8).copy()).to(self.device)
+
+    def forward(self, indices: torch.Tensor, offsets: torch.Tensor, output: torch.Tensor | None = None,
+                slot: int = 0) -> torch.Tensor:
+        """``offsets`` has ``T*B + 1`` entries; returns ``[indices.numel(),
+        D (+ qparams)]``.  Asynchronous on torch's current stream."""
+        _index_tensors(indices, offsets)
+        assert (offsets.numel() - 1) % self.T == 0
+        B = (offsets.numel() - 1) // self.T
+        n = indices.numel()
+        if output is None:
+            output = torch.zeros((n, self.out_cols), dtype=self.out_dtype, device=self.device)
+        assert output.is_contiguous() and output.dtype == self.out_dtype and output.numel() == n * self.out_cols
+        if B == 0 or n == 0:
+            return output
+        ctx = E.get_context(self.device.index)
+        rc = E._capi.lib().fbgemm_b200_sequence_lookup(
+            ctx.handle, self.dev_weights.data_ptr(), self._desc.data_ptr(), self.T, B, self.D, indices.data_ptr(),
+            offsets.data_ptr(), indices.element_size(), n, output.data_ptr(), self.out_code, self.out_row_bytes,
+            int(self.scale_bias_last), self.fp8[0], self.fp8[1], slot,
+            torch.cuda.current_stream(self.device).cuda_stream)
+        E._capi.check(rc, "fbgemm_b200_sequence_lookup")
+        return output
+
+
+def int_nbit_split_embedding_nobag_codegen_forward_unweighted(
+        dev_weights, weights_offsets, weights_tys, D, indices, offsets, pooling_mode=PoolingMode.NONE,
+        row_alignment=1, output_dtype=SparseType.FP16, fp8_exponent_bits=4, fp8_exponent_bias=7,
+        scale_bias_last=False):
+    """One call with the reference operator's arguments (placement and UVM
+    arguments left out; ``pooling_mode`` is accepted and, bags being one row
+    long, changes nothing)."""
+    op = IntNBitSequenceEmbedding(dev_weights, weights_offsets, weights_tys, D, row_alignment, output_dtype,
+                                  scale_bias_last, fp8_exponent_bits, fp8_exponent_bias)
+    return op.forward(indices, offsets)
+
+
+def int_nbit_split_embedding_codegen_lookup_function(
+        dev_weights, uvm_weights, weights_placements, weights_offsets, weights_tys, D_offsets, total_D, max_int2_D,
+        max_int4_D, max_int8_D, max_float16_D, max_float32_D, indices, offsets, pooling_mode, indice_weights=None,
+        output_dtype=SparseType.FP16, lxu_cache_weights=None, lxu_cache_locations=None, row_alignment=None,
+        max_float8_D=None, fp8_exponent_bits=None, fp8_exponent_bias=None, scale_bias_last=False):
+    """``fbgemm::int_nbit_split_embedding_codegen_lookup_function`` with the
+    reference's argument list (embedding_forward_quantized_host_cpu.cpp:84-227):
+    ``PoolingMode.NONE`` goes to the sequence operator with ``D`` = the largest
+    of the ``max_*_D``, otherwise to the pooled operator, weighted when
+    ``indice_weights`` holds anything.  All tables live in ``dev_weights`` on
+    the GPU: ``uvm_weights``, ``weights_placements`` and the cache arguments
+    are accepted and must describe nothing (placement is not part of this path)."""
+    if uvm_weights is not None and uvm_weights.numel() > 0:
+        raise ValueError("tables in unified memory are outside this path: put every table in dev_weights")
+    if offsets.dtype != indices.dtype:
+        offsets = offsets.to(indices.dtype)
+    align = 1 if row_alignment is None else int(row_alignment)
+    bits = 4 if fp8_exponent_bits is None or fp8_exponent_bits < 0 else int(fp8_exponent_bits)
+    bias = 7 if fp8_exponent_bias is None or fp8_exponent_bias < 0 else int(fp8_exponent_bias)
+    if PoolingMode(pooling_mode) == PoolingMode.NONE:
+        max_D = max(int(max_int2_D), int(max_int4_D), int(max_int8_D), int(max_float8_D or 0), int(max_float16_D),
+                    int(max_float32_D))
+        return int_nbit_split_embedding_nobag_codegen_forward_unweighted(
+            dev_weights, weights_offsets, weights_tys, max_D, indices, offsets, pooling_mode, align, output_dtype,
+            bits, bias, scale_bias_last)
+    weighted = indice_weights is not None and indice_weights.numel() > 0
+    op = IntNBitTableBatchedEmbeddingBags(dev_weights, weights_offsets, weights_tys, D_offsets, total_D, pooling_mode,
+                                          align, output_dtype, scale_bias_last, weighted, indices.dtype, bits, bias)
+    return op.forward(indices, offsets, indice_weights if weighted else None)

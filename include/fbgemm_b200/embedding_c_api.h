@@ -442,6 +442,60 @@ FBGEMM_B200_API int fbgemm_b200_pruned_hashmap_insert_host(
     int32_t hash_bytes,
     const int64_t* hash_table_offsets);
 
+/* ---- sequence ("nobag") lookup over the tables of a table-batched call --- */
+
+#define FBGEMM_B200_OUT_INT4 4 /* sequence lookup only: packed 4-bit rows copied whole */
+
+/* One table of the call; an array of T of these lives in DEVICE memory.  type
+ * is the SparseType code of fbgemm_gpu/include/fbgemm_gpu/embedding_common.h:20-32
+ * (FP32 0, FP16 1, INT8 2, INT4 3, INT2 4, FP8 6). */
+typedef struct fbgemm_b200_sequence_table {
+  int64_t weight_offset; /* byte offset of the table's first row in dev_weights */
+  int64_t rows;
+  int32_t row_bytes;     /* padded row size (nbit::padded_row_size_in_bytes)   */
+  int32_t type;
+} fbgemm_b200_sequence_table;
+
+/*
+ * int_nbit_split_embedding_nobag_codegen_forward_unweighted_cpu
+ * (fbgemm_gpu/codegen/inference/embedding_forward_quantized_cpu_template.cpp:206-520,
+ * the `nobag` branch): no pooling, one output row per index.  Position k of
+ * `indices` belongs to the table t with offsets[t*B] <= k < offsets[(t+1)*B]
+ * (offsets: T*B+1 entries of the index type); output row k starts at byte
+ * k * out_row_bytes of `out` and holds
+ *   F32/F16/BF16: the D dequantized columns of row indices[k] - what the
+ *                 pooled kernel of the table's type gives for a bag of that one
+ *                 row without weights (:391-395, :421-473); with scale and bias
+ *                 first, index -1 is a pruned row and gives zeros;
+ *   U8:           min(out_row_bytes, row_bytes) bytes of the row (8-bit tables;
+ *                 the reference's out_row_bytes is D + 4);
+ *   INT4:         the row_bytes bytes of the row (4-bit tables; the caller
+ *                 makes out_row_bytes = row_bytes = (D + 8 + 1) / 2).
+ * All tables share D.  Everything is a device pointer; rows of positions that
+ * no table covers, or whose index is out of range (reported in status slot
+ * `slot`), are left as they were.  Asynchronous on `stream`; returns 0 or a
+ * negative code.
+ */
+FBGEMM_B200_API int fbgemm_b200_sequence_lookup(
+    fbgemm_b200_ctx* ctx,
+    const void* dev_weights,
+    const fbgemm_b200_sequence_table* tables,
+    int32_t T,
+    int32_t B,
+    int32_t D,
+    const void* indices,
+    const void* offsets,
+    int32_t index_bytes,
+    int64_t index_size,
+    void* out,
+    int32_t out_dtype,
+    int64_t out_row_bytes,
+    int32_t scale_bias_last,
+    int32_t fp8_exponent_bits,
+    int32_t fp8_exponent_bias,
+    int32_t slot,
+    void* stream);
+
 /* ---- pooled lookup, host pointers -------------------------------------- */
 
 /*
