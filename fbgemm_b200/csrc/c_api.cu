@@ -284,8 +284,11 @@ int fbgemm_b200::build_lookup_params(
   p.fp8_exponent_bias = cfg->fp8_exponent_bias;
   if (cfg->in_dtype != FBGEMM_B200_IN_QUANTIZED) {
     const int ebytes = cfg->in_dtype == FBGEMM_B200_IN_F32 ? 4 : (cfg->in_dtype == FBGEMM_B200_IN_FP8 ? 1 : 2);
-    if (cit || reinterpret_cast<uintptr_t>(input) % ebytes != 0) {
-      set_error("unquantized tables: no pruning map, and the table must be aligned to its element type");
+    // EmbeddingSpMDMRowWiseSparse_ref exists for float and fp16 rows only (src/RefImplementations.cc:1688-1743).
+    const bool map_ok = !cit || cfg->in_dtype == FBGEMM_B200_IN_F32 || cfg->in_dtype == FBGEMM_B200_IN_F16;
+    if (!map_ok || reinterpret_cast<uintptr_t>(input) % ebytes != 0) {
+      set_error("unquantized tables: a pruning map only with fp32 or fp16 rows, and the table must be aligned to "
+                "its element type");
       return FBGEMM_B200_EINVAL;
     }
   }

@@ -337,10 +337,11 @@ GenerateEmbeddingSpMDMRowWiseSparse(
     int /*prefetch*/,
     bool is_weight_positional,
     bool use_offsets) {
-  static_assert(std::is_same<InType, std::uint8_t>::value, "only fused 8-bit rows (InType = uint8_t)");
+  // InType uint8_t: fused 8-bit rows; float, float16 and uint16_t (read as fp16 here, as in
+  // EmbeddingSpMDMRowWiseSparse_ref, src/RefImplementations.cc:1720-1728): rows of block_size elements.
   const fbgemm_b200_spmdm_config cfg = make_config(
       8, sizeof(IndexType), sizeof(OffsetType), FBGEMM_B200_OUT_F32, block_size, has_weight, normalize_by_lengths,
-      is_weight_positional, use_offsets, -1, -1);
+      is_weight_positional, use_offsets, -1, -1, true, false, false, in_dtype<InType>(false));
   return [cfg](
              std::int64_t output_size,
              std::int64_t index_size,
@@ -428,9 +429,15 @@ GenerateEmbeddingSpMDMNBitRowWiseSparse(
       const int, const std::int64_t, bool, bool, int, bool, bool, std::int64_t, std::int64_t, bool, const bool, \
       const bool, int);
 
+#define INST_SPARSE_IN(IN, IDX, OFF)                                                                 \
+  template FBGEMM_B200_API typename EmbeddingSpMDMRowWiseSparseKernelSignature<IN, IDX, OFF>::Type   \
+  GenerateEmbeddingSpMDMRowWiseSparse<IN, IDX, OFF>(const std::int64_t, bool, bool, int, bool, bool);
+
 #define INST_SPARSE(IDX, OFF)                                                                                  \
-  template FBGEMM_B200_API typename EmbeddingSpMDMRowWiseSparseKernelSignature<std::uint8_t, IDX, OFF>::Type   \
-  GenerateEmbeddingSpMDMRowWiseSparse<std::uint8_t, IDX, OFF>(const std::int64_t, bool, bool, int, bool, bool); \
+  INST_SPARSE_IN(std::uint8_t, IDX, OFF)                                                                       \
+  INST_SPARSE_IN(float, IDX, OFF)                                                                              \
+  INST_SPARSE_IN(float16, IDX, OFF)                                                                            \
+  INST_SPARSE_IN(std::uint16_t, IDX, OFF)                                                                      \
   template FBGEMM_B200_API typename EmbeddingSpMDMRowWiseSparseKernelSignature<std::uint8_t, IDX, OFF>::Type   \
   GenerateEmbeddingSpMDMNBitRowWiseSparse<IDX, OFF>(int, const std::int64_t, bool, bool, int, bool, bool);
 

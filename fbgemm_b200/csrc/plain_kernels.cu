@@ -148,7 +148,8 @@ __global__ void __launch_bounds__(kThreads) plain_rows_kernel(const __grid_const
             report(p.status, FBGEMM_B200_STATUS_BAD_INDEX, bag, pos, idx);
           }
         } else {
-          row_of[r] = idx;
+          // a pruning map turns the index into a row of the compressed table, or -1: pruned, slot still consumed
+          row_of[r] = p.cit ? (int64_t)__ldg(p.cit + idx) : idx;
         }
         if (weighted) {
           w[r] = __ldg(p.weights + (positional ? (int64_t)(r0 + r) : pos));
@@ -242,7 +243,7 @@ __global__ void __launch_bounds__(kThreads) rows_copy_kernel(
   }
 }
 
-using PlainFn = void (*)(const SpmdmParams);using PlainFn = void (*)(const SpmdmParams);
+using PlainFn = void (*)(const SpmdmParams);
 
 template <bool WORD>
 PlainFn pick(int kind) {

@@ -399,11 +399,16 @@ def GenerateEmbeddingSpMDMNBitWithStrides(input_bit_rate, block_size, has_weight
 
 def GenerateEmbeddingSpMDMRowWiseSparse(block_size, has_weight, normalize_by_lengths, prefetch=16,
                                         is_weight_positional=False, use_offsets=True, *, index_dtype=np.int64,
-                                        offset_dtype=np.int32) -> SpmdmKernel:
-    """fbgemm::GenerateEmbeddingSpMDMRowWiseSparse<uint8_t, ...>
-    (include/fbgemm/FbgemmEmbedding.h:229-243): pruned 8-bit table."""
-    return SpmdmKernel(_config(8, block_size, has_weight, normalize_by_lengths, is_weight_positional, use_offsets,
-                               -1, -1, index_dtype, offset_dtype, np.float32), True)
+                                        offset_dtype=np.int32, in_dtype=np.uint8) -> SpmdmKernel:
+    """fbgemm::GenerateEmbeddingSpMDMRowWiseSparse<InType, ...>
+    (include/fbgemm/FbgemmEmbedding.h:229-243): pruned table of fused 8-bit
+    rows (``in_dtype`` uint8), or of float32 / float16 rows."""
+    if np.dtype(in_dtype) not in (np.dtype(np.uint8), np.dtype(np.float32), np.dtype(np.float16)):
+        raise ValueError("InType must be uint8, float32 or float16")
+    cfg = _config(8, block_size, has_weight, normalize_by_lengths, is_weight_positional, use_offsets,
+                  -1, -1, index_dtype, offset_dtype, np.float32)
+    cfg.in_dtype = _in_code(in_dtype, False)[0]
+    return SpmdmKernel(cfg, True)
 
 
 def GenerateEmbeddingSpMDMNBitRowWiseSparse(bit_rate, block_size, has_weight, normalize_by_lengths, prefetch=16,

@@ -194,6 +194,26 @@ class _Lookups:
         return bool(ok), out
 
 
+    def spmdm_plain_rowwise_sparse(self, in_kind, block_size, uncompressed_data_size, table, indices,
+                                   compressed_indices_table, offsets_or_lengths, weights=None,
+                                   normalize_by_lengths=False, is_weight_positional=False, use_offsets=True):
+        """Pruned lookup over float ("f32") or fp16 ("f16": uint16 bit patterns;
+        "u16": the reference's InType uint16_t, read as fp16 too) rows."""
+        kind = {"f32": 1, "f16": 2, "u16": 3}[in_kind]
+        if self.prefix == "oracle" and kind == 3:
+            kind = 2
+        indices = np.ascontiguousarray(indices)
+        offsets_or_lengths = np.ascontiguousarray(offsets_or_lengths)
+        output_size = len(offsets_or_lengths) - (1 if use_offsets else 0)
+        out = np.zeros(max(output_size, 1) * block_size, dtype=np.float32)
+        f = self._fn(self.prefix + "_embedding_spmdm_plain_rowwise_sparse", _SPARSE_ARGS)
+        ok = f(kind, block_size, output_size, len(indices), uncompressed_data_size, _ptr(table), _ptr(indices),
+               indices.dtype.itemsize, _ptr(compressed_indices_table), _ptr(offsets_or_lengths),
+               offsets_or_lengths.dtype.itemsize, _ptr(weights), int(normalize_by_lengths), _ptr(out),
+               int(is_weight_positional), int(use_offsets))
+        return bool(ok), out
+
+
 class Oracle(_Lookups):
     """The plain-C restatement."""
 

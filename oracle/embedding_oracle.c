@@ -962,3 +962,70 @@ ORACLE_API int oracle_pruned_array_lookup(
   }
   return ok;
 }
+
+/* ------------------------------------------------------------------------- */
+/* Pruned (row-wise sparse) pooled lookup over a table that is not quantized: */
+/* the non-8-bit branch of EmbeddingSpMDMRowWiseSparse_ref,                   */
+/* src/RefImplementations.cc:1688-1743.  in_kind 1: float rows; 2: fp16 rows  */
+/* (InType float16, and InType uint16_t, which that function also reads as    */
+/* fp16, :1723-1726).  Rows are block_size elements apart, fp32 output.       */
+/* Pinned bit-for-bit against the compiled reference like the rest.           */
+/* ------------------------------------------------------------------------- */
+ORACLE_API int oracle_embedding_spmdm_plain_rowwise_sparse(
+    int in_kind,
+    int64_t block_size,
+    int64_t output_size,
+    int64_t index_size,
+    int64_t uncompressed_data_size,
+    const void* input,
+    const void* indices,
+    int index_bytes,
+    const int32_t* compressed_indices_table,
+    const void* offsets_or_lengths,
+    int offset_bytes,
+    const float* weights,
+    int normalize_by_lengths,
+    float* out,
+    int is_weight_positional,
+    int use_offsets) {
+  if (in_kind != 1 && in_kind != 2) {
+    return 0;
+  }
+  int64_t current = 0;
+  for (int64_t m = 0; m < output_size; ++m) {
+    memset(out, 0, sizeof(float) * (size_t)block_size);
+    const int len = use_offsets
+        ? (int)(load_int(offsets_or_lengths, m + 1, offset_bytes) - load_int(offsets_or_lengths, m, offset_bytes))
+        : (int)load_int(offsets_or_lengths, m, offset_bytes);
+    if (current + len > index_size) {
+      return 0;
+    }
+    for (int i = 0; i < len; ++i, ++current) {
+      const int64_t uidx = load_int(indices, current, index_bytes);
+      if (uidx < 0 || uidx >= uncompressed_data_size) { /* :1701-1704 */
+        return 0;
+      }
+      const int64_t idx = compressed_indices_table[uidx];
+      if (idx == -1) { /* :1706-1709: pruned, slot still consumed */
+        continue;
+      }
+      float w = 1.f;
+      if (weights) {
+        w = weights[is_weight_positional ? i : current];
+      }
+      for (int64_t j = 0; j < block_size; ++j) {
+        const float x = in_kind == 1 ? ((const float*)input)[block_size * idx + j]
+                                     : oracle_half_to_float(((const uint16_t*)input)[block_size * idx + j]);
+        out[j] = fmaf(w, x, out[j]); /* :1729 */
+      }
+    }
+    if (normalize_by_lengths && len) {
+      const float inv = 1.f / (float)len;
+      for (int64_t j = 0; j < block_size; ++j) {
+        out[j] *= inv;
+      }
+    }
+    out += block_size;
+  }
+  return current == index_size;
+}

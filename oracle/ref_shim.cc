@@ -327,6 +327,46 @@ int ref_embedding_spmdm_rowwise_sparse(
   });
 }
 
+// fbgemm::EmbeddingSpMDMRowWiseSparse_ref<float | float16 | uint16_t> (:1617,
+// the branch at :1688-1743).  in_kind 1 float, 2 float16, 3 uint16_t (which
+// that function reads as fp16 as well).
+int ref_embedding_spmdm_plain_rowwise_sparse(
+    int in_kind,
+    std::int64_t block_size,
+    std::int64_t output_size,
+    std::int64_t index_size,
+    std::int64_t uncompressed_data_size,
+    const void* input,
+    const void* indices,
+    int index_bytes,
+    const std::int32_t* compressed_indices_table,
+    const void* offsets_or_lengths,
+    int offset_bytes,
+    const float* weights,
+    int normalize_by_lengths,
+    float* out,
+    int is_weight_positional,
+    int use_offsets) {
+  return dispatch_idx_off(index_bytes, offset_bytes, [&](auto i, auto o) {
+    using I = decltype(i);
+    using O = decltype(o);
+    auto run = [&](auto* table) {
+      using T = std::remove_cv_t<std::remove_pointer_t<decltype(table)>>;
+      return (int)fbgemm::EmbeddingSpMDMRowWiseSparse_ref<T, I, O>(
+          block_size, output_size, index_size, uncompressed_data_size, table, static_cast<const I*>(indices),
+          compressed_indices_table, static_cast<const O*>(offsets_or_lengths), weights, normalize_by_lengths != 0,
+          out, is_weight_positional != 0, use_offsets != 0);
+    };
+    if (in_kind == 1) {
+      return run(static_cast<const float*>(input));
+    }
+    if (in_kind == 2) {
+      return run(static_cast<const fbgemm::float16*>(input));
+    }
+    return run(static_cast<const std::uint16_t*>(input));
+  });
+}
+
 // The reference's auto-vectorised kernels (src/EmbeddingSpMDMAutovec.cc),
 // reached through their generators.  bit_rate 8 -> ...WithStrides_autovec,
 // 4/2 -> ...NBitWithStrides_autovec.  A CPU baseline for timing.

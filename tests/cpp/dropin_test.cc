@@ -22,6 +22,8 @@ int oracle_embedding_spmdm_nbit(int, int64_t, int64_t, int64_t, int64_t, const u
                                 int, const float*, int, void*, int, int, int, int64_t, int64_t);
 int oracle_embedding_spmdm_rowwise_sparse(int, int64_t, int64_t, int64_t, int64_t, const uint8_t*, const void*, int,
                                           const int32_t*, const void*, int, const float*, int, float*, int, int);
+int oracle_embedding_spmdm_plain_rowwise_sparse(int, int64_t, int64_t, int64_t, int64_t, const void*, const void*, int,
+                                                const int32_t*, const void*, int, const float*, int, float*, int, int);
 int oracle_embedding_spmdm_ex(int, int64_t, int64_t, int64_t, int64_t, const uint8_t*, const void*, int, const void*, int,
                               const float*, int, void*, int, int, int, int64_t, int64_t, int, int);
 int oracle_embedding_spmdm_plain(int, int64_t, int64_t, int64_t, int64_t, const void*, const void*, int, const void*, int,
@@ -223,6 +225,39 @@ int main() {
       CHECK(std::memcmp(o8.data(), r8.data(), o8.size() * 2) == 0);
     }
     fbgemm_b200::InvalidateTable(fp8.data());
+  }
+  // --- a pruned table of float rows: GenerateEmbeddingSpMDMRowWiseSparse<float>, device pointers
+  {
+    const int batch = 19, rows = 500, dim = 48;
+    std::vector<int32_t> mapping(rows);
+    int dense = 0;
+    for (auto& m : mapping) m = (g() % 3 == 0) ? -1 : dense++;
+    Inputs in = make(g, 4, batch, rows, dim, 11, 0);
+    std::vector<float> table((size_t)dense * dim);
+    std::normal_distribution<float> nd;
+    for (auto& v : table) v = nd(g);
+    auto kernel = fbgemm::GenerateEmbeddingSpMDMRowWiseSparse<float, int32_t, int64_t>(dim, true, false);
+    std::vector<float> ref((size_t)batch * dim), out((size_t)batch * dim);
+    CHECK(oracle_embedding_spmdm_plain_rowwise_sparse(1, dim, batch, in.n, rows, table.data(), in.idx32.data(), 4,
+                                                      mapping.data(), in.off64.data(), 8, in.weights.data(), 0,
+                                                      ref.data(), 0, 1));
+    void *d_table, *d_idx, *d_off, *d_w, *d_out, *d_map;
+    cudaMalloc(&d_table, table.size() * 4);
+    cudaMalloc(&d_idx, in.n * 4);
+    cudaMalloc(&d_off, in.off64.size() * 8);
+    cudaMalloc(&d_w, in.n * 4);
+    cudaMalloc(&d_out, out.size() * 4);
+    cudaMalloc(&d_map, rows * 4);
+    cudaMemcpy(d_table, table.data(), table.size() * 4, cudaMemcpyHostToDevice);
+    cudaMemcpy(d_idx, in.idx32.data(), in.n * 4, cudaMemcpyHostToDevice);
+    cudaMemcpy(d_off, in.off64.data(), in.off64.size() * 8, cudaMemcpyHostToDevice);
+    cudaMemcpy(d_w, in.weights.data(), in.n * 4, cudaMemcpyHostToDevice);
+    cudaMemcpy(d_map, mapping.data(), rows * 4, cudaMemcpyHostToDevice);
+    const bool ok = kernel(batch, in.n, rows, (const float*)d_table, (const int32_t*)d_idx, (const int64_t*)d_off,
+                           (const float*)d_w, (float*)d_out, (const int32_t*)d_map);
+    cudaMemcpy(out.data(), d_out, out.size() * 4, cudaMemcpyDeviceToHost);
+    CHECK(ok);
+    CHECK(std::memcmp(out.data(), ref.data(), out.size() * 4) == 0);
   }
   // --- what the sm_100a path does not provide is refused when the kernel is generated
   bool threw = false;

@@ -2,12 +2,13 @@
 the lookups with the generators' remaining options - rows with fp16 scale,
 bias FIRST and -1 as a pruned index (scale_bias_last = false, the layout of
 table-batched embeddings), bf16 output, padded rows, and no_bag - and the
-lookups on tables that are not row-wise quantized (fp32, fp16, bf16, fp8 rows).
+lookups on tables that are not row-wise quantized (fp32, fp16, bf16, fp8 rows),
+also through a pruning map (fp32, fp16).
 
     python tests/golden/make_golden_ex.py
 
 Outputs come from fbgemm::EmbeddingSpMDM_ref / EmbeddingSpMDMNBit_ref /
-EmbeddingSpMDMFP8_ref compiled
+EmbeddingSpMDMFP8_ref / EmbeddingSpMDMRowWiseSparse_ref compiled
 from the reference tree into oracle/_ref/libfbgemm_ref.so (oracle/Makefile).
 The fixture pins the CPU oracle (tests/test_oracle.py) and the CUDA kernels
 (tests/test_golden_gpu.py); it travels with the repository, the reference
@@ -23,7 +24,7 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
-from helpers import lengths_indices_weights, random_fused_table, random_plain_table  # noqa: E402
+from helpers import lengths_indices_weights, mapping_table, random_fused_table, random_plain_table  # noqa: E402
 from oracle import checker  # noqa: E402
 
 KINDS = ("f32", "f16", "bf16")
@@ -121,9 +122,34 @@ def main():
         out[k + "out"] = res[:batch * dim]
         m += 1
     out["n_plain"] = np.array(m)
+    # Pruned (row-wise sparse) lookups over float and fp16 rows: EmbeddingSpMDMRowWiseSparse_ref<float|float16|uint16_t>.
+    # (in_kind, batch, uncompressed rows, dim, avg_len, sparsity, weighted, normalize, index type)
+    q = 0
+    for in_kind, batch, urows, dim, avg_len, sparsity, weighted, normalize, idt in [
+            ("f32", 9, 400, 64, 10, 0.5, True, False, np.int64), ("f32", 6, 150, 7, 6, 0.8, False, True, np.int32),
+            ("f16", 8, 300, 128, 12, 0.5, True, True, np.int32), ("f16", 5, 90, 40, 5, 0.2, False, False, np.int64),
+            ("u16", 7, 200, 32, 8, 0.5, True, False, np.int32)]:
+        cit, rows = mapping_table(rng, urows, sparsity)
+        table = random_plain_table(rng, rows, dim, "f32" if in_kind == "f32" else "f16")
+        _, offsets, indices, weights, cnt = lengths_indices_weights(rng, batch, urows, avg_len, idt, np.int32)
+        ok, res = ref.spmdm_plain_rowwise_sparse(in_kind, dim, urows, table, indices, cit, offsets,
+                                                 weights if weighted else None, normalize)
+        assert ok
+        k = f"sparse{q}_"
+        out[k + "meta"] = np.array([("f32", "f16", "u16").index(in_kind), batch, urows, dim, int(weighted),
+                                    int(normalize)], dtype=np.int64)
+        out[k + "table"] = table
+        out[k + "cit"] = cit
+        out[k + "indices"] = indices
+        out[k + "offsets"] = offsets
+        out[k + "weights"] = weights
+        out[k + "out"] = res[:batch * dim]
+        q += 1
+    out["n_sparse"] = np.array(q)
     path = os.path.join(HERE, "lookup_ex_golden.npz")
     np.savez_compressed(path, **out)
-    print(path, os.path.getsize(path), "bytes;", n, "quantized-row cases,", m, "plain-row cases")
+    print(path, os.path.getsize(path), "bytes;", n, "quantized-row cases,", m, "plain-row cases,", q,
+          "pruned plain-row cases")
 
 
 if __name__ == "__main__":

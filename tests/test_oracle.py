@@ -162,6 +162,28 @@ def test_oracle_plain_rows_match_reference_fixtures(oracle):
         np.testing.assert_array_equal(bits(got), bits(want))
 
 
+SPARSE_KINDS = ("f32", "f16", "u16")
+
+
+def run_sparse_plain_fixture(lookups, ex, i):
+    """One pruned plain-row case of lookup_ex_golden.npz."""
+    k = f"sparse{i}_"
+    in_kind, batch, urows, dim, weighted, normalize = (int(v) for v in ex[k + "meta"])
+    ok, got = lookups.spmdm_plain_rowwise_sparse(SPARSE_KINDS[in_kind], dim, urows, ex[k + "table"], ex[k + "indices"],
+                                                 ex[k + "cit"], ex[k + "offsets"],
+                                                 ex[k + "weights"] if weighted else None, bool(normalize))
+    return ok, got[:batch * dim], ex[k + "out"]
+
+
+def test_oracle_pruned_plain_rows_match_reference_fixtures(oracle):
+    ex = np.load(os.path.join(os.path.dirname(GOLDEN), "lookup_ex_golden.npz"))
+    assert int(ex["n_sparse"]) >= 5
+    for i in range(int(ex["n_sparse"])):
+        ok, got, want = run_sparse_plain_fixture(oracle, ex, i)
+        assert ok
+        np.testing.assert_array_equal(bits(got), bits(want))
+
+
 # ---- live against the reference's own code ------------------------------------------
 
 @pytest.mark.parametrize("bit_rate", [8, 4, 2])
@@ -299,3 +321,23 @@ def test_oracle_plain_rows_match_reference_live(oracle, reference, in_kind):
             a, b = oracle.spmdm_plain(*args), reference.spmdm_plain(*args)
             assert a[0] and b[0]
             np.testing.assert_array_equal(bits(a[1]), bits(b[1]))
+
+
+@pytest.mark.parametrize("in_kind", SPARSE_KINDS)
+def test_oracle_pruned_plain_rows_match_reference_live(oracle, reference, in_kind):
+    rng = np.random.default_rng(270 + SPARSE_KINDS.index(in_kind))
+    for shape_i, (batch, urows, dim, avg_len) in enumerate(REFERENCE_SHAPES[2:12]):
+        cit, rows = mapping_table(rng, urows, (0.5, 0.9, 0.0)[shape_i % 3])
+        table = random_plain_table(rng, max(rows, 1), dim, "f32" if in_kind == "f32" else "f16")
+        for corner in (None, "oob", "unmatched+"):
+            idt, odt = ((np.int32, np.int64), (np.int64, np.int32))[shape_i % 2]
+            lengths, offsets, indices, weights, n = lengths_indices_weights(rng, batch, urows, avg_len, idt, odt, corner)
+            for weighted, normalize, positional, use_offsets in ((False, True, False, True), (True, False, False, False),
+                                                                 (True, True, True, True)):
+                args = (in_kind, dim, urows, table, indices, cit, offsets if use_offsets else lengths,
+                        weights if weighted else None, normalize, positional, use_offsets)
+                a = oracle.spmdm_plain_rowwise_sparse(*args)
+                b = reference.spmdm_plain_rowwise_sparse(*args)
+                assert a[0] == b[0] == (corner is None)
+                if a[0]:
+                    np.testing.assert_array_equal(bits(a[1]), bits(b[1]))

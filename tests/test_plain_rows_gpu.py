@@ -11,7 +11,7 @@ import torch
 
 import fbgemm_b200 as F
 from conftest import bits
-from helpers import REFERENCE_SHAPES, lengths_indices_weights, random_plain_table
+from helpers import REFERENCE_SHAPES, lengths_indices_weights, mapping_table, random_plain_table
 from test_oracle import IN_KINDS, KINDS
 from test_variants_gpu import NP_KIND, TORCH_KIND, dev, out_bits
 
@@ -100,3 +100,49 @@ def test_no_bag_and_fp8_formats(gpu_ctx, oracle):
         out = torch.zeros(4 * 64, device="cuda")
         assert kern(4, 4, 4, dev(table), dev(idx), dev(off), None, out) and ok_ref
         np.testing.assert_array_equal(out_bits(out), bits(ref))
+
+
+# ---- the same rows through a pruning map: GenerateEmbeddingSpMDMRowWiseSparse<float | float16> -------------
+
+SPARSE_KINDS = ("f32", "f16", "u16")
+
+
+def test_pruned_fixtures_made_by_the_reference(gpu_ctx):
+    ex = np.load(EX)
+    for i in range(int(ex["n_sparse"])):
+        k = f"sparse{i}_"
+        in_kind, batch, urows, dim, weighted, normalize = (int(v) for v in ex[k + "meta"])
+        idx, off = ex[k + "indices"], ex[k + "offsets"]
+        kern = F.GenerateEmbeddingSpMDMRowWiseSparse(dim, bool(weighted), bool(normalize), 16, False, True,
+                                                     index_dtype=idx.dtype.type, offset_dtype=off.dtype.type,
+                                                     in_dtype=np.float32 if in_kind == 0 else np.float16)
+        out = torch.zeros(batch * dim, dtype=torch.float32, device="cuda")
+        ok = kern(batch, len(idx), urows, dev(ex[k + "table"]), dev(idx), dev(off),
+                  dev(ex[k + "weights"]) if weighted else None, out, dev(ex[k + "cit"]))
+        assert ok, i
+        np.testing.assert_array_equal(out_bits(out), bits(ex[k + "out"]), err_msg=f"case {i}")
+
+
+@pytest.mark.parametrize("in_kind", ["f32", "f16"])
+def test_pruned_reference_shapes(gpu_ctx, oracle, in_kind):
+    rng = np.random.default_rng(6100 + SPARSE_KINDS.index(in_kind))
+    for shape_i, (batch, urows, dim, avg_len) in enumerate(REFERENCE_SHAPES + [(6, 300, 1000, 12)]):
+        idt, odt = ((np.int32, np.int64), (np.int64, np.int32))[shape_i % 2]
+        weighted, normalize, use_offsets = shape_i % 2 == 0, shape_i % 3 == 1, shape_i % 4 != 3
+        positional = weighted and shape_i % 4 == 2
+        cit, rows = mapping_table(rng, urows, (0.5, 0.9, 0.0, 1.0)[shape_i % 4])
+        table = random_plain_table(rng, max(rows, 1), dim, in_kind)
+        kern = F.GenerateEmbeddingSpMDMRowWiseSparse(dim, weighted, normalize, 16, positional, use_offsets,
+                                                     index_dtype=idt, offset_dtype=odt, in_dtype=IN_NP[in_kind])
+        for corner in (None, "oob", "empty"):
+            lengths, offsets, indices, weights, n = lengths_indices_weights(rng, batch, urows, avg_len, idt, odt, corner)
+            ol = offsets if use_offsets else lengths
+            ok_ref, ref = oracle.spmdm_plain_rowwise_sparse(in_kind, dim, urows, table, indices, cit, ol,
+                                                            weights if weighted else None, normalize, positional,
+                                                            use_offsets)
+            out = torch.zeros(batch * dim, dtype=torch.float32, device="cuda")
+            ok = kern(batch, n, urows, dev(table), dev(indices) if n else None, dev(ol),
+                      dev(weights) if weighted and n else None, out, dev(cit))
+            assert ok == ok_ref == (corner != "oob")
+            if ok:
+                np.testing.assert_array_equal(out_bits(out), bits(ref), err_msg=f"shape {shape_i} {corner}")
