@@ -10,8 +10,8 @@
 // thread does not depend on how ragged the bags are and index loads and result
 // stores are coalesced; the thread finds its table by bisection over the T+1
 // table starts offsets[t*B] (staged in shared memory when they fit) and then
-// probes alone: at the load factors in use (0.5-0.8) a probe sequence is one
-// or two neighbouring slots, i.e. one 32-byte sector.
+// probes alone: at a load factor of 0.8 a hit walks about 3 slots and a miss
+// about 13, i.e. one to four neighbouring 32-byte sectors.
 //
 // The reference's probe loop has no end on a full table that lacks the key;
 // here it stops after `capacity` slots with -1, so no launch can spin.
@@ -102,6 +102,10 @@ __global__ void __launch_bounds__(kThreads) pruned_lookup_kernel(const PrunedArg
     } else if (HASH) {
       const uint64_t h = a.index64 ? hash64((uint64_t)idx) : (uint64_t)hash32((uint32_t)idx);
       int64_t slot = (int64_t)(h % (uint64_t)capacity);
+      // One slot per step.  Examining four slots per step with their loads in flight together was
+      // measured slower (950 against 700 us for 7.9 M positions over 16 tables of 2.5 M slots): the
+      // limit is the rate of random 32-byte sectors, not the chain of dependent loads, and a window of
+      // four slots straddles sectors that a probe sequence would not have touched.
       for (int64_t probes = 0; probes < capacity; ++probes) {
         int64_t key, value;
         if (a.map64) {

@@ -74,6 +74,8 @@ class IntNBitTableBatchedEmbeddingBags:
     """The tables of one table-batched operator and what does not change from
     call to call (row sizes, row counts, kernels)."""
 
+    MAX_PLANS = 16  # cached multi-table plans (one per set of buffer addresses and sizes)
+
     def __init__(self, dev_weights: torch.Tensor, weights_offsets, weights_tys, D_offsets, total_D: int,
                  pooling_mode: int = PoolingMode.SUM, row_alignment: int = 1, output_dtype: int = SparseType.FP16,
                  scale_bias_last: bool = False, weighted: bool = False, index_dtype=torch.int32,
@@ -161,9 +163,12 @@ class IntNBitTableBatchedEmbeddingBags:
         if use_plan:
             key = (indices.data_ptr(), offsets.data_ptr(), indice_weights.data_ptr() if self.weighted else 0,
                    output.data_ptr(), B, indices.numel(), slot)
-            plan = self._plans.get(key)
+            plan = self._plans.pop(key, None)
             if plan is None:
-                plan = self._plans[key] = E.MultiTablePlan(calls, self.device.index, slot)
+                plan = E.MultiTablePlan(calls, self.device.index, slot)
+                while len(self._plans) >= self.MAX_PLANS:      # least recently used first
+                    self._plans.pop(next(iter(self._plans)))
+            self._plans[key] = plan
             plan.launch()
             return output
         cur = torch.cuda.current_stream(self.device)

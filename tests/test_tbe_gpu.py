@@ -130,3 +130,18 @@ def test_operator_with_unquantized_and_fp8_tables(gpu_ctx, oracle):
         assert ok_ref
         np.testing.assert_array_equal(np.ascontiguousarray(got[:, D_off[t]:D_off[t + 1]]).reshape(-1), bits(ref),
                                       err_msg=f"table {t}")
+
+
+def test_plan_cache_is_bounded(gpu_ctx):
+    rng = np.random.default_rng(8400)
+    tys, dims, rows, B = [tbe.SparseType.INT4, tbe.SparseType.INT8], [32, 64], [60, 50], 5
+    tables, blob, w_off, D_off, offsets, indices, _ = build_op_inputs(rng, tys, dims, rows, B, 4, 16, False, np.int32)
+    op = tbe.IntNBitTableBatchedEmbeddingBags(torch.from_numpy(blob).cuda(), w_off, np.array([int(t) for t in tys], np.uint8),
+                                              D_off, 96, tbe.PoolingMode.SUM, 16, tbe.SparseType.FP16)
+    d_idx, d_off = torch.from_numpy(indices).cuda(), torch.from_numpy(offsets).cuda()
+    first = op.forward(d_idx, d_off, use_plan=True).clone()
+    outs = [torch.zeros((B, 96), dtype=torch.float16, device="cuda") for _ in range(op.MAX_PLANS + 6)]
+    for o in outs:
+        op.forward(d_idx, d_off, output=o, use_plan=True)
+    assert F.status_read(0)[0] and len(op._plans) == op.MAX_PLANS
+    assert all(torch.equal(o, first) for o in outs)
