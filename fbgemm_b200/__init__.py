@@ -8,8 +8,11 @@ Layers, bottom up:
                    built in-tree into ``libfbgemm_b200.so`` (``build.py``)
 * ``_capi.py``     ctypes binding of the C ABI
 * ``embedding.py`` the reference's generator API in Python (host mirror)
+* ``tbe.py``       the table-batched operator above the generators (pooled and
+                   sequence form, the pruning lookups that run before it)
 * ``workloads.py`` seeded synthetic inputs of the benchmark configurations
 * ``sharding.py``  table-wise sharding over the GPUs of one box
+* ``caller_bench.py`` timing of the kernels either side of the pooled lookup
 
 Importing the package does not need a GPU; creating a context does, and fails
 loudly without one.  There is no CPU path.
