@@ -213,6 +213,7 @@ __global__ void __launch_bounds__(kThreads) sequence_rows_kernel(const SeqArgs a
   // Prologue, one position per lane: table, index, bounds, row address, scale and bias.  The chain of
   // dependent loads (offsets -> index -> descriptor -> scale, bias) is paid once per 32 positions.
   int my_state = kSkip, my_type = 0, my_row_bytes = 0;
+  bool my_fours = false;
   const uint8_t* my_row = nullptr;
   float my_scale = 0.f, my_start = 0.f;
   {
@@ -233,6 +234,14 @@ __global__ void __launch_bounds__(kThreads) sequence_rows_kernel(const SeqArgs a
       } else {
         my_state = kRow;
         my_row = a.weights + tab.weight_offset + idx * (int64_t)tab.row_bytes;
+        if (!copy) {
+          // where the columns start, and whether the four-column path can take this row: the bytes that
+          // hold four columns are the alignment it needs
+          const bool quantized = my_type == kINT8 || my_type == kINT4 || my_type == kINT2;
+          const int unit = my_type == kFP32 ? 16 : (my_type == kFP16 ? 8 : (my_type == kINT4 ? 2 : (my_type == kINT2 ? 1 : 4)));
+          const uint8_t* data = my_row + (quantized && !a.sb_last ? 4 : 0);
+          my_fours = a.by_fours && (reinterpret_cast<uintptr_t>(data) & (unit - 1)) == 0;
+        }
         // Ask for the row now: the warp reaches it up to 31 positions later, and by then it sits in L2.
         for (int b = 0; b < tab.row_bytes; b += 128) {
           asm volatile("prefetch.global.L2 [%0];" ::"l"(my_row + b));
@@ -256,13 +265,16 @@ __global__ void __launch_bounds__(kThreads) sequence_rows_kernel(const SeqArgs a
     }
   }
 
+  // what the warp needs to know first about a position, in one word: state | type << 2 | four-column path << 5
+  const int my_code = my_state | (my_type << 2) | ((int)my_fours << 5);
   const int count = (int)(a.index_size - first < 32 ? a.index_size - first : 32);
-  for (int i = 0; i < count; ++i) {
-    const int state = __shfl_sync(0xffffffffu, my_state, i);
+  uint8_t* orow = a.out + first * a.out_row_bytes;
+  for (int i = 0; i < count; ++i, orow += a.out_row_bytes) {
+    const int code = __shfl_sync(0xffffffffu, my_code, i);
+    const int state = code & 3;
     if (state == kSkip) {
       continue;
     }
-    uint8_t* orow = a.out + (first + i) * a.out_row_bytes;
     if (state == kZeros) {
       if constexpr (!copy) {
         for (int j = lane; j < a.D; j += 32) {
@@ -273,7 +285,7 @@ __global__ void __launch_bounds__(kThreads) sequence_rows_kernel(const SeqArgs a
     }
     const uint8_t* row = reinterpret_cast<const uint8_t*>(
         __shfl_sync(0xffffffffu, (unsigned long long)reinterpret_cast<uintptr_t>(my_row), i));
-    const int type = __shfl_sync(0xffffffffu, my_type, i);
+    const int type = (code >> 2) & 7;
 
     if constexpr (copy) {
       // byte copy of the row: 8-bit rows min(output row, table row) bytes, 4-bit rows the whole table row
@@ -293,12 +305,13 @@ __global__ void __launch_bounds__(kThreads) sequence_rows_kernel(const SeqArgs a
       }
     } else {
       const bool quantized = type == kINT8 || type == kINT4 || type == kINT2;
-      const float scale = __shfl_sync(0xffffffffu, my_scale, i);
-      const float start = __shfl_sync(0xffffffffu, my_start, i);
+      float scale = 0.f, start = 0.f;
+      if (quantized) {
+        scale = __shfl_sync(0xffffffffu, my_scale, i);
+        start = __shfl_sync(0xffffffffu, my_start, i);
+      }
       const uint8_t* data = row + (quantized && !a.sb_last ? 4 : 0);
-      // bytes that hold four columns = the alignment the four-column path needs
-      const int unit = type == kFP32 ? 16 : (type == kFP16 ? 8 : (type == kINT4 ? 2 : (type == kINT2 ? 1 : 4)));
-      if (a.by_fours && (reinterpret_cast<uintptr_t>(data) & (unit - 1)) == 0) {
+      if (code & 32) {
         switch (type) {
           case kINT8: emit_row_by_fours<kINT8, OUT>(data, orow, a.D, scale, start, fp8_mult, fp8_shift, lane); break;
           case kINT4: emit_row_by_fours<kINT4, OUT>(data, orow, a.D, scale, start, fp8_mult, fp8_shift, lane); break;
