@@ -98,6 +98,8 @@ SIGNATURES = {
                                                   _p, _p, C.c_int32, _p]),
     "fbgemm_b200_sequence_lookup": (C.c_int, [_p, _p, _p, C.c_int32, C.c_int32, C.c_int32, _p, _p, C.c_int32, _i64, _p,
                                               C.c_int32, _i64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _p]),
+    "fbgemm_b200_pruned_hashmap_insert": (C.c_int, [_p, C.c_int32, C.c_int32, _p, _p, _p, C.c_int32, _i64, _p, C.c_int32,
+                                                    _p, C.c_int32, _p]),
     "fbgemm_b200_pruned_hashmap_insert_host": (C.c_int, [C.c_int32, C.c_int32, _p, _p, _p, C.c_int32, _p, C.c_int32,
                                                          _p]),
     "fbgemm_b200_table_register": (C.c_int, [_p, _p, C.c_size_t]),

@@ -957,6 +957,40 @@ int fbgemm_b200_sequence_lookup(
   return 0;
 }
 
+int fbgemm_b200_pruned_hashmap_insert(
+    fbgemm_b200_ctx* ctx,
+    int32_t T,
+    int32_t B,
+    const void* indices,
+    const void* dense_indices,
+    const void* offsets,
+    int32_t index_bytes,
+    int64_t index_size,
+    void* hash_table,
+    int32_t hash_bytes,
+    const int64_t* hash_table_offsets,
+    int32_t slot,
+    void* stream) {
+  if (!ctx || slot < 0 || slot >= FBGEMM_B200_STATUS_SLOTS) {
+    set_error("bad context or status slot");
+    return FBGEMM_B200_EINVAL;
+  }
+  if (T < 1 || B < 1 || (index_bytes != 4 && index_bytes != 8) || (hash_bytes != 4 && hash_bytes != 8) ||
+      index_size < 0 || !offsets || !hash_table_offsets || (index_size > 0 && (!indices || !dense_indices)) ||
+      reinterpret_cast<uintptr_t>(hash_table) % (2 * (size_t)hash_bytes) != 0) {
+    set_error("pruned_hashmap_insert: bad argument");
+    return FBGEMM_B200_EINVAL;
+  }
+  DeviceGuard guard(ctx->device);
+  const cudaError_t e = launch_pruned_hashmap_insert(
+      T, B, indices, dense_indices, offsets, index_bytes, index_size, hash_table, hash_bytes, hash_table_offsets,
+      ctx->status + 4 * slot, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) {
+    return fail_cuda(e, "hash-map insert launch");
+  }
+  return 0;
+}
+
 int fbgemm_b200_pruned_hashmap_insert_host(
     int32_t T,
     int32_t B,

@@ -184,6 +184,21 @@ cudaError_t launch_pruned_lookup(
     int32_t* status,
     cudaStream_t stream);
 
+// Fills the hash maps of launch_pruned_lookup on the device (compare-and-swap per position).
+cudaError_t launch_pruned_hashmap_insert(
+    int32_t T,
+    int32_t B,
+    const void* indices,
+    const void* dense_indices,
+    const void* offsets,
+    int index_bytes,
+    int64_t index_size,
+    void* hash_table,
+    int hash_bytes,
+    const int64_t* hash_table_offsets,
+    int32_t* status,
+    cudaStream_t stream);
+
 // Sequence ("nobag") lookup over the tables of a table-batched call
 // (sequence_kernels.cu): one output row per index position, one launch.
 using SequenceTable = fbgemm_b200_sequence_table;

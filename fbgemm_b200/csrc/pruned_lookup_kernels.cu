@@ -220,6 +220,53 @@ __global__ void __launch_bounds__(kThreads) pruned_hashmap_kernel(const PrunedAr
   }
 }
 
+// Filling the hash map on the device.  The reference only inserts on the host, one key after the
+// other; here every position claims the first free slot of its probe sequence with a compare-and-swap
+// on the key, so the slots a cluster's keys end up in depend on the order the threads arrive in - the
+// table differs from the host-built one byte for byte but every lookup gives the same answer (a key
+// sits within its probe sequence, before the first empty slot).  Positions whose dense index is -1
+// are not inserted, as in the reference; a table without a free slot is reported.
+template <bool MAP64>
+__global__ void __launch_bounds__(kThreads) pruned_hashmap_insert_kernel(const PrunedArgs a, const void* dense_indices) {
+  __shared__ int64_t starts_s[kSharedStarts];
+  const int64_t* starts = stage_table_starts(a, starts_s);
+  const int64_t k = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+  const int t = k < a.index_size ? table_of(a, starts, k) : -1;
+  if (t < 0) {
+    return;
+  }
+  const int64_t dense = load_int(dense_indices, k, a.index64);
+  const int64_t map_start = __ldg(a.map_offsets + t);
+  const int64_t capacity = __ldg(a.map_offsets + t + 1) - map_start;
+  if (dense == -1 || capacity <= 0) {
+    return;
+  }
+  const int64_t idx = load_int(a.indices, k, a.index64);
+  const uint64_t h = a.index64 ? hash64((uint64_t)idx) : (uint64_t)hash32((uint32_t)idx);
+  int64_t slot = (int64_t)(h % (uint64_t)capacity);
+  for (int64_t probes = 0; probes < capacity; ++probes) {
+    const int64_t at = 2 * (map_start + slot);
+    int64_t seen;
+    if constexpr (MAP64) {
+      unsigned long long* keys = static_cast<unsigned long long*>(const_cast<void*>(a.map));
+      seen = (int64_t)atomicCAS(keys + at, ~0ULL, (unsigned long long)idx);
+      if (seen == -1 || seen == idx) {
+        reinterpret_cast<long long*>(keys)[at + 1] = dense;
+        return;
+      }
+    } else {
+      int* keys = static_cast<int*>(const_cast<void*>(a.map));
+      seen = atomicCAS(keys + at, -1, (int)idx);
+      if (seen == -1 || seen == (int)idx) {
+        keys[at + 1] = (int)dense;
+        return;
+      }
+    }
+    slot = slot + 1 == capacity ? 0 : slot + 1;
+  }
+  report(a, FBGEMM_B200_STATUS_TABLE_FULL, t, k, idx);
+}
+
 }  // namespace
 
 cudaError_t launch_pruned_lookup(
@@ -262,6 +309,50 @@ cudaError_t launch_pruned_lookup(
     pruned_hashmap_kernel<true><<<(unsigned)blocks, kThreads, 0, stream>>>(a);
   } else {
     pruned_hashmap_kernel<false><<<(unsigned)blocks, kThreads, 0, stream>>>(a);
+  }
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError();
+}
+
+}  // namespace fbgemm_b200
+
+namespace fbgemm_b200 {
+
+cudaError_t launch_pruned_hashmap_insert(
+    int32_t T,
+    int32_t B,
+    const void* indices,
+    const void* dense_indices,
+    const void* offsets,
+    int index_bytes,
+    int64_t index_size,
+    void* hash_table,
+    int hash_bytes,
+    const int64_t* hash_table_offsets,
+    int32_t* status,
+    cudaStream_t stream) {
+  if (index_size == 0) {
+    return cudaSuccess;
+  }
+  PrunedArgs a{};
+  a.indices = indices;
+  a.offsets = offsets;
+  a.map = hash_table;
+  a.map_offsets = hash_table_offsets;
+  a.status = status;
+  a.index_size = index_size;
+  a.T = T;
+  a.B = B;
+  a.index64 = index_bytes == 8;
+  a.map64 = hash_bytes == 8;
+  const int64_t blocks = (index_size + kThreads - 1) / kThreads;
+  if (blocks > 0x7fffffffLL) {
+    return cudaErrorInvalidValue;
+  }
+  if (a.map64) {
+    pruned_hashmap_insert_kernel<true><<<(unsigned)blocks, kThreads, 0, stream>>>(a, dense_indices);
+  } else {
+    pruned_hashmap_insert_kernel<false><<<(unsigned)blocks, kThreads, 0, stream>>>(a, dense_indices);
   }
   g_launch_count.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError();

@@ -241,11 +241,32 @@ def pruned_array_lookup(indices: torch.Tensor, offsets: torch.Tensor, index_rema
 
 
 def pruned_hashmap_insert(indices: torch.Tensor, dense_indices: torch.Tensor, offsets: torch.Tensor,
-                          hash_table: torch.Tensor, hash_table_offsets: torch.Tensor) -> bool:
-    """``torch.ops.fbgemm.pruned_hashmap_insert`` (same file, :124-204): host
-    tensors, ``hash_table`` filled in place (start from -1 everywhere); move it
-    to the GPU afterwards, as the reference's own GPU module does.  Returns
-    False if a table had no free slot left for a key."""
+                          hash_table: torch.Tensor, hash_table_offsets: torch.Tensor, slot: int = 0) -> bool:
+    """``torch.ops.fbgemm.pruned_hashmap_insert`` (same file, :124-204):
+    ``hash_table`` is filled in place (start from -1 everywhere).  With host
+    tensors the table is built as the reference builds it, one key after the
+    other (move it to the GPU afterwards, as the reference's own GPU module
+    does).  With CUDA tensors one kernel inserts all keys at once; that table
+    can differ byte for byte from the host-built one, the lookups do not.
+    Returns False if a table had no free slot left for a key."""
+    if hash_table.is_cuda:
+        for x in (indices, dense_indices, offsets, hash_table, hash_table_offsets):
+            assert x.is_cuda and x.is_contiguous()
+        assert indices.dtype == offsets.dtype == dense_indices.dtype and indices.dtype in (torch.int32, torch.int64)
+        assert hash_table.dim() == 2 and hash_table.shape[1] == 2 and hash_table.dtype in (torch.int32, torch.int64)
+        assert hash_table_offsets.dtype == torch.int64
+        T = hash_table_offsets.numel() - 1
+        assert T > 0 and (offsets.numel() - 1) % T == 0
+        B = (offsets.numel() - 1) // T
+        if B <= 0:
+            raise ValueError("B must be positive")
+        ctx = E.get_context(hash_table.device.index)
+        rc = E._capi.lib().fbgemm_b200_pruned_hashmap_insert(
+            ctx.handle, T, B, E._ptr(indices), E._ptr(dense_indices), E._ptr(offsets), indices.element_size(),
+            indices.numel(), E._ptr(hash_table), hash_table.element_size(), E._ptr(hash_table_offsets), slot,
+            torch.cuda.current_stream(hash_table.device).cuda_stream)
+        E._capi.check(rc, "fbgemm_b200_pruned_hashmap_insert")
+        return E.status_read(slot, hash_table.device.index)[0]
     for x in (indices, dense_indices, offsets, hash_table, hash_table_offsets):
         assert not x.is_cuda and x.is_contiguous()
     assert indices.dtype == offsets.dtype == dense_indices.dtype and indices.dtype in (torch.int32, torch.int64)

@@ -68,6 +68,7 @@ extern "C" {
 #define FBGEMM_B200_STATUS_BAD_INDEX 1   /* idx < 0 || idx >= data_size      */
 #define FBGEMM_B200_STATUS_BAG_OVERRUN 2 /* current + len > index_size       */
 #define FBGEMM_B200_STATUS_SIZE_MISMATCH 3 /* sum of lengths != index_size   */
+#define FBGEMM_B200_STATUS_TABLE_FULL 4 /* hash-map insert found no free slot */
 
 /* Number of status slots a context owns (see fbgemm_b200_spmdm_launch). */
 #define FBGEMM_B200_STATUS_SLOTS 1024
@@ -421,6 +422,31 @@ FBGEMM_B200_API int fbgemm_b200_pruned_array_lookup(
     int32_t remap_bytes,
     const int64_t* remappings_offsets,
     void* dense_indices,
+    int32_t slot,
+    void* stream);
+
+/*
+ * pruned_hashmap_insert on the device (the reference has no such form: its
+ * GPU module fills the table on the host).  Device pointers; hash_table must
+ * start as -1 everywhere.  Every position whose dense index is not -1 claims
+ * the first free slot of its probe sequence with a compare-and-swap, so the
+ * table may differ byte for byte from the one the host insert builds while
+ * every lookup answers the same.  Asynchronous on `stream`; a table without a
+ * free slot shows as FBGEMM_B200_STATUS_TABLE_FULL in status slot `slot`.
+ * Returns 0 or a negative code.
+ */
+FBGEMM_B200_API int fbgemm_b200_pruned_hashmap_insert(
+    fbgemm_b200_ctx* ctx,
+    int32_t T,
+    int32_t B,
+    const void* indices,
+    const void* dense_indices,
+    const void* offsets,
+    int32_t index_bytes,
+    int64_t index_size,
+    void* hash_table,
+    int32_t hash_bytes,
+    const int64_t* hash_table_offsets,
     int32_t slot,
     void* stream);
 

@@ -127,3 +127,39 @@ def test_remap_then_lookup_equals_the_minus_one_lookup(gpu_ctx, oracle):
         assert ok
         np.testing.assert_array_equal(np.ascontiguousarray(out[:, t * D:(t + 1) * D]).view(np.uint32).reshape(-1),
                                       want.view(np.uint32))
+
+
+@pytest.mark.parametrize("idt", [np.int32, np.int64])
+@pytest.mark.parametrize("hdt", [np.int32, np.int64])
+def test_insert_on_the_device(gpu_ctx, oracle, idt, hdt):
+    """The table a kernel fills by compare-and-swap need not equal the host-built one slot for slot, but
+    it holds the same keys, and both the GPU lookup and the oracle's lookup read the same answers from it."""
+    rng = np.random.default_rng(1900 + np.dtype(idt).itemsize + 3 * np.dtype(hdt).itemsize)
+    for T, B, max_len, lf in ((1, 1, 5, 0.8), (4, 50, 12, 0.8), (3, 4000, 8, 0.95), (2, 2000, 10, 1.0)):
+        indices, dense, offsets, table, hto = pruning_case(rng, T, B, max_len, idt, hdt, lf,
+                                                           unpruned_tables=(1,) if T > 1 else ())
+        d_idx, d_dense, d_off, d_hto = dev(indices), dev(dense), dev(offsets), dev(hto)
+        d_table = dev(table) if table.size else torch.empty((0, 2), dtype=torch.int64 if hdt == np.int64 else torch.int32,
+                                                            device="cuda")
+        assert tbe.pruned_hashmap_insert(d_idx, d_dense, d_off, d_table, d_hto, slot=5)
+        built = d_table.cpu().numpy()
+        host = table.copy()
+        assert oracle.pruned_hashmap_insert(T, B, indices, dense, offsets, host, hto)
+        for t in range(T):   # the same keys with the same dense indices in every table
+            lo, hi = int(hto[t]), int(hto[t + 1])
+            got = {int(k): int(v) for k, v in built[lo:hi] if k != -1}
+            want = {int(k): int(v) for k, v in host[lo:hi] if k != -1}
+            assert got == want
+            assert int((built[lo:hi, 0] != -1).sum()) == len(want)   # no key twice
+        expect = oracle.pruned_hashmap_lookup(T, B, indices, offsets, host, hto)
+        np.testing.assert_array_equal(oracle.pruned_hashmap_lookup(T, B, indices, offsets, built, hto), expect)
+        np.testing.assert_array_equal(tbe.pruned_hashmap_lookup(d_idx, d_off, d_table, d_hto).cpu().numpy(), expect)
+        other = np.full_like(indices, np.iinfo(np.int32).max)
+        np.testing.assert_array_equal(tbe.pruned_hashmap_lookup(dev(other), d_off, d_table, d_hto).cpu().numpy(),
+                                      oracle.pruned_hashmap_lookup(T, B, other, offsets, host, hto))
+    # a table with fewer slots than keys: reported, nothing written outside it
+    indices = np.arange(6, dtype=idt)
+    small = torch.full((4, 2), -1, dtype=torch.int64 if hdt == np.int64 else torch.int32, device="cuda")
+    ok = tbe.pruned_hashmap_insert(dev(indices), dev(indices.copy()), dev(np.array([0, 6], dtype=idt)), small,
+                                   dev(np.array([0, 4], dtype=np.int64)), slot=5)
+    assert not ok and int((small[:, 0] != -1).sum()) == 4
