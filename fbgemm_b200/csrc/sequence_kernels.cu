@@ -288,9 +288,9 @@ __global__ void __launch_bounds__(kThreads) sequence_rows_kernel(const SeqArgs a
     const int type = (code >> 2) & 7;
 
     if constexpr (copy) {
-      // byte copy of the row: 8-bit rows min(output row, table row) bytes, 4-bit rows the whole table row
+      // byte copy of the row: min(output row, table row) bytes (for 4-bit rows the caller makes the two equal)
       const int64_t row_bytes = __shfl_sync(0xffffffffu, my_row_bytes, i);
-      const int64_t width = a.out_kind == FBGEMM_B200_OUT_U8 && a.out_row_bytes < row_bytes ? a.out_row_bytes : row_bytes;
+      const int64_t width = a.out_row_bytes < row_bytes ? a.out_row_bytes : row_bytes;
       if (((reinterpret_cast<uintptr_t>(row) | reinterpret_cast<uintptr_t>(orow)) & 3) == 0) {
         for (int64_t b = lane; b < width / 4; b += 32) {
           reinterpret_cast<uint32_t*>(orow)[b] = __ldg(reinterpret_cast<const uint32_t*>(row) + b);

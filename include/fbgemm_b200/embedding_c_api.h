@@ -495,8 +495,9 @@ typedef struct fbgemm_b200_sequence_table {
  *                 first, index -1 is a pruned row and gives zeros;
  *   U8:           min(out_row_bytes, row_bytes) bytes of the row (8-bit tables;
  *                 the reference's out_row_bytes is D + 4);
- *   INT4:         the row_bytes bytes of the row (4-bit tables; the caller
- *                 makes out_row_bytes = row_bytes = (D + 8 + 1) / 2).
+ *   INT4:         the bytes of the row (4-bit tables; the caller makes
+ *                 out_row_bytes = row_bytes = (D + 8 + 1) / 2; never more than
+ *                 out_row_bytes are written).
  * All tables share D.  Everything is a device pointer; rows of positions that
  * no table covers, or whose index is out of range (reported in status slot
  * `slot`), are left as they were.  Asynchronous on `stream`; returns 0 or a
