@@ -129,3 +129,22 @@ def test_out_of_range_index_is_reported_and_lookup_function_dispatches(gpu_ctx, 
                                                          tbe.PoolingMode.NONE, None, ST.FP16, row_alignment=16)
     ok, info = F.status_read(0)
     assert not ok and info[:4] == [1, 1, hi - 1, 30]
+
+
+def test_more_tables_than_fit_in_shared_memory(gpu_ctx, oracle):
+    """Beyond 2047 tables the position -> table bisection reads the offsets from global memory."""
+    rng = np.random.default_rng(9800)
+    T, B, D, rows = 2100, 1, 8, 4
+    tys = [ST.INT8] * T
+    tables, blob, w_off, _, offsets, indices, _ = build_op_inputs(rng, tys, [D] * T, [rows] * T, B, 2, 4, True, np.int64)
+    op = tbe.IntNBitSequenceEmbedding(torch.from_numpy(blob).cuda(), w_off, np.array([int(t) for t in tys], np.uint8), D, 4,
+                                      ST.FP32, True)
+    out = op.forward(torch.from_numpy(indices).cuda(), torch.from_numpy(offsets).cuda(), slot=33)
+    assert F.status_read(33)[0]
+    got = out.cpu().numpy().view(np.uint32)
+    for t in range(0, T, 97):
+        lo, hi = int(offsets[t * B]), int(offsets[(t + 1) * B])
+        if hi > lo:
+            ok_ref, ref = reference_rows(oracle, ST.INT8, D, rows, tables[t], indices[lo:hi], "f32", True)
+            assert ok_ref
+            np.testing.assert_array_equal(got[lo:hi].reshape(-1), bits(ref)[:(hi - lo) * D])
