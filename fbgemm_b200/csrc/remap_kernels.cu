@@ -132,35 +132,23 @@ __global__ void __launch_bounds__(kThreads) remap_count(const RemapArgs a) {
   }
 }
 
-// One block: tile_counts[0..tiles) -> exclusive prefix, tile_counts[tiles] = total.
+// One block: tile_counts[0..tiles) -> exclusive prefix, tile_counts[tiles] = total.  A tile holds at
+// most kTile kept entries, so a chunk of kThreads counts is scanned in 32 bits and carried in 64.
 __global__ void __launch_bounds__(kThreads) remap_scan_tiles(int64_t* tile_counts, int64_t tiles) {
-  __shared__ int64_t carry_s;
-  __shared__ int64_t chunk[kThreads];
-  if (threadIdx.x == 0) {
-    carry_s = 0;
-  }
-  __syncthreads();
+  __shared__ int total;
+  int64_t carry = 0;
   for (int64_t b = 0; b < tiles; b += kThreads) {
     const int64_t i = b + threadIdx.x;
-    chunk[threadIdx.x] = i < tiles ? tile_counts[i] : 0;
-    __syncthreads();
-    if (threadIdx.x == 0) {  // at most a few thousand tiles: a serial pass over shared memory is enough
-      int64_t c = carry_s;
-      for (int j = 0; j < kThreads; ++j) {
-        const int64_t v = chunk[j];
-        chunk[j] = c;
-        c += v;
-      }
-      carry_s = c;
-    }
-    __syncthreads();
+    const int v = i < tiles ? (int)tile_counts[i] : 0;
+    const int before = block_exclusive_scan(v, &total);
     if (i < tiles) {
-      tile_counts[i] = chunk[threadIdx.x];
+      tile_counts[i] = carry + before;
     }
-    __syncthreads();
+    carry += total;
+    __syncthreads();  // `total` is rewritten by the next chunk's scan
   }
   if (threadIdx.x == 0) {
-    tile_counts[tiles] = carry_s;
+    tile_counts[tiles] = carry;
   }
 }
 

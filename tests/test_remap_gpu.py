@@ -96,3 +96,12 @@ def test_remap_then_lookup_equals_rowwise_sparse_lookup(gpu_ctx, oracle, bit_rat
     assert plain(batch, kept, dense, d_table, ri[:kept].contiguous(), ro, rw[:kept].contiguous(), got)
     # sum pooling: skipping a pruned row and never seeing it are the same arithmetic
     np.testing.assert_array_equal(bits(got.cpu().numpy()), bits(want.cpu().numpy()))
+
+
+def test_more_tiles_than_one_chunk_of_the_tile_scan(gpu_ctx, oracle):
+    """Over 256 tiles of 2048 positions the scan of the tile counts carries from chunk to chunk."""
+    rng = np.random.default_rng(9200)
+    mapping, _ = mapping_table(rng, 300000, 0.5)
+    _, offsets, indices, weights, n = lengths_indices_weights(rng, 40000, 300000, 20, np.int64, np.int64)
+    assert n > 3 * 256 * 2048 // 2
+    check(oracle, indices, mapping, offsets, weights)
