@@ -1,12 +1,16 @@
 """ctypes access to the CPU checkers.  TEST INFRASTRUCTURE - not the product.
 
-Three libraries, all built by the Makefile in this directory:
+Four libraries, all built by the Makefile in this directory:
 
 * ``liboracle.so``            the plain-C restatement (``embedding_oracle.c``)
 * ``_ref/libfbgemm_ref.so``   the reference's own scalar and auto-vectorised
                               sources compiled where they lie (``ref_shim.cc``)
 * ``_ref/libfbgemm_jit.so``   the reference's asmjit kernels as bundled in
                               ``libtorch_cpu.so`` (``ref_jit_shim.cc``)
+* ``_ref/libfbgemm_tbe_ref.so`` the reference's table-batched CPU operator and
+                              pruning lookups, rendered from its template and
+                              compiled (``render_tbe_template.py``,
+                              ``ref_tbe_shim.cc``)
 
 Only ``tests/``, ``__graft_entry__.smoke()`` and the CPU legs of ``bench.py``
 may import this module.  All arrays are numpy arrays in host memory.
@@ -23,6 +27,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "liboracle.so")
 REF_SO = os.path.join(HERE, "_ref", "libfbgemm_ref.so")
 JIT_SO = os.path.join(HERE, "_ref", "libfbgemm_jit.so")
+TBE_SO = os.path.join(HERE, "_ref", "libfbgemm_tbe_ref.so")
 
 _i64 = C.c_int64
 _int = C.c_int
@@ -34,10 +39,26 @@ _SPARSE_ARGS = [_int, _i64, _i64, _i64, _i64, _p, _p, _int, _p, _p, _int, _p,
                 _int, _p, _int, _int]
 
 
-def build(targets=("oracle",), ref_root="/root/reference") -> None:
-    """Run ``make`` for the named targets (oracle, ref, jit)."""
-    subprocess.run(["make", "-C", HERE, "-j8", f"REF_ROOT={ref_root}", *targets],
-                   check=True, stdout=subprocess.DEVNULL)
+def reference_root():
+    """Where a checkout of the reference (FBGEMM) lies: the directory named by
+    the environment variable FBGEMM_REFERENCE_ROOT, else a directory called
+    ``reference`` beside this repository; None when neither holds the sources."""
+    cands = [os.environ.get("FBGEMM_REFERENCE_ROOT"),
+             os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")]
+    for c in cands:
+        if c and os.path.isdir(os.path.join(c, "src")) and os.path.isdir(os.path.join(c, "include", "fbgemm")):
+            return c
+    return None
+
+
+def build(targets=("oracle",), ref_root=None) -> None:
+    """Run ``make`` for the named targets (oracle, ref, jit, tbe); ``ref`` and
+    ``tbe`` need the reference tree."""
+    cmd = ["make", "-C", HERE, "-j8", *targets]
+    ref_root = ref_root or reference_root()
+    if ref_root:
+        cmd.append(f"REF_ROOT={ref_root}")
+    subprocess.run(cmd, check=True, stdout=subprocess.DEVNULL)
 
 
 def _ptr(a):
@@ -374,3 +395,79 @@ class ReferenceJit(_Lookups):
                       indices.dtype.itemsize, _ptr(offsets), offsets.dtype.itemsize, _ptr(weights),
                       int(normalize_by_lengths), _ptr(out), int(out.dtype == np.float16),
                       _ptr(compressed_indices_table), threads))
+
+
+class ReferenceTbe:
+    """The reference's table-batched CPU operator and its pruning lookups
+    (fbgemm_gpu/codegen/inference/embedding_forward_quantized_cpu_template.cpp
+    of FBGEMM, compiled from its rendered template)."""
+
+    def __init__(self):
+        self.lib = None
+        if os.path.exists(TBE_SO):
+            import torch  # noqa: F401  (libtorch_cpu.so and libc10.so must be loaded first)
+
+            self.lib = C.CDLL(TBE_SO)
+            self.lib.ref_tbe_last_error.restype = C.c_char_p
+        self.available = self.lib is not None
+
+    def _check(self, rc):
+        if rc != 0:
+            raise RuntimeError(self.lib.ref_tbe_last_error().decode())
+
+    def pruned_hashmap_insert(self, T, B, indices, dense_indices, offsets, hash_table, hash_table_offsets):
+        indices = np.ascontiguousarray(indices)
+        dense_indices = np.ascontiguousarray(dense_indices, dtype=indices.dtype)
+        offsets = np.ascontiguousarray(offsets, dtype=indices.dtype)
+        hto = np.ascontiguousarray(hash_table_offsets, dtype=np.int64)
+        assert hash_table.flags.c_contiguous and hash_table.shape[1] == 2
+        f = self.lib.ref_tbe_pruned_hashmap_insert
+        f.argtypes = [C.c_int32, C.c_int32, _p, _p, _p, _int, _p, _int, _i64, _p]
+        self._check(f(T, B, _ptr(indices), _ptr(dense_indices), _ptr(offsets), indices.dtype.itemsize,
+                      _ptr(hash_table), hash_table.dtype.itemsize, hash_table.shape[0], _ptr(hto)))
+
+    def pruned_hashmap_lookup(self, T, B, indices, offsets, hash_table, hash_table_offsets):
+        indices = np.ascontiguousarray(indices)
+        offsets = np.ascontiguousarray(offsets, dtype=indices.dtype)
+        hto = np.ascontiguousarray(hash_table_offsets, dtype=np.int64)
+        out = np.full_like(indices, -7)
+        f = self.lib.ref_tbe_pruned_hashmap_lookup
+        f.argtypes = [C.c_int32, C.c_int32, _p, _p, _int, _p, _int, _i64, _p, _p]
+        self._check(f(T, B, _ptr(indices), _ptr(offsets), indices.dtype.itemsize, _ptr(hash_table),
+                      hash_table.dtype.itemsize, hash_table.shape[0], _ptr(hto), _ptr(out)))
+        return out
+
+    def pruned_array_lookup(self, T, B, indices, offsets, remappings, remappings_offsets):
+        indices = np.ascontiguousarray(indices)
+        offsets = np.ascontiguousarray(offsets, dtype=indices.dtype)
+        ro = np.ascontiguousarray(remappings_offsets, dtype=np.int64)
+        remappings = np.ascontiguousarray(remappings)
+        out = np.full_like(indices, -7)
+        f = self.lib.ref_tbe_pruned_array_lookup
+        f.argtypes = [C.c_int32, C.c_int32, _p, _p, _int, _p, _int, _i64, _p, _p]
+        self._check(f(T, B, _ptr(indices), _ptr(offsets), indices.dtype.itemsize, _ptr(remappings),
+                      remappings.dtype.itemsize, len(remappings), _ptr(ro), _ptr(out)))
+        return out
+
+    def forward(self, dev_weights, weights_offsets, weights_tys, D_offsets, dim, indices, offsets, B, pooling_mode,
+                row_alignment, indice_weights, output_dtype, scale_bias_last, nobag=False, fp8_exponent_bits=-1,
+                fp8_exponent_bias=-1, out_shape=None, out_dtype=None):
+        """``int_nbit_split_embedding[_nobag]_codegen_forward_{unweighted,weighted}_cpu``;
+        ``dim`` is total_D (pooled) or D (nobag).  Returns the output as a
+        numpy array of ``out_dtype`` and ``out_shape``."""
+        dev_weights = np.ascontiguousarray(dev_weights, dtype=np.uint8)
+        w_off = np.ascontiguousarray(weights_offsets, dtype=np.int64)
+        tys = np.ascontiguousarray(weights_tys, dtype=np.uint8)
+        dims = np.ascontiguousarray(D_offsets, dtype=np.int32) if D_offsets is not None else None
+        indices = np.ascontiguousarray(indices)
+        offsets = np.ascontiguousarray(offsets, dtype=indices.dtype)
+        w = np.ascontiguousarray(indice_weights, dtype=np.float32) if indice_weights is not None else None
+        out = np.zeros(out_shape, dtype=out_dtype)
+        f = self.lib.ref_tbe_forward
+        f.argtypes = [_int, _p, _i64, _p, _p, C.c_int32, _p, _i64, _p, _p, _int, C.c_int32, _i64, _i64, _p, _i64, _i64,
+                      _i64, _int, _p, _i64]
+        self._check(f(int(nobag), _ptr(dev_weights), dev_weights.size, _ptr(w_off), _ptr(tys), len(w_off), _ptr(dims),
+                      dim, _ptr(indices), _ptr(offsets), indices.dtype.itemsize, B, int(pooling_mode), row_alignment,
+                      _ptr(w), int(output_dtype), fp8_exponent_bits, fp8_exponent_bias, int(scale_bias_last),
+                      _ptr(out), out.nbytes))
+        return out

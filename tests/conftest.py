@@ -30,7 +30,7 @@ def reference():
     snapshot)."""
     from oracle import checker
 
-    if not os.path.exists(checker.REF_SO) and os.path.isdir("/root/reference/src"):
+    if not os.path.exists(checker.REF_SO) and checker.reference_root():
         checker.build(("ref",))
     ref = checker.Reference()
     if not ref.available:

@@ -2,7 +2,9 @@
 restatement of pruned_hashmap_insert / pruned_hashmap_lookup /
 pruned_array_lookup (fbgemm_gpu/codegen/inference/
 embedding_forward_quantized_cpu_template.cpp:102-204, :524-659 of FBGEMM)
-against the property the reference's own test checks
+against fixtures made by the reference's own compiled functions
+(tests/golden/make_golden_tbe.py; live against that library where it was
+built), the property the reference's own test checks
 (fbgemm_gpu/test/tbe/utils/split_embeddings_utils_test.py:476-620), the hash
 against an independent statement of the MurmurHash3 finalisers, and the
 library's host-side insert against the oracle's (same table bytes)."""
@@ -12,6 +14,7 @@ import numpy as np
 import pytest
 
 from fbgemm_b200 import _capi
+from helpers import pruning_case
 
 
 def fmix32(h):
@@ -33,29 +36,6 @@ def fmix64(k):
     k = (k * 0xC4CEB9FE1A85EC53) & m
     k ^= k >> 33
     return k
-
-
-def pruning_case(rng, T, B, max_len, idt, hdt, load_factor=0.8, unpruned_tables=()):
-    """The reference test's construction with ragged bags: unique sparse
-    indices per table, half of them pruned (dense index -1)."""
-    lengths = rng.integers(0, max_len + 1, size=T * B)
-    offsets = np.concatenate([[0], np.cumsum(lengths)]).astype(idt)
-    n = int(offsets[-1])
-    indices = np.zeros(n, dtype=idt)
-    dense = np.zeros(n, dtype=idt)
-    capacities = []
-    for t in range(T):
-        lo, hi = int(offsets[t * B]), int(offsets[(t + 1) * B])
-        cnt = hi - lo
-        space = max(4 * cnt, 16)
-        indices[lo:hi] = rng.choice(space, size=cnt, replace=False).astype(idt)
-        d = rng.integers(0, 1000, size=cnt).astype(idt)
-        d[rng.random(cnt) < 0.5] = -1
-        dense[lo:hi] = d
-        capacities.append(0 if t in unpruned_tables else int(cnt / load_factor) + 1)
-    hto = np.concatenate([[0], np.cumsum(capacities)]).astype(np.int64)
-    table = np.full((int(hto[-1]), 2), -1, dtype=hdt)
-    return indices, dense, offsets, table, hto
 
 
 def test_hash_is_the_murmur3_finaliser(oracle):
@@ -160,3 +140,53 @@ def test_library_insert_builds_the_same_table(oracle, idt, hdt):
                                                     hto.ctypes.data)
     assert rc == 0 and (small[:, 0] != -1).all()
     assert lib.fbgemm_b200_pruned_hashmap_insert_host(0, 1, None, None, None, 4, None, 8, None) < 0
+
+
+def test_oracle_matches_the_reference_fixtures(oracle):
+    """oracle_pruned_* against tables and answers produced by the reference's
+    own pruned_hashmap_insert_unweighted_cpu, pruned_hashmap_lookup_unweighted_cpu
+    and pruned_array_lookup_cpu (tests/golden/make_golden_tbe.py)."""
+    from helpers import load_golden
+
+    g = load_golden("tbe_golden.npz")
+    assert int(g["n_hash"]) >= 12 and int(g["n_arr"]) >= 4
+    for i in range(int(g["n_hash"])):
+        k = f"hash{i}_"
+        T, B = (int(x) for x in g[k + "meta"])
+        table = np.full_like(g[k + "table"], -1)
+        assert oracle.pruned_hashmap_insert(T, B, g[k + "indices"], g[k + "dense"], g[k + "offsets"], table, g[k + "hto"])
+        np.testing.assert_array_equal(table, g[k + "table"], err_msg=k)   # same slots, not only the same answers
+        np.testing.assert_array_equal(
+            oracle.pruned_hashmap_lookup(T, B, g[k + "indices"], g[k + "offsets"], table, g[k + "hto"]), g[k + "lookup"])
+        np.testing.assert_array_equal(
+            oracle.pruned_hashmap_lookup(T, B, g[k + "probe"], g[k + "offsets"], table, g[k + "hto"]),
+            g[k + "probe_lookup"])
+    for i in range(int(g["n_arr"])):
+        k = f"arr{i}_"
+        T, B = (int(x) for x in g[k + "meta"])
+        ok, got = oracle.pruned_array_lookup(T, B, g[k + "indices"], g[k + "offsets"], g[k + "remap"], g[k + "ro"])
+        assert ok
+        np.testing.assert_array_equal(got, g[k + "lookup"], err_msg=k)
+
+
+@pytest.mark.parametrize("idt", [np.int32, np.int64])
+@pytest.mark.parametrize("hdt", [np.int32, np.int64])
+def test_oracle_matches_the_compiled_reference_live(oracle, idt, hdt):
+    """Fresh random cases against the reference's compiled template, where that
+    library was built (it needs the reference tree at build time)."""
+    from oracle import checker
+
+    ref = checker.ReferenceTbe()
+    if not ref.available:
+        pytest.skip("oracle/_ref/libfbgemm_tbe_ref.so not built")
+    rng = np.random.default_rng(4100 + np.dtype(idt).itemsize + 3 * np.dtype(hdt).itemsize)
+    for T, B, max_len, lf in ((1, 1, 5, 0.8), (5, 40, 20, 0.5), (3, 200, 9, 0.95)):
+        indices, dense, offsets, table, hto = pruning_case(rng, T, B, max_len, idt, hdt, lf,
+                                                           unpruned_tables=(1,) if T > 1 else ())
+        ours = table.copy()
+        ref.pruned_hashmap_insert(T, B, indices, dense, offsets, table, hto)
+        assert oracle.pruned_hashmap_insert(T, B, indices, dense, offsets, ours, hto)
+        np.testing.assert_array_equal(ours, table)
+        for probe in (indices, indices[::-1].copy(), np.full_like(indices, 2 ** 31 - 1), -indices - 1):
+            np.testing.assert_array_equal(oracle.pruned_hashmap_lookup(T, B, probe, offsets, ours, hto),
+                                          ref.pruned_hashmap_lookup(T, B, probe, offsets, table, hto))

@@ -9,7 +9,7 @@ import torch
 
 import fbgemm_b200 as F
 from fbgemm_b200 import tbe
-from test_pruned_lookup_cpu import pruning_case
+from helpers import pruning_case
 
 pytestmark = pytest.mark.gpu
 
@@ -163,3 +163,35 @@ def test_insert_on_the_device(gpu_ctx, oracle, idt, hdt):
     ok = tbe.pruned_hashmap_insert(dev(indices), dev(indices.copy()), dev(np.array([0, 6], dtype=idt)), small,
                                    dev(np.array([0, 4], dtype=np.int64)), slot=5)
     assert not ok and int((small[:, 0] != -1).sum()) == 4
+
+
+def test_lookups_match_the_reference_fixtures(gpu_ctx):
+    """The kernels against tables built, and answers given, by the reference's
+    own pruned_hashmap_insert/lookup_unweighted_cpu and pruned_array_lookup_cpu
+    (tests/golden/make_golden_tbe.py); the host-side insert the library ships
+    against the reference's table, slot for slot."""
+    from helpers import load_golden
+
+    g = load_golden("tbe_golden.npz")
+    for i in range(int(g["n_hash"])):
+        k = f"hash{i}_"
+        T, B = (int(x) for x in g[k + "meta"])
+        table, hto, offsets = g[k + "table"], g[k + "hto"], g[k + "offsets"]
+        for probe, want in ((g[k + "indices"], g[k + "lookup"]), (g[k + "probe"], g[k + "probe_lookup"])):
+            got = tbe.pruned_hashmap_lookup(dev(probe), dev(offsets), dev(table), dev(hto), slot=7)
+            np.testing.assert_array_equal(got.cpu().numpy(), want, err_msg=k)
+        built = torch.full(table.shape, -1, dtype=torch.from_numpy(table).dtype)
+        assert tbe.pruned_hashmap_insert(torch.from_numpy(g[k + "indices"]), torch.from_numpy(g[k + "dense"]),
+                                         torch.from_numpy(offsets), built, torch.from_numpy(hto))
+        np.testing.assert_array_equal(built.numpy(), table, err_msg=k)
+        # the device-built table gives the reference's answers too
+        d_built = torch.full(table.shape, -1, dtype=built.dtype, device="cuda")
+        assert tbe.pruned_hashmap_insert(dev(g[k + "indices"]), dev(g[k + "dense"]), dev(offsets), d_built, dev(hto), slot=7)
+        got = tbe.pruned_hashmap_lookup(dev(g[k + "probe"]), dev(offsets), d_built, dev(hto), slot=7)
+        np.testing.assert_array_equal(got.cpu().numpy(), g[k + "probe_lookup"], err_msg=k)
+    for i in range(int(g["n_arr"])):
+        k = f"arr{i}_"
+        got = tbe.pruned_array_lookup(dev(g[k + "indices"]), dev(g[k + "offsets"]), dev(g[k + "remap"]), dev(g[k + "ro"]),
+                                      slot=7)
+        np.testing.assert_array_equal(got.cpu().numpy(), g[k + "lookup"], err_msg=k)
+    assert F.status_read(7)[0]

@@ -148,3 +148,24 @@ def test_more_tables_than_fit_in_shared_memory(gpu_ctx, oracle):
             ok_ref, ref = reference_rows(oracle, ST.INT8, D, rows, tables[t], indices[lo:hi], "f32", True)
             assert ok_ref
             np.testing.assert_array_equal(got[lo:hi].reshape(-1), bits(ref)[:(hi - lo) * D])
+
+
+def test_sequence_operator_matches_the_reference_operator_fixtures(gpu_ctx):
+    """Outputs of the reference's own
+    int_nbit_split_embedding_nobag_codegen_forward_unweighted_cpu
+    (tests/golden/make_golden_tbe.py), bit for bit."""
+    from helpers import load_golden
+
+    g = load_golden("tbe_golden.npz")
+    for i in range(int(g["n_seq"])):
+        k = f"seq{i}_"
+        B, sbl, out_ty, D, align = (int(x) for x in g[k + "meta"])
+        op = tbe.IntNBitSequenceEmbedding(torch.from_numpy(g[k + "blob"]).cuda(), g[k + "w_off"],
+                                          g[k + "tys"].astype(np.uint8), D, align, out_ty, bool(sbl))
+        out = op.forward(torch.from_numpy(g[k + "indices"]).cuda(), torch.from_numpy(g[k + "offsets"]).cuda(), slot=34)
+        ok, info = F.status_read(34)
+        assert ok, info
+        got = out.cpu().view(torch.int32 if out.dtype == torch.float32 else torch.int16).numpy()
+        want = g[k + "out"]
+        np.testing.assert_array_equal(got.view(np.uint32 if out.dtype == torch.float32 else np.uint16),
+                                      want.view(np.uint32) if want.dtype == np.float32 else want, err_msg=k)

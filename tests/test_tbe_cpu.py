@@ -31,3 +31,35 @@ def test_row_sizes_of_unquantized_types():
     assert tbe.padded_row_size_in_bytes(64, tbe.SparseType.FP16, 16) == 128
     assert tbe.padded_row_size_in_bytes(30, tbe.SparseType.FP32, 16) == 128
     assert tbe.padded_row_size_in_bytes(36, tbe.SparseType.FP8, 16) == 48
+
+
+def test_oracle_composition_matches_the_reference_operator():
+    """The oracle's single-table lookups, composed table by table as the tests
+    compose them, against outputs of the reference's own
+    int_nbit_split_embedding_codegen_forward_{unweighted,weighted}_cpu and
+    ..._nobag_... (fixtures made by tests/golden/make_golden_tbe.py)."""
+    import numpy as np
+
+    from helpers import load_golden, oracle_op_forward, oracle_sequence_forward
+    from oracle.checker import Oracle
+
+    oracle = Oracle()
+    g = load_golden("tbe_golden.npz")
+    assert int(g["n_op"]) >= 16 and int(g["n_seq"]) >= 9
+    for i in range(int(g["n_op"])):
+        k = f"op{i}_"
+        B, sbl, out_ty, weighted, pooling, align = (int(x) for x in g[k + "meta"])
+        got = oracle_op_forward(oracle, g[k + "tys"], g[k + "dims"], g[k + "rows"], g[k + "blob"], g[k + "w_off"],
+                                g[k + "D_off"], g[k + "indices"], g[k + "offsets"], g[k + "weights"] if weighted else None,
+                                B, pooling == 1, out_ty, bool(sbl), align, (5, 15))
+        want = g[k + "out"]
+        want = want.view(np.uint32) if want.dtype == np.float32 else want
+        np.testing.assert_array_equal(got, want, err_msg=k)
+    for i in range(int(g["n_seq"])):
+        k = f"seq{i}_"
+        B, sbl, out_ty, D, align = (int(x) for x in g[k + "meta"])
+        got = oracle_sequence_forward(oracle, g[k + "tys"], D, g[k + "rows"], g[k + "blob"], g[k + "w_off"],
+                                      g[k + "indices"], g[k + "offsets"], B, out_ty, bool(sbl), align)
+        want = g[k + "out"]
+        want = want.view(np.uint32) if want.dtype == np.float32 else want
+        np.testing.assert_array_equal(got, want, err_msg=k)

@@ -11,41 +11,13 @@ import torch
 import fbgemm_b200 as F
 from fbgemm_b200 import tbe
 from conftest import bits
-from helpers import random_fused_table, random_plain_table
+from helpers import build_op_inputs
 
 pytestmark = pytest.mark.gpu
 
 KIND = {tbe.SparseType.FP32: "f32", tbe.SparseType.FP16: "f16", tbe.SparseType.BF16: "bf16"}
 BITS = {tbe.SparseType.INT8: 8, tbe.SparseType.INT4: 4, tbe.SparseType.INT2: 2}
 PLAIN = {tbe.SparseType.FP32: "f32", tbe.SparseType.FP16: "f16", tbe.SparseType.FP8: "fp8"}
-
-
-def build_op_inputs(rng, tys, dims, rows, B, mean_len, row_alignment, scale_bias_last, idt):
-    T = len(tys)
-    tables, offs_w, blob = [], [], []
-    at = 0
-    for ty, D, R in zip(tys, dims, rows):
-        sb = 8 if (ty == tbe.SparseType.INT8 and scale_bias_last) else 4
-        stride = tbe.padded_row_size_in_bytes(D, ty, row_alignment, sb)
-        if ty in PLAIN:
-            eb = {"f32": 4, "f16": 2, "fp8": 1}[PLAIN[ty]]
-            t = random_plain_table(rng, R, D, PLAIN[ty], stride // eb)
-            t = t.view(np.uint8).reshape(R, stride)
-        else:
-            t = random_fused_table(rng, R, D, BITS[ty], stride, not scale_bias_last)
-        tables.append(t)
-        offs_w.append(at)
-        blob.append(t.reshape(-1))
-        at += t.size
-    lengths = rng.poisson(mean_len, T * B)
-    lengths[rng.integers(0, T * B, 3)] = 0
-    offsets = np.concatenate([[0], np.cumsum(lengths)]).astype(idt)
-    indices = np.concatenate([rng.integers(0, rows[t], int(lengths[t * B:(t + 1) * B].sum())) for t in range(T)]).astype(idt)
-    if not scale_bias_last:
-        indices[rng.integers(0, len(indices), len(indices) // 8)] = -1   # pruned rows
-    weights = rng.standard_normal(len(indices)).astype(np.float32)
-    D_offsets = np.concatenate([[0], np.cumsum(dims)]).astype(np.int32)
-    return tables, np.concatenate(blob), np.array(offs_w, np.int64), D_offsets, offsets, indices, weights
 
 
 @pytest.mark.parametrize("scale_bias_last", [False, True])
@@ -145,3 +117,31 @@ def test_plan_cache_is_bounded(gpu_ctx):
         op.forward(d_idx, d_off, output=o, use_plan=True)
     assert F.status_read(0)[0] and len(op._plans) == op.MAX_PLANS
     assert all(torch.equal(o, first) for o in outs)
+
+
+def test_operator_matches_the_reference_operator_fixtures(gpu_ctx):
+    """Outputs of the reference's own
+    int_nbit_split_embedding_codegen_forward_{unweighted,weighted}_cpu
+    (tests/golden/make_golden_tbe.py), bit for bit."""
+    from helpers import load_golden
+
+    g = load_golden("tbe_golden.npz")
+    for i in range(int(g["n_op"])):
+        k = f"op{i}_"
+        B, sbl, out_ty, weighted, pooling, align = (int(x) for x in g[k + "meta"])
+        indices, offsets = g[k + "indices"], g[k + "offsets"]
+        tdt = torch.int32 if indices.dtype == np.int32 else torch.int64
+        total_D = int(g[k + "D_off"][-1])
+        op = tbe.IntNBitTableBatchedEmbeddingBags(
+            torch.from_numpy(g[k + "blob"]).cuda(), g[k + "w_off"], g[k + "tys"].astype(np.uint8), g[k + "D_off"], total_D,
+            pooling, align, out_ty, bool(sbl), bool(weighted), tdt, 5, 15)
+        d_w = torch.from_numpy(g[k + "weights"]).cuda() if weighted else None
+        for use_plan in (False, True):
+            out = op.forward(torch.from_numpy(indices).cuda(), torch.from_numpy(offsets).cuda(), d_w, slot=23,
+                             use_plan=use_plan)
+            ok, info = F.status_read(23)
+            assert ok, info
+            got = out.cpu().view(torch.int32 if out.dtype == torch.float32 else torch.int16).numpy()
+            want = g[k + "out"]
+            np.testing.assert_array_equal(got.view(np.uint32 if out.dtype == torch.float32 else np.uint16),
+                                          want.view(np.uint32) if want.dtype == np.float32 else want, err_msg=k)
