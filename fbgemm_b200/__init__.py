@@ -12,7 +12,6 @@ Layers, bottom up:
                    sequence form, the pruning lookups that run before it)
 * ``workloads.py`` seeded synthetic inputs of the benchmark configurations
 * ``sharding.py``  table-wise sharding over the GPUs of one box
-* ``caller_bench.py`` timing of the kernels either side of the pooled lookup
 
 Importing the package does not need a GPU; creating a context does, and fails
 loudly without one.  There is no CPU path.
@@ -28,6 +27,7 @@ from .embedding import (  # noqa: F401
     GenerateEmbeddingSpMDMNBitWithStrides,
     GenerateEmbeddingSpMDMRowWiseSparse,
     GenerateEmbeddingSpMDMWithStrides,
+    MultiTableHostCall,
     MultiTablePlan,
     SpmdmKernel,
     compressed_indices_remap,

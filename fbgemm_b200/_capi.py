@@ -14,6 +14,8 @@ from . import build as _build
 
 STATUS_SLOTS = 1024
 HOST_LANES = 8
+USER_SLOTS = STATUS_SLOTS - HOST_LANES - 1
+STATUS_PEER_TIMEOUT = 5
 NOALLOC_MAX_BAGS = 1 << 20
 MAX_PEERS = 8
 OUT_F32 = 0
@@ -64,6 +66,19 @@ class TableCall(C.Structure):
     ]
 
 
+class PeerSync(C.Structure):
+    """``fbgemm_b200_peer_sync``."""
+
+    _fields_ = [
+        ("num_peers", C.c_int32),
+        ("ready_flags", C.POINTER(C.c_void_p)),
+        ("ready_local", C.c_void_p),
+        ("ack_flags", C.POINTER(C.c_void_p)),
+        ("ack_local", C.c_void_p),
+        ("timeout_us", C.c_uint64),
+    ]
+
+
 class Fbgemmb200Error(RuntimeError):
     pass
 
@@ -108,7 +123,13 @@ SIGNATURES = {
     "fbgemm_b200_spmdm_host_submit": (C.c_int, [_p, C.c_int, _cfgp, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p]),
     "fbgemm_b200_spmdm_host_wait": (C.c_int, [_p, C.c_int]),
     "fbgemm_b200_spmdm_host": (C.c_int, [_p, _cfgp, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p]),
-    "fbgemm_b200_probe_row_gather": (C.c_int, [_p, _i64, C.c_int32, _p, _i64, C.c_int32, _p, _p]),
+    "fbgemm_b200_peer_signal": (C.c_int, [_p, C.POINTER(_p), C.c_int, C.c_uint64, _p]),
+    "fbgemm_b200_peer_wait": (C.c_int, [_p, _p, C.c_int, C.c_uint64, C.c_uint64, C.c_int, _p]),
+    "fbgemm_b200_multi_host_create": (C.c_int, [_p, C.POINTER(TableCall), C.c_int32, C.POINTER(_i64), C.c_int32, _i64,
+                                                _p, C.c_size_t, C.POINTER(PeerSync), C.c_int, C.POINTER(_p)]),
+    "fbgemm_b200_multi_host_submit": (C.c_int, [_p, C.POINTER(_p), C.POINTER(_p), C.POINTER(_p), C.POINTER(_i64), _p]),
+    "fbgemm_b200_multi_host_wait": (C.c_int, [_p, C.POINTER(C.c_int32)]),
+    "fbgemm_b200_multi_host_destroy": (None, [_p]),
     "fbgemm_b200_float_to_fused_8bit_rowwise": (C.c_int, [_p, _i64, C.c_int32, _p, _p]),
     "fbgemm_b200_float_to_fused_nbit_rowwise": (C.c_int, [C.c_int32, _p, _i64, C.c_int32, _p, _p]),
 }

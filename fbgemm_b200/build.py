@@ -22,7 +22,7 @@ INCLUDE = os.path.join(ROOT, "include")
 LIB_PATH = os.path.join(PKG_DIR, "libfbgemm_b200.so")
 STAMP_PATH = os.path.join(PKG_DIR, "csrc", ".build_stamp")
 
-CUDA_SOURCES = ["spmdm_kernels.cu", "spmdm_direct_8.cu", "spmdm_direct_4.cu", "spmdm_direct_2.cu", "scan_kernels.cu", "quantize_kernels.cu", "remap_kernels.cu", "pruned_lookup_kernels.cu", "sequence_kernels.cu", "stage_kernels.cu", "plain_kernels.cu", "c_api.cu", "noalloc_entry.cu", "gather_probe.cu"]
+CUDA_SOURCES = ["spmdm_kernels.cu", "spmdm_direct_8.cu", "spmdm_direct_4.cu", "spmdm_direct_2.cu", "scan_kernels.cu", "quantize_kernels.cu", "remap_kernels.cu", "pruned_lookup_kernels.cu", "sequence_kernels.cu", "stage_kernels.cu", "plain_kernels.cu", "c_api.cu", "noalloc_entry.cu", "peer_sync_kernels.cu", "multi_host.cu"]
 CXX_SOURCES = ["generators.cc"]
 
 NVCC_FLAGS = [

@@ -9,7 +9,7 @@
 #include <type_traits>
 #include <vector>
 
-#include "internal.h"
+#include "context.h"
 
 namespace fbgemm_b200 {
 
@@ -28,116 +28,32 @@ int fail_cuda(cudaError_t e, const char* what) {
 
 int max_chunks_per_bag(int bit_rate);  // spmdm_kernels.cu
 
-namespace {
-
-// Grow-only device buffer; contents are not preserved.
-cudaError_t reserve(DeviceBuffer& b, size_t bytes) {
-  if (bytes <= b.bytes) {
-    return cudaSuccess;
-  }
-  if (b.ptr) {
-    cudaFree(b.ptr);
-    b.ptr = nullptr;
-    b.bytes = 0;
-  }
-  const size_t want = bytes + bytes / 4 + 256;
-  cudaError_t e = cudaMalloc(&b.ptr, want);
-  if (e == cudaSuccess) {
-    b.bytes = want;
-  }
-  return e;
-}
-
-struct PinnedBuffer {
-  void* ptr = nullptr;
-  size_t bytes = 0;
-};
-
-cudaError_t reserve(PinnedBuffer& b, size_t bytes) {
-  if (bytes <= b.bytes) {
-    return cudaSuccess;
-  }
-  if (b.ptr) {
-    cudaFreeHost(b.ptr);
-    b.ptr = nullptr;
-    b.bytes = 0;
-  }
-  const size_t want = bytes + bytes / 4 + 256;
-  cudaError_t e = cudaMallocHost(&b.ptr, want);
-  if (e == cudaSuccess) {
-    b.bytes = want;
-  }
-  return e;
-}
-
-// One staging lane of the host-pointer pipeline.
-struct Lane {
-  cudaStream_t stream = nullptr;
-  DeviceBuffer d_in;    // indices | offsets | weights
-  DeviceBuffer d_out;   // pooled rows
-  DeviceBuffer d_scan;  // lengths-mode scratch of this lane
-  PinnedBuffer h_in;
-  PinnedBuffer h_out;
-  PinnedBuffer h_status;
-  bool busy = false;
-  // what to do at wait()
-  void* user_out = nullptr;
-  size_t out_row_bytes = 0;   // bytes of one pooled row (block_size elements)
-  size_t out_pitch_bytes = 0; // bytes between rows in the user's buffer
-  int64_t out_rows = 0;
-  bool trivially_true = false;
-  bool trivially_false = false;
-};
-
-struct Derived {
-  int data_bytes;
-  int sb_bytes;
-  int64_t input_stride;
-  int64_t output_stride;
-};
-
-}  // namespace
-
 }  // namespace fbgemm_b200
 
 using namespace fbgemm_b200;
 
-struct fbgemm_b200_ctx {
-  int device = 0;
-  std::mutex mu;
-  int32_t* status = nullptr;         // device, FBGEMM_B200_STATUS_SLOTS x 4
-  int32_t* status_host = nullptr;    // pinned, same shape (read-back)
-  DeviceBuffer scan;                 // lengths-mode scratch (device-pointer path)
-  std::unordered_map<const void*, DeviceBuffer> tables;
-  Lane lanes[FBGEMM_B200_HOST_LANES];
-};
-
-struct fbgemm_b200_multi_plan {
-  int device = 0;
-  MultiPlan plan;
-};
-
 namespace {
 
-class DeviceGuard {
- public:
-  explicit DeviceGuard(int dev) {
-    cudaGetDevice(&prev_);
-    if (prev_ != dev) {
-      cudaSetDevice(dev);
-      changed_ = true;
-    }
-  }
-  ~DeviceGuard() {
-    if (changed_) {
-      cudaSetDevice(prev_);
-    }
-  }
+// Status slots: callers own [0, FBGEMM_B200_USER_SLOTS); then one for the
+// index remap; the last FBGEMM_B200_HOST_LANES belong to the host-pointer lanes.
+constexpr int kRemapSlot = FBGEMM_B200_USER_SLOTS;
+static_assert(FBGEMM_B200_USER_SLOTS + 1 + FBGEMM_B200_HOST_LANES == FBGEMM_B200_STATUS_SLOTS, "slot ranges");
 
- private:
-  int prev_ = 0;
-  bool changed_ = false;
-};
+// The lengths-mode scratch of `stream` (ctx->mu held).  A context that has
+// seen very many streams drops the scratch of all of them once, after waiting
+// for the device, instead of growing without bound.
+DeviceBuffer& scan_scratch_of(fbgemm_b200_ctx* ctx, cudaStream_t stream) {
+  constexpr size_t kMaxStreams = 256;
+  auto it = ctx->scan.find(stream);
+  if (it == ctx->scan.end() && ctx->scan.size() >= kMaxStreams) {
+    cudaDeviceSynchronize();
+    for (auto& kv : ctx->scan) {
+      cudaFree(kv.second.ptr);
+    }
+    ctx->scan.clear();
+  }
+  return ctx->scan[stream];
+}
 
 int check_config(const fbgemm_b200_spmdm_config* c, Derived* d) {
   if (!c) {
@@ -250,6 +166,10 @@ int fbgemm_b200::build_lookup_params(
   }
   if (cfg->has_weight && !weights && index_size > 0) {
     set_error("has_weight set but weights is null");
+    return FBGEMM_B200_EINVAL;
+  }
+  if ((index_size > 0 && (!input || !indices)) || (output_size > 0 && !out && num_peers <= 0)) {
+    set_error("null table, indices or output pointer");
     return FBGEMM_B200_EINVAL;
   }
   if (cfg->no_bag && (output_size != index_size || cit || cfg->is_weight_positional)) {
@@ -404,6 +324,10 @@ int fbgemm_b200::enqueue_lookup(
     return rc;
   }
   uint32_t flags = p.flags;
+  if (!cfg->no_bag && !offsets_or_lengths) {
+    set_error("null offsets (or lengths) pointer");
+    return FBGEMM_B200_EINVAL;
+  }
   if (cfg->no_bag) {
     p.offsets = nullptr;  // bag m is the single index m
   } else if (cfg->use_offsets) {
@@ -599,9 +523,12 @@ void fbgemm_b200_ctx_destroy(fbgemm_b200_ctx* ctx) {
     cudaFreeHost(l.h_status.ptr);
   }
   for (auto& kv : ctx->tables) {
+    cudaFree(kv.second.buf.ptr);
+  }
+  for (auto& kv : ctx->scan) {
     cudaFree(kv.second.ptr);
   }
-  cudaFree(ctx->scan.ptr);
+  cudaFree(ctx->remap_scratch.ptr);
   cudaFree(ctx->status);
   cudaFreeHost(ctx->status_host);
   delete ctx;
@@ -633,8 +560,8 @@ int fbgemm_b200_spmdm_launch(
     const int32_t* compressed_indices_table,
     int slot,
     void* stream) {
-  if (!ctx || slot < 0 || slot >= FBGEMM_B200_STATUS_SLOTS) {
-    set_error("bad context or status slot");
+  if (!ctx || slot < 0 || slot >= FBGEMM_B200_USER_SLOTS) {
+    set_error("bad context or status slot (callers own slots 0 .. FBGEMM_B200_USER_SLOTS - 1)");
     return FBGEMM_B200_EINVAL;
   }
   DeviceGuard guard(ctx->device);
@@ -654,13 +581,17 @@ int fbgemm_b200_spmdm_launch(
     }
     return 0;
   }
-  std::unique_lock<std::mutex> lock(ctx->mu, std::defer_lock);
   if (cfg && !cfg->use_offsets && !cfg->no_bag) {
-    lock.lock();  // the scan scratch is shared by device-pointer calls
+    // Lengths mode: the scanned offsets live in scratch that belongs to the
+    // stream, so that launches on different streams never share it.
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    return enqueue_lookup(cfg, output_size, index_size, data_size, input, indices, offsets_or_lengths, weights, out,
+                          compressed_indices_table, ctx->status + 4 * slot,
+                          scan_scratch_of(ctx, static_cast<cudaStream_t>(stream)), static_cast<cudaStream_t>(stream));
   }
+  DeviceBuffer unused;  // only lengths mode touches the scratch
   return enqueue_lookup(cfg, output_size, index_size, data_size, input, indices, offsets_or_lengths, weights, out,
-                        compressed_indices_table, ctx->status + 4 * slot, ctx->scan,
-                        static_cast<cudaStream_t>(stream));
+                        compressed_indices_table, ctx->status + 4 * slot, unused, static_cast<cudaStream_t>(stream));
 }
 
 int fbgemm_b200_spmdm_launch_sharded(
@@ -678,8 +609,8 @@ int fbgemm_b200_spmdm_launch_sharded(
     int64_t bags_per_peer,
     int slot,
     void* stream) {
-  if (!ctx || slot < 0 || slot >= FBGEMM_B200_STATUS_SLOTS) {
-    set_error("bad context or status slot");
+  if (!ctx || slot < 0 || slot >= FBGEMM_B200_USER_SLOTS) {
+    set_error("bad context or status slot (callers own slots 0 .. FBGEMM_B200_USER_SLOTS - 1)");
     return FBGEMM_B200_EINVAL;
   }
   if (!cfg || !cfg->use_offsets || output_size <= 0 || num_peers <= 0) {
@@ -687,8 +618,9 @@ int fbgemm_b200_spmdm_launch_sharded(
     return FBGEMM_B200_EINVAL;
   }
   DeviceGuard guard(ctx->device);
+  DeviceBuffer unused;  // offsets mode: no scratch
   return enqueue_lookup(cfg, output_size, index_size, data_size, input, indices, offsets, weights, nullptr, nullptr,
-                        ctx->status + 4 * slot, ctx->scan, static_cast<cudaStream_t>(stream), peer_out, num_peers,
+                        ctx->status + 4 * slot, unused, static_cast<cudaStream_t>(stream), peer_out, num_peers,
                         bags_per_peer);
 }
 
@@ -703,7 +635,7 @@ int fbgemm_b200_multi_plan_create(
   if (out) {
     *out = nullptr;
   }
-  if (!ctx || !out || slot < 0 || slot >= FBGEMM_B200_STATUS_SLOTS) {
+  if (!ctx || !out || slot < 0 || slot >= FBGEMM_B200_USER_SLOTS) {
     set_error("bad context, plan pointer or status slot");
     return FBGEMM_B200_EINVAL;
   }
@@ -728,6 +660,10 @@ int fbgemm_b200_multi_plan_create(
                                        num_peers, bags_per_peer, &params[(size_t)t]);
     if (rc) {
       return rc;
+    }
+    if (!c.cfg.no_bag && !c.offsets) {
+      set_error("a table of the plan has no offsets");
+      return FBGEMM_B200_EINVAL;
     }
     params[(size_t)t].offsets = c.cfg.no_bag ? nullptr : c.offsets;
     params[(size_t)t].flags |= c.cfg.offset_bytes == 8 ? kOff64 : 0;
@@ -854,16 +790,18 @@ int fbgemm_b200_compressed_indices_remap(
     return FBGEMM_B200_EINVAL;
   }
   DeviceGuard guard(ctx->device);
-  // The scratch and the status slot (the last one) are the context's: one remap at a time.
+  // The scratch and the status slot (one reserved for this call, outside the
+  // callers' and the lanes' ranges) are the context's: one remap at a time;
+  // the call returns only after its kernels have finished.
   std::lock_guard<std::mutex> lock(ctx->mu);
-  cudaError_t e = reserve(ctx->scan, remap_scratch_bytes(index_size));
+  cudaError_t e = reserve(ctx->remap_scratch, remap_scratch_bytes(index_size));
   if (e != cudaSuccess) {
     return fail_cuda(e, "scratch for the index remap");
   }
-  const int slot = FBGEMM_B200_STATUS_SLOTS - 1;
+  const int slot = kRemapSlot;
   e = launch_compressed_indices_remap(offsets_len, indices, index_bytes, index_size, compressed_indices_mapping,
                                       mapping_size, offsets, weights, out_indices, out_offsets, out_weights,
-                                      ctx->status + 4 * slot, ctx->scan.ptr, static_cast<cudaStream_t>(stream));
+                                      ctx->status + 4 * slot, ctx->remap_scratch.ptr, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) {
     return fail_cuda(e, "index remap launch");
   }
@@ -1051,13 +989,17 @@ int fbgemm_b200_table_register(fbgemm_b200_ctx* ctx, const void* host_ptr, size_
     cudaFree(buf.ptr);
     return fail_cuda(e, "table upload");
   }
+  ResidentTable entry;
+  entry.buf = buf;
+  entry.fingerprint = table_fingerprint(host_ptr, bytes);
   std::lock_guard<std::mutex> lock(ctx->mu);
   auto it = ctx->tables.find(host_ptr);
   if (it != ctx->tables.end()) {
-    cudaFree(it->second.ptr);
-    it->second = buf;
+    cudaDeviceSynchronize();  // a lookup still in flight may be reading the old copy
+    cudaFree(it->second.buf.ptr);
+    it->second = entry;
   } else {
-    ctx->tables.emplace(host_ptr, buf);
+    ctx->tables.emplace(host_ptr, entry);
   }
   return 0;
 }
@@ -1074,7 +1016,7 @@ int fbgemm_b200_table_unregister(fbgemm_b200_ctx* ctx, const void* host_ptr) {
     return FBGEMM_B200_EINVAL;
   }
   cudaDeviceSynchronize();
-  cudaFree(it->second.ptr);
+  cudaFree(it->second.buf.ptr);
   ctx->tables.erase(it);
   return 0;
 }
@@ -1085,8 +1027,57 @@ const void* fbgemm_b200_table_device_ptr(fbgemm_b200_ctx* ctx, const void* host_
   }
   std::lock_guard<std::mutex> lock(ctx->mu);
   auto it = ctx->tables.find(host_ptr);
-  return it == ctx->tables.end() ? nullptr : it->second.ptr;
+  return it == ctx->tables.end() ? nullptr : it->second.buf.ptr;
 }
+
+namespace {
+
+// The resident copy of the caller's host array `host` for a call that will
+// read its first `need_bytes` bytes (0: the size is not part of the call).
+// A copy is keyed by the host address alone, and an address can come back
+// from the allocator with another table behind it: the copy is used only if
+// it is at least as large as the call needs and the caller's memory still has
+// the fingerprint taken at registration.  Otherwise a copy this library made
+// on its own is refreshed, and an explicit registration is refused with a
+// clear error (the caller registers again).  Returns 0 or a negative code.
+int resident_table(fbgemm_b200_ctx* ctx, const void* host, size_t need_bytes, bool may_create, const void** dptr) {
+  *dptr = nullptr;
+  bool stale = false, found = false, implicit = false;
+  {
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    auto it = ctx->tables.find(host);
+    if (it != ctx->tables.end()) {
+      found = true;
+      implicit = it->second.implicit;
+      stale = need_bytes > it->second.buf.bytes ||
+          table_fingerprint(host, it->second.buf.bytes) != it->second.fingerprint;
+      if (!stale) {
+        *dptr = it->second.buf.ptr;
+        return 0;
+      }
+    }
+  }
+  if (found && !implicit) {
+    set_error("the table registered under this host address no longer matches the caller's memory (the call needs " +
+              std::to_string(need_bytes) + " bytes, or the contents changed): register it again");
+    return FBGEMM_B200_EINVAL;
+  }
+  if (!may_create || need_bytes == 0) {
+    set_error("table not resident: register it first (its size is not part of the call)");
+    return FBGEMM_B200_EINVAL;
+  }
+  const int rc = fbgemm_b200_table_register(ctx, host, need_bytes);
+  if (rc) {
+    return rc;
+  }
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  auto it = ctx->tables.find(host);
+  it->second.implicit = true;
+  *dptr = it->second.buf.ptr;
+  return 0;
+}
+
+}  // namespace
 
 /* ---- host-pointer pipeline ---------------------------------------------- */
 
@@ -1147,32 +1138,27 @@ int fbgemm_b200_spmdm_host_submit(
     return 0;
   }
 
-  // Tables live on the device; find (or create) the resident copies.
-  const void* d_table = fbgemm_b200_table_device_ptr(ctx, input);
-  if (!d_table) {
-    const int64_t rows = cit ? 0 : data_size;
-    if (cit) {
-      // The compressed row count is not part of the signature (the reference
-      // has the same gap: FbgemmEmbedding.h:212 "TODO: add compressed_data_size").
-      set_error("pruned lookup: register the compressed table first (its size is not part of the call)");
-      return FBGEMM_B200_EINVAL;
-    }
-    rc = fbgemm_b200_table_register(ctx, input, (size_t)(rows * d.input_stride));
-    if (rc) {
-      return rc;
-    }
-    d_table = fbgemm_b200_table_device_ptr(ctx, input);
+  // Tables live on the device; find (or create) the resident copies.  With a
+  // pruning map the compressed row count is not part of the signature (the
+  // reference has the same gap: FbgemmEmbedding.h:212 "TODO: add
+  // compressed_data_size"), so that table has to be registered beforehand.
+  if (!input || (index_size > 0 && !indices) || !offsets_or_lengths || !out) {
+    set_error("null table, indices, offsets or output pointer");
+    return FBGEMM_B200_EINVAL;
+  }
+  const void* d_table = nullptr;
+  rc = resident_table(ctx, input, cit ? 0 : (size_t)(data_size * d.input_stride), !cit, &d_table);
+  if (rc) {
+    return rc;
   }
   const int32_t* d_cit = nullptr;
   if (cit) {
-    d_cit = static_cast<const int32_t*>(fbgemm_b200_table_device_ptr(ctx, cit));
-    if (!d_cit) {
-      rc = fbgemm_b200_table_register(ctx, cit, (size_t)data_size * sizeof(int32_t));
-      if (rc) {
-        return rc;
-      }
-      d_cit = static_cast<const int32_t*>(fbgemm_b200_table_device_ptr(ctx, cit));
+    const void* v = nullptr;
+    rc = resident_table(ctx, cit, (size_t)data_size * sizeof(int32_t), true, &v);
+    if (rc) {
+      return rc;
     }
+    d_cit = static_cast<const int32_t*>(v);
   }
 
   // Pack indices | offsets | weights into one pinned block, one H2D copy.

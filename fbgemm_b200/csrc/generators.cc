@@ -4,6 +4,8 @@
 // (src/EmbeddingSpMDM.cc:1680-1703, src/EmbeddingSpMDMNBit.cc:1461-1484).
 #include <cuda_runtime.h>
 
+#include <algorithm>
+#include <cstdint>
 #include <map>
 #include <mutex>
 #include <stdexcept>
@@ -162,6 +164,105 @@ void RegisterTable(const void* host_table, std::size_t bytes, int device) {
 void InvalidateTable(const void* host_table, int device) {
   fbgemm_b200_table_unregister(GetContext(device), host_table);
 }
+
+template <typename IndexType>
+void compressed_indices_remap(
+    std::int32_t offsets_numel,
+    const IndexType* indices,
+    const std::int32_t* compressed_indices_mapping,
+    const IndexType* offsets,
+    const float* weights,
+    IndexType* out_indices,
+    IndexType* out_offsets,
+    float* out_weights) {
+  if (offsets_numel < 1) {
+    return;
+  }
+  fbgemm_b200_ctx* ctx = GetContext(-1);
+  auto check = [](cudaError_t e) {
+    if (e != cudaSuccess) {
+      throw std::runtime_error(std::string("fbgemm_b200 compressed_indices_remap: ") + cudaGetErrorString(e));
+    }
+  };
+  if (on_device(offsets)) {
+    // entries in `indices`: the last offset (one small read-back)
+    IndexType last = 0;
+    check(cudaMemcpyAsync(&last, offsets + offsets_numel - 1, sizeof(IndexType), cudaMemcpyDeviceToHost,
+                          static_cast<cudaStream_t>(t_stream)));
+    check(cudaStreamSynchronize(static_cast<cudaStream_t>(t_stream)));
+    const int rc = fbgemm_b200_compressed_indices_remap(
+        ctx, offsets_numel, indices, (std::int32_t)sizeof(IndexType), (std::int64_t)last, compressed_indices_mapping,
+        INT64_MAX, offsets, weights, out_indices, out_offsets, out_weights, t_stream);
+    if (rc < 0) {
+      throw_runtime("fbgemm_b200 compressed_indices_remap failed");
+    }
+    return;
+  }
+  // Host arrays: stage everything, remap on the device, bring the results back.
+  const std::int64_t first = (std::int64_t)offsets[0];
+  const std::int64_t n = (std::int64_t)offsets[offsets_numel - 1];
+  std::int64_t max_index = -1;
+  for (std::int64_t k = first < 0 ? 0 : first; k < n; ++k) {
+    max_index = std::max<std::int64_t>(max_index, (std::int64_t)indices[k]);
+  }
+  const std::int64_t map_size = max_index + 1;
+  const std::size_t idx_bytes = (std::size_t)(n > 0 ? n : 0) * sizeof(IndexType);
+  const std::size_t off_bytes = (std::size_t)offsets_numel * sizeof(IndexType);
+  const std::size_t w_bytes = weights ? (std::size_t)(n > 0 ? n : 0) * sizeof(float) : 0;
+  const std::size_t map_bytes = (std::size_t)map_size * sizeof(std::int32_t);
+  auto up = [](std::size_t v) { return (v + 255) & ~std::size_t(255); };
+  const std::size_t total = 2 * up(idx_bytes) + 2 * up(off_bytes) + 2 * up(w_bytes) + up(map_bytes) + 256;
+  char* d = nullptr;
+  check(cudaMalloc(&d, total));
+  char* d_idx = d;
+  char* d_off = d_idx + up(idx_bytes);
+  char* d_w = d_off + up(off_bytes);
+  char* d_map = d_w + up(w_bytes);
+  char* d_oidx = d_map + up(map_bytes);
+  char* d_ooff = d_oidx + up(idx_bytes);
+  char* d_ow = d_ooff + up(off_bytes);
+  int rc = 0;
+  try {
+    if (idx_bytes) {
+      check(cudaMemcpy(d_idx, indices, idx_bytes, cudaMemcpyHostToDevice));
+    }
+    check(cudaMemcpy(d_off, offsets, off_bytes, cudaMemcpyHostToDevice));
+    if (w_bytes) {
+      check(cudaMemcpy(d_w, weights, w_bytes, cudaMemcpyHostToDevice));
+    }
+    if (map_bytes) {
+      check(cudaMemcpy(d_map, compressed_indices_mapping, map_bytes, cudaMemcpyHostToDevice));
+    }
+    rc = fbgemm_b200_compressed_indices_remap(
+        ctx, offsets_numel, d_idx, (std::int32_t)sizeof(IndexType), n > 0 ? n : 0,
+        reinterpret_cast<const std::int32_t*>(d_map), map_size, d_off, weights ? reinterpret_cast<const float*>(d_w) : nullptr,
+        d_oidx, d_ooff, weights ? reinterpret_cast<float*>(d_ow) : nullptr, nullptr);
+    if (rc >= 0) {
+      check(cudaMemcpy(out_offsets, d_ooff, off_bytes, cudaMemcpyDeviceToHost));
+      const std::int64_t kept = (std::int64_t)out_offsets[offsets_numel - 1];
+      if (kept > 0) {
+        check(cudaMemcpy(out_indices, d_oidx, (std::size_t)kept * sizeof(IndexType), cudaMemcpyDeviceToHost));
+        if (weights) {
+          check(cudaMemcpy(out_weights, d_ow, (std::size_t)kept * sizeof(float), cudaMemcpyDeviceToHost));
+        }
+      }
+    }
+  } catch (...) {
+    cudaFree(d);
+    throw;
+  }
+  cudaFree(d);
+  if (rc < 0) {
+    throw_runtime("fbgemm_b200 compressed_indices_remap failed");
+  }
+}
+
+template FBGEMM_B200_API void compressed_indices_remap<std::int32_t>(
+    std::int32_t, const std::int32_t*, const std::int32_t*, const std::int32_t*, const float*, std::int32_t*,
+    std::int32_t*, float*);
+template FBGEMM_B200_API void compressed_indices_remap<std::int64_t>(
+    std::int32_t, const std::int64_t*, const std::int32_t*, const std::int64_t*, const float*, std::int64_t*,
+    std::int64_t*, float*);
 
 // InType of the 8-bit generator: the fused quantized row (uint8_t) or a table
 // that is not quantized (float, float16, or 16-bit storage that is_bf16_in

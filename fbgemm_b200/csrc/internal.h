@@ -231,6 +231,14 @@ struct StageSegment {
 };
 cudaError_t launch_stage_inputs(const StageSegment (&seg)[3], cudaStream_t stream);
 
+// Counters between the GPUs of a sharded lookup (peer_sync_kernels.cu): publish
+// `value` to n words (one per peer, possibly in peer memory), and wait until n
+// local words have reached `value`, giving up after timeout_us with a
+// FBGEMM_B200_STATUS_PEER_TIMEOUT record in `status`.
+cudaError_t launch_peer_signal(void* const* flags, int n, uint64_t value, cudaStream_t stream);
+cudaError_t launch_peer_wait(const void* flags, int n, uint64_t value, uint64_t timeout_us, int32_t* status,
+                             cudaStream_t stream);
+
 // Row-wise quantizers (quantize_kernels.cu).
 cudaError_t launch_quantize_8bit(const float* in, int64_t rows, int cols, uint8_t* out, cudaStream_t s);
 cudaError_t launch_quantize_nbit(int bit_rate, const float* in, int64_t rows, int cols, uint8_t* out, cudaStream_t s);

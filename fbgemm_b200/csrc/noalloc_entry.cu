@@ -84,8 +84,23 @@ extern "C" int fbgemm_b200_spmdm_lengths_noalloc(
     set_error("the no-allocation entry point is the lengths flavour: cfg->use_offsets must be 0");
     return FBGEMM_B200_EINVAL;
   }
+  // Everything is validated before the first kernel: the length scan below
+  // would otherwise read `lengths` for configurations that carry none.
+  const int cfg_rc = fbgemm_b200_spmdm_check_config(cfg);
+  if (cfg_rc) {
+    return cfg_rc;
+  }
+  if (cfg->no_bag || cfg->absolute_offsets || cfg->out_dtype == FBGEMM_B200_OUT_U8) {
+    set_error("the no-allocation entry point pools bags given by lengths: no no_bag, absolute_offsets or 8-bit output");
+    return FBGEMM_B200_EINVAL;
+  }
   if (output_size < 0 || index_size < 0 || data_size < 0) {
     set_error("negative size");
+    return FBGEMM_B200_EINVAL;
+  }
+  if (output_size > 0 && (!lengths || !out || (index_size > 0 && (!input || !indices)) ||
+                          (cfg->has_weight && index_size > 0 && !weights))) {
+    set_error("null lengths, table, indices, weights or output pointer");
     return FBGEMM_B200_EINVAL;
   }
   if (output_size > kMaxBags) {
@@ -94,8 +109,7 @@ extern "C" int fbgemm_b200_spmdm_lengths_noalloc(
     return FBGEMM_B200_EINVAL;
   }
   if (output_size == 0) {
-    const int rc = fbgemm_b200_spmdm_check_config(cfg);
-    return rc ? rc : (index_size == 0 ? 1 : 0);
+    return index_size == 0 ? 1 : 0;
   }
   if ((int64_t)scan_scratch_elems(output_size) > kMaxBags / kScanTile + 2) {
     set_error("length-scan tiling does not fit the fixed scratch");

@@ -248,6 +248,88 @@ class MultiTablePlan:
             pass
 
 
+class MultiTableHostCall:
+    """``fbgemm_b200_multi_host_*``: the tables of one operator call pooled from
+    HOST index arrays into a host output buffer, the tables resident in HBM -
+    what the reference's multi-table caller is given
+    (fbgemm_gpu/codegen/inference/embedding_forward_quantized_cpu_template.cpp:208-280
+    of FBGEMM).
+
+    ``tables`` is a list of ``(kernel, output_size, data_size, device_table,
+    out, index_capacity)``; ``out`` is the device address the table's pooled
+    rows start at, or with ``peer_ptrs`` (one list of ``num_peers`` addresses
+    per table) the rows go to the peers as in
+    ``fbgemm_b200_spmdm_launch_sharded``.  ``out_dev`` is the device tensor
+    whose bytes travel to the host buffer at the end of a step; ``sync`` an
+    optional ``_capi.PeerSync``."""
+
+    def __init__(self, tables, out_dev, device: int | None = None, slot: int = 0, peer_ptrs=None,
+                 bags_per_peer: int = 0, sync=None):
+        self.ctx = get_context(device)
+        self._keep = (list(tables), out_dev, sync)
+        n = len(tables)
+        arr = (_capi.TableCall * n)()
+        caps = (C.c_int64 * n)()
+        self._peer_arrays = []
+        num_peers = len(peer_ptrs[0]) if peer_ptrs else 0
+        self.weighted = False
+        for t, (kern, output_size, data_size, table, out, cap) in enumerate(tables):
+            c = arr[t]
+            c.cfg = kern.cfg
+            c.output_size, c.index_size, c.data_size = output_size, 0, data_size
+            c.input = _ptr(table)
+            c.out = out if isinstance(out, int) or out is None else _ptr(out)
+            caps[t] = cap
+            self.weighted = self.weighted or bool(kern.cfg.has_weight)
+            if peer_ptrs:
+                pa = (C.c_void_p * num_peers)(*peer_ptrs[t])
+                self._peer_arrays.append(pa)
+                c.peer_out = pa
+        self.n = n
+        self.out_bytes = out_dev.numel() * out_dev.element_size()
+        handle = C.c_void_p()
+        rc = _capi.lib().fbgemm_b200_multi_host_create(
+            self.ctx.handle, arr, n, caps, num_peers, bags_per_peer, out_dev.data_ptr(), self.out_bytes,
+            C.byref(sync) if sync is not None else None, slot, C.byref(handle))
+        _capi.check(rc, "fbgemm_b200_multi_host_create")
+        self._handle = handle
+        self._idx = (C.c_void_p * n)()
+        self._off = (C.c_void_p * n)()
+        self._w = (C.c_void_p * n)()
+        self._sizes = (C.c_int64 * n)()
+
+    def submit(self, indices, offsets, weights, out_host) -> None:
+        """``indices[t]``, ``offsets[t]``, ``weights[t]`` (or None) are host
+        arrays (numpy; pinned memory keeps the copies asynchronous);
+        ``out_host`` receives ``out_dev``'s bytes."""
+        for t in range(self.n):
+            self._idx[t] = indices[t].ctypes.data
+            self._off[t] = offsets[t].ctypes.data
+            self._w[t] = weights[t].ctypes.data if (weights is not None and weights[t] is not None) else None
+            self._sizes[t] = indices[t].shape[0]
+        rc = _capi.lib().fbgemm_b200_multi_host_submit(self._handle, self._idx, self._off,
+                                                       self._w if self.weighted else None, self._sizes,
+                                                       out_host.ctypes.data)
+        _capi.check(rc, "fbgemm_b200_multi_host_submit")
+
+    def wait(self):
+        """(ok, info[4]) once the rows are in the host buffer."""
+        info = (C.c_int32 * 4)()
+        rc = _capi.check(_capi.lib().fbgemm_b200_multi_host_wait(self._handle, info), "fbgemm_b200_multi_host_wait")
+        return bool(rc), list(info)
+
+    def close(self) -> None:
+        if self._handle:
+            _capi.lib().fbgemm_b200_multi_host_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 def status_read(slot: int = 0, device: int | None = None, stream=None):
     """(ok, info[4]) of status slot ``slot`` after waiting for ``stream``."""
     import torch

@@ -17,7 +17,12 @@ Two ways to get them there:
   (``fbgemm_b200_spmdm_launch_sharded``): lookup and all-to-all are one kernel,
   no staging buffer, no collective call.  The output buffers are symmetric
   memory (``torch.distributed._symmetric_memory``), which hands every rank the
-  peers' buffer addresses.  Plain peer stores only - no multicast.
+  peers' buffer addresses.  Plain peer stores only - no multicast.  When a
+  buffer may be read, and when it may be overwritten, is settled on the device
+  by counters in the same symmetric memory (``fbgemm_b200_peer_signal`` /
+  ``fbgemm_b200_peer_wait``): ``step`` below = wait for the peers' acks of the
+  buffer's previous use, look up, publish "ready", wait for the peers' "ready";
+  ``release`` publishes the ack once the consumer is done with the rows.
 * ``mode="nccl"`` (the baseline): pool into a local ``[B, sum D_local]``
   buffer, then ``all_to_all_single`` over NCCL and a local copy into the
   column blocks.
@@ -166,6 +171,17 @@ class ShardedLookup:
             else:
                 self.out = torch.zeros((num_buffers, self.rows, plan.total_dim), dtype=out_dtype, device=device)
                 base = [self.out.data_ptr()]
+            # Counters [ready|ack][buffer][writer rank], 8 bytes each, zero to start with.
+            if self.world > 1:
+                self._flags = symm.empty((2, num_buffers, self.world), dtype=torch.int64, device=device)
+                self._flags.zero_()
+                self._flag_base = [int(p) for p in symm.rendezvous(self._flags, self.group).buffer_ptrs]
+                torch.cuda.synchronize(device)
+                dist.barrier(group=self.group)   # nobody signals before everybody's counters are zero
+            else:
+                self._flags = torch.zeros((2, num_buffers, 1), dtype=torch.int64, device=device)
+                self._flag_base = [self._flags.data_ptr()]
+            self.steps = [0] * num_buffers       # steps begun per buffer
             buf_bytes = self.rows * plan.total_dim * esize
             # peer pointer arrays per (buffer, table): column offset folded in
             self._peer_ptrs = {}
@@ -235,8 +251,90 @@ class ShardedLookup:
         if self.world == 1:
             self.out[buffer].copy_(self.local_out[buffer][:, :self.plan.total_dim])
         else:
-            self.out[buffer].copy_(exchange_pooled(self.local_out[buffer], self.plan, self.rank, self.group))
+            # a rank that owns no table sends nothing (its local buffer has one spare column)
+            mine = self.local_out[buffer][:, :self.plan.local_dim(self.rank)].contiguous()
+            self.out[buffer].copy_(exchange_pooled(mine, self.plan, self.rank, self.group))
         return self.out[buffer]
+
+    # ---- device-side ordering of the peer stores (p2p mode) ------------------------
+
+    READY, ACK = 0, 1
+
+    def _flag_addr(self, kind: int, buffer: int, writer: int, on_rank: int) -> int:
+        return self._flag_base[on_rank] + ((kind * self.num_buffers + buffer) * self.world + writer) * 8
+
+    def signal(self, kind: int, buffer: int, value: int, stream=None) -> None:
+        """After everything already on ``stream``: write ``value`` to this rank's
+        word of counter ``kind`` of ``buffer`` on every rank."""
+        if stream is None:
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+        arr = (C.c_void_p * self.world)(*[self._flag_addr(kind, buffer, self.rank, g) for g in range(self.world)])
+        _capi.check(_capi.lib().fbgemm_b200_peer_signal(self.ctx.handle, arr, self.world, value, stream), "peer_signal")
+
+    def wait(self, kind: int, buffer: int, value: int, slot: int = 0, stream=None, timeout_us: int = 2_000_000) -> None:
+        """Hold ``stream`` until every rank's word of counter ``kind`` of
+        ``buffer`` on this rank has reached ``value`` (or record a timeout in
+        status slot ``slot``)."""
+        if stream is None:
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+        _capi.check(_capi.lib().fbgemm_b200_peer_wait(self.ctx.handle, self._flag_addr(kind, buffer, 0, self.rank),
+                                                      self.world, value, timeout_us, slot, stream), "peer_wait")
+
+    def step(self, batches: dict, buffer: int = 0, slot_base: int = 0, streams=None, plan=None,
+             timeout_us: int = 2_000_000) -> int:
+        """One whole step on the current stream, ordered on the device: wait
+        until every peer has released ``buffer``'s previous rows, pool and store
+        this rank's tables (``plan``: a multi-table plan made by ``make_plan``
+        for this buffer, else one launch per table over ``streams``), publish
+        "ready", wait for every peer's "ready".  When the stream gets past the
+        last wait, this rank's ``out[buffer]`` holds every table's rows for its
+        slice of the batch.  Returns the step number to pass to ``release``."""
+        assert self.mode == "p2p"
+        self.steps[buffer] += 1
+        n = self.steps[buffer]
+        cur = torch.cuda.current_stream(self.device)
+        self.wait(self.ACK, buffer, n - 1, slot_base, cur.cuda_stream, timeout_us)
+        if plan is not None:
+            plan.launch(cur.cuda_stream)
+        elif streams:
+            for s in streams:
+                s.wait_stream(cur)
+            self.launch(batches, buffer, slot_base, streams=[s.cuda_stream for s in streams])
+            for s in streams:
+                cur.wait_stream(s)
+        else:
+            self.launch(batches, buffer, slot_base, stream=cur.cuda_stream)
+        self.signal(self.READY, buffer, n, cur.cuda_stream)
+        self.wait(self.READY, buffer, n, slot_base, cur.cuda_stream, timeout_us)
+        return n
+
+    def release(self, buffer: int, n: int) -> None:
+        """The consumer of ``out[buffer]`` is done with step ``n`` (everything
+        enqueued so far on the current stream): let the peers overwrite it."""
+        self.signal(self.ACK, buffer, n)
+
+    def make_host_call(self, buffer: int, capacities: dict, slot: int = 0, timeout_us: int = 2_000_000):
+        """``fbgemm_b200_multi_host_*`` for this rank's tables and ``buffer``:
+        host index arrays in, this rank's ``[B/G, total_dim]`` slice out, with
+        the counters of ``buffer`` ordering the peers.  ``capacities[t]`` bounds
+        the indices a step may bring for table t.  The handle counts its own
+        steps: do not mix it with ``step`` on the same buffer."""
+        from .embedding import MultiTableHostCall
+
+        assert self.mode == "p2p"
+        tables, peers = [], []
+        for t in self.local:
+            tables.append((self.kernels[t], self.B, self.specs[t].rows, self.tables[t], None, int(capacities[t])))
+            peers.append([int(p) for p in self._peer_ptrs[(buffer, t)]])
+        G = self.world
+        ready = (C.c_void_p * G)(*[self._flag_addr(self.READY, buffer, self.rank, g) for g in range(G)])
+        ack = (C.c_void_p * G)(*[self._flag_addr(self.ACK, buffer, self.rank, g) for g in range(G)])
+        sync = _capi.PeerSync(G, ready, self._flag_addr(self.READY, buffer, 0, self.rank), ack,
+                              self._flag_addr(self.ACK, buffer, 0, self.rank), timeout_us)
+        call = MultiTableHostCall(tables, self.out[buffer], self.device.index, slot, peer_ptrs=peers,
+                                  bags_per_peer=self.rows, sync=sync)
+        call._sync_arrays = (ready, ack)
+        return call
 
     def barrier(self) -> None:
         """All ranks' kernels (and therefore their peer stores) are complete."""

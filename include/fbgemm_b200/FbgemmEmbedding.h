@@ -189,6 +189,25 @@ GenerateEmbeddingSpMDMNBitRowWiseSparse(
     bool is_weight_positional = false,
     bool use_offsets = true);
 
+/* include/fbgemm/FbgemmEmbedding.h:392-401 (src/EmbeddingSpMDM.cc:1714-1770,
+ * scalar form src/RefImplementations.cc:2308-2333): rewrite (indices, offsets,
+ * weights) so that rows the map prunes (-1) disappear and the rest address
+ * the compressed table.  The arrays are all host pointers or all device
+ * pointers.  With host pointers the map is read up to the largest index that
+ * occurs; with device pointers the entries of the map are trusted to cover
+ * every index, as in the reference (the C ABI form takes the map's size and
+ * checks).  Throws std::runtime_error on a CUDA failure. */
+template <typename IndexType>
+FBGEMM_B200_API void compressed_indices_remap(
+    std::int32_t offsets_numel,
+    const IndexType* indices,
+    const std::int32_t* compressed_indices_mapping,
+    const IndexType* offsets,
+    const float* weights,  // optional, can be null
+    IndexType* out_indices,
+    IndexType* out_offsets,
+    float* out_weights);
+
 /* ---- not in the reference: what a GPU back end additionally needs -------- */
 
 /* Stream (cudaStream_t as void*) that functors called from this thread with

@@ -69,11 +69,15 @@ extern "C" {
 #define FBGEMM_B200_STATUS_BAG_OVERRUN 2 /* current + len > index_size       */
 #define FBGEMM_B200_STATUS_SIZE_MISMATCH 3 /* sum of lengths != index_size   */
 #define FBGEMM_B200_STATUS_TABLE_FULL 4 /* hash-map insert found no free slot */
+#define FBGEMM_B200_STATUS_PEER_TIMEOUT 5 /* a peer's counter did not arrive in time */
 
 /* Number of status slots a context owns (see fbgemm_b200_spmdm_launch). */
 #define FBGEMM_B200_STATUS_SLOTS 1024
 /* Number of staging lanes of the host-pointer pipeline. */
 #define FBGEMM_B200_HOST_LANES 8
+/* Status slots a caller may pass: 0 .. FBGEMM_B200_USER_SLOTS - 1.  The rest
+ * are the library's (one for the index remap, one per host-pointer lane). */
+#define FBGEMM_B200_USER_SLOTS (FBGEMM_B200_STATUS_SLOTS - FBGEMM_B200_HOST_LANES - 1)
 
 typedef struct fbgemm_b200_ctx fbgemm_b200_ctx;
 
@@ -164,11 +168,15 @@ FBGEMM_B200_API int fbgemm_b200_spmdm_check_config(const fbgemm_b200_spmdm_confi
  *
  * All pointers are device pointers valid on the context's device.  The call
  * enqueues work on `stream` and returns without synchronising; it allocates
- * nothing except, in lengths mode, a one-off growth of the context's scratch.
+ * nothing except, in lengths mode (cfg->use_offsets = 0), the scratch for the
+ * scanned offsets: one grow-only buffer per stream the context has seen, so
+ * lengths-mode calls on different streams may overlap; growing a buffer frees
+ * and allocates device memory, which waits for the device - warm up with the
+ * largest batch, or use offsets, where that matters.
  * Errors found by the kernel are recorded first-writer-wins in status slot
- * `slot` (0 <= slot < FBGEMM_B200_STATUS_SLOTS); read it with
- * fbgemm_b200_status_read once the stream has caught up.  Calls that overlap
- * on the GPU should use distinct slots.
+ * `slot` (0 <= slot < FBGEMM_B200_USER_SLOTS; the slots above belong to the
+ * library); read it with fbgemm_b200_status_read once the stream has caught
+ * up.  Calls that overlap on the GPU should use distinct slots.
  *
  * Returns 0 when enqueued, or a negative error code.
  */
@@ -585,25 +593,113 @@ FBGEMM_B200_API int fbgemm_b200_spmdm_host(
     void* out,
     const int32_t* compressed_indices_table);
 
-/* ---- measuring stick ---------------------------------------------------- */
+/* ---- ordering between the GPUs of a sharded lookup ---------------------- */
 
-/* Reads n random rows (row_bytes of each, int32 row numbers in `indices`,
- * rows `stride` bytes apart) with the lookup's lane layout and memory-level
- * parallelism but no arithmetic: the time it takes is the practical floor for
- * any gather of such rows on this GPU, which for small unaligned rows is far
- * from what a streaming copy reaches (DRAM serves 32-byte sectors of 64-byte
- * atoms).  Benchmarks report the lookup against it.  rows_per_group mimics the
- * bag length; `sink` is 4 bytes of device memory.  No counterpart in the
- * reference.  Enqueues one kernel; returns 0 or a negative code. */
-FBGEMM_B200_API int fbgemm_b200_probe_row_gather(
-    const void* table,
-    int64_t stride,
-    int32_t row_bytes,
-    const int32_t* indices,
-    int64_t n,
-    int32_t rows_per_group,
-    void* sink,
+/*
+ * fbgemm_b200_spmdm_launch_sharded stores pooled rows into peer GPUs' memory;
+ * these two calls tell a GPU, on the device and per step, when it may read or
+ * overwrite such a buffer.  A counter is an 8-byte word in some GPU's memory
+ * (peer-mapped where another GPU writes it), starting at 0 and only growing.
+ * The reference orders its peer copies with events between the streams of one
+ * process (fbgemm_gpu/src/merge_pooled_embedding_ops/merge_pooled_embedding_ops_gpu.cpp:223-230,454-461);
+ * with one process per GPU these counters take that role.
+ *
+ * fbgemm_b200_peer_signal enqueues, after everything already on `stream`, one
+ * small kernel that writes `value` to the num_flags words flags[i] (release
+ * stores at system scope: the stores of earlier kernels on the stream are
+ * visible to whoever then reads the value).
+ * fbgemm_b200_peer_wait enqueues one small kernel that returns when each of
+ * the num_flags consecutive words at `flags` (this GPU's memory) has reached
+ * `value`, or after timeout_us (1 us .. 60 s); in that case it records
+ * {FBGEMM_B200_STATUS_PEER_TIMEOUT, word that lagged, its value, `value`} in
+ * status slot `slot`, later work on the stream still runs and the context stays
+ * usable - read the slot before trusting the buffer.  Plain loads and stores,
+ * no multicast.  Both return 0 when enqueued or a negative code.
+ */
+FBGEMM_B200_API int fbgemm_b200_peer_signal(
+    fbgemm_b200_ctx* ctx,
+    void* const* flags,
+    int num_flags,
+    uint64_t value,
     void* stream);
+FBGEMM_B200_API int fbgemm_b200_peer_wait(
+    fbgemm_b200_ctx* ctx,
+    const void* flags,
+    int num_flags,
+    uint64_t value,
+    uint64_t timeout_us,
+    int slot,
+    void* stream);
+
+/* The counters of one rank of a table-wise sharded job, as
+ * fbgemm_b200_multi_host_create takes them.  "ready": rank r writes
+ * ready_flags[g] (a word in GPU g's memory, slot r of g's ready_local array)
+ * once its rows for g's slice are stored; "ack": rank g writes ack_flags[r]
+ * (slot g of r's ack_local array) once it has consumed its slice. */
+typedef struct fbgemm_b200_peer_sync {
+  int32_t num_peers;        /* G, the same as the lookups' num_peers */
+  void* const* ready_flags; /* [G] words this rank writes, one per peer */
+  const void* ready_local;  /* G consecutive words in this GPU's memory */
+  void* const* ack_flags;   /* [G] words this rank writes, one per peer */
+  const void* ack_local;    /* G consecutive words in this GPU's memory */
+  uint64_t timeout_us;      /* per wait; 0 = 2 s */
+} fbgemm_b200_peer_sync;
+
+/* ---- several tables per call, host pointers ------------------------------ */
+
+/*
+ * The reference's multi-table caller on host tensors
+ * (fbgemm_gpu/codegen/inference/embedding_forward_quantized_cpu_template.cpp:208-280,343-473:
+ * host indices/offsets/weights of T tables in, output[B, total_D] out) with the
+ * tables resident in HBM.  A handle is built once per set of tables and output
+ * buffer; each step
+ *   1. copies every table's indices, offsets and weights from the caller's
+ *      host arrays into the handle's device staging block,
+ *   2. runs one lookup per table (offsets flavour), the pooled rows going to
+ *      calls[t].out - or, with num_peers > 0, to calls[t].peer_out as in
+ *      fbgemm_b200_spmdm_launch_sharded,
+ *   3. with `sync`: publishes this rank's "ready" counters and waits for the
+ *      peers' (fbgemm_b200_peer_signal / _wait),
+ *   4. copies out_bytes from out_dev (the device buffer the rows of THIS rank's
+ *      bags land in) to the caller's host buffer,
+ *   5. with `sync`: publishes the "ack" counters; the next step on this handle
+ *      first waits for all peers' acks, so no buffer is overwritten while a
+ *      peer still reads it.
+ * calls[t]: cfg, output_size, data_size, input (DEVICE pointer of the resident
+ * table, e.g. fbgemm_b200_table_device_ptr), compressed_indices_table (device),
+ * out / peer_out; its indices/offsets/weights/index_size fields are ignored.
+ * index_capacity[t] bounds the indices a step may bring for table t.  Every
+ * rank of a sharded job must submit the same number of steps on corresponding
+ * handles.  submit enqueues on the handle's own stream and returns; wait
+ * blocks until the rows are in the host buffer and returns 1 (every table's
+ * functor result true), 0 (a lookup or a counter wait failed: info[4] as in
+ * fbgemm_b200_status_read) or a negative code.  Pinned host arrays keep the
+ * copies asynchronous.  create allocates (staging, streams); submit and wait
+ * allocate nothing.
+ */
+typedef struct fbgemm_b200_multi_host fbgemm_b200_multi_host;
+
+FBGEMM_B200_API int fbgemm_b200_multi_host_create(
+    fbgemm_b200_ctx* ctx,
+    const fbgemm_b200_table_call* calls,
+    int32_t num_tables,
+    const int64_t* index_capacity,
+    int32_t num_peers,
+    int64_t bags_per_peer,
+    void* out_dev,
+    size_t out_bytes,
+    const fbgemm_b200_peer_sync* sync, /* NULL: no peers to wait for */
+    int slot,
+    fbgemm_b200_multi_host** handle);
+FBGEMM_B200_API int fbgemm_b200_multi_host_submit(
+    fbgemm_b200_multi_host* handle,
+    const void* const* indices,   /* [T] host arrays */
+    const void* const* offsets,   /* [T] host arrays of output_size + 1 */
+    const float* const* weights,  /* [T] host arrays, or NULL when no table is weighted */
+    const int64_t* index_sizes,   /* [T] */
+    void* out_host);
+FBGEMM_B200_API int fbgemm_b200_multi_host_wait(fbgemm_b200_multi_host* handle, int32_t* info);
+FBGEMM_B200_API void fbgemm_b200_multi_host_destroy(fbgemm_b200_multi_host* handle);
 
 /* ---- row-wise quantizers, device pointers ------------------------------ */
 

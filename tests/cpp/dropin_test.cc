@@ -28,6 +28,8 @@ int oracle_embedding_spmdm_ex(int, int64_t, int64_t, int64_t, int64_t, const uin
                               const float*, int, void*, int, int, int, int64_t, int64_t, int, int);
 int oracle_embedding_spmdm_plain(int, int64_t, int64_t, int64_t, int64_t, const void*, const void*, int, const void*, int,
                                  const float*, int, void*, int, int, int, int64_t, int64_t, int, int, int, int);
+void oracle_compressed_indices_remap(int32_t, const void*, int, const int32_t*, const void*, const float*, void*, void*,
+                                     float*);
 }
 
 static int failures = 0;
@@ -258,6 +260,44 @@ int main() {
     cudaMemcpy(out.data(), d_out, out.size() * 4, cudaMemcpyDeviceToHost);
     CHECK(ok);
     CHECK(std::memcmp(out.data(), ref.data(), out.size() * 4) == 0);
+  }
+  // --- fbgemm::compressed_indices_remap<IndexType>: host vectors, then device pointers
+  {
+    const int batch = 23, rows = 700;
+    std::vector<int32_t> mapping(rows);
+    int dense = 0;
+    for (auto& m : mapping) m = (g() % 2 == 0) ? -1 : dense++;
+    Inputs in = make(g, 4, batch, rows, 32, 9, 0);
+    std::vector<int64_t> ri(in.n), ro(batch + 1), oi(in.n), oo(batch + 1);
+    std::vector<float> rw(in.n), ow(in.n);
+    oracle_compressed_indices_remap(batch + 1, in.idx64.data(), 8, mapping.data(), in.off64.data(), in.weights.data(),
+                                    ri.data(), ro.data(), rw.data());
+    fbgemm::compressed_indices_remap<int64_t>(batch + 1, in.idx64.data(), mapping.data(), in.off64.data(),
+                                              in.weights.data(), oi.data(), oo.data(), ow.data());
+    const int64_t kept = ro[batch];
+    CHECK(oo == ro);
+    CHECK(std::memcmp(oi.data(), ri.data(), (size_t)kept * 8) == 0);
+    CHECK(std::memcmp(ow.data(), rw.data(), (size_t)kept * 4) == 0);
+    // int32, no weights, device pointers
+    std::vector<int32_t> ri32(in.n), ro32(batch + 1), oi32(in.n), oo32(batch + 1);
+    std::vector<int32_t> off32(in.off64.begin(), in.off64.end());
+    oracle_compressed_indices_remap(batch + 1, in.idx32.data(), 4, mapping.data(), off32.data(), nullptr, ri32.data(),
+                                    ro32.data(), nullptr);
+    void *d_idx, *d_off, *d_map, *d_oi, *d_oo;
+    cudaMalloc(&d_idx, in.n * 4);
+    cudaMalloc(&d_off, (batch + 1) * 4);
+    cudaMalloc(&d_map, rows * 4);
+    cudaMalloc(&d_oi, in.n * 4);
+    cudaMalloc(&d_oo, (batch + 1) * 4);
+    cudaMemcpy(d_idx, in.idx32.data(), in.n * 4, cudaMemcpyHostToDevice);
+    cudaMemcpy(d_off, off32.data(), (batch + 1) * 4, cudaMemcpyHostToDevice);
+    cudaMemcpy(d_map, mapping.data(), rows * 4, cudaMemcpyHostToDevice);
+    fbgemm::compressed_indices_remap<int32_t>(batch + 1, (const int32_t*)d_idx, (const int32_t*)d_map,
+                                              (const int32_t*)d_off, nullptr, (int32_t*)d_oi, (int32_t*)d_oo, nullptr);
+    cudaMemcpy(oi32.data(), d_oi, in.n * 4, cudaMemcpyDeviceToHost);
+    cudaMemcpy(oo32.data(), d_oo, (batch + 1) * 4, cudaMemcpyDeviceToHost);
+    CHECK(oo32 == ro32);
+    CHECK(std::memcmp(oi32.data(), ri32.data(), (size_t)ro32[batch] * 4) == 0);
   }
   // --- what the sm_100a path does not provide is refused when the kernel is generated
   bool threw = false;

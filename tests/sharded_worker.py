@@ -69,6 +69,69 @@ def main():
     for mode, got in results.items():
         assert (got.view(np.uint16) == want.view(np.uint16)).all(), f"rank {rank} mode {mode} differs from the oracle"
     dist.barrier()
+
+    # Steps ordered on the device only: no host barrier between them, two
+    # buffers, new indices every step.  Each rank checks its own slice - rows
+    # that peers stored - as soon as its stream is past the "ready" wait.
+    def step_inputs(step):
+        host = {}
+        for t, s in enumerate(specs):
+            g = torch.Generator().manual_seed(5000 + 100 * step + t)
+            lengths = torch.randint(0, 17, (B,), generator=g)
+            off = torch.zeros(B + 1, dtype=torch.int32)
+            off[1:] = torch.cumsum(lengths, 0).to(torch.int32)
+            idx = torch.randint(0, s.rows, (int(off[-1]),), generator=g, dtype=torch.int32)
+            host[t] = (idx.numpy(), off.numpy())
+        return host
+
+    def expected(host):
+        w = np.zeros((rows, plan.total_dim), dtype=np.float16)
+        lo, hi = rank * rows, (rank + 1) * rows
+        for t, s in enumerate(specs):
+            idx, off = host[t]
+            ok, ref = oracle.spmdm(s.bit_rate, s.dim, s.rows, merged[t], idx[off[lo]:off[hi]], off[lo:hi + 1], None,
+                                   False, np.float16)
+            assert ok
+            c0 = plan.column_start(t)
+            w[:, c0:c0 + s.dim] = ref.reshape(rows, s.dim)
+        return w
+
+    sl = ShardedLookup(specs, plan, rank, B, dev, torch.float16, mode="p2p", num_buffers=2,
+                       tables={t: torch.from_numpy(merged[t]).to(dev) for t in plan.tables_of(rank)})
+    streams = [torch.cuda.Stream() for _ in range(2)]
+    for step in range(6):
+        host = step_inputs(step)
+        b = {t: Batch(torch.from_numpy(host[t][0]).to(dev), torch.from_numpy(host[t][1]).to(dev), None, B,
+                      len(host[t][0]), len(host[t][0])) for t in sl.local}
+        buf = step % 2
+        n = sl.step(b, buffer=buf, slot_base=100, streams=streams)
+        got = sl.out[buf].cpu().numpy()
+        sl.release(buf, n)
+        for i in range(len(sl.local)):
+            ok, info = E.status_read(100 + i, dev.index)
+            assert ok, (step, info)
+        assert (got.view(np.uint16) == expected(host).view(np.uint16)).all(), f"rank {rank} ordered step {step} differs"
+    dist.barrier()
+
+    # Host arrays in, this rank's slice out, through fbgemm_b200_multi_host_* with the counters.
+    sl = ShardedLookup(specs, plan, rank, B, dev, torch.float16, mode="p2p", num_buffers=2, tables=sl.tables)
+    calls = [sl.make_host_call(bf, {t: 20 * B for t in sl.local}, slot=200 + bf) for bf in range(2)]
+    outs = [torch.zeros((rows, plan.total_dim), dtype=torch.float16).pin_memory().numpy() for _ in range(2)]
+    hosts = {}
+    for step in range(6):
+        bf = step % 2
+        if step >= 2:
+            ok, info = calls[bf].wait()
+            assert ok, (step, info)
+            assert (outs[bf].view(np.uint16) == expected(hosts[step - 2]).view(np.uint16)).all(), \
+                f"rank {rank} host step {step - 2} differs"
+        hosts[step] = step_inputs(100 + step)
+        calls[bf].submit([hosts[step][t][0] for t in sl.local], [hosts[step][t][1] for t in sl.local], None, outs[bf])
+    for step in (4, 5):
+        ok, info = calls[step % 2].wait()
+        assert ok, (step, info)
+        assert (outs[step % 2].view(np.uint16) == expected(hosts[step]).view(np.uint16)).all()
+    dist.barrier()
     if rank == 0:
         print(f"SHARDED_OK world={world} tables={len(specs)} total_dim={plan.total_dim}")
     dist.destroy_process_group()

@@ -7,6 +7,7 @@ coin-flipped options (index/offset width, normalize, offsets-vs-lengths)
 enumerated from a seed instead.  The bar is the reference's: EXPECT_EQ on every
 element, i.e. bit-exact fp32 and fp16.
 """
+import ctypes as C
 import itertools
 import os
 
@@ -15,6 +16,7 @@ import pytest
 import torch
 
 import fbgemm_b200 as F
+from fbgemm_b200 import _capi
 from helpers import REFERENCE_SHAPES, lengths_indices_weights, mapping_table, random_fused_table, row_bytes
 from conftest import bits
 
@@ -316,3 +318,87 @@ def test_async_launch_and_status_slots(gpu_ctx, oracle):
     assert ok6_again  # reading clears the slot
     _, ref = oracle.spmdm(8, dim, rows, table, indices, offsets, None, False, np.float32)
     np.testing.assert_array_equal(bits(out1.cpu().numpy()), bits(ref))
+
+
+def test_resident_copy_is_checked_against_the_callers_table(gpu_ctx, oracle):
+    """A resident copy is keyed by the host address alone, and an address can
+    come back with another table behind it.  A call that needs more bytes than
+    the registered copy holds, or whose host table no longer has the registered
+    contents, is refused before any kernel runs (explicit registration) or gets
+    a fresh copy (a copy the library made on its own)."""
+    rng = np.random.default_rng(9300)
+    rows, dim, batch = 400, 64, 20
+    big = random_fused_table(rng, 2 * rows, dim, 4)
+    lengths, offsets, indices, weights, n = lengths_indices_weights(rng, batch, rows, 8, np.int32, np.int32)
+    kern = make_kernel(4, dim, False, False, False, True, np.int32, np.int32, np.float32)
+    out = np.zeros(batch * dim, dtype=np.float32)
+    # explicit registration of the first half only, then a call that addresses the whole array
+    gpu_ctx.register_table(big[:rows])
+    assert kern(batch, n, rows, big, indices, offsets, None, out)
+    before = F.launch_count()
+    with pytest.raises(_capi.Fbgemmb200Error, match="register it again"):
+        kern(batch, n, 2 * rows, big, indices, offsets, None, out)
+    # same size, other contents behind the same address: refused as well
+    big[:rows] = random_fused_table(rng, rows, dim, 4)
+    with pytest.raises(_capi.Fbgemmb200Error, match="register it again"):
+        kern(batch, n, rows, big, indices, offsets, None, out)
+    assert F.launch_count() == before          # nothing ran
+    gpu_ctx.register_table(big[:rows])         # registering again is the cure
+    assert kern(batch, n, rows, big, indices, offsets, None, out)
+    _, ref = oracle.spmdm(4, dim, rows, big, indices, offsets, None, False, np.float32)
+    np.testing.assert_array_equal(bits(out), bits(ref))
+    gpu_ctx.unregister_table(big)
+    # a copy made by the call itself follows the caller's memory
+    table = random_fused_table(rng, rows, dim, 4)
+    assert kern(batch, n, rows, table, indices, offsets, None, out)
+    table[:] = random_fused_table(rng, rows, dim, 4)
+    assert kern(batch, n, rows, table, indices, offsets, None, out)
+    _, ref = oracle.spmdm(4, dim, rows, table, indices, offsets, None, False, np.float32)
+    np.testing.assert_array_equal(bits(out), bits(ref))
+    gpu_ctx.unregister_table(table)
+
+
+def test_lengths_mode_on_two_streams_does_not_share_scratch(gpu_ctx, oracle):
+    """Lengths-mode launches on different streams overlap: each stream has its
+    own scanned offsets."""
+    rng = np.random.default_rng(9400)
+    rows, dim = 3000, 64
+    table = random_fused_table(rng, rows, dim, 4)
+    d_table = dev(table)
+    kern = make_kernel(4, dim, False, False, False, False, np.int32, np.int32, np.float32)
+    streams = [torch.cuda.Stream() for _ in range(3)]
+    jobs = []
+    for rep in range(4):
+        for i, s in enumerate(streams):
+            batch = 2000 + 700 * i
+            lengths, offsets, indices, weights, n = lengths_indices_weights(rng, batch, rows, 6 + 3 * i, np.int32, np.int32)
+            d_len, d_idx = dev(lengths), dev(indices)
+            out = torch.zeros(batch * dim, device="cuda")
+            torch.cuda.synchronize()
+            jobs.append((lengths, indices, n, batch, d_len, d_idx, out, 70 + i, s))
+    for lengths, indices, n, batch, d_len, d_idx, out, slot, s in jobs:
+        kern.launch(batch, n, rows, d_table, d_idx, d_len, None, out, slot=slot, stream=s.cuda_stream)
+    torch.cuda.synchronize()
+    for i in range(3):
+        assert F.status_read(70 + i)[0]
+    for lengths, indices, n, batch, d_len, d_idx, out, slot, s in jobs:
+        _, ref = oracle.spmdm(4, dim, rows, table, indices, lengths, None, False, np.float32, False, False)
+        np.testing.assert_array_equal(bits(out.cpu().numpy()), bits(ref))
+
+
+def test_null_pointers_and_reserved_slots_are_refused_on_the_host(gpu_ctx):
+    lib = _capi.lib()
+    kern = make_kernel(4, 64, False, False, False, True, np.int32, np.int32, np.float32)
+    t = torch.zeros(64 * 36, dtype=torch.uint8, device="cuda")
+    idx = torch.zeros(8, dtype=torch.int32, device="cuda")
+    off = torch.arange(0, 9, dtype=torch.int32, device="cuda")
+    out = torch.zeros(8 * 64, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    args = lambda **kw: [gpu_ctx.handle, C.byref(kern.cfg), 8, 8, 64, kw.get("t", t.data_ptr()), kw.get("i", idx.data_ptr()),  # noqa: E731
+                         kw.get("o", off.data_ptr()), None, kw.get("out", out.data_ptr()), None, kw.get("slot", 3), st]
+    before = F.launch_count()
+    for bad in (dict(t=None), dict(i=None), dict(o=None), dict(out=None), dict(slot=_capi.USER_SLOTS),
+                dict(slot=_capi.STATUS_SLOTS - 1)):
+        assert lib.fbgemm_b200_spmdm_launch(*args(**bad)) == _capi.EINVAL, bad
+    assert F.launch_count() == before
+    assert lib.fbgemm_b200_spmdm_launch(*args()) == 0 and F.status_read(3)[0]

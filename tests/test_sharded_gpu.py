@@ -61,3 +61,112 @@ def test_two_gpu_sharded_lookup_matches_oracle():
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert "SHARDED_OK" in res.stdout
+
+
+def test_peer_counters_signal_wait_and_time_out(gpu_ctx):
+    """A wait whose counters were published passes; a wait on a counter that
+    nobody writes gives up after its time limit with a status record naming
+    the laggard - no hang, no trap - and the context keeps working."""
+    import time
+
+    lib = _capi.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    flags = torch.zeros(4, dtype=torch.int64, device="cuda")
+    arr = (C.c_void_p * 3)(*[flags.data_ptr() + 8 * i for i in range(3)])
+    assert lib.fbgemm_b200_peer_signal(gpu_ctx.handle, arr, 3, 5, stream) == 0
+    assert lib.fbgemm_b200_peer_wait(gpu_ctx.handle, flags.data_ptr(), 3, 5, 1000, 40, stream) == 0
+    ok, info = F.status_read(40)
+    assert ok and flags.cpu().tolist() == [5, 5, 5, 0]
+    # word 3 stays at 0: the wait for 1 runs out (50 ms limit)
+    t0 = time.perf_counter()
+    assert lib.fbgemm_b200_peer_wait(gpu_ctx.handle, flags.data_ptr(), 4, 1, 50_000, 40, stream) == 0
+    ok, info = F.status_read(40)
+    dt = time.perf_counter() - t0
+    assert not ok and info == [_capi.STATUS_PEER_TIMEOUT, 3, 0, 1]
+    assert 0.04 < dt < 5.0
+    # the slot was cleared by the read and the context is usable
+    assert lib.fbgemm_b200_peer_wait(gpu_ctx.handle, flags.data_ptr(), 3, 5, 1000, 40, stream) == 0
+    assert F.status_read(40)[0]
+    # argument checks happen on the host
+    assert lib.fbgemm_b200_peer_wait(gpu_ctx.handle, flags.data_ptr(), 3, 5, 0, 40, stream) < 0
+    assert lib.fbgemm_b200_peer_wait(gpu_ctx.handle, flags.data_ptr() + 4, 3, 5, 10, 40, stream) < 0
+    assert lib.fbgemm_b200_peer_signal(gpu_ctx.handle, arr, 9, 5, stream) < 0
+
+
+def _specs_and_batches(B, seed=0, tables=5):
+    from fbgemm_b200.workloads import TableSpec
+
+    specs = [TableSpec(900 + 150 * t, (64, 128, 32)[t % 3], (8, 4, 2)[t % 3], 300 + t) for t in range(tables)]
+    rng = np.random.default_rng(seed)
+    host = {}
+    for t, s in enumerate(specs):
+        lengths = rng.integers(0, 15, B)
+        off = np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)
+        host[t] = (rng.integers(0, s.rows, int(off[-1])).astype(np.int32), off)
+    return specs, host
+
+
+def _oracle_rows(oracle, specs, plan, tables, host, rows_lo, rows_hi):
+    want = np.zeros((rows_hi - rows_lo, plan.total_dim), dtype=np.float16)
+    for t, s in enumerate(specs):
+        idx, off = host[t]
+        ok, ref = oracle.spmdm(s.bit_rate, s.dim, s.rows, tables[t], idx[off[rows_lo]:off[rows_hi]],
+                               off[rows_lo:rows_hi + 1], None, False, np.float16)
+        assert ok
+        c0 = plan.column_start(t)
+        want[:, c0:c0 + s.dim] = ref.reshape(rows_hi - rows_lo, s.dim)
+    return want
+
+
+def test_ordered_steps_and_host_call_on_one_gpu(gpu_ctx, oracle):
+    """World size 1: the device-ordered step (ack wait, lookups, ready signal,
+    ready wait, release) over two buffers, and the host-pointer multi-table
+    call with its counters, both against the oracle."""
+    from fbgemm_b200.sharding import ShardedLookup, TableWisePlan
+    from fbgemm_b200.workloads import Batch
+
+    B, dev = 64, torch.device("cuda", 0)
+    specs, _ = _specs_and_batches(B)
+    plan = TableWisePlan([0] * len(specs), [s.dim for s in specs], 1)
+    sl = ShardedLookup(specs, plan, 0, B, dev, torch.float16, mode="p2p", num_buffers=2)
+    tables = {t: sl.tables[t].cpu().numpy() for t in sl.local}
+    streams = [torch.cuda.Stream() for _ in range(2)]
+    for step in range(5):
+        _, host = _specs_and_batches(B, seed=10 + step)
+        batches = {t: Batch(torch.from_numpy(host[t][0]).cuda(), torch.from_numpy(host[t][1]).cuda(), None, B,
+                            len(host[t][0]), len(host[t][0])) for t in sl.local}
+        buf = step % 2
+        n = sl.step(batches, buffer=buf, slot_base=50, streams=streams)
+        got = sl.out[buf].cpu().numpy()      # the copy is ordered after the ready wait on this stream
+        sl.release(buf, n)
+        assert n == step // 2 + 1
+        for i in range(len(sl.local)):
+            ok, info = F.status_read(50 + i)
+            assert ok, info
+        want = _oracle_rows(oracle, specs, plan, tables, host, 0, B)
+        np.testing.assert_array_equal(got.view(np.uint16), want.view(np.uint16))
+    # host arrays in, host rows out
+    sl2 = ShardedLookup(specs, plan, 0, B, dev, torch.float16, mode="p2p", num_buffers=1, tables=sl.tables)
+    call = sl2.make_host_call(0, {t: 2000 for t in sl2.local}, slot=60)
+    out_host = torch.zeros((B, plan.total_dim), dtype=torch.float16).pin_memory().numpy()
+    for step in range(3):
+        _, host = _specs_and_batches(B, seed=20 + step)
+        call.submit([host[t][0] for t in sl2.local], [host[t][1] for t in sl2.local], None, out_host)
+        ok, info = call.wait()
+        assert ok, info
+        want = _oracle_rows(oracle, specs, plan, tables, host, 0, B)
+        np.testing.assert_array_equal(out_host.view(np.uint16), want.view(np.uint16))
+    # more indices than the handle was built for: refused on the host, nothing enqueued
+    big = np.zeros(2001, dtype=np.int32)
+    with pytest.raises(_capi.Fbgemmb200Error):
+        call.submit([big] * len(sl2.local), [host[t][1] for t in sl2.local], None, out_host)
+    # a bad index makes the step false and the next step is clean again
+    _, host = _specs_and_batches(B, seed=30)
+    host[2][0][5] = specs[2].rows
+    call.submit([host[t][0] for t in sl2.local], [host[t][1] for t in sl2.local], None, out_host)
+    ok, info = call.wait()
+    assert not ok and info[0] == 1 and info[3] == specs[2].rows
+    _, host = _specs_and_batches(B, seed=31)
+    call.submit([host[t][0] for t in sl2.local], [host[t][1] for t in sl2.local], None, out_host)
+    assert call.wait()[0]
+    call.close()

@@ -47,7 +47,7 @@ def _call_pair(ctx, cfg, batch, n, rows, table, indices, lengths, weights, dim, 
 
 
 @pytest.mark.parametrize("bit_rate,out_dtype", [(8, torch.float32), (4, torch.float16), (2, torch.float32)])
-def test_no_alloc_entry_matches_regular_entry_twice(gpu_ctx, bit_rate, out_dtype):
+def test_no_alloc_entry_matches_regular_entry_twice(gpu_ctx, oracle, bit_rate, out_dtype):
     rng = np.random.default_rng(100 + bit_rate)
     rows, dim = 3000, 64
     table = random_fused_table(rng, rows, dim, bit_rate)
@@ -65,6 +65,11 @@ def test_no_alloc_entry_matches_regular_entry_twice(gpu_ctx, bit_rate, out_dtype
                                            out_dtype)
         assert ok_r == 1 and ok_n == 1
         np.testing.assert_array_equal(bits(got), bits(want))
+        # and directly against the CPU oracle's lengths flavour
+        ok_ref, ref = oracle.spmdm(bit_rate, dim, rows, table, indices, lengths, weights, True,
+                                   np.float16 if out_dtype == torch.float16 else np.float32, False, False)
+        assert ok_ref
+        np.testing.assert_array_equal(bits(got), bits(ref))
 
 
 def test_no_alloc_entry_reports_and_clears_errors(gpu_ctx):
@@ -104,3 +109,21 @@ def test_no_alloc_entry_refuses_sizes_beyond_its_maximum(gpu_ctx):
     rc = lib.fbgemm_b200_spmdm_lengths_noalloc(C.byref(cfg), 4, 0, 1, t.data_ptr(), t.data_ptr(), t.data_ptr(),
                                                None, t.data_ptr(), None, None)
     assert rc == _capi.EINVAL
+    # configurations without lengths, and null pointers, are refused before any kernel is enqueued
+    before = F.launch_count()
+    cfg.use_offsets = 0
+    cfg.no_bag = 1
+    rc = lib.fbgemm_b200_spmdm_lengths_noalloc(C.byref(cfg), 4, 4, 1, t.data_ptr(), t.data_ptr(), None, None,
+                                               t.data_ptr(), None, None)
+    assert rc == _capi.EINVAL
+    cfg.no_bag = 0
+    for args in ((t.data_ptr(), t.data_ptr(), None, t.data_ptr()), (None, t.data_ptr(), t.data_ptr(), t.data_ptr()),
+                 (t.data_ptr(), None, t.data_ptr(), t.data_ptr()), (t.data_ptr(), t.data_ptr(), t.data_ptr(), None)):
+        rc = lib.fbgemm_b200_spmdm_lengths_noalloc(C.byref(cfg), 4, 4, 1, args[0], args[1], args[2], None, args[3],
+                                                   None, None)
+        assert rc == _capi.EINVAL, args
+    cfg.offset_bytes = 3
+    rc = lib.fbgemm_b200_spmdm_lengths_noalloc(C.byref(cfg), 4, 4, 1, t.data_ptr(), t.data_ptr(), t.data_ptr(), None,
+                                               t.data_ptr(), None, None)
+    assert rc == _capi.EINVAL
+    assert F.launch_count() == before
