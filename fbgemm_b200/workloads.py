@@ -80,20 +80,25 @@ def offsets_from_lengths(lengths: torch.Tensor, dtype) -> torch.Tensor:
     return off.to(dtype)
 
 
-def random_table(rows: int, dim: int, bit_rate: int, device, seed: int, chunk_rows: int = 1 << 20) -> torch.Tensor:
-    """N(0,1) fp32 rows quantized row-wise into fused rows on the device, in
-    chunks so that the fp32 source never has to exist at once."""
-    from .embedding import FloatToFused8BitRowwiseQuantizedSBFloat, FloatToFusedNBitRowwiseQuantizedSBHalf
-
+def random_rows(rows: int, dim: int, device, seed: int, chunk_rows: int = 1 << 20):
+    """The seeded N(0,1) fp32 rows of a table, as (first row, chunk) pieces so
+    that the fp32 source never has to exist at once."""
     g = _gen(device, seed)
-    out = torch.empty((rows, fused_row_bytes(bit_rate, dim)), dtype=torch.uint8, device=device)
     for r0 in range(0, rows, chunk_rows):
         r1 = min(rows, r0 + chunk_rows)
-        x = torch.randn((r1 - r0, dim), generator=g, device=device, dtype=torch.float32)
+        yield r0, torch.randn((r1 - r0, dim), generator=g, device=device, dtype=torch.float32)
+
+
+def random_table(rows: int, dim: int, bit_rate: int, device, seed: int) -> torch.Tensor:
+    """``random_rows`` quantized row-wise into fused rows on the device."""
+    from .embedding import FloatToFused8BitRowwiseQuantizedSBFloat, FloatToFusedNBitRowwiseQuantizedSBHalf
+
+    out = torch.empty((rows, fused_row_bytes(bit_rate, dim)), dtype=torch.uint8, device=device)
+    for r0, x in random_rows(rows, dim, device, seed):
         if bit_rate == 8:
-            FloatToFused8BitRowwiseQuantizedSBFloat(x, out[r0:r1])
+            FloatToFused8BitRowwiseQuantizedSBFloat(x, out[r0:r0 + len(x)])
         else:
-            FloatToFusedNBitRowwiseQuantizedSBHalf(bit_rate, x, out[r0:r1])
+            FloatToFusedNBitRowwiseQuantizedSBHalf(bit_rate, x, out[r0:r0 + len(x)])
     return out
 
 
@@ -155,11 +160,11 @@ def _scaled(n: int, scale: float, floor: int = 1) -> int:
     return max(floor, int(round(n * scale)))
 
 
-def config0(device, scale: float = 1.0, seed: int = SEED) -> Workload:
+def config0(device, scale: float = 1.0, seed: int = SEED, table_maker=random_table) -> Workload:
     """8-bit, 1,000,000 x 128, batch 10,000, pooling 20 fixed, uniform int64
     indices, int64 offsets, unweighted sum, fp32 out."""
     rows, dim, B, L = _scaled(1_000_000, scale, 64), 128, _scaled(10_000, scale, 8), 20
-    table = random_table(rows, dim, 8, device, seed)
+    table = table_maker(rows, dim, 8, device, seed)
 
     def make_batch(s):
         g = _gen(device, seed + 1000 + s)
@@ -171,12 +176,12 @@ def config0(device, scale: float = 1.0, seed: int = SEED) -> Workload:
                     torch.float32, False, False, B, make_batch)
 
 
-def config1(device, scale: float = 1.0, seed: int = SEED) -> Workload:
+def config1(device, scale: float = 1.0, seed: int = SEED, table_maker=random_table) -> Workload:
     """4-bit, 10,000,000 x 64, batch 4,096, bag lengths uniform in [0, 64],
     int32 Zipf(1.05) indices over a seeded permutation, per-sample weights
     U(0,1), weighted sum, fp16 out."""
     rows, dim, B = _scaled(10_000_000, scale, 64), 64, _scaled(4_096, scale, 8)
-    table = random_table(rows, dim, 4, device, seed)
+    table = table_maker(rows, dim, 4, device, seed)
     perm = row_permutation(rows, device, seed + 5)
 
     def make_batch(s):
@@ -192,7 +197,7 @@ def config1(device, scale: float = 1.0, seed: int = SEED) -> Workload:
                     torch.int32, torch.float16, True, False, B, make_batch)
 
 
-def config2(device, scale: float = 1.0, seed: int = SEED) -> Workload:
+def config2(device, scale: float = 1.0, seed: int = SEED, table_maker=random_table) -> Workload:
     """2-bit pruned, 20,000,000 logical rows x 128 with a random 50 % mapped to
     -1, batch 8,192, bag lengths Poisson(30), int64 Zipf(1.1) indices, mean
     pooling, fp32 out."""
@@ -202,7 +207,7 @@ def config2(device, scale: float = 1.0, seed: int = SEED) -> Workload:
     cit = torch.full((rows,), -1, dtype=torch.int32, device=device)
     n_dense = int(keep.sum())
     cit[keep] = torch.arange(n_dense, dtype=torch.int32, device=device)
-    table = random_table(max(n_dense, 1), dim, 2, device, seed)
+    table = table_maker(max(n_dense, 1), dim, 2, device, seed)
     perm = row_permutation(rows, device, seed + 5)
 
     def make_batch(s):
