@@ -646,7 +646,10 @@ def main_multi(args):
                        weighted=weighted, index_dtype=tnp, offset_dtype=tnp)
     sets = make_input_sets(specs, sl.local, B, alpha, idt, weighted, mean_len, lengths_kind, dev, NUM_SETS)
     bytes_local = float(np.mean([sum(b.index_size * specs[t].row_bytes for t, b in d.items()) for d in sets]))
-    streams = [torch.cuda.Stream(device=dev) for _ in range(4)]
+    # One lane per output buffer: its own stream (and side streams for the tables' launches), so that the counter
+    # waits and the tail of one global batch overlap with the lookups of the next.
+    lanes = [torch.cuda.Stream(device=dev) for _ in range(nbuf)]
+    side = [[torch.cuda.Stream(device=dev) for _ in range(3)] for _ in range(nbuf)]
     bps = max(1, args.batches_per_step)
 
     plans = None
@@ -666,26 +669,37 @@ def main_multi(args):
     counter = [0]
 
     def global_batch():
-        """One global batch: input set j % NUM_SETS into buffer j % 2."""
+        """One global batch: input set j % NUM_SETS into buffer j % 2, on that buffer's lane."""
         j = counter[0]
         counter[0] += 1
         s, b = j % NUM_SETS, j % nbuf
-        if p2p:
-            n = sl.step(sets[s], buffer=b, slot_base=(j % 4) * 100, streams=None if plans else streams,
-                        plan=plans[(s, b)] if plans else None)
-            sl.release(b, n)   # this benchmark's consumer has nothing to do with the rows
-        else:
-            cur = torch.cuda.current_stream()
-            if plans:
-                plans[(s, b)].launch(cur.cuda_stream)
+        with torch.cuda.stream(lanes[b]):
+            streams = [lanes[b]] + side[b]
+            if p2p:
+                n = sl.step(sets[s], buffer=b, slot_base=(j % 4) * 100, streams=None if plans else streams,
+                            plan=plans[(s, b)] if plans else None)
+                sl.release(b, n)   # this benchmark's consumer has nothing to do with the rows
             else:
-                for st in streams:
-                    st.wait_stream(cur)
-                sl.launch(sets[s], buffer=b, slot_base=(j % 4) * 100, streams=[st.cuda_stream for st in streams])
-                for st in streams:
-                    cur.wait_stream(st)
-            sl.exchange(b)
+                if plans:
+                    plans[(s, b)].launch(lanes[b].cuda_stream)
+                else:
+                    for st in side[b]:
+                        st.wait_stream(lanes[b])
+                    sl.launch(sets[s], buffer=b, slot_base=(j % 4) * 100, streams=[st.cuda_stream for st in streams])
+                    for st in side[b]:
+                        lanes[b].wait_stream(st)
+                sl.exchange(b)
         return s, b
+
+    def fork_lanes():
+        cur = torch.cuda.current_stream()
+        for ln in lanes:
+            ln.wait_stream(cur)
+
+    def join_lanes():
+        cur = torch.cuda.current_stream()
+        for ln in lanes:
+            cur.wait_stream(ln)
 
     def status_ok():
         return all(F.status_read(s, dev.index)[0] for s in range(400 + NUM_SETS * nbuf + 1))
@@ -730,9 +744,11 @@ def main_multi(args):
     marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     with ClockSampler(local_rank) as clocks:
         marks[0].record()
+        fork_lanes()
         for k in range(args.steps):
             for _ in range(bps):
                 global_batch()
+            join_lanes()            # the step's mark waits for both lanes; the next step's batches follow without a gap
             marks[k + 1].record()
         torch.cuda.synchronize(dev)
     barrier()
@@ -864,7 +880,8 @@ def main_multi(args):
                                           "NCCL all_to_all_single after the lookups"),
                        "launch": (f"multi-table plan, {launches_per_batch} kernel launches per global batch" if plans else
                                   f"one launch per table over 4 streams ({launches_per_batch} kernel launches per "
-                                  "global batch and rank, counters included)"),
+                                  "global batch and rank, counters included)") + f"; {nbuf} global batches in flight, "
+                                 "one per output buffer",
                        "l2": "tables are far larger than L2; the input sets rotate"},
             "results_ok": bool(ok),
             "results_check": f"{parity_rows} pooled rows (sampled bags x all tables, each on the rank whose buffer "
