@@ -93,6 +93,7 @@ SIGNATURES = {
     "fbgemm_b200_ctx_destroy": (None, [_p]),
     "fbgemm_b200_last_error": (C.c_char_p, []),
     "fbgemm_b200_launch_count": (C.c_uint64, []),
+    "fbgemm_b200_set_kernel_choice": (C.c_int, [C.c_int]),
     "fbgemm_b200_spmdm_check_config": (C.c_int, [_cfgp]),
     "fbgemm_b200_spmdm_launch": (C.c_int, [_p, _cfgp, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, C.c_int, _p]),
     "fbgemm_b200_spmdm_launch_sharded": (C.c_int, [_p, _cfgp, _i64, _i64, _i64, _p, _p, _p, _p, C.POINTER(_p),

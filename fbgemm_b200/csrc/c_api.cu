@@ -542,6 +542,14 @@ uint64_t fbgemm_b200_launch_count(void) {
   return g_launch_count.load(std::memory_order_relaxed);
 }
 
+int fbgemm_b200_set_kernel_choice(int choice) {
+  if (choice != FBGEMM_B200_KERNEL_AUTO && choice != FBGEMM_B200_KERNEL_GENERIC) {
+    set_error("unknown kernel choice");
+    return FBGEMM_B200_EINVAL;
+  }
+  return g_kernel_choice.exchange(choice, std::memory_order_relaxed);
+}
+
 int fbgemm_b200_spmdm_check_config(const fbgemm_b200_spmdm_config* cfg) {
   return check_config(cfg, nullptr);
 }

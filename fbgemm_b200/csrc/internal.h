@@ -292,6 +292,9 @@ int build_lookup_params(
 // Process-wide count of kernels launched by this library.
 extern std::atomic<uint64_t> g_launch_count;
 
+// fbgemm_b200_set_kernel_choice: which lookup kernel quantized rows take.
+extern std::atomic<int> g_kernel_choice;
+
 // Thread-local error text behind fbgemm_b200_last_error().
 void set_error(const std::string& msg);
 int fail_cuda(cudaError_t e, const char* what);

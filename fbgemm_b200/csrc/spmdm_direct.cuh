@@ -230,9 +230,46 @@ __device__ __forceinline__ void fetch_rows(
 
 // One step: U rows of the bag.  All row loads are issued before the first
 // use; then the rows are pooled in order.
-template <int BITS, int VEC, int LPB, int CPL, int U>
+// Where a lane finds its payload chunks.  EXACT: the row's payload is exactly
+// LPB * CPL chunks, so chunk ci of the lane lies ci * LPB * VEC bytes after its
+// first one: one address computation per row, the CPL loads differ by
+// immediate offsets, and one pointer is kept instead of CPL.  Otherwise lanes
+// whose chunk lies beyond the payload (row width not a multiple of LPB * CPL
+// chunks) read chunk 0 instead and simply do not store.
+template <int VEC, int LPB, int CPL, bool EXACT>
+struct LaneChunks {
+  const uint8_t* base[EXACT ? 1 : CPL];  // table + payload offset + byte offset of this lane's chunk ci
+  __device__ __forceinline__ void init(const uint8_t* data_base, int gl, int nchunks) {
+    if constexpr (EXACT) {
+      base[0] = data_base + gl * VEC;
+    } else {
+#pragma unroll
+      for (int ci = 0; ci < CPL; ++ci) {
+        const int c = gl + ci * LPB;
+        base[ci] = data_base + (c < nchunks ? c * VEC : 0);
+      }
+    }
+  }
+  // the CPL chunks of row `row` into d[0..CPL)
+  __device__ __forceinline__ void load_row(Vec<VEC> (&d)[CPL], uint32_t row, uint32_t stride) const {
+    if constexpr (EXACT) {
+      const uint8_t* r = row_address(base[0], row, stride);
+#pragma unroll
+      for (int ci = 0; ci < CPL; ++ci) {
+        d[ci].load(r + ci * LPB * VEC);
+      }
+    } else {
+#pragma unroll
+      for (int ci = 0; ci < CPL; ++ci) {
+        d[ci].load(row_address(base[ci], row, stride));
+      }
+    }
+  }
+};
+
+template <int BITS, int VEC, int LPB, int CPL, int U, bool EXACT>
 __device__ __forceinline__ void pool_step(
-    const uint8_t* const (&chunk_base)[CPL],  // table + byte offset of this lane's chunk ci
+    const LaneChunks<VEC, LPB, CPL, EXACT>& lc,
     const uint8_t* sb_base,                   // table + data_bytes
     uint32_t stride,
     unsigned gmask,
@@ -252,10 +289,7 @@ __device__ __forceinline__ void pool_step(
   ScaleBias<BITS, VEC> sb[U];
 #pragma unroll
   for (int u = 0; u < U; ++u) {
-#pragma unroll
-    for (int ci = 0; ci < CPL; ++ci) {
-      d[u][ci].load(row_address(chunk_base[ci], rid[u], stride));
-    }
+    lc.load_row(d[u], rid[u], stride);
     sb[u].load(row_address(sb_base, rid[u], stride), half_sb);
   }
   const u64 nm2 = pack2(-8388608.0f, -8388608.0f);
@@ -306,11 +340,11 @@ __device__ __forceinline__ void store_columns(const SpmdmParams& p, int64_t bag,
         h[i] = (uint32_t)to_16bit(v[2 * i], bf16) | ((uint32_t)to_16bit(v[2 * i + 1], bf16) << 16);
       }
       if constexpr (CPC == 4) {
-        *reinterpret_cast<uint2*>(o) = make_uint2(h[0], h[1]);
+        *(reinterpret_cast<uint2*>(o)) = make_uint2(h[0], h[1]);
       } else {
 #pragma unroll
         for (int i = 0; i < CPC / 8; ++i) {
-          reinterpret_cast<uint4*>(o)[i] = make_uint4(h[4 * i], h[4 * i + 1], h[4 * i + 2], h[4 * i + 3]);
+          *(reinterpret_cast<uint4*>(o) + i) = make_uint4(h[4 * i], h[4 * i + 1], h[4 * i + 2], h[4 * i + 3]);
         }
       }
     } else {
@@ -326,7 +360,7 @@ __device__ __forceinline__ void store_columns(const SpmdmParams& p, int64_t bag,
     if (full && (p.flags & kOutVec)) {
 #pragma unroll
       for (int i = 0; i < CPC / 4; ++i) {
-        reinterpret_cast<float4*>(o)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        *(reinterpret_cast<float4*>(o) + i) = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
       }
     } else {
 #pragma unroll
@@ -341,7 +375,7 @@ __device__ __forceinline__ void store_columns(const SpmdmParams& p, int64_t bag,
 
 // The work of one thread block: block `block` of the launch that covers the
 // bags of `p` (32/LPB bags per warp, kWarpsPerBlock warps).
-template <int BITS, int VEC, int LPB, int CPL>
+template <int BITS, int VEC, int LPB, int CPL, bool EXACT>
 __device__ __forceinline__ void direct_block(const SpmdmParams& p, int64_t block) {
   constexpr int GPW = 32 / LPB;                       // bags per warp
   constexpr int CPC = VEC * 8 / BITS;                 // columns per chunk
@@ -349,11 +383,7 @@ __device__ __forceinline__ void direct_block(const SpmdmParams& p, int64_t block
   // Rows per step.  Measured on B200: 4 beats 2, 8 and 16 for every row format
   // (more rows per step cost registers, hence resident warps, and that costs
   // more than the extra loads in flight per warp bring).
-#ifdef FBGEMM_B200_UMAX
-  constexpr int UMAX = FBGEMM_B200_UMAX;
-#else
   constexpr int UMAX = 4;
-#endif
   constexpr int OWN = (UMAX + LPB - 1) / LPB;
 
   const int lane = threadIdx.x & 31;
@@ -398,12 +428,8 @@ __device__ __forceinline__ void direct_block(const SpmdmParams& p, int64_t block
   // Lanes whose chunk lies beyond the payload (row width not a multiple of
   // LPB*CPL chunks) read chunk 0 instead and simply do not store.
   const int nchunks = p.data_bytes / VEC;
-  const uint8_t* chunk_base[CPL];
-#pragma unroll
-  for (int ci = 0; ci < CPL; ++ci) {
-    const int c = gl + ci * LPB;
-    chunk_base[ci] = p.table + p.data_row_off + (c < nchunks ? c * VEC : 0);
-  }
+  LaneChunks<VEC, LPB, CPL, EXACT> lc;
+  lc.init(p.table + p.data_row_off, gl, nchunks);
   const uint8_t* sb_base = p.table + p.sb_row_off;
   const bool half_sb = BITS != 8 || (p.flags & kSbFirst);
   const uint32_t stride = (uint32_t)p.input_stride;
@@ -469,7 +495,7 @@ __device__ __forceinline__ void direct_block(const SpmdmParams& p, int64_t block
   for (int s = 0; s < nfull; ++s) {
     issue(s + 2, raw_2, w_2);
     resolve(s + 1, raw_1, id_1);
-    pool_step<BITS, VEC, LPB, CPL, UMAX>(chunk_base, sb_base, stride, gmask, lane0, half_sb, weighted, id_cur, w_cur, acc);
+    pool_step<BITS, VEC, LPB, CPL, UMAX, EXACT>(lc, sb_base, stride, gmask, lane0, half_sb, weighted, id_cur, w_cur, acc);
 #pragma unroll
     for (int j = 0; j < OWN; ++j) {
       id_cur[j] = id_1[j];
@@ -480,36 +506,18 @@ __device__ __forceinline__ void direct_block(const SpmdmParams& p, int64_t block
   }
   // The remaining rows, largest power of two first (each such step is full).
   int r = nfull * UMAX;
-  if constexpr (UMAX >= 16) {
-    if (len - r >= 8) {
-      uint32_t id8[(8 + LPB - 1) / LPB];
-      float w8[(8 + LPB - 1) / LPB];
-      fetch_rows<LPB, 8>(p, gl, bag, start + r, r, id8, w8);
-      pool_step<BITS, VEC, LPB, CPL, 8>(chunk_base, sb_base, stride, gmask, lane0, half_sb, weighted, id8, w8, acc);
-      r += 8;
-    }
-  }
-  if constexpr (UMAX >= 8) {
-    if (len - r >= 4) {
-      uint32_t id4[(4 + LPB - 1) / LPB];
-      float w4[(4 + LPB - 1) / LPB];
-      fetch_rows<LPB, 4>(p, gl, bag, start + r, r, id4, w4);
-      pool_step<BITS, VEC, LPB, CPL, 4>(chunk_base, sb_base, stride, gmask, lane0, half_sb, weighted, id4, w4, acc);
-      r += 4;
-    }
-  }
-  if (UMAX >= 4 && len - r >= 2) {
+  if (len - r >= 2) {
     uint32_t id2[(2 + LPB - 1) / LPB];
     float w2[(2 + LPB - 1) / LPB];
     fetch_rows<LPB, 2>(p, gl, bag, start + r, r, id2, w2);
-    pool_step<BITS, VEC, LPB, CPL, 2>(chunk_base, sb_base, stride, gmask, lane0, half_sb, weighted, id2, w2, acc);
+    pool_step<BITS, VEC, LPB, CPL, 2, EXACT>(lc, sb_base, stride, gmask, lane0, half_sb, weighted, id2, w2, acc);
     r += 2;
   }
   if (len - r >= 1) {
     uint32_t id1[1];
     float w1[1];
     fetch_rows<LPB, 1>(p, gl, bag, start + r, r, id1, w1);
-    pool_step<BITS, VEC, LPB, CPL, 1>(chunk_base, sb_base, stride, gmask, lane0, half_sb, weighted, id1, w1, acc);
+    pool_step<BITS, VEC, LPB, CPL, 1, EXACT>(lc, sb_base, stride, gmask, lane0, half_sb, weighted, id1, w1, acc);
   }
 
   if ((p.flags & kNormalize) && bag_len != 0) {
@@ -540,16 +548,13 @@ struct KnownRows {
   Vec<VEC> d[U][CPL];
   ScaleBias<BITS, VEC> sb[U];
 
-  __device__ __forceinline__ void load(const uint8_t* const (&chunk_base)[CPL], const uint8_t* sb_base, uint32_t stride,
-                                       bool half_sb, const uint2* entry) {
+  template <int LPB, bool EXACT>
+  __device__ __forceinline__ void load(const LaneChunks<VEC, LPB, CPL, EXACT>& lc, const uint8_t* sb_base,
+                                       uint32_t stride, bool half_sb, const uint2* entry) {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const uint32_t row = entry[u].x;
-#pragma unroll
-      for (int ci = 0; ci < CPL; ++ci) {
-        d[u][ci].load(row_address(chunk_base[ci], row, stride));
-      }
-      sb[u].load(row_address(sb_base, row, stride), half_sb);
+      lc.load_row(d[u], entry[u].x, stride);
+      sb[u].load(row_address(sb_base, entry[u].x, stride), half_sb);
     }
   }
 
@@ -589,15 +594,13 @@ struct KnownRows {
 // rows at a time.  Only rows that exist reach the arithmetic.
 // Queue entries per lane group: 8 KB of shared memory per block whatever the
 // group width (fewer, wider groups get longer queues), 128 entries at most.
-#ifndef FBGEMM_B200_QUEUE_BYTES
-#define FBGEMM_B200_QUEUE_BYTES 8192
-#endif
+constexpr int kQueueBytes = 8192;
 __host__ __device__ constexpr int queue_entries(int groups_per_warp) {
-  const int q = FBGEMM_B200_QUEUE_BYTES / (kWarpsPerBlock * groups_per_warp * 8);
+  const int q = kQueueBytes / (kWarpsPerBlock * groups_per_warp * 8);
   return q > 128 ? 128 : q;
 }
 
-template <int BITS, int VEC, int LPB, int CPL>
+template <int BITS, int VEC, int LPB, int CPL, bool EXACT>
 __device__ __forceinline__ void direct_block_compact(const SpmdmParams& p, int64_t block) {
   constexpr int GPW = 32 / LPB;
   constexpr int CPC = VEC * 8 / BITS;
@@ -605,11 +608,7 @@ __device__ __forceinline__ void direct_block_compact(const SpmdmParams& p, int64
   constexpr int kQueue = queue_entries(GPW);
   // rows of the next step in flight during the arithmetic: only where a row is
   // at most two words per lane, or the extra registers cost resident warps
-#ifdef FBGEMM_B200_COMPACT_PREFETCH
-  constexpr bool kPrefetch = FBGEMM_B200_COMPACT_PREFETCH != 0;
-#else
   constexpr bool kPrefetch = CPL * (VEC / 4) <= 2;
-#endif
   __shared__ uint2 queue_s[kWarpsPerBlock * GPW][kQueue];
 
   const int lane = threadIdx.x & 31;
@@ -654,12 +653,8 @@ __device__ __forceinline__ void direct_block_compact(const SpmdmParams& p, int64
   }
 
   const int nchunks = p.data_bytes / VEC;
-  const uint8_t* chunk_base[CPL];
-#pragma unroll
-  for (int ci = 0; ci < CPL; ++ci) {
-    const int c = gl + ci * LPB;
-    chunk_base[ci] = p.table + p.data_row_off + (c < nchunks ? c * VEC : 0);
-  }
+  LaneChunks<VEC, LPB, CPL, EXACT> lc;
+  lc.init(p.table + p.data_row_off, gl, nchunks);
   const uint8_t* sb_base = p.table + p.sb_row_off;
   const uint32_t stride = (uint32_t)p.input_stride;
 
@@ -724,16 +719,16 @@ __device__ __forceinline__ void direct_block_compact(const SpmdmParams& p, int64
     if constexpr (kPrefetch) {
       KnownRows<BITS, VEC, CPL, 4> a, b;
       if (nfull > 0) {
-        a.load(chunk_base, sb_base, stride, half_sb, queue);
+        a.load(lc, sb_base, stride, half_sb, queue);
       }
       for (int s = 0; s < nfull; s += 2) {
         if (s + 1 < nfull) {
-          b.load(chunk_base, sb_base, stride, half_sb, queue + 4 * (s + 1));
+          b.load(lc, sb_base, stride, half_sb, queue + 4 * (s + 1));
         }
         a.pool(half_sb, weighted, queue + 4 * s, acc);
         if (s + 1 < nfull) {
           if (s + 2 < nfull) {
-            a.load(chunk_base, sb_base, stride, half_sb, queue + 4 * (s + 2));
+            a.load(lc, sb_base, stride, half_sb, queue + 4 * (s + 2));
           }
           b.pool(half_sb, weighted, queue + 4 * (s + 1), acc);
         }
@@ -741,20 +736,20 @@ __device__ __forceinline__ void direct_block_compact(const SpmdmParams& p, int64
     } else {
       for (int s = 0; s < nfull; ++s) {
         KnownRows<BITS, VEC, CPL, 4> a;
-        a.load(chunk_base, sb_base, stride, half_sb, queue + 4 * s);
+        a.load(lc, sb_base, stride, half_sb, queue + 4 * s);
         a.pool(half_sb, weighted, queue + 4 * s, acc);
       }
     }
     int r = 4 * nfull;
     if (count - r >= 2) {
       KnownRows<BITS, VEC, CPL, 2> t;
-      t.load(chunk_base, sb_base, stride, half_sb, queue + r);
+      t.load(lc, sb_base, stride, half_sb, queue + r);
       t.pool(half_sb, weighted, queue + r, acc);
       r += 2;
     }
     if (count - r >= 1) {
       KnownRows<BITS, VEC, CPL, 1> t;
-      t.load(chunk_base, sb_base, stride, half_sb, queue + r);
+      t.load(lc, sb_base, stride, half_sb, queue + r);
       t.pool(half_sb, weighted, queue + r, acc);
     }
     __syncwarp(gmask);  // the queue is rewritten by the next stretch
@@ -781,10 +776,10 @@ __device__ __forceinline__ void direct_block_compact(const SpmdmParams& p, int64
 }
 
 // One table per launch; the parameters travel in constant memory.
-template <int BITS, int VEC, int LPB, int CPL>
+template <int BITS, int VEC, int LPB, int CPL, bool EXACT>
 __global__ void __launch_bounds__(kThreads)
 spmdm_direct_kernel(const __grid_constant__ SpmdmParams p) {
-  direct_block<BITS, VEC, LPB, CPL>(p, blockIdx.x);
+  direct_block<BITS, VEC, LPB, CPL, EXACT>(p, blockIdx.x);
 }
 
 // Several tables of the same row format in one launch (the reference's
@@ -793,7 +788,7 @@ spmdm_direct_kernel(const __grid_constant__ SpmdmParams p) {
 // The tables' parameters arrive by value, i.e. in constant memory as in the
 // single-table kernel; a block finds its table by comparing its index with
 // the tables' first blocks (at most kMultiTables - 1 uniform comparisons).
-template <int BITS, int VEC, int LPB, int CPL>
+template <int BITS, int VEC, int LPB, int CPL, bool EXACT>
 __global__ void __launch_bounds__(kThreads)
 spmdm_direct_multi_kernel(const __grid_constant__ MultiArgs a) {
   int t = 0;
@@ -801,18 +796,18 @@ spmdm_direct_multi_kernel(const __grid_constant__ MultiArgs a) {
   for (int i = 1; i < kMultiTables; ++i) {
     t += (i < a.count && blockIdx.x >= (unsigned)a.first_block[i]) ? 1 : 0;
   }
-  direct_block<BITS, VEC, LPB, CPL>(a.t[t], (int64_t)blockIdx.x - a.first_block[t]);
+  direct_block<BITS, VEC, LPB, CPL, EXACT>(a.t[t], (int64_t)blockIdx.x - a.first_block[t]);
 }
 
 // One table per launch, rows compacted before they are pooled (pruned tables).
-template <int BITS, int VEC, int LPB, int CPL>
+template <int BITS, int VEC, int LPB, int CPL, bool EXACT>
 __global__ void __launch_bounds__(kThreads)
 spmdm_direct_compact_kernel(const __grid_constant__ SpmdmParams p) {
-  direct_block_compact<BITS, VEC, LPB, CPL>(p, blockIdx.x);
+  direct_block_compact<BITS, VEC, LPB, CPL, EXACT>(p, blockIdx.x);
 }
 
 // Several such tables in one launch (see spmdm_direct_multi_kernel).
-template <int BITS, int VEC, int LPB, int CPL>
+template <int BITS, int VEC, int LPB, int CPL, bool EXACT>
 __global__ void __launch_bounds__(kThreads)
 spmdm_direct_compact_multi_kernel(const __grid_constant__ MultiArgs a) {
   int t = 0;
@@ -820,17 +815,19 @@ spmdm_direct_compact_multi_kernel(const __grid_constant__ MultiArgs a) {
   for (int i = 1; i < kMultiTables; ++i) {
     t += (i < a.count && blockIdx.x >= (unsigned)a.first_block[i]) ? 1 : 0;
   }
-  direct_block_compact<BITS, VEC, LPB, CPL>(a.t[t], (int64_t)blockIdx.x - a.first_block[t]);
+  direct_block_compact<BITS, VEC, LPB, CPL, EXACT>(a.t[t], (int64_t)blockIdx.x - a.first_block[t]);
 }
 
 using KernelFn = void (*)(const SpmdmParams);
 using MultiKernelFn = void (*)(const MultiArgs);
 
+// One (VEC, LPB, CPL) combination; each kernel in two forms, indexed by whether
+// the row's payload is exactly LPB * CPL chunks (see LaneChunks).
 struct Variant {
-  KernelFn fn;
-  MultiKernelFn multi;
-  KernelFn compact;
-  MultiKernelFn compact_multi;
+  KernelFn fn[2];
+  MultiKernelFn multi[2];
+  KernelFn compact[2];
+  MultiKernelFn compact_multi[2];
   int vec, lpb, cpl;
 };
 

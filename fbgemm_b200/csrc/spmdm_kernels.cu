@@ -435,14 +435,24 @@ const Variant* variants(int* count) {
   }
 }
 
+// Overrides of the variant choice exist only in tuning builds
+// (-DFBGEMM_B200_TUNING, which also instantiates variants the dispatcher never
+// picks); the product's launch path reads no environment variable.
+#ifdef FBGEMM_B200_TUNING
 int env_int(const char* name, int dflt) {
   const char* s = std::getenv(name);
   return (s && *s) ? std::atoi(s) : dflt;
 }
+#else
+constexpr int env_int(const char*, int dflt) {
+  return dflt;
+}
+#endif
 
 }  // namespace
 
 std::atomic<uint64_t> g_launch_count{0};
+std::atomic<int> g_kernel_choice{FBGEMM_B200_KERNEL_AUTO};
 
 int max_chunks_per_bag(int bit_rate) {
   return 32 * (bit_rate == 8 ? 8 : bit_rate == 4 ? 4 : 2);
@@ -512,6 +522,11 @@ static const direct::Variant* pick_direct(const SpmdmParams& p, int bit_rate) {
   return pick;
 }
 
+// 1 when the row's payload is exactly the variant's LPB * CPL chunks.
+static int direct_exact(const direct::Variant* v, const SpmdmParams& p) {
+  return p.data_bytes == v->vec * v->lpb * v->cpl ? 1 : 0;
+}
+
 static int64_t direct_blocks(const direct::Variant* v, int64_t bags) {
   const int64_t bags_per_block = (int64_t)direct::kWarpsPerBlock * (32 / v->lpb);
   return (bags + bags_per_block - 1) / bags_per_block;
@@ -530,10 +545,10 @@ static cudaError_t launch_direct(const SpmdmParams& p, int bit_rate, cudaStream_
   }
   // Tables in which an index may name no row (a pruning map, or the layout in
   // which -1 is a pruned index) take the compacting kernel; the plain one has
-  // no notion of a skipped row.  FBGEMM_B200_COMPACT=1 sends dense tables there
-  // too (a tuning aid).
+  // no notion of a skipped row.
   const bool compact = (p.flags & (kPruned | kSbFirst)) || env_int("FBGEMM_B200_COMPACT", 0) == 1;
-  (compact ? pick->compact : pick->fn)<<<(unsigned)blocks, direct::kThreads, 0, stream>>>(p);
+  const int exact = direct_exact(pick, p);
+  (compact ? pick->compact[exact] : pick->fn[exact])<<<(unsigned)blocks, direct::kThreads, 0, stream>>>(p);
   g_launch_count.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError();
 }
@@ -572,19 +587,22 @@ cudaError_t build_multi_plan(const std::vector<SpmdmParams>& tables, const std::
       plan->singles.push_back({tables[t], bit_rates[t]});
     }
   }
-  auto may_skip = [&](size_t t) { return (tables[t].flags & (kPruned | kSbFirst)) != 0; };
+  // what decides a table's kernel besides the variant: 2 = rows may be skipped, 1 = exact-fit addressing
+  auto form = [&](size_t t) {
+    return ((tables[t].flags & (kPruned | kSbFirst)) != 0 ? 2 : 0) + direct_exact(variant[t], tables[t]);
+  };
   std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) {
-    return variant[a] != variant[b] ? variant[a] < variant[b] : may_skip(a) < may_skip(b);
+    return variant[a] != variant[b] ? variant[a] < variant[b] : form(a) < form(b);
   });
   for (size_t i = 0; i < order.size();) {
     const direct::Variant* v = variant[order[i]];
-    const bool skip = may_skip(order[i]);
+    const int f = form(order[i]);
     plan->groups.emplace_back();
     MultiPlan::Launch& g = plan->groups.back();
-    g.fn = skip ? v->compact_multi : v->multi;
+    g.fn = (f & 2) ? v->compact_multi[f & 1] : v->multi[f & 1];
     g.args = MultiArgs{};
     int64_t blocks = 0;
-    for (; i < order.size() && variant[order[i]] == v && may_skip(order[i]) == skip && g.args.count < kMultiTables; ++i) {
+    for (; i < order.size() && variant[order[i]] == v && form(order[i]) == f && g.args.count < kMultiTables; ++i) {
       const int64_t b = direct_blocks(v, tables[order[i]].output_size);
       if (blocks + b > 0x7fffffffLL) {
         break;  // the rest of this variant's tables start a new launch
@@ -665,8 +683,8 @@ cudaError_t launch_spmdm(const SpmdmParams& p_in, int bit_rate, cudaStream_t str
   if (p_in.in_kind != 0) {
     return launch_plain_rows(p_in, stream);
   }
-  const char* force = std::getenv("FBGEMM_B200_KERNEL");
-  if (!(force && std::strcmp(force, "staged") == 0)) {  // forces the generic kernel (tuning aid)
+  const bool staged_only = g_kernel_choice.load(std::memory_order_relaxed) == FBGEMM_B200_KERNEL_GENERIC;
+  if (!staged_only) {
     const cudaError_t e = launch_direct(p_in, bit_rate, stream);
     if (e != cudaErrorNotSupported) {
       return e;
@@ -678,8 +696,7 @@ cudaError_t launch_spmdm(const SpmdmParams& p_in, int bit_rate, cudaStream_t str
   const int nchunks = (p.data_bytes + 3) / 4;
 
   // Smallest lane group that covers the payload with one chunk per lane; wide
-  // rows take a full warp and several chunks per lane.  FBGEMM_B200_LPB /
-  // FBGEMM_B200_CPL override the choice (tuning aid).
+  // rows take a full warp and several chunks per lane.
   int want_lpb = nchunks <= 8 ? 8 : nchunks <= 16 ? 16 : 32;
   int want_cpl = 1;
   while (want_lpb * want_cpl < nchunks) {

@@ -593,6 +593,20 @@ FBGEMM_B200_API int fbgemm_b200_spmdm_host(
     void* out,
     const int32_t* compressed_indices_table);
 
+/* ---- kernel choice (tests and comparisons) ---------------------------------- */
+
+/* Quantized rows are pooled by one of two kernels with identical results: the
+ * register-resident one (rows whose address, pitch and width allow 4- or
+ * 8-byte loads) and a generic one that stages rows in shared memory and takes
+ * every shape.  FBGEMM_B200_KERNEL_AUTO picks per call; _GENERIC sends every
+ * call to the generic kernel, so that both can be compared on the same
+ * inputs.  Process-wide.  Returns the previous choice, or a negative code.
+ * No counterpart in the reference (whose ISA dispatch is by CPU feature,
+ * src/EmbeddingSpMDM.cc:1012-1130). */
+#define FBGEMM_B200_KERNEL_AUTO 0
+#define FBGEMM_B200_KERNEL_GENERIC 1
+FBGEMM_B200_API int fbgemm_b200_set_kernel_choice(int choice);
+
 /* ---- ordering between the GPUs of a sharded lookup ---------------------- */
 
 /*

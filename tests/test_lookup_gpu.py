@@ -144,11 +144,11 @@ def test_offsets_stepping_backwards_return_false(gpu_ctx, oracle, bit_rate):
         kern = make_kernel(bit_rate, dim, False, False, False, True, np.int64, odt, np.float32)
         out = torch.zeros(3 * dim, device="cuda")
         assert not kern(3, 8, rows, dev(table), dev(indices), dev(offsets), None, out)
-        os.environ["FBGEMM_B200_KERNEL"] = "staged"
+        _capi.lib().fbgemm_b200_set_kernel_choice(1)   # the generic kernel
         try:
             assert not kern(3, 8, rows, dev(table), dev(indices), dev(offsets), None, out)
         finally:
-            del os.environ["FBGEMM_B200_KERNEL"]
+            _capi.lib().fbgemm_b200_set_kernel_choice(0)
 
 
 @pytest.mark.parametrize("bit_rate", [8, 4, 2])

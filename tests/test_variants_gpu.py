@@ -39,9 +39,17 @@ def generate(bit_rate, dim, weighted, normalize, use_offsets, idt, odt, kind, sb
 
 
 @pytest.mark.parametrize("kernel", ["default", "staged"])
-def test_fixtures_made_by_the_reference(gpu_ctx, kernel, monkeypatch):
-    if kernel == "staged":
-        monkeypatch.setenv("FBGEMM_B200_KERNEL", "staged")
+def test_fixtures_made_by_the_reference(gpu_ctx, kernel):
+    from fbgemm_b200 import _capi
+
+    _capi.lib().fbgemm_b200_set_kernel_choice(1 if kernel == "staged" else 0)
+    try:
+        _fixtures_made_by_the_reference()
+    finally:
+        _capi.lib().fbgemm_b200_set_kernel_choice(0)
+
+
+def _fixtures_made_by_the_reference():
     ex = np.load(EX)
     for i in range(int(ex["n_ex"])):
         k = f"ex{i}_"
