@@ -55,11 +55,12 @@ PARITY_BAGS = 64        # bags per table compared with the oracle inside the run
 # DRAM bytes (read + write) of the lookup kernels per unit of work, from ncu captures
 # (dram__bytes_read.sum + dram__bytes_write.sum; the files under profiles/ say how each was taken).
 TRAFFIC = {
-    # single-table workloads: bytes per functor call of the configuration's batch (16-batch capture / 16)
-    0: {"bytes_per_call": (438_465_024 + 71_525_888) / 16, "source": "profiles/spmdm_direct_kernel__workload0_16batches.md"},
-    1: {"bytes_per_call": 13_766_144, "source": "profiles/spmdm_direct_kernel__workload1_one_batch.md"},
-    2: {"bytes_per_call": (233_486_336 + 49_955_840) / 16,
-        "source": "profiles/spmdm_direct_compact_kernel__workload2_16batches.md"},
+    # single-table workloads: DRAM bytes per functor call of the configuration's batch in the benchmark's steady state
+    0: {"bytes_per_call": 25_902_699 + 5_179_565, "source": "profiles/lookup_kernels__workloads012_steady_state_dram.md"},
+    1: {"bytes_per_call": 10_020_888 + 629_504, "source": "profiles/lookup_kernels__workloads012_steady_state_dram.md"},
+    2: {"bytes_per_call": 13_405_040 + 4_003_784, "source": "profiles/lookup_kernels__workloads012_steady_state_dram.md"},
+    # the 64-table configuration: DRAM bytes of all kernels of one global batch (captured at a quarter of the batch, x 4)
+    3: {"bytes_per_global_batch": 4 * (2_174_574_080 + 178_803_456) / 2, "source": "profiles/lookup_kernels__default_workload_dram.md"},
 }
 
 
@@ -461,12 +462,18 @@ def run_single(args, cfg_index, dev, rank, world, steps, warmup, full, seed_shif
                 cit_key)
             _capi.check(rc, "host_submit")
 
+        host_s = [0.0, 0.0]   # host time inside submit / inside wait
+
         def run_calls(n):
             ok = True
             for i in range(n):
                 if i >= lanes:
+                    t = time.perf_counter()
                     ok = kern.host_wait(i % lanes) and ok
+                    host_s[1] += time.perf_counter() - t
+                t = time.perf_counter()
                 submit(i)
+                host_s[0] += time.perf_counter() - t
             for i in range(min(lanes, n)):
                 ok = kern.host_wait((n + i) % lanes) and ok
             return ok
@@ -474,6 +481,7 @@ def run_single(args, cfg_index, dev, rank, world, steps, warmup, full, seed_shif
         e2e_steps = max(1, min(args.e2e_steps, steps))
         ok = run_calls(cps)   # warm-up step
         torch.cuda.synchronize()
+        host_s[0] = host_s[1] = 0.0
         t0 = time.perf_counter()
         for _ in range(e2e_steps):
             ok = run_calls(cps) and ok
@@ -489,6 +497,10 @@ def run_single(args, cfg_index, dev, rank, world, steps, warmup, full, seed_shif
                       "h2d_bytes_per_step": round(h2d * cps), "d2h_bytes_per_step": round(d2h * cps),
                       "steps": e2e_steps, "calls_per_step": cps, "ms_per_step": dt / e2e_steps * 1e3,
                       "ms_per_call": dt / calls * 1e3, "bags_per_s": bags_per_call * calls / dt, "results_ok": bool(ok),
+                      "host_us_per_call": {"in_submit": host_s[0] / calls * 1e6, "blocked_in_wait": host_s[1] / calls * 1e6,
+                                           "note": "one host thread issues every call: the time inside submit (checks, "
+                                                   "pointer queries, one staging launch or three copies, the lookup, two "
+                                                   "downloads) bounds the rate when the GPU side is shorter"},
                       "path": "fbgemm_b200_spmdm_host_submit/wait, 8 pipelined lanes, pinned host buffers, table resident",
                       "timer": "host perf_counter bracketed by device synchronisation"}
         ctx.unregister_table(host_tbl)

@@ -16,11 +16,11 @@ namespace fbgemm_b200 {
 const direct::Variant* direct_variants_8(int* count) {
   using namespace direct;
   static const Variant v[] = {
-      V(4, 4, 1), V(4, 4, 2), V(4, 4, 4), V(4, 4, 8), V(4, 8, 8), V(4, 16, 8), V(4, 32, 8),
-      V(8, 4, 1), V(8, 4, 2), V(8, 4, 4), V(8, 8, 4), V(8, 16, 4), V(8, 32, 4),
+      V(4, 4, 1), V(4, 4, 2), V(4, 4, 4), V(4, 4, 8), V(4, 8, 8), V(4, 16, 4), V(4, 32, 4), V(4, 32, 8),
+      V(8, 4, 1), V(8, 4, 2), V(8, 4, 4), V(8, 8, 4), V(8, 16, 2), V(8, 32, 2), V(8, 32, 4),
 #ifdef FBGEMM_B200_TUNING
-      V(4, 8, 1), V(4, 8, 2), V(4, 8, 4), V(4, 16, 1), V(4, 16, 2), V(4, 16, 4),
-      V(8, 8, 1), V(8, 8, 2), V(8, 16, 1), V(8, 16, 2), V(8, 32, 1), V(8, 32, 2),
+      V(4, 8, 1), V(4, 8, 2), V(4, 8, 4), V(4, 16, 1), V(4, 16, 2), V(4, 16, 8),
+      V(8, 8, 1), V(8, 8, 2), V(8, 16, 1), V(8, 16, 4), V(8, 32, 1),
 #endif
   };
   *count = (int)(sizeof(v) / sizeof(v[0]));

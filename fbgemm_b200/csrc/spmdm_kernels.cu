@@ -494,7 +494,10 @@ static const direct::Variant* pick_direct(const SpmdmParams& p, int bit_rate) {
   // not scale with D, wide ones keep registers (and so resident warps) in
   // check.  Measured best on B200: 32 columns for 8-bit rows, 16 for 4- and
   // 2-bit rows (whose unpacking needs more registers per column).
-  const int cols_target = bit_rate == 8 ? 32 : 16;
+  // Rows of 256 and more 8-bit columns do better with 16 again (two bags per
+  // warp instead of four: 67 against 73 ps per row at D = 256, the ragged bags
+  // of a warp wait less for each other).
+  const int cols_target = bit_rate == 8 ? (p.data_bytes >= 256 ? 16 : 32) : 16;
   int cpl_target = cols_target / cpc < 1 ? 1 : cols_target / cpc;
   cpl_target = cpl_target > cpl_max ? cpl_max : cpl_target;
   // At least 4 lanes per bag: with 2 (sixteen bags per warp) an 8-bit D=64
