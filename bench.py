@@ -87,6 +87,9 @@ def parse_args():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-pointer leg")
     ap.add_argument("--no-single", action="store_true", help="skip the single_table sub-records of the default run")
+    ap.add_argument("--peer-ab", action="store_true",
+                    help="workloads 3/4, N > 1: time the same steps again with every pooled row stored into the rank's own "
+                         "buffer instead of its owner's (what the stores across NVLink cost)")
     ap.add_argument("--e2e-batches", type=int, default=12, help="workloads 3/4: global batches of the host-pointer leg")
     ap.add_argument("--e2e-steps", type=int, default=4, help="workloads 0-2: steps of the host-pointer leg")
     ap.add_argument("--cpu-seconds", type=float, default=4.0, help="wall-time bound of the CPU sample")
@@ -454,13 +457,17 @@ def run_single(args, cfg_index, dev, rank, world, steps, warmup, full, seed_shif
             ctx.register_table(host_cit)
             cit_key = host_cit.ctypes.data
 
+        # what a C or C++ caller holds anyway: the raw addresses of its arrays
+        raw = [(x[0].ctypes.data, x[1].ctypes.data, x[2].ctypes.data if x[2] is not None else None, x[3].ctypes.data,
+                x[4].output_size, x[4].index_size) for x in hb]
+        host_submit = _capi.lib().fbgemm_b200_spmdm_host_submit
+        cfg_ref = C.byref(kern.cfg)
+
         def submit(i):
-            idx, off, wts, out, b = hb[i % NUM_BATCHES]
-            rc = _capi.lib().fbgemm_b200_spmdm_host_submit(
-                ctx.handle, i % lanes, C.byref(kern.cfg), b.output_size, b.index_size, w.rows, host_key,
-                idx.ctypes.data, off.ctypes.data, wts.ctypes.data if wts is not None else None, out.ctypes.data,
-                cit_key)
-            _capi.check(rc, "host_submit")
+            p_idx, p_off, p_w, p_out, osz, isz = raw[i % NUM_BATCHES]
+            rc = host_submit(ctx.handle, i % lanes, cfg_ref, osz, isz, w.rows, host_key, p_idx, p_off, p_w, p_out, cit_key)
+            if rc < 0:
+                _capi.check(rc, "host_submit")
 
         host_s = [0.0, 0.0]   # host time inside submit / inside wait
 
@@ -832,6 +839,31 @@ def main_multi(args):
             c.close()
         del sl_h, host_sets, host_out
 
+    # ---- the same steps with no store leaving the GPU (what the peer stores cost) -----------------------------
+    peer_ab = None
+    if args.peer_ab and p2p and world > 1:
+        sl_main = sl
+        sl = ShardedLookup(specs, plan, rank, B, dev, torch.float16, mode="p2p", num_buffers=nbuf, tables=sl_main.tables,
+                           weighted=weighted, index_dtype=tnp, offset_dtype=tnp, route_local=True)
+        for _ in range(3 * bps):
+            global_batch()
+        barrier()
+        m0, m1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        m0.record()
+        fork_lanes()
+        for _ in range(args.steps * bps):
+            global_batch()
+        join_lanes()
+        m1.record()
+        torch.cuda.synchronize(dev)
+        barrier()
+        local_ms = torch.tensor([m0.elapsed_time(m1)], device=dev, dtype=torch.float64)
+        import torch.distributed as dist
+
+        dist.all_reduce(local_ms, op=dist.ReduceOp.MAX)
+        peer_ab = {"local_only_ms_per_global_batch": float(local_ms) / (args.steps * bps)}
+        sl = sl_main
+
     # ---- reduce over ranks ---------------------------------------------------------------------
     red = torch.tensor([ms, -float(ok)], device=dev, dtype=torch.float64)
     tot = torch.tensor([bytes_local, float(launches), float(parity_rows)], device=dev, dtype=torch.float64)
@@ -911,7 +943,11 @@ def main_multi(args):
                          "note": "per GPU: gathered-row bytes of one global batch / device time per global batch (the "
                                  "tables' launches overlap on 4 streams); traffic = DRAM bytes of all lookup kernels of "
                                  "one global batch per GPU"},
-            "e2e": e2e, "cpu_baseline": cpu, "single_table": single}))
+            "e2e": e2e, "cpu_baseline": cpu, "single_table": single,
+            "peer_store_ab": dict(peer_ab, peer_stores_ms_per_global_batch=ms / nbatches,
+                                  note="the same lookups, counters and launch order with every pooled row stored into the "
+                                       "rank's own buffer (no store crosses NVLink) against the benchmark's routing, where "
+                                       "(N-1)/N of each rank's rows are peer stores") if peer_ab else None}))
     if world > 1:
         import torch.distributed as dist
 

@@ -137,7 +137,7 @@ class ShardedLookup:
     def __init__(self, specs: list[TableSpec], plan: TableWisePlan, rank: int, global_batch: int,
                  device: torch.device, out_dtype=torch.float16, mode: str = "p2p", num_buffers: int = 1,
                  tables: dict[int, torch.Tensor] | None = None, group=None, weighted: bool = False,
-                 index_dtype=np.int32, offset_dtype=np.int32):
+                 index_dtype=np.int32, offset_dtype=np.int32, route_local: bool = False):
         import torch.distributed as dist
 
         from . import embedding as E
@@ -194,7 +194,10 @@ class ShardedLookup:
             for b in range(num_buffers):
                 for t in self.local:
                     col = plan.column_start(t) * esize
-                    arr = (C.c_void_p * self.world)(*[base[r] + b * buf_bytes + col for r in range(self.world)])
+                    # route_local (a measuring aid): every slice's rows go to THIS rank's buffer, so the same
+                    # kernels run with no store leaving the GPU; the buffer's contents are then meaningless
+                    dest = [base[self.rank if route_local else r] for r in range(self.world)]
+                    arr = (C.c_void_p * self.world)(*[d + b * buf_bytes + col for d in dest])
                     self._peer_ptrs[(b, t)] = arr
         else:
             self.local_out = torch.zeros((num_buffers, self.B, max(plan.local_dim(rank), 1)), dtype=out_dtype,
