@@ -47,6 +47,7 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
+os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # stdout carries the one JSON line, NCCL's own messages do not
 
 FALLBACK_HBM_GBS = 6650.0
 NUM_BATCHES = 32        # distinct pre-generated batches a single-table run rotates over
@@ -72,7 +73,8 @@ def parse_args():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", type=int, default=3,
                     help="benchmark configuration 0..4: 8-bit, 4-bit, pruned 2-bit single tables; 64 mixed tables "
-                         "(default); 256 large tables")
+                         "(default); 256 large tables; 5: the kernels either side of the lookup (pruning lookups, index "
+                         "remap, sequence lookup), one GPU")
     ap.add_argument("--batches-per-step", type=int, default=16, help="workloads 3/4: global batches per step")
     ap.add_argument("--calls-per-step", type=int, default=512, help="workloads 0-2: functor calls per step (one graph)")
     ap.add_argument("--streams", type=int, default=16, help="workloads 0-2: streams the graph spreads the calls over")
@@ -93,6 +95,9 @@ def parse_args():
     ap.add_argument("--e2e-batches", type=int, default=12, help="workloads 3/4: global batches of the host-pointer leg")
     ap.add_argument("--e2e-steps", type=int, default=4, help="workloads 0-2: steps of the host-pointer leg")
     ap.add_argument("--cpu-seconds", type=float, default=4.0, help="wall-time bound of the CPU sample")
+    ap.add_argument("--callers-only", choices=["hashmap", "array", "sequence", "remap"], default=None,
+                    help="workload 5: one of the caller-side kernels instead of all")
+    ap.add_argument("--caller-iters", type=int, default=20, help="workload 5: timed calls per kernel")
     return ap.parse_args()
 
 
@@ -955,6 +960,148 @@ def main_multi(args):
     return 0
 
 
+# ---- the kernels either side of the pooled lookup (--workload 5) -------------------------------
+
+def _caller_time(fn, iters, warm=3):
+    import torch
+
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(iters + 1)]
+    ev[0].record()
+    for i in range(iters):
+        fn()
+        ev[i + 1].record()
+    torch.cuda.synchronize()
+    ts = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(iters))
+    return ts[len(ts) // 2] * 1e-3
+
+
+def pruning_lookups(res, which, iters, dev):
+    import torch
+
+    import fbgemm_b200 as F
+    from fbgemm_b200 import tbe
+
+    rng = np.random.default_rng(5)
+    T, B, E = 16, 16384, 4_000_000
+    lengths = rng.poisson(30, T * B)
+    offsets = np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)
+    n = int(offsets[-1])
+    indices = rng.integers(0, E, n).astype(np.int32)
+    want = np.where(indices % 2 == 0, indices // 2, -1)   # the even sparse indices are the rows that were kept
+    for idt, mdt in ((np.int32, np.int32), (np.int64, np.int64)):
+        ib, mb = np.dtype(idt).itemsize, np.dtype(mdt).itemsize
+        keys = np.arange(0, E, 2, dtype=idt)
+        dense = np.arange(len(keys), dtype=idt)
+        d_idx = torch.from_numpy(indices.astype(idt)).to(dev)
+        d_off = torch.from_numpy(offsets.astype(idt)).to(dev)
+        if which in (None, "hashmap"):
+            cap = int(len(keys) / 0.8) + 1
+            hto = np.arange(T + 1, dtype=np.int64) * cap
+            table = np.full((T * cap, 2), -1, dtype=mdt)
+            assert tbe.pruned_hashmap_insert(
+                torch.from_numpy(np.tile(keys, T)), torch.from_numpy(np.tile(dense, T)),
+                torch.from_numpy((np.arange(T + 1, dtype=np.int64) * len(keys)).astype(idt)), torch.from_numpy(table),
+                torch.from_numpy(hto))
+            d_tab, d_hto = torch.from_numpy(table).to(dev), torch.from_numpy(hto).to(dev)
+            assert (tbe.pruned_hashmap_lookup(d_idx, d_off, d_tab, d_hto).cpu().numpy() == want).all()
+            dt = _caller_time(lambda: tbe.pruned_hashmap_lookup(d_idx, d_off, d_tab, d_hto), iters)
+            res[f"pruned_hashmap_lookup_index{ib * 8}_table{mb * 8}"] = {
+                "positions": n, "us": round(dt * 1e6, 1), "Gpositions_s": round(n / dt / 1e9, 2),
+                "alg_GBs": round(n * (2 * ib + 2 * mb) / dt / 1e9, 1), "table_MB": round(table.nbytes / 1e6)}
+            del d_tab
+        if which in (None, "array"):
+            remap = np.full(T * E, -1, dtype=mdt)
+            for t in range(T):
+                remap[t * E:(t + 1) * E:2] = dense
+            d_remap = torch.from_numpy(remap).to(dev)
+            d_ro = torch.from_numpy(np.arange(T + 1, dtype=np.int64) * E).to(dev)
+            assert (tbe.pruned_array_lookup(d_idx, d_off, d_remap, d_ro).cpu().numpy() == want).all()
+            dt = _caller_time(lambda: tbe.pruned_array_lookup(d_idx, d_off, d_remap, d_ro), iters)
+            res[f"pruned_array_lookup_index{ib * 8}_map{mb * 8}"] = {
+                "positions": n, "us": round(dt * 1e6, 1), "Gpositions_s": round(n / dt / 1e9, 2),
+                "alg_GBs": round(n * (2 * ib + mb) / dt / 1e9, 1), "map_MB": round(remap.nbytes / 1e6)}
+            del d_remap
+
+
+def sequence_lookup(res, iters, dev):
+    import torch
+
+    import fbgemm_b200 as F
+    from fbgemm_b200 import tbe
+
+    rng = np.random.default_rng(6)
+    T, rows, D, B = 8, 2_000_000, 128, 32768
+    for ty, name in ((tbe.SparseType.INT4, "int4"), (tbe.SparseType.INT8, "int8"), (tbe.SparseType.FP16, "fp16")):
+        for out_ty, oname, ob in ((tbe.SparseType.FP16, "f16", 2), (tbe.SparseType.FP32, "f32", 4)):
+            rb = tbe.padded_row_size_in_bytes(D, ty, 16)
+            w = torch.randint(0, 256, (T * rows * rb,), dtype=torch.uint8, device=dev)
+            lengths = rng.poisson(16, T * B)
+            off = torch.from_numpy(np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)).to(dev)
+            n = int(lengths.sum())
+            idx = torch.randint(0, rows, (n,), dtype=torch.int32, device=dev)
+            op = tbe.IntNBitSequenceEmbedding(w, [t * rows * rb for t in range(T)], [int(ty)] * T, D, 16, out_ty)
+            out = torch.zeros((n, D), dtype=op.out_dtype, device=dev)
+            dt = _caller_time(lambda: op.forward(idx, off, out), iters)
+            assert F.status_read(0)[0]
+            res[f"sequence_lookup_{name}_to_{oname}"] = {
+                "positions": n, "us": round(dt * 1e6, 1), "alg_GBs": round(n * (rb + D * ob + 4) / dt / 1e9, 1),
+                "row_bytes": rb, "out_row_bytes": D * ob}
+            del w, out
+
+
+def index_remap(res, iters, dev):
+    import torch
+
+    import fbgemm_b200 as F
+    from fbgemm_b200 import tbe
+
+    rng = np.random.default_rng(7)
+    lengths = rng.poisson(30, 262144)
+    off = np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)
+    n, U = int(off[-1]), 20_000_000
+    mapping = np.where(rng.random(U) < 0.5, -1, 1).astype(np.int32)
+    mapping[mapping > 0] = np.arange(int((mapping > 0).sum()), dtype=np.int32)
+    d_map, d_off = torch.from_numpy(mapping).to(dev), torch.from_numpy(off).to(dev)
+    d_idx = torch.randint(0, U, (n,), dtype=torch.int32, device=dev)
+    d_w = torch.rand(n, device=dev)
+    dt = _caller_time(lambda: F.compressed_indices_remap(d_idx, d_map, d_off, d_w), iters)
+    res["compressed_indices_remap_weighted"] = {
+        "positions": n, "us": round(dt * 1e6, 1), "Gpositions_s": round(n / dt / 1e9, 2),
+        "alg_GBs": round(n * (4 + 4 + 4 + 0.5 * 8) / dt / 1e9, 1), "launches": 4,
+        "note": "includes the status read-back the call waits for"}
+
+
+def main_callers(args):
+    """Timing of the pruning lookups, ``compressed_indices_remap`` and the
+    sequence ("nobag") lookup on seeded synthetic inputs: CUDA events around
+    each call on torch's current stream, median of ``--caller-iters`` calls
+    after 3 warm-up calls.  ``alg_GBs`` counts the bytes a call has to move once
+    (indices, one hash slot or map entry, the row, the output row), not the
+    sectors it touches.  Shapes: 16 tables x 16384 bags x Poisson(30) indices
+    with half of the keys present at a hash-table load factor of 0.8; 8 tables
+    of 2 M rows x D = 128 and 32768 bags x Poisson(16) per table for the
+    sequence lookup; 262144 bags x Poisson(30) over a 20 M-row map, half
+    pruned, for the remap."""
+    import torch
+
+    dev = torch.device("cuda:0")
+    res = {}
+    only = args.callers_only
+    if only in (None, "hashmap", "array"):
+        pruning_lookups(res, only, args.caller_iters, dev)
+    if only in (None, "sequence"):
+        sequence_lookup(res, args.caller_iters, dev)
+    if only in (None, "remap"):
+        index_remap(res, args.caller_iters, dev)
+    print(json.dumps({"metric": "caller_kernel_times", "unit": "us per call (median)", "n_gpus": 1, "data": "synthetic",
+                      "config": {"workload": "pruning lookups, index remap and sequence lookup", "iters": args.caller_iters},
+                      "records": res}))
+    return 0
+
+
 # ---- the reference arm: the reference's CPU path on the same configuration ---------------------
 
 def reference_table(spec_bits, rows, dim, seed, dev):
@@ -1051,6 +1198,8 @@ def main():
     if not torch.cuda.is_available():
         print(json.dumps({"error": "no CUDA device: fbgemm_b200 has no CPU path"}))
         return 1
+    if args.workload == 5:
+        return main_callers(args)
     return main_multi(args) if args.workload in (3, 4) else main_single(args)
 
 

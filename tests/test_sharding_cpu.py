@@ -138,3 +138,49 @@ def test_a_rank_that_leaves_is_detected_by_the_others():
     assert results[1][0] == "left"
     assert results[0][0] == "exchange failed", results      # detected, not hung
     assert results[0][1] < 60
+
+
+def _rank_with_padded_buffer(rank, world, port, dims, owner, B, q):
+    """As ShardedLookup.exchange does it: the local buffer has at least one
+    column even on a rank that owns no table; only the rank's own columns are
+    sent."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        plan = TableWisePlan(owner, dims, world)
+        local = torch.full((B, max(plan.local_dim(rank), 1)), -1.0)
+        col0 = 0
+        for t in plan.tables_of(rank):
+            bag = torch.arange(B, dtype=torch.float32).view(B, 1)
+            col = torch.arange(dims[t], dtype=torch.float32).view(1, -1)
+            local[:, col0:col0 + dims[t]] = pooled_value(t, bag, col)
+            col0 += dims[t]
+        out = exchange_pooled(local[:, :plan.local_dim(rank)].contiguous(), plan, rank)
+        rows = B // world
+        want = torch.empty((rows, plan.total_dim))
+        for t in range(len(dims)):
+            c0 = plan.column_start(t)
+            bag = torch.arange(rank * rows, (rank + 1) * rows, dtype=torch.float32).view(rows, 1)
+            col = torch.arange(dims[t], dtype=torch.float32).view(1, -1)
+            want[:, c0:c0 + dims[t]] = pooled_value(t, bag, col)
+        q.put((rank, bool(torch.equal(out, want)), tuple(out.shape)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_more_ranks_than_tables():
+    """Rank 1 owns nothing: it sends zero columns and still receives its slice of everyone else's."""
+    dims, owner, world, B = [4, 6], [2, 0], 3, 12
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_rank_with_padded_buffer, args=(r, world, port, dims, owner, B, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert sorted(results) == [(r, True, (4, 10)) for r in range(3)]
