@@ -47,7 +47,24 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
-os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # stdout carries the one JSON line, NCCL's own messages do not
+
+_JSON_OUT = None
+
+
+def claim_stdout():
+    """stdout carries the one JSON line and nothing else: whatever libraries
+    print there from now on (NCCL's version banner, for one) goes to stderr."""
+    global _JSON_OUT
+    if _JSON_OUT is None:
+        sys.stdout.flush()
+        _JSON_OUT = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    out = _JSON_OUT or sys.stdout
+    out.write(json.dumps(line) + "\n")
+    out.flush()
 
 FALLBACK_HBM_GBS = 6650.0
 NUM_BATCHES = 32        # distinct pre-generated batches a single-table run rotates over
@@ -588,7 +605,7 @@ def main_single(args):
                                  "different streams overlap; traffic = DRAM bytes per call from the ncu capture named"},
             "cpu_baseline": rec.get("cpu_baseline"),
         }
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         import torch.distributed as dist
 
@@ -912,7 +929,7 @@ def main_multi(args):
     if rank == 0:
         traffic = TRAFFIC.get(args.workload)
         traffic_ok = traffic and args.scale == 1.0 and args.tables_scale == 1.0 and args.batch_scale == 1.0
-        print(json.dumps({
+        emit(({
             "metric": "gathered_row_GBps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong" if args.workload == 3 else "weak", "vs_baseline": None,
@@ -1096,7 +1113,7 @@ def main_callers(args):
         sequence_lookup(res, args.caller_iters, dev)
     if only in (None, "remap"):
         index_remap(res, args.caller_iters, dev)
-    print(json.dumps({"metric": "caller_kernel_times", "unit": "us per call (median)", "n_gpus": 1, "data": "synthetic",
+    emit(({"metric": "caller_kernel_times", "unit": "us per call (median)", "n_gpus": 1, "data": "synthetic",
                       "config": {"workload": "pruning lookups, index remap and sequence lookup", "iters": args.caller_iters},
                       "records": res}))
     return 0
@@ -1176,7 +1193,7 @@ def main_reference(args):
         scaling = "strong" if args.workload == 3 else "weak"
     r = time_cpu(tabs, threads, cps, max(1, args.steps), 240.0, warmup_steps=max(1, args.warmup))
     gbs = r["bytes"] / r["seconds"] / 1e9
-    print(json.dumps({
+    emit(({
         "impl": "reference", "metric": "gathered_row_GBps", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": r["steps"], "warmup": max(1, args.warmup), "ms_per_step": r["seconds"] / max(r["steps"], 1) * 1e3,
         "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": dtype, "data": "synthetic",
@@ -1191,12 +1208,13 @@ def main_reference(args):
 
 def main():
     args = parse_args()
+    claim_stdout()
     if args.impl == "reference":
         return main_reference(args)
     import torch
 
     if not torch.cuda.is_available():
-        print(json.dumps({"error": "no CUDA device: fbgemm_b200 has no CPU path"}))
+        emit(({"error": "no CUDA device: fbgemm_b200 has no CPU path"}))
         return 1
     if args.workload == 5:
         return main_callers(args)
