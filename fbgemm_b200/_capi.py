@@ -16,6 +16,7 @@ STATUS_SLOTS = 1024
 HOST_LANES = 8
 USER_SLOTS = STATUS_SLOTS - HOST_LANES - 1
 STATUS_PEER_TIMEOUT = 5
+IPC_HANDLE_BYTES = 64
 NOALLOC_MAX_BAGS = 1 << 20
 MAX_PEERS = 8
 OUT_F32 = 0
@@ -126,6 +127,10 @@ SIGNATURES = {
     "fbgemm_b200_spmdm_host": (C.c_int, [_p, _cfgp, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p]),
     "fbgemm_b200_peer_signal": (C.c_int, [_p, C.POINTER(_p), C.c_int, C.c_uint64, _p]),
     "fbgemm_b200_peer_wait": (C.c_int, [_p, _p, C.c_int, C.c_uint64, C.c_uint64, C.c_int, _p]),
+    "fbgemm_b200_peer_buffer_alloc": (C.c_int, [_p, C.c_size_t, C.POINTER(_p), C.c_char_p]),
+    "fbgemm_b200_peer_buffer_open": (C.c_int, [_p, C.c_char_p, C.POINTER(_p)]),
+    "fbgemm_b200_peer_buffer_close": (C.c_int, [_p, _p]),
+    "fbgemm_b200_peer_buffer_free": (C.c_int, [_p, _p]),
     "fbgemm_b200_multi_host_create": (C.c_int, [_p, C.POINTER(TableCall), C.c_int32, C.POINTER(_i64), C.c_int32, _i64,
                                                 _p, C.c_size_t, C.POINTER(PeerSync), C.c_int, C.POINTER(_p)]),
     "fbgemm_b200_multi_host_submit": (C.c_int, [_p, C.POINTER(_p), C.POINTER(_p), C.POINTER(_p), C.POINTER(_i64), _p]),

@@ -308,6 +308,70 @@ int fbgemm_b200_multi_host_wait(fbgemm_b200_multi_host* h, int32_t* info) {
   return rec[0] == 0 ? 1 : 0;
 }
 
+/* ---- buffers that peer processes can map ------------------------------------------- */
+
+int fbgemm_b200_peer_buffer_alloc(fbgemm_b200_ctx* ctx, size_t bytes, void** ptr, unsigned char* handle) {
+  if (!ctx || !ptr || !handle || bytes == 0) {
+    set_error("peer_buffer_alloc: bad argument");
+    return FBGEMM_B200_EINVAL;
+  }
+  static_assert(sizeof(cudaIpcMemHandle_t) == FBGEMM_B200_IPC_HANDLE_BYTES, "handle size");
+  DeviceGuard guard(ctx->device);
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e == cudaSuccess) {
+    e = cudaMemset(p, 0, bytes);
+  }
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) {
+    e = cudaIpcGetMemHandle(&h, p);
+  }
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return fail_cuda(e, "peer_buffer_alloc");
+  }
+  std::memcpy(handle, &h, sizeof(h));
+  *ptr = p;
+  return 0;
+}
+
+int fbgemm_b200_peer_buffer_open(fbgemm_b200_ctx* ctx, const unsigned char* handle, void** ptr) {
+  if (!ctx || !ptr || !handle) {
+    set_error("peer_buffer_open: bad argument");
+    return FBGEMM_B200_EINVAL;
+  }
+  DeviceGuard guard(ctx->device);
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, sizeof(h));
+  void* p = nullptr;
+  const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) {
+    return fail_cuda(e, "peer_buffer_open");
+  }
+  *ptr = p;
+  return 0;
+}
+
+int fbgemm_b200_peer_buffer_close(fbgemm_b200_ctx* ctx, void* ptr) {
+  if (!ctx || !ptr) {
+    set_error("peer_buffer_close: bad argument");
+    return FBGEMM_B200_EINVAL;
+  }
+  DeviceGuard guard(ctx->device);
+  const cudaError_t e = cudaIpcCloseMemHandle(ptr);
+  return e == cudaSuccess ? 0 : fail_cuda(e, "peer_buffer_close");
+}
+
+int fbgemm_b200_peer_buffer_free(fbgemm_b200_ctx* ctx, void* ptr) {
+  if (!ctx || !ptr) {
+    set_error("peer_buffer_free: bad argument");
+    return FBGEMM_B200_EINVAL;
+  }
+  DeviceGuard guard(ctx->device);
+  const cudaError_t e = cudaFree(ptr);
+  return e == cudaSuccess ? 0 : fail_cuda(e, "peer_buffer_free");
+}
+
 /* ---- the counters on their own --------------------------------------------------- */
 
 int fbgemm_b200_peer_signal(fbgemm_b200_ctx* ctx, void* const* flags, int num_flags, uint64_t value, void* stream) {

@@ -137,7 +137,8 @@ class ShardedLookup:
     def __init__(self, specs: list[TableSpec], plan: TableWisePlan, rank: int, global_batch: int,
                  device: torch.device, out_dtype=torch.float16, mode: str = "p2p", num_buffers: int = 1,
                  tables: dict[int, torch.Tensor] | None = None, group=None, weighted: bool = False,
-                 index_dtype=np.int32, offset_dtype=np.int32, route_local: bool = False):
+                 index_dtype=np.int32, offset_dtype=np.int32, route_local: bool = False,
+                 rendezvous: str = "symmetric_memory"):
         import torch.distributed as dist
 
         from . import embedding as E
@@ -166,27 +167,29 @@ class ShardedLookup:
         esize = 2 if out_dtype == torch.float16 else 4
         self.num_buffers = num_buffers
         if mode == "p2p":
-            # Output buffers in symmetric memory: every rank learns the peers' addresses.
-            if self.world > 1:
+            # Output buffers and counters every rank can address: torch's symmetric memory, or (rendezvous="ipc") the
+            # library's own peer buffers, their CUDA IPC handles exchanged through the process group.
+            # Counters: [ready|ack][buffer][writer rank], 8 bytes each, zero to start with.
+            out_shape, flag_shape = (num_buffers, self.rows, plan.total_dim), (2, num_buffers, self.world)
+            assert rendezvous in ("symmetric_memory", "ipc")
+            if self.world == 1:
+                self.out = torch.zeros(out_shape, dtype=out_dtype, device=device)
+                self._flags = torch.zeros(flag_shape, dtype=torch.int64, device=device)
+                base, self._flag_base = [self.out.data_ptr()], [self._flags.data_ptr()]
+            elif rendezvous == "ipc":
+                self.out, base = self._ipc_buffer(out_shape, out_dtype)
+                self._flags, self._flag_base = self._ipc_buffer(flag_shape, torch.int64)
+            else:
                 import torch.distributed._symmetric_memory as symm
 
-                self._symm = symm.empty((num_buffers, self.rows, plan.total_dim), dtype=out_dtype, device=device)
-                self._hdl = symm.rendezvous(self._symm, self.group)
-                base = [int(p) for p in self._hdl.buffer_ptrs]
-                self.out = self._symm
-            else:
-                self.out = torch.zeros((num_buffers, self.rows, plan.total_dim), dtype=out_dtype, device=device)
-                base = [self.out.data_ptr()]
-            # Counters [ready|ack][buffer][writer rank], 8 bytes each, zero to start with.
-            if self.world > 1:
-                self._flags = symm.empty((2, num_buffers, self.world), dtype=torch.int64, device=device)
+                self.out = symm.empty(out_shape, dtype=out_dtype, device=device)
+                base = [int(p) for p in symm.rendezvous(self.out, self.group).buffer_ptrs]
+                self._flags = symm.empty(flag_shape, dtype=torch.int64, device=device)
                 self._flags.zero_()
                 self._flag_base = [int(p) for p in symm.rendezvous(self._flags, self.group).buffer_ptrs]
+            if self.world > 1:
                 torch.cuda.synchronize(device)
                 dist.barrier(group=self.group)   # nobody signals before everybody's counters are zero
-            else:
-                self._flags = torch.zeros((2, num_buffers, 1), dtype=torch.int64, device=device)
-                self._flag_base = [self._flags.data_ptr()]
             self.steps = [0] * num_buffers       # steps begun per buffer
             buf_bytes = self.rows * plan.total_dim * esize
             # peer pointer arrays per (buffer, table): column offset folded in
@@ -203,6 +206,53 @@ class ShardedLookup:
             self.local_out = torch.zeros((num_buffers, self.B, max(plan.local_dim(rank), 1)), dtype=out_dtype,
                                          device=device)
             self.out = torch.zeros((num_buffers, self.rows, plan.total_dim), dtype=out_dtype, device=device)
+
+    def _ipc_buffer(self, shape, dtype):
+        """A zeroed device tensor of ``shape`` in a buffer the peer processes
+        can map (``fbgemm_b200_peer_buffer_*``), and the addresses of every
+        rank's copy as seen from this process."""
+        import torch.distributed as dist
+
+        lib = _capi.lib()
+        nbytes = int(np.prod(shape)) * torch.empty((), dtype=dtype).element_size()
+        ptr, handle = C.c_void_p(), C.create_string_buffer(_capi.IPC_HANDLE_BYTES)
+        _capi.check(lib.fbgemm_b200_peer_buffer_alloc(self.ctx.handle, nbytes, C.byref(ptr), handle), "peer_buffer_alloc")
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle.raw, group=self.group)
+        base = []
+        for r in range(self.world):
+            if r == self.rank:
+                base.append(int(ptr.value))
+            else:
+                peer = C.c_void_p()
+                _capi.check(lib.fbgemm_b200_peer_buffer_open(self.ctx.handle, handles[r], C.byref(peer)), "peer_buffer_open")
+                base.append(int(peer.value))
+        self._ipc_keep = getattr(self, "_ipc_keep", []) + [(int(ptr.value), [b for r, b in enumerate(base) if r != self.rank])]
+
+        class _Raw:   # the buffer as torch sees it (__cuda_array_interface__)
+            pass
+
+        raw = _Raw()
+        typestr = {torch.float16: "<f2", torch.float32: "<f4", torch.int64: "<i8"}[dtype]
+        raw.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr.value), False),
+                                        "version": 2, "strides": None}
+        return torch.as_tensor(raw, device=self.device), base
+
+    def close(self) -> None:
+        """Unmap the peers' buffers and free this rank's (``rendezvous="ipc"``);
+        every rank calls it, after a barrier that ends the last step."""
+        lib = _capi.lib()
+        keep, self._ipc_keep = getattr(self, "_ipc_keep", []), []
+        for _, peers in keep:
+            for p in peers:
+                lib.fbgemm_b200_peer_buffer_close(self.ctx.handle, p)
+        if keep and self.world > 1:
+            import torch.distributed as dist
+
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.group)   # nobody frees what a peer still has mapped
+        for own, _ in keep:
+            lib.fbgemm_b200_peer_buffer_free(self.ctx.handle, own)
 
     def launch(self, batches: dict, buffer: int = 0, slot_base: int = 0, stream=None, streams=None) -> None:
         """Enqueue the lookups of every local table for one global batch

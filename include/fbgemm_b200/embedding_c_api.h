@@ -645,6 +645,31 @@ FBGEMM_B200_API int fbgemm_b200_peer_wait(
     int slot,
     void* stream);
 
+/*
+ * Buffers for the two calls above and for the peer_out of a sharded lookup,
+ * for callers with one process per GPU and no framework to exchange addresses
+ * for them: _alloc gives `bytes` of zeroed device memory on the context's
+ * device and a 64-byte handle; the handle travels to the peer processes of the
+ * same box over any channel (a file, a socket, MPI), where _open maps the
+ * buffer (the address it returns is valid on that process's device; loads and
+ * stores through it cross NVLink).  _close unmaps, _free releases the original
+ * (after the peers have closed it).  CUDA IPC underneath; these calls allocate
+ * and synchronise - set-up time only.  No counterpart in the reference, whose
+ * multi-GPU operators live in one process.  Return 0 or a negative code.
+ */
+#define FBGEMM_B200_IPC_HANDLE_BYTES 64
+FBGEMM_B200_API int fbgemm_b200_peer_buffer_alloc(
+    fbgemm_b200_ctx* ctx,
+    size_t bytes,
+    void** ptr,
+    unsigned char* handle /* [FBGEMM_B200_IPC_HANDLE_BYTES] */);
+FBGEMM_B200_API int fbgemm_b200_peer_buffer_open(
+    fbgemm_b200_ctx* ctx,
+    const unsigned char* handle,
+    void** ptr);
+FBGEMM_B200_API int fbgemm_b200_peer_buffer_close(fbgemm_b200_ctx* ctx, void* ptr);
+FBGEMM_B200_API int fbgemm_b200_peer_buffer_free(fbgemm_b200_ctx* ctx, void* ptr);
+
 /* The counters of one rank of a table-wise sharded job, as
  * fbgemm_b200_multi_host_create takes them.  "ready": rank r writes
  * ready_flags[g] (a word in GPU g's memory, slot r of g's ready_local array)

@@ -113,6 +113,26 @@ def main():
         assert (got.view(np.uint16) == expected(host).view(np.uint16)).all(), f"rank {rank} ordered step {step} differs"
     dist.barrier()
 
+    # The same ordered steps on buffers from the library's own rendezvous (CUDA IPC handles through the process
+    # group) instead of torch's symmetric memory.
+    sl_ipc = ShardedLookup(specs, plan, rank, B, dev, torch.float16, mode="p2p", num_buffers=2, tables=sl.tables,
+                           rendezvous="ipc")
+    for step in range(4):
+        host = step_inputs(50 + step)
+        b = {t: Batch(torch.from_numpy(host[t][0]).to(dev), torch.from_numpy(host[t][1]).to(dev), None, B,
+                      len(host[t][0]), len(host[t][0])) for t in sl_ipc.local}
+        buf = step % 2
+        n = sl_ipc.step(b, buffer=buf, slot_base=150, streams=streams)
+        got = sl_ipc.out[buf].cpu().numpy()
+        sl_ipc.release(buf, n)
+        for i in range(len(sl_ipc.local)):
+            ok, info = E.status_read(150 + i, dev.index)
+            assert ok, (step, info)
+        assert (got.view(np.uint16) == expected(host).view(np.uint16)).all(), f"rank {rank} ipc step {step} differs"
+    torch.cuda.synchronize()
+    dist.barrier()
+    sl_ipc.close()
+
     # Host arrays in, this rank's slice out, through fbgemm_b200_multi_host_* with the counters.
     sl = ShardedLookup(specs, plan, rank, B, dev, torch.float16, mode="p2p", num_buffers=2, tables=sl.tables)
     calls = [sl.make_host_call(bf, {t: 20 * B for t in sl.local}, slot=200 + bf) for bf in range(2)]
