@@ -805,8 +805,24 @@ def main_multi(args):
                              weighted=weighted, index_dtype=tnp, offset_dtype=tnp)
         caps = {t: max(sets[s][t].index_size for s in range(NUM_SETS)) for t in sl.local}
         calls = [sl_h.make_host_call(b, caps, slot=450 + b) for b in range(nbuf)]
-        pin = lambda x: x.cpu().pin_memory().numpy() if x is not None else None  # noqa: E731
-        host_sets = [{t: (pin(d[t].indices), pin(d[t].offsets), pin(d[t].weights)) for t in sl.local} for d in sets]
+
+        def host_views(arrays):
+            """The arrays back to back in ONE page-locked block - how the reference's multi-table caller holds
+            its indices, offsets and weights - and a view of the block per table."""
+            if arrays[0] is None:
+                return [None] * len(arrays)
+            block = torch.empty(sum(a.numel() for a in arrays), dtype=arrays[0].dtype).pin_memory()
+            views, at = [], 0
+            for a in arrays:
+                block[at:at + a.numel()].copy_(a)
+                views.append(block[at:at + a.numel()].numpy())
+                at += a.numel()
+            return views
+
+        host_sets = []
+        for d in sets:
+            cols = [host_views([getattr(d[t], name) for t in sl.local]) for name in ("indices", "offsets", "weights")]
+            host_sets.append({t: (cols[0][k], cols[1][k], cols[2][k]) for k, t in enumerate(sl.local)})
         host_out = [torch.zeros((rows, plan.total_dim), dtype=torch.float16).pin_memory().numpy() for _ in range(nbuf)]
 
         def run_host(nb):
@@ -853,8 +869,8 @@ def main_multi(args):
                "ms_per_step": dt / nb * bps * 1e3, "unit": "GB/s",
                "h2d_bytes_per_step": round(float(red[2]) * bps), "d2h_bytes_per_step": round(float(red[3]) * bps),
                "results_ok": bool(good),
-               "path": f"fbgemm_b200_multi_host_submit/wait on every rank, {nbuf} pipelined handles, pinned host arrays: "
-                       "indices+offsets(+weights) of the rank's tables up, lookups with peer stores, ready/ack counters, "
+               "path": f"fbgemm_b200_multi_host_submit/wait on every rank, {nbuf} pipelined handles, per-table views of "
+                       "one pinned indices, one offsets (and one weights) array per step: those go up, lookups with peer stores, ready/ack counters, "
                        "the rank's [B/G, total_D] slice down; tables resident",
                "timer": "host perf_counter bracketed by barriers and device synchronisation, max over ranks"}
         for c in calls:

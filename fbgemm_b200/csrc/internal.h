@@ -230,6 +230,8 @@ struct StageSegment {
   size_t bytes;
 };
 cudaError_t launch_stage_inputs(const StageSegment (&seg)[3], cudaStream_t stream);
+// A call's 4-word error record to page-locked host memory (`host_view` is the address the GPU sees it at).
+cudaError_t launch_status_to_host(const int32_t* status, int32_t* host_view, cudaStream_t stream);
 
 // Counters between the GPUs of a sharded lookup (peer_sync_kernels.cu): publish
 // `value` to n words (one per peer, possibly in peer memory), and wait until n

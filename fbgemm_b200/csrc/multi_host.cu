@@ -29,6 +29,12 @@ constexpr int kSideStreams = 3;
 size_t up16(size_t v) {
   return (v + 15) & ~size_t(15);
 }
+// Consecutive host arrays that touch or overlap in memory go up as one copy.
+struct HostRun {
+  const uint8_t* src;
+  size_t bytes;
+  size_t at;  // byte offset inside the staging block
+};
 }  // namespace
 
 struct fbgemm_b200_multi_host {
@@ -38,7 +44,8 @@ struct fbgemm_b200_multi_host {
   std::vector<fbgemm_b200_table_call> calls;
   std::vector<std::vector<void*>> peer_out;  // copies of the callers' pointer arrays
   std::vector<int64_t> capacity;             // indices a table's staging can hold
-  std::vector<size_t> idx_at, off_at, w_at;  // byte offsets inside the staging block
+  std::vector<size_t> idx_at, off_at, w_at;  // this step's byte offsets inside the staging block
+  std::vector<HostRun> runs;                 // this step's uploads
   DeviceBuffer staging;
   int num_peers = 0;
   int64_t bags_per_peer = 0;
@@ -144,13 +151,14 @@ int fbgemm_b200_multi_host_create(
       h->peer_out.back().assign(c.peer_out, c.peer_out + num_peers);
     }
     h->capacity.push_back(index_capacity[t]);
-    h->idx_at.push_back(at);
-    at += up16((size_t)index_capacity[t] * c.cfg.index_bytes);
-    h->off_at.push_back(at);
-    at += up16((size_t)(c.output_size + 1) * c.cfg.offset_bytes);
-    h->w_at.push_back(at);
-    at += c.cfg.has_weight ? up16((size_t)index_capacity[t] * sizeof(float)) : 0;
+    // every array may start on its own 16-byte line, shifted by its host address modulo 16
+    at += up16((size_t)index_capacity[t] * c.cfg.index_bytes) + 32;
+    at += up16((size_t)(c.output_size + 1) * c.cfg.offset_bytes) + 32;
+    at += c.cfg.has_weight ? up16((size_t)index_capacity[t] * sizeof(float)) + 32 : 0;
   }
+  h->idx_at.assign((size_t)num_tables, 0);
+  h->off_at.assign((size_t)num_tables, 0);
+  h->w_at.assign((size_t)num_tables, 0);
   if (sync) {
     h->has_sync = true;
     h->ready_flags.assign(sync->ready_flags, sync->ready_flags + num_peers);
@@ -219,19 +227,54 @@ int fbgemm_b200_multi_host_submit(
   if (h->has_sync) {
     e = launch_peer_wait(h->ack_local, h->num_peers, step - 1, h->timeout_us, status, h->stream);
   }
-  for (size_t t = 0; t < T && e == cudaSuccess; ++t) {
-    const fbgemm_b200_table_call& c = h->calls[t];
-    const size_t n = (size_t)index_sizes[t];
-    if (n) {
-      e = cudaMemcpyAsync(st + h->idx_at[t], indices[t], n * c.cfg.index_bytes, cudaMemcpyHostToDevice, h->stream);
+  // Lay the step's arrays out in the staging block the way they lie in host memory: arrays that touch or overlap
+  // there (per-table views of ONE indices, ONE offsets and ONE weights array, which is what the reference's
+  // multi-table caller holds) go up as one copy.  The number of copies matters: each waits for its own completion
+  // word, and while another handle's rows are on their way to the host those words queue behind that transfer -
+  // measured with 64 separate tables, 192 copies took 7.7 ms beside a 330 MB download and 2.9 ms alone.
+  for (int merge = 1; merge >= 0; --merge) {
+    h->runs.clear();
+    size_t cursor = 0;
+    auto place = [&](const void* host, size_t bytes) -> size_t {
+      const uint8_t* src = static_cast<const uint8_t*>(host);
+      if (merge && !h->runs.empty()) {
+        HostRun& r = h->runs.back();
+        if (src >= r.src && src <= r.src + r.bytes) {
+          const size_t off = (size_t)(src - r.src);
+          r.bytes = off + bytes > r.bytes ? off + bytes : r.bytes;
+          cursor = r.at + r.bytes;
+          return r.at + off;
+        }
+      }
+      cursor = up16(cursor) + (reinterpret_cast<uintptr_t>(src) & 15);
+      h->runs.push_back(HostRun{src, bytes, cursor});
+      cursor += bytes;
+      return cursor - bytes;
+    };
+    // all indices, then all offsets, then all weights: the order in which a caller's three arrays are contiguous
+    for (size_t t = 0; t < T; ++t) {
+      const size_t n = (size_t)index_sizes[t];
+      h->idx_at[t] = n ? place(indices[t], n * h->calls[t].cfg.index_bytes) : 0;
     }
-    if (e == cudaSuccess) {
-      e = cudaMemcpyAsync(st + h->off_at[t], offsets[t], (size_t)(c.output_size + 1) * c.cfg.offset_bytes,
-                          cudaMemcpyHostToDevice, h->stream);
+    for (size_t t = 0; t < T; ++t) {
+      h->off_at[t] = place(offsets[t], (size_t)(h->calls[t].output_size + 1) * h->calls[t].cfg.offset_bytes);
     }
-    if (e == cudaSuccess && c.cfg.has_weight && n) {
-      e = cudaMemcpyAsync(st + h->w_at[t], weights[t], n * sizeof(float), cudaMemcpyHostToDevice, h->stream);
+    for (size_t t = 0; t < T; ++t) {
+      const size_t n = (size_t)index_sizes[t];
+      h->w_at[t] = h->calls[t].cfg.has_weight && n ? place(weights[t], n * sizeof(float)) : 0;
     }
+    for (size_t k = 0; k < h->runs.size() && e == cudaSuccess; ++k) {
+      const HostRun& r = h->runs[k];
+      e = cudaMemcpyAsync(st + r.at, r.src, r.bytes, cudaMemcpyHostToDevice, h->stream);
+    }
+    // A merged range may span two page-locked allocations that happen to be neighbours; if the runtime refuses such
+    // a copy, send every array on its own.
+    if (e == cudaErrorInvalidValue && merge && h->runs.size() < 3 * T) {
+      cudaGetLastError();
+      e = cudaSuccess;
+      continue;
+    }
+    break;
   }
   if (e != cudaSuccess) {
     return fail_cuda(e, "multi_host_submit: input upload");
@@ -277,7 +320,7 @@ int fbgemm_b200_multi_host_submit(
     e = launch_peer_signal(h->ack_flags.data(), h->num_peers, step, h->stream);
   }
   if (e == cudaSuccess) {
-    e = cudaMemcpyAsync(h->h_status.ptr, status, 16, cudaMemcpyDeviceToHost, h->stream);
+    e = launch_status_to_host(status, static_cast<int32_t*>(h->h_status.ptr), h->stream);
   }
   if (e != cudaSuccess) {
     return fail_cuda(e, "multi_host_submit");

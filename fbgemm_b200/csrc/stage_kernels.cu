@@ -50,7 +50,23 @@ __global__ void __launch_bounds__(kStageThreads) stage_inputs(StageSegment a, St
   stage_segment(c, tid, nth);
 }
 
+// The 4-word error record of a call, written to page-locked host memory by a
+// kernel: a DMA copy of these 16 bytes would queue behind whatever download
+// another stream has in the copy engine.
+__global__ void status_to_host(const int32_t* __restrict__ status, int32_t* __restrict__ host) {
+  if (threadIdx.x < 4) {
+    host[threadIdx.x] = status[threadIdx.x];
+  }
+  __threadfence_system();
+}
+
 }  // namespace
+
+cudaError_t launch_status_to_host(const int32_t* status, int32_t* host_view, cudaStream_t stream) {
+  status_to_host<<<1, 32, 0, stream>>>(status, host_view);
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_stage_inputs(const StageSegment (&seg)[3], cudaStream_t stream) {
   stage_inputs<<<kStageBlocks, kStageThreads, 0, stream>>>(seg[0], seg[1], seg[2]);

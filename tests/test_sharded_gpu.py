@@ -170,3 +170,63 @@ def test_ordered_steps_and_host_call_on_one_gpu(gpu_ctx, oracle):
     call.submit([host[t][0] for t in sl2.local], [host[t][1] for t in sl2.local], None, out_host)
     assert call.wait()[0]
     call.close()
+
+
+@pytest.mark.parametrize("layout", ["one_block", "shared_offsets", "odd_start", "reversed"])
+def test_host_call_with_arrays_that_touch_in_host_memory(gpu_ctx, oracle, layout):
+    """The host-pointer multi-table call sends arrays that touch or overlap in
+    host memory as one copy.  one_block: per-table views of one pinned indices
+    and one pinned offsets array; shared_offsets: the reference caller's form,
+    ONE offsets array of T*B+1 positions into ONE indices array, table t's
+    view starting at element t*B (neighbours share an element); odd_start:
+    the block starts 4 bytes past a 16-byte line; reversed: the views of the
+    block are handed over last table first (nothing to merge)."""
+    from fbgemm_b200.sharding import ShardedLookup, TableWisePlan
+
+    B, dev = 64, torch.device("cuda", 0)
+    specs, host = _specs_and_batches(B, seed=40)
+    T = len(specs)
+    plan = TableWisePlan([0] * T, [s.dim for s in specs], 1)
+    sl = ShardedLookup(specs, plan, 0, B, dev, torch.float16, mode="p2p", num_buffers=1)
+    tables = {t: sl.tables[t].cpu().numpy() for t in sl.local}
+    call = sl.make_host_call(0, {t: 2000 for t in sl.local}, slot=70)
+    out_host = torch.zeros((B, plan.total_dim), dtype=torch.float16).pin_memory().numpy()
+    pad = 1 if layout == "odd_start" else 0
+    n_idx = sum(len(host[t][0]) for t in range(T))
+    idx_block = torch.zeros(n_idx + pad, dtype=torch.int32).pin_memory().numpy()[pad:]
+    idx_views, at = [], 0
+    for t in range(T):
+        n = len(host[t][0])
+        idx_block[at:at + n] = host[t][0]
+        idx_views.append(idx_block[at:at + n])
+        at += n
+    if layout == "shared_offsets":
+        off_block = torch.zeros(T * B + 1, dtype=torch.int32).pin_memory().numpy()
+        at = 0
+        for t in range(T):
+            off_block[t * B:(t + 1) * B + 1] = host[t][1] + at
+            at += len(host[t][0])
+        off_views = [off_block[t * B:(t + 1) * B + 1] for t in range(T)]
+    else:
+        off_block = torch.zeros(T * (B + 1) + pad, dtype=torch.int32).pin_memory().numpy()[pad:]
+        for t in range(T):
+            off_block[t * (B + 1):(t + 1) * (B + 1)] = host[t][1]
+        off_views = [off_block[t * (B + 1):(t + 1) * (B + 1)] for t in range(T)]
+    order = list(range(T))
+    if layout == "reversed":
+        # the handle's tables keep their order; what changes is where each table's arrays lie
+        idx_block2 = torch.zeros(n_idx, dtype=torch.int32).pin_memory().numpy()
+        at = n_idx
+        for t in range(T):
+            n = len(host[t][0])
+            at -= n
+            idx_block2[at:at + n] = host[t][0]
+            idx_views[t] = idx_block2[at:at + n]
+    for _ in range(2):
+        out_host[:] = 0
+        call.submit([idx_views[t] for t in order], [off_views[t] for t in order], None, out_host)
+        ok, info = call.wait()
+        assert ok, info
+        want = _oracle_rows(oracle, specs, plan, tables, host, 0, B)
+        np.testing.assert_array_equal(out_host.view(np.uint16), want.view(np.uint16))
+    call.close()
