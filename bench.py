@@ -464,7 +464,7 @@ def run_single(args, cfg_index, dev, rank, world, steps, warmup, full, seed_shif
 
         from fbgemm_b200 import _capi
 
-        lanes = 8
+        lanes = _capi.HOST_LANES
         hb = []
         for b in batches:
             pin = lambda t: t.cpu().pin_memory().numpy() if t is not None else None  # noqa: E731
@@ -530,7 +530,7 @@ def run_single(args, cfg_index, dev, rank, world, steps, warmup, full, seed_shif
                                            "note": "one host thread issues every call: the time inside submit (checks, "
                                                    "pointer queries, one staging launch or three copies, the lookup, two "
                                                    "downloads) bounds the rate when the GPU side is shorter"},
-                      "path": "fbgemm_b200_spmdm_host_submit/wait, 8 pipelined lanes, pinned host buffers, table resident",
+                      "path": f"fbgemm_b200_spmdm_host_submit/wait, {lanes} pipelined lanes, pinned host buffers, table resident",
                       "timer": "host perf_counter bracketed by device synchronisation"}
         ctx.unregister_table(host_tbl)
         if host_cit is not None:

@@ -13,7 +13,7 @@ import os
 from . import build as _build
 
 STATUS_SLOTS = 1024
-HOST_LANES = 8
+HOST_LANES = 16
 USER_SLOTS = STATUS_SLOTS - HOST_LANES - 1
 STATUS_PEER_TIMEOUT = 5
 IPC_HANDLE_BYTES = 64

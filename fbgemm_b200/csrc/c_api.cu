@@ -1231,7 +1231,8 @@ int fbgemm_b200_spmdm_host_submit(
   // it is used only where the upload is the larger transfer; otherwise the
   // three pieces go up as DMA copies.
   const bool all_pinned = (!idx_bytes || v_idx) && v_off && (!n_w || v_w);
-  if (all_pinned && in_bytes > out_bytes) {
+  const bool upload_dominant = all_pinned && in_bytes > out_bytes;
+  if (upload_dominant) {
     const StageSegment seg[3] = {
         {v_idx, di, idx_bytes}, {v_off, di + off_at, off_bytes}, {v_w, di + w_at, n_w * sizeof(float)}};
     e = launch_stage_inputs(seg, L.stream);
@@ -1297,7 +1298,14 @@ int fbgemm_b200_spmdm_host_submit(
                           cudaMemcpyDeviceToHost, L.stream);
   }
   if (e == cudaSuccess) {
-    e = cudaMemcpyAsync(L.h_status.ptr, ctx->status + 4 * slot, 16, cudaMemcpyDeviceToHost, L.stream);
+    // The status record follows the rows.  As a DMA copy it takes its turn in the copy engine behind the other
+    // lanes' rows; where the uploads are the larger transfer that wait is what holds the lane back, and a one-warp
+    // kernel writes the record to the page-locked word instead (measured on the 4-bit configuration with 8 lanes:
+    // 31.8 -> 27.5 us per call).  Where the rows are the larger transfer the copy stays: with the kernel the 8-bit
+    // configuration ran 9 % faster and the pruned 2-bit one 15 % slower.
+    e = upload_dominant
+            ? launch_status_to_host(ctx->status + 4 * slot, static_cast<int32_t*>(L.h_status.ptr), L.stream)
+            : cudaMemcpyAsync(L.h_status.ptr, ctx->status + 4 * slot, 16, cudaMemcpyDeviceToHost, L.stream);
   }
   if (e != cudaSuccess) {
     return fail_cuda(e, "result download");

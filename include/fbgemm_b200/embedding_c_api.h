@@ -74,7 +74,7 @@ extern "C" {
 /* Number of status slots a context owns (see fbgemm_b200_spmdm_launch). */
 #define FBGEMM_B200_STATUS_SLOTS 1024
 /* Number of staging lanes of the host-pointer pipeline. */
-#define FBGEMM_B200_HOST_LANES 8
+#define FBGEMM_B200_HOST_LANES 16
 /* Status slots a caller may pass: 0 .. FBGEMM_B200_USER_SLOTS - 1.  The rest
  * are the library's (one for the index remap, one per host-pointer lane). */
 #define FBGEMM_B200_USER_SLOTS (FBGEMM_B200_STATUS_SLOTS - FBGEMM_B200_HOST_LANES - 1)
