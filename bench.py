@@ -853,6 +853,7 @@ def main_multi(args):
             for t in range(len(specs)):
                 c0 = plan.column_start(t)
                 good = good and same_bits(hb[sample[mine] - rank * rows][:, c0:c0 + specs[t].dim], expected[t][mine])
+        phases = np.mean([c.last_step_ms() for c in calls], axis=0)    # this rank's last step on each handle
         h2d = float(np.mean([sum(a.nbytes for tup in hs.values() for a in tup if a is not None) for hs in host_sets]))
         d2h = float(host_out[0].nbytes + 16)
         red = torch.tensor([dt, -float(good), h2d, d2h], device=dev, dtype=torch.float64)
@@ -869,6 +870,10 @@ def main_multi(args):
                "ms_per_step": dt / nb * bps * 1e3, "unit": "GB/s",
                "h2d_bytes_per_step": round(float(red[2]) * bps), "d2h_bytes_per_step": round(float(red[3]) * bps),
                "results_ok": bool(good),
+               "last_step_ms": {"uploads": float(phases[0]), "lookups_and_counters": float(phases[1]),
+                                "download": float(phases[2]),
+                                "note": "device time of the phases of rank 0's last step on each handle, averaged; "
+                                        "the handles' phases overlap, so they add up to more than ms_per_global_batch"},
                "path": f"fbgemm_b200_multi_host_submit/wait on every rank, {nbuf} pipelined handles, per-table views of "
                        "one pinned indices, one offsets (and one weights) array per step: those go up, lookups with peer stores, ready/ack counters, "
                        "the rank's [B/G, total_D] slice down; tables resident",

@@ -63,6 +63,8 @@ struct fbgemm_b200_multi_host {
   cudaEvent_t join[kSideStreams] = {};
   PinnedBuffer h_status;
   bool busy = false;
+  cudaEvent_t mark[4] = {};  // step start, uploads done, rows complete, download done
+  bool timed = false;        // the marks belong to a step that wait() has returned
 };
 
 extern "C" {
@@ -85,6 +87,11 @@ void fbgemm_b200_multi_host_destroy(fbgemm_b200_multi_host* h) {
   }
   if (h->fork) {
     cudaEventDestroy(h->fork);
+  }
+  for (cudaEvent_t m : h->mark) {
+    if (m) {
+      cudaEventDestroy(m);
+    }
   }
   if (h->stream) {
     cudaStreamDestroy(h->stream);
@@ -181,6 +188,9 @@ int fbgemm_b200_multi_host_create(
       e = cudaEventCreateWithFlags(&h->join[i], cudaEventDisableTiming);
     }
   }
+  for (int i = 0; i < 4 && e == cudaSuccess; ++i) {
+    e = cudaEventCreate(&h->mark[i]);
+  }
   if (e == cudaSuccess) {
     e = reserve(h->h_status, 16);
   }
@@ -222,9 +232,10 @@ int fbgemm_b200_multi_host_submit(
   int32_t* status = ctx->status + 4 * h->slot;
   uint8_t* st = static_cast<uint8_t*>(h->staging.ptr);
   const uint64_t step = h->step + 1;
-  cudaError_t e = cudaSuccess;
+  h->timed = false;
+  cudaError_t e = cudaEventRecord(h->mark[0], h->stream);
   // The buffers this step writes were last read as step - 1: wait for every consumer's word.
-  if (h->has_sync) {
+  if (e == cudaSuccess && h->has_sync) {
     e = launch_peer_wait(h->ack_local, h->num_peers, step - 1, h->timeout_us, status, h->stream);
   }
   // Lay the step's arrays out in the staging block the way they lie in host memory: arrays that touch or overlap
@@ -280,7 +291,10 @@ int fbgemm_b200_multi_host_submit(
     return fail_cuda(e, "multi_host_submit: input upload");
   }
   // One lookup per table, round-robin over the handle's stream and its side streams.
-  e = cudaEventRecord(h->fork, h->stream);
+  e = cudaEventRecord(h->mark[1], h->stream);
+  if (e == cudaSuccess) {
+    e = cudaEventRecord(h->fork, h->stream);
+  }
   for (int i = 0; i < kSideStreams && e == cudaSuccess; ++i) {
     e = cudaStreamWaitEvent(h->side[i], h->fork, 0);
   }
@@ -314,7 +328,13 @@ int fbgemm_b200_multi_host_submit(
     }
   }
   if (e == cudaSuccess) {
+    e = cudaEventRecord(h->mark[2], h->stream);
+  }
+  if (e == cudaSuccess) {
     e = cudaMemcpyAsync(out_host, h->out_dev, h->out_bytes, cudaMemcpyDeviceToHost, h->stream);
+  }
+  if (e == cudaSuccess) {
+    e = cudaEventRecord(h->mark[3], h->stream);
   }
   if (e == cudaSuccess && h->has_sync) {
     e = launch_peer_signal(h->ack_flags.data(), h->num_peers, step, h->stream);
@@ -341,6 +361,7 @@ int fbgemm_b200_multi_host_wait(fbgemm_b200_multi_host* h, int32_t* info) {
   if (e != cudaSuccess) {
     return fail_cuda(e, "multi_host_wait");
   }
+  h->timed = true;
   const int32_t* rec = static_cast<const int32_t*>(h->h_status.ptr);
   if (info) {
     std::memcpy(info, rec, 16);
@@ -352,6 +373,21 @@ int fbgemm_b200_multi_host_wait(fbgemm_b200_multi_host* h, int32_t* info) {
 }
 
 /* ---- buffers that peer processes can map ------------------------------------------- */
+
+int fbgemm_b200_multi_host_last_step_ms(fbgemm_b200_multi_host* h, float* ms) {
+  if (!h || !ms || !h->timed) {
+    set_error("multi_host_last_step_ms: no step has been waited for");
+    return FBGEMM_B200_EINVAL;
+  }
+  DeviceGuard guard(h->device);
+  for (int i = 0; i < 3; ++i) {
+    const cudaError_t e = cudaEventElapsedTime(&ms[i], h->mark[i], h->mark[i + 1]);
+    if (e != cudaSuccess) {
+      return fail_cuda(e, "multi_host_last_step_ms");
+    }
+  }
+  return 0;
+}
 
 int fbgemm_b200_peer_buffer_alloc(fbgemm_b200_ctx* ctx, size_t bytes, void** ptr, unsigned char* handle) {
   if (!ctx || !ptr || !handle || bytes == 0) {

@@ -318,6 +318,14 @@ class MultiTableHostCall:
         rc = _capi.check(_capi.lib().fbgemm_b200_multi_host_wait(self._handle, info), "fbgemm_b200_multi_host_wait")
         return bool(rc), list(info)
 
+    def last_step_ms(self):
+        """Device time (ms) of the last waited step's (uploads, lookups,
+        download); the phases of two handles overlap."""
+        ms = (C.c_float * 3)()
+        _capi.check(_capi.lib().fbgemm_b200_multi_host_last_step_ms(self._handle, ms),
+                    "fbgemm_b200_multi_host_last_step_ms")
+        return list(ms)
+
     def close(self) -> None:
         if self._handle:
             _capi.lib().fbgemm_b200_multi_host_destroy(self._handle)

@@ -713,8 +713,15 @@ typedef struct fbgemm_b200_peer_sync {
  * blocks until the rows are in the host buffer and returns 1 (every table's
  * functor result true), 0 (a lookup or a counter wait failed: info[4] as in
  * fbgemm_b200_status_read) or a negative code.  Pinned host arrays keep the
- * copies asynchronous.  create allocates (staging, streams); submit and wait
- * allocate nothing.
+ * copies asynchronous.  Arrays that touch or overlap in host memory (per-table
+ * views of one indices, one offsets, one weights array) go up as ONE copy; the
+ * number of copies is what bounds a step beside another handle's download.
+ * create allocates (staging, streams); submit and wait allocate nothing.
+ * fbgemm_b200_multi_host_last_step_ms: device time of the three phases of the
+ * step that the last wait returned - ms[0] from the step's first operation
+ * (with `sync`: the wait for the peers' acks) to the end of the uploads, ms[1]
+ * the lookups (with `sync`: and the ready counters), ms[2] the download.  The
+ * phases of two handles overlap; each handle reports its own.
  */
 typedef struct fbgemm_b200_multi_host fbgemm_b200_multi_host;
 
@@ -738,6 +745,7 @@ FBGEMM_B200_API int fbgemm_b200_multi_host_submit(
     const int64_t* index_sizes,   /* [T] */
     void* out_host);
 FBGEMM_B200_API int fbgemm_b200_multi_host_wait(fbgemm_b200_multi_host* handle, int32_t* info);
+FBGEMM_B200_API int fbgemm_b200_multi_host_last_step_ms(fbgemm_b200_multi_host* handle, float* ms /* [3] */);
 FBGEMM_B200_API void fbgemm_b200_multi_host_destroy(fbgemm_b200_multi_host* handle);
 
 /* ---- row-wise quantizers, device pointers ------------------------------ */

@@ -149,11 +149,15 @@ def test_ordered_steps_and_host_call_on_one_gpu(gpu_ctx, oracle):
     sl2 = ShardedLookup(specs, plan, 0, B, dev, torch.float16, mode="p2p", num_buffers=1, tables=sl.tables)
     call = sl2.make_host_call(0, {t: 2000 for t in sl2.local}, slot=60)
     out_host = torch.zeros((B, plan.total_dim), dtype=torch.float16).pin_memory().numpy()
+    with pytest.raises(_capi.Fbgemmb200Error):
+        call.last_step_ms()              # nothing has been waited for yet
     for step in range(3):
         _, host = _specs_and_batches(B, seed=20 + step)
         call.submit([host[t][0] for t in sl2.local], [host[t][1] for t in sl2.local], None, out_host)
         ok, info = call.wait()
         assert ok, info
+        phases = call.last_step_ms()     # uploads, lookups, download of the step just waited for
+        assert len(phases) == 3 and all(0.0 <= ms < 1000.0 for ms in phases) and sum(phases) > 0.0
         want = _oracle_rows(oracle, specs, plan, tables, host, 0, B)
         np.testing.assert_array_equal(out_host.view(np.uint16), want.view(np.uint16))
     # more indices than the handle was built for: refused on the host, nothing enqueued
