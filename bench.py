@@ -527,9 +527,10 @@ def run_single(args, cfg_index, dev, rank, world, steps, warmup, full, seed_shif
                       "steps": e2e_steps, "calls_per_step": cps, "ms_per_step": dt / e2e_steps * 1e3,
                       "ms_per_call": dt / calls * 1e3, "bags_per_s": bags_per_call * calls / dt, "results_ok": bool(ok),
                       "host_us_per_call": {"in_submit": host_s[0] / calls * 1e6, "blocked_in_wait": host_s[1] / calls * 1e6,
-                                           "note": "one host thread issues every call: the time inside submit (checks, "
-                                                   "pointer queries, one staging launch or three copies, the lookup, two "
-                                                   "downloads) bounds the rate when the GPU side is shorter"},
+                                           "note": "one host thread issues every call; the time inside submit is checks, "
+                                                   "pointer queries, one staging launch or three copies, the lookup, the "
+                                                   "download and the status record.  Two or four submitting threads gave the "
+                                                   "same rate, so the transfers bound the call, not this thread"},
                       "path": f"fbgemm_b200_spmdm_host_submit/wait, {lanes} pipelined lanes, pinned host buffers, table resident",
                       "timer": "host perf_counter bracketed by device synchronisation"}
         ctx.unregister_table(host_tbl)

@@ -297,6 +297,40 @@ def test_host_pipeline_lanes(gpu_ctx, oracle):
     gpu_ctx.unregister_table(table)
 
 
+def test_host_pipeline_with_pinned_upload_dominant_calls(gpu_ctx, oracle):
+    """Page-locked caller arrays whose uploads outweigh the rows coming back
+    (long bags, narrow rows): the inputs are read in place by the staging
+    kernel and the status record is written by a kernel.  Every lane, a bad
+    index on one of them, and the lane clean again afterwards."""
+    rng = np.random.default_rng(9150)
+    rows, dim, batch = 3000, 32, 24
+    table = random_fused_table(rng, rows, dim, 4)
+    gpu_ctx.register_table(table)
+    kern = make_kernel(4, dim, True, False, False, True, np.int64, np.int64, np.float16)
+    pin = lambda a: torch.from_numpy(a).pin_memory().numpy()  # noqa: E731
+    jobs = []
+    for lane in range(_capi.HOST_LANES):
+        lengths, offsets, indices, weights, n = lengths_indices_weights(rng, batch, rows, 60, np.int64, np.int64)
+        assert indices.nbytes + offsets.nbytes + weights.nbytes > batch * dim * 2   # uploads are the larger transfer
+        if lane == 5:
+            indices = indices.copy()
+            indices[11] = rows + 3
+        indices, offsets, weights = pin(indices), pin(offsets), pin(weights)
+        out = torch.zeros(batch * dim, dtype=torch.float16).pin_memory().numpy()
+        kern.host_submit(lane, batch, n, rows, table, indices, offsets, weights, out)
+        jobs.append((lane, offsets, indices, weights, out, n))
+    for lane, offsets, indices, weights, out, n in jobs:
+        ok = kern.host_wait(lane)
+        assert ok == (lane != 5)
+        if ok:
+            _, ref = oracle.spmdm(4, dim, rows, table, indices, offsets, weights, False, np.float16)
+            np.testing.assert_array_equal(bits(out), bits(ref))
+    lane, offsets, indices, weights, out, n = jobs[4]
+    kern.host_submit(5, batch, n, rows, table, indices, offsets, weights, out)     # lane 5 again, good indices
+    assert kern.host_wait(5)
+    gpu_ctx.unregister_table(table)
+
+
 def test_async_launch_and_status_slots(gpu_ctx, oracle):
     rng = np.random.default_rng(9200)
     rows, dim, batch = 500, 32, 40
