@@ -1228,8 +1228,24 @@ def main_reference(args):
     return 0
 
 
+def relaunch_with_ranks(args) -> None:
+    """``python bench.py --gpus N`` without a launcher: run the same command line
+    as N ranks of one node (what ``python -m torch.distributed.run
+    --nproc-per-node N bench.py --gpus N`` does) and leave with its exit code."""
+    import socket
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.abspath(__file__), *sys.argv[1:]]
+    os.execv(sys.executable, cmd)
+
+
 def main():
     args = parse_args()
+    if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
+        relaunch_with_ranks(args)
     claim_stdout()
     if args.impl == "reference":
         return main_reference(args)

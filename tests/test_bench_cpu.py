@@ -44,3 +44,15 @@ def test_defaults_are_the_sharded_configuration():
     assert set(bench.TRAFFIC) == {0, 1, 2, 3}
     for v in bench.TRAFFIC.values():
         assert os.path.exists(os.path.join(ROOT, v["source"]))
+
+
+def test_gpus_n_without_a_launcher_starts_n_ranks():
+    """``python bench.py --gpus 2`` re-executes itself under torch.distributed.run;
+    without a device each of the two ranks refuses with its own line."""
+    env = {k: None for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT")}
+    e = {k: v for k, v in dict(os.environ, CUDA_VISIBLE_DEVICES="").items() if k not in env}
+    res = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--gpus", "2", "--steps", "1", "--warmup", "1"],
+                         capture_output=True, text=True, timeout=300, env=e)
+    assert res.returncode != 0
+    lines = [l for l in res.stdout.splitlines() if l.strip().startswith("{")]
+    assert len(lines) == 2 and all("no CPU path" in json.loads(l)["error"] for l in lines)
