@@ -99,6 +99,9 @@ def parse_args():
     ap.add_argument("--scale", type=float, default=1.0, help="shrink table rows (and, for workloads 0-2, the batch)")
     ap.add_argument("--tables-scale", type=float, default=1.0, help="workloads 3/4: fraction of the tables")
     ap.add_argument("--batch-scale", type=float, default=1.0, help="workloads 3/4: fraction of the batch")
+    ap.add_argument("--shard", default=None, metavar="K/G",
+                    help="workload 3 on one GPU: only the tables that rank K of a G-rank table-wise plan owns (what that "
+                         "rank's lookups take per global batch, with no store leaving the GPU)")
     ap.add_argument("--launch", default="streams", choices=["plan", "streams"],
                     help="workloads 3/4: one multi-table plan (a launch per kernel variant) or a launch per table")
     ap.add_argument("--redistribution", default="p2p", choices=["p2p", "nccl"],
@@ -675,6 +678,13 @@ def main_multi(args):
     from oracle.checker import Oracle
 
     specs, B, alpha, idt, weighted, name, mean_len, lengths_kind = multi_specs(args, world)
+    if args.shard:
+        if args.workload != 3 or world != 1:
+            raise SystemExit("--shard K/G sizes one rank's share of workload 3 on a single GPU")
+        k, g = (int(x) for x in args.shard.split("/"))
+        owner = TableWisePlan.balanced([expected_cost(s, B, mean_len) for s in specs], [s.dim for s in specs], g).owner
+        specs = [s for t, s in enumerate(specs) if owner[t] == k]
+        name += f", shard {k} of {g}"
     if args.workload == 3:
         plan = TableWisePlan.balanced([expected_cost(s, B, mean_len) for s in specs], [s.dim for s in specs], world)
     else:
@@ -950,7 +960,8 @@ def main_multi(args):
 
     if rank == 0:
         traffic = TRAFFIC.get(args.workload)
-        traffic_ok = traffic and args.scale == 1.0 and args.tables_scale == 1.0 and args.batch_scale == 1.0
+        traffic_ok = (traffic and args.scale == 1.0 and args.tables_scale == 1.0 and args.batch_scale == 1.0
+                      and not args.shard)
         emit(({
             "metric": "gathered_row_GBps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
