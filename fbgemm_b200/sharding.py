@@ -87,14 +87,24 @@ class TableWisePlan:
         raise ValueError(table)
 
 
+# Picoseconds per pooled row as (constant, per column), fitted per bit width to the
+# times measured on B200 over the nine (bit width, D) classes of the mixed
+# configuration (16 384 bags, Poisson(30) lengths, 12 M-row tables): 8-bit rows
+# 24.5 / 41.6 / 67.1 ps at D = 64 / 128 / 256, 4-bit 22.3 / 37.2 / 65.3, 2-bit
+# 20.1 / 34.6 / 60.6.
+_ROW_COST_PS = {8: (10.3, 0.222), 4: (8.0, 0.224), 2: (6.6, 0.211)}
+
+
 def expected_cost(spec: TableSpec, bags: int, mean_len: float) -> float:
-    """Relative time of one table's lookup.  Measured on B200 over the nine
-    (bit width, D) classes of the mixed configuration, a pooled row costs
-    about 7 + 0.24 * D picoseconds whatever its bit width (20/33/60 ps at
-    D = 64/128/256 for 2-bit rows, 23/39/69 for 4-bit, 26/40/72 for 8-bit): the
-    lookup is bound by the per-column arithmetic, not by the bytes of the row,
-    so balancing on bytes would overload the ranks that own narrow-bit tables."""
-    return bags * mean_len * (spec.dim + 28.0)
+    """Expected time of one table's lookup, in picoseconds.  The lookup is
+    bound by the per-column arithmetic, not by the bytes of the row - a pooled
+    row costs about 7 + 0.24 * D ps whatever its bit width - so balancing on
+    bytes would overload the ranks that own narrow-bit tables.  The per-width
+    fit matters at eight ranks: measured shard by shard, the slowest of eight
+    shards balanced with one line for all widths took 3.5 % longer than the
+    mean; with this fit the prediction is 0.9 %."""
+    const, per_column = _ROW_COST_PS.get(spec.bit_rate, (7.0, 0.24))
+    return bags * mean_len * (const + per_column * spec.dim)
 
 
 def exchange_pooled(local_out: torch.Tensor, plan: TableWisePlan, rank: int, group=None) -> torch.Tensor:
