@@ -34,6 +34,7 @@ from __future__ import annotations
 
 import ctypes as C
 import dataclasses
+import math
 
 import numpy as np
 import torch
@@ -93,6 +94,11 @@ class TableWisePlan:
 # 24.5 / 41.6 / 67.1 ps at D = 64 / 128 / 256, 4-bit 22.3 / 37.2 / 65.3, 2-bit
 # 20.1 / 34.6 / 60.6.
 _ROW_COST_PS = {8: (10.3, 0.222), 4: (8.0, 0.224), 2: (6.6, 0.211)}
+# A larger table costs a little more per row (fewer of its rows stay in L2):
+# 2 M against 12 M rows is 1.5 ps on average over the nine classes, i.e. about
+# 0.84 ps per e-fold of rows.
+_ROW_COST_PS_PER_LOG_ROWS = 0.84
+_ROW_COST_ROWS = 12e6
 
 
 def expected_cost(spec: TableSpec, bags: int, mean_len: float) -> float:
@@ -102,9 +108,10 @@ def expected_cost(spec: TableSpec, bags: int, mean_len: float) -> float:
     bytes would overload the ranks that own narrow-bit tables.  The per-width
     fit matters at eight ranks: measured shard by shard, the slowest of eight
     shards balanced with one line for all widths took 3.5 % longer than the
-    mean; with this fit the prediction is 0.9 %."""
+    mean, with this fit 2.3 %, with the table-size term 1.5 %."""
     const, per_column = _ROW_COST_PS.get(spec.bit_rate, (7.0, 0.24))
-    return bags * mean_len * (const + per_column * spec.dim)
+    size_term = _ROW_COST_PS_PER_LOG_ROWS * math.log(max(spec.rows, 1) / _ROW_COST_ROWS)
+    return bags * mean_len * (const + per_column * spec.dim + size_term)
 
 
 def exchange_pooled(local_out: torch.Tensor, plan: TableWisePlan, rank: int, group=None) -> torch.Tensor:
