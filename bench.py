@@ -710,6 +710,20 @@ def main_multi(args):
                  for b in range(nbuf)}
     launches_per_batch = (plans[(0, 0)].num_launches if plans else len(sl.local)) + (4 if p2p else 0)
 
+    def make_step_calls(lookup):
+        """One handle per output buffer that enqueues a whole ordered step with one call from the host, and its
+        pointer arrays for every input set: the host side of a global batch is then a single C call."""
+        if not (p2p and plans is None and lookup.local):
+            return None, None
+        calls_ = [lookup.make_step_call(b, slot=460 + b) for b in range(nbuf)]
+        args_ = {s: calls_[0].device_args([sets[s][t].indices for t in lookup.local],
+                                          [sets[s][t].offsets for t in lookup.local],
+                                          [sets[s][t].weights for t in lookup.local] if weighted else None)
+                 for s in range(NUM_SETS)}
+        return calls_, args_
+
+    step_calls, step_args = make_step_calls(sl)
+
     def barrier():
         torch.cuda.synchronize(dev)
         if world > 1:
@@ -727,7 +741,10 @@ def main_multi(args):
         s, b = j % NUM_SETS, j % nbuf
         with torch.cuda.stream(lanes[b]):
             streams = [lanes[b]] + side[b]
-            if p2p:
+            if p2p and step_calls:
+                # ack wait, the lookups over four streams, ready signal and wait, release: one call
+                step_calls[b].step_device(step_args[s], True, lanes[b].cuda_stream)
+            elif p2p:
                 n = sl.step(sets[s], buffer=b, slot_base=(j % 4) * 100, streams=None if plans else streams,
                             plan=plans[(s, b)] if plans else None)
                 sl.release(b, n)   # this benchmark's consumer has nothing to do with the rows
@@ -754,7 +771,8 @@ def main_multi(args):
             cur.wait_stream(ln)
 
     def status_ok():
-        return all(F.status_read(s, dev.index)[0] for s in range(400 + NUM_SETS * nbuf + 1))
+        slots = list(range(400 + NUM_SETS * nbuf + 1)) + [460 + b for b in range(nbuf)]   # per-table, plans, step handles
+        return all(F.status_read(s, dev.index)[0] for s in slots)
 
     # ---- parity inside the run: sampled bags of every table, on the rank that received them ----
     oracle = Oracle()
@@ -807,6 +825,17 @@ def main_multi(args):
     launches = int(F.launch_count() - before)
     ms = marks[0].elapsed_time(marks[args.steps])
     per_step_ms = sorted(marks[k].elapsed_time(marks[k + 1]) for k in range(args.steps))
+    ok = ok and status_ok()
+
+    # ---- host time to enqueue one global batch (nothing waited for: 8 batches fit the launch queue) ----
+    barrier()
+    fork_lanes()
+    t_host = time.perf_counter()
+    for _ in range(8):
+        global_batch()
+    enqueue_us = (time.perf_counter() - t_host) / 8 * 1e6
+    join_lanes()
+    barrier()
     ok = ok and status_ok()
 
     # ---- e2e: host index arrays in, this rank's [B/G, total_D] slice out --------------------
@@ -899,6 +928,8 @@ def main_multi(args):
         sl_main = sl
         sl = ShardedLookup(specs, plan, rank, B, dev, torch.float16, mode="p2p", num_buffers=nbuf, tables=sl_main.tables,
                            weighted=weighted, index_dtype=tnp, offset_dtype=tnp, route_local=True)
+        main_calls = step_calls
+        step_calls, step_args = make_step_calls(sl)
         for _ in range(3 * bps):
             global_batch()
         barrier()
@@ -991,6 +1022,7 @@ def main_multi(args):
             "bags_per_s": len(specs) * B * nbatches / sec,
             "frac_of_hbm_peak": value / world / peak, "clocks": clocks.summary(),
             "gpu_launches": launches,
+            "host_enqueue_us_per_global_batch": enqueue_us,
             "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s",
                          "frac": value / world / peak,
                          "traffic": traffic["bytes_per_global_batch"] / world if traffic_ok else None,

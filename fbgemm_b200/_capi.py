@@ -136,6 +136,9 @@ SIGNATURES = {
     "fbgemm_b200_multi_host_submit": (C.c_int, [_p, C.POINTER(_p), C.POINTER(_p), C.POINTER(_p), C.POINTER(_i64), _p]),
     "fbgemm_b200_multi_host_wait": (C.c_int, [_p, C.POINTER(C.c_int32)]),
     "fbgemm_b200_multi_host_last_step_ms": (C.c_int, [_p, C.POINTER(C.c_float)]),
+    "fbgemm_b200_multi_host_step_device": (C.c_int64, [_p, C.POINTER(_p), C.POINTER(_p), C.POINTER(_p), C.POINTER(_i64),
+                                           C.c_int, _p]),
+    "fbgemm_b200_multi_host_release": (C.c_int, [_p, C.c_int64, _p]),
     "fbgemm_b200_multi_host_destroy": (None, [_p]),
     "fbgemm_b200_float_to_fused_8bit_rowwise": (C.c_int, [_p, _i64, C.c_int32, _p, _p]),
     "fbgemm_b200_float_to_fused_nbit_rowwise": (C.c_int, [C.c_int32, _p, _i64, C.c_int32, _p, _p]),

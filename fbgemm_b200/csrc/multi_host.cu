@@ -46,6 +46,8 @@ struct fbgemm_b200_multi_host {
   std::vector<int64_t> capacity;             // indices a table's staging can hold
   std::vector<size_t> idx_at, off_at, w_at;  // this step's byte offsets inside the staging block
   std::vector<HostRun> runs;                 // this step's uploads
+  std::vector<const void*> d_idx, d_off;     // this step's arrays as the lookups see them (device)
+  std::vector<const float*> d_w;
   DeviceBuffer staging;
   int num_peers = 0;
   int64_t bags_per_peer = 0;
@@ -66,6 +68,44 @@ struct fbgemm_b200_multi_host {
   cudaEvent_t mark[4] = {};  // step start, uploads done, rows complete, download done
   bool timed = false;        // the marks belong to a step that wait() has returned
 };
+
+namespace {
+
+// One lookup per table on device arrays, round-robin over `stream` and the handle's side streams, which are forked
+// from `stream` and joined back into it.
+int fan_out_lookups(fbgemm_b200_multi_host* h, cudaStream_t stream, const void* const* idx, const void* const* off,
+                    const float* const* w, const int64_t* index_sizes, int32_t* status) {
+  cudaError_t e = cudaEventRecord(h->fork, stream);
+  for (int i = 0; i < kSideStreams && e == cudaSuccess; ++i) {
+    e = cudaStreamWaitEvent(h->side[i], h->fork, 0);
+  }
+  if (e != cudaSuccess) {
+    return fail_cuda(e, "multi-table step: fork");
+  }
+  DeviceBuffer unused;  // offsets mode: no scan scratch
+  const size_t T = h->calls.size();
+  for (size_t t = 0; t < T; ++t) {
+    const fbgemm_b200_table_call& c = h->calls[t];
+    const size_t k = t % (kSideStreams + 1);
+    cudaStream_t s = k == 0 ? stream : h->side[k - 1];
+    const int rc = enqueue_lookup(&c.cfg, c.output_size, index_sizes[t], c.data_size, c.input, idx[t], off[t],
+                                  c.cfg.has_weight ? w[t] : nullptr, h->num_peers > 0 ? nullptr : c.out,
+                                  c.compressed_indices_table, status, unused, s,
+                                  h->num_peers > 0 ? h->peer_out[t].data() : nullptr, h->num_peers, h->bags_per_peer);
+    if (rc) {
+      return rc;
+    }
+  }
+  for (int i = 0; i < kSideStreams && e == cudaSuccess; ++i) {
+    e = cudaEventRecord(h->join[i], h->side[i]);
+    if (e == cudaSuccess) {
+      e = cudaStreamWaitEvent(stream, h->join[i], 0);
+    }
+  }
+  return e == cudaSuccess ? 0 : fail_cuda(e, "multi-table step: join");
+}
+
+}  // namespace
 
 extern "C" {
 
@@ -166,6 +206,9 @@ int fbgemm_b200_multi_host_create(
   h->idx_at.assign((size_t)num_tables, 0);
   h->off_at.assign((size_t)num_tables, 0);
   h->w_at.assign((size_t)num_tables, 0);
+  h->d_idx.assign((size_t)num_tables, nullptr);
+  h->d_off.assign((size_t)num_tables, nullptr);
+  h->d_w.assign((size_t)num_tables, nullptr);
   if (sync) {
     h->has_sync = true;
     h->ready_flags.assign(sync->ready_flags, sync->ready_flags + num_peers);
@@ -290,36 +333,17 @@ int fbgemm_b200_multi_host_submit(
   if (e != cudaSuccess) {
     return fail_cuda(e, "multi_host_submit: input upload");
   }
-  // One lookup per table, round-robin over the handle's stream and its side streams.
   e = cudaEventRecord(h->mark[1], h->stream);
-  if (e == cudaSuccess) {
-    e = cudaEventRecord(h->fork, h->stream);
-  }
-  for (int i = 0; i < kSideStreams && e == cudaSuccess; ++i) {
-    e = cudaStreamWaitEvent(h->side[i], h->fork, 0);
-  }
   if (e != cudaSuccess) {
-    return fail_cuda(e, "multi_host_submit: fork");
+    return fail_cuda(e, "multi_host_submit");
   }
-  DeviceBuffer unused;  // offsets mode: no scan scratch
   for (size_t t = 0; t < T; ++t) {
-    const fbgemm_b200_table_call& c = h->calls[t];
-    const size_t k = t % (kSideStreams + 1);
-    cudaStream_t s = k == 0 ? h->stream : h->side[k - 1];
-    const int rc = enqueue_lookup(
-        &c.cfg, c.output_size, index_sizes[t], c.data_size, c.input, st + h->idx_at[t], st + h->off_at[t],
-        c.cfg.has_weight ? reinterpret_cast<const float*>(st + h->w_at[t]) : nullptr, h->num_peers > 0 ? nullptr : c.out,
-        c.compressed_indices_table, status, unused, s, h->num_peers > 0 ? h->peer_out[t].data() : nullptr,
-        h->num_peers, h->bags_per_peer);
-    if (rc) {
-      return rc;
-    }
+    h->d_idx[t] = st + h->idx_at[t];
+    h->d_off[t] = st + h->off_at[t];
+    h->d_w[t] = reinterpret_cast<const float*>(st + h->w_at[t]);
   }
-  for (int i = 0; i < kSideStreams && e == cudaSuccess; ++i) {
-    e = cudaEventRecord(h->join[i], h->side[i]);
-    if (e == cudaSuccess) {
-      e = cudaStreamWaitEvent(h->stream, h->join[i], 0);
-    }
+  if (const int rc = fan_out_lookups(h, h->stream, h->d_idx.data(), h->d_off.data(), h->d_w.data(), index_sizes, status)) {
+    return rc;
   }
   if (e == cudaSuccess && h->has_sync) {
     e = launch_peer_signal(h->ready_flags.data(), h->num_peers, step, h->stream);
@@ -348,6 +372,77 @@ int fbgemm_b200_multi_host_submit(
   h->step = step;
   h->busy = true;
   return 0;
+}
+
+int64_t fbgemm_b200_multi_host_step_device(
+    fbgemm_b200_multi_host* h,
+    const void* const* indices,
+    const void* const* offsets,
+    const float* const* weights,
+    const int64_t* index_sizes,
+    int release,
+    void* stream_) {
+  if (!h || !indices || !offsets || !index_sizes) {
+    set_error("multi_host_step_device: bad argument");
+    return FBGEMM_B200_EINVAL;
+  }
+  if (h->busy) {
+    set_error("the handle has a host-array step in flight; call fbgemm_b200_multi_host_wait first");
+    return FBGEMM_B200_EBUSY;
+  }
+  const size_t T = h->calls.size();
+  for (size_t t = 0; t < T; ++t) {
+    const fbgemm_b200_table_call& c = h->calls[t];
+    if (index_sizes[t] < 0 || !offsets[t] || (index_sizes[t] > 0 && !indices[t]) ||
+        (c.cfg.has_weight && index_sizes[t] > 0 && (!weights || !weights[t]))) {
+      set_error("multi_host_step_device: table " + std::to_string(t) + ": null array");
+      return FBGEMM_B200_EINVAL;
+    }
+  }
+  DeviceGuard guard(h->device);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  int32_t* status = h->ctx->status + 4 * h->slot;
+  const uint64_t step = h->step + 1;
+  cudaError_t e = cudaSuccess;
+  if (h->has_sync) {
+    e = launch_peer_wait(h->ack_local, h->num_peers, step - 1, h->timeout_us, status, stream);
+    if (e != cudaSuccess) {
+      return fail_cuda(e, "multi_host_step_device");
+    }
+  }
+  for (size_t t = 0; t < T; ++t) {
+    h->d_w[t] = weights ? weights[t] : nullptr;
+  }
+  if (const int rc = fan_out_lookups(h, stream, indices, offsets, h->d_w.data(), index_sizes, status)) {
+    return rc;
+  }
+  if (h->has_sync) {
+    e = launch_peer_signal(h->ready_flags.data(), h->num_peers, step, stream);
+    if (e == cudaSuccess) {
+      e = launch_peer_wait(h->ready_local, h->num_peers, step, h->timeout_us, status, stream);
+    }
+    if (e == cudaSuccess && release) {
+      e = launch_peer_signal(h->ack_flags.data(), h->num_peers, step, stream);
+    }
+    if (e != cudaSuccess) {
+      return fail_cuda(e, "multi_host_step_device");
+    }
+  }
+  h->step = step;
+  return (int64_t)step;
+}
+
+int fbgemm_b200_multi_host_release(fbgemm_b200_multi_host* h, int64_t step, void* stream) {
+  if (!h || step <= 0 || (uint64_t)step > h->step) {
+    set_error("multi_host_release: not a step of this handle");
+    return FBGEMM_B200_EINVAL;
+  }
+  if (!h->has_sync) {
+    return 0;
+  }
+  DeviceGuard guard(h->device);
+  const cudaError_t e = launch_peer_signal(h->ack_flags.data(), h->num_peers, (uint64_t)step, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? 0 : fail_cuda(e, "multi_host_release");
 }
 
 int fbgemm_b200_multi_host_wait(fbgemm_b200_multi_host* h, int32_t* info) {

@@ -318,6 +318,30 @@ class MultiTableHostCall:
         rc = _capi.check(_capi.lib().fbgemm_b200_multi_host_wait(self._handle, info), "fbgemm_b200_multi_host_wait")
         return bool(rc), list(info)
 
+    def device_args(self, indices, offsets, weights):
+        """The pointer arrays ``step_device`` takes, built once per set of device
+        tensors (``indices[t]``, ``offsets[t]``, ``weights[t]`` or None); keep the
+        tensors alive as long as the result is used."""
+        idx, off, w, sizes = (C.c_void_p * self.n)(), (C.c_void_p * self.n)(), (C.c_void_p * self.n)(), (C.c_int64 * self.n)()
+        for t in range(self.n):
+            idx[t], off[t] = indices[t].data_ptr(), offsets[t].data_ptr()
+            w[t] = weights[t].data_ptr() if (weights is not None and weights[t] is not None) else None
+            sizes[t] = indices[t].shape[0]
+        return idx, off, (w if self.weighted else None), sizes
+
+    def step_device(self, args, release: bool, stream: int) -> int:
+        """One step on device arrays (``args`` from ``device_args``), enqueued
+        on ``stream`` (a raw CUDA stream); returns the step number."""
+        idx, off, w, sizes = args
+        n = _capi.lib().fbgemm_b200_multi_host_step_device(self._handle, idx, off, w, sizes, 1 if release else 0, stream)
+        if n <= 0:
+            _capi.check(int(n), "fbgemm_b200_multi_host_step_device")
+        return int(n)
+
+    def release(self, step: int, stream: int) -> None:
+        _capi.check(_capi.lib().fbgemm_b200_multi_host_release(self._handle, step, stream),
+                    "fbgemm_b200_multi_host_release")
+
     def last_step_ms(self):
         """Device time (ms) of the last waited step's (uploads, lookups,
         download); the phases of two handles overlap."""

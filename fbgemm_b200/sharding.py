@@ -412,6 +412,13 @@ class ShardedLookup:
         call._sync_arrays = (ready, ack)
         return call
 
+    def make_step_call(self, buffer: int, slot: int = 0, timeout_us: int = 2_000_000):
+        """The handle of ``make_host_call`` for DEVICE index arrays
+        (``MultiTableHostCall.device_args`` / ``step_device``): the whole
+        ordered step - ack wait, this rank's lookups over four streams, ready
+        signal and wait, release - in one call from the host per global batch."""
+        return self.make_host_call(buffer, {t: 0 for t in self.local}, slot, timeout_us)
+
     def barrier(self) -> None:
         """All ranks' kernels (and therefore their peer stores) are complete."""
         torch.cuda.synchronize(self.device)

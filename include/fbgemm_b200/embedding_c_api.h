@@ -717,6 +717,21 @@ typedef struct fbgemm_b200_peer_sync {
  * views of one indices, one offsets, one weights array) go up as ONE copy; the
  * number of copies is what bounds a step beside another handle's download.
  * create allocates (staging, streams); submit and wait allocate nothing.
+ * fbgemm_b200_multi_host_step_device: the same step for a caller whose index,
+ * offset and weight arrays are already on the device: no upload, no download,
+ * everything enqueued on the CALLER's `stream` (the handle's side streams fork
+ * from it and join it): wait for the peers' acks, the lookups, publish "ready"
+ * and wait for the peers'; when `stream` gets past it, out_dev holds this rank's
+ * rows.  Returns the step number (> 0) or a negative code; errors of the lookups
+ * and counter waits go to status slot `slot` (fbgemm_b200_status_read).  With
+ * `release` != 0 the "ack" counters are published right away (the caller has no
+ * use for the rows, e.g. a benchmark); otherwise call
+ * fbgemm_b200_multi_host_release(handle, step, stream) after the work that
+ * reads out_dev has been enqueued on `stream`.  One call from the host per
+ * step instead of one per table and counter: with 8 tables per rank the host
+ * needs 169-186 us per step through per-table calls from Python, as long as
+ * the GPU needs for the lookups.  A handle is used either with host arrays
+ * (submit / wait) or with device arrays, not both.
  * fbgemm_b200_multi_host_last_step_ms: device time of the three phases of the
  * step that the last wait returned - ms[0] from the step's first operation
  * (with `sync`: the wait for the peers' acks) to the end of the uploads, ms[1]
@@ -745,6 +760,15 @@ FBGEMM_B200_API int fbgemm_b200_multi_host_submit(
     const int64_t* index_sizes,   /* [T] */
     void* out_host);
 FBGEMM_B200_API int fbgemm_b200_multi_host_wait(fbgemm_b200_multi_host* handle, int32_t* info);
+FBGEMM_B200_API int64_t fbgemm_b200_multi_host_step_device(
+    fbgemm_b200_multi_host* handle,
+    const void* const* indices,   /* [T] device arrays */
+    const void* const* offsets,   /* [T] device arrays of output_size + 1 */
+    const float* const* weights,  /* [T] device arrays, or NULL when no table is weighted */
+    const int64_t* index_sizes,   /* [T] */
+    int release,
+    void* stream);
+FBGEMM_B200_API int fbgemm_b200_multi_host_release(fbgemm_b200_multi_host* handle, int64_t step, void* stream);
 FBGEMM_B200_API int fbgemm_b200_multi_host_last_step_ms(fbgemm_b200_multi_host* handle, float* ms /* [3] */);
 FBGEMM_B200_API void fbgemm_b200_multi_host_destroy(fbgemm_b200_multi_host* handle);
 

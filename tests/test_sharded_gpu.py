@@ -234,3 +234,49 @@ def test_host_call_with_arrays_that_touch_in_host_memory(gpu_ctx, oracle, layout
         want = _oracle_rows(oracle, specs, plan, tables, host, 0, B)
         np.testing.assert_array_equal(out_host.view(np.uint16), want.view(np.uint16))
     call.close()
+
+
+def test_device_array_steps_of_the_multi_table_handle(gpu_ctx, oracle):
+    """``fbgemm_b200_multi_host_step_device``: the ordered step on device arrays
+    in one call - ack wait, lookups over the handle's streams, ready signal and
+    wait - with the release either inside the call or after the consumer."""
+    from fbgemm_b200.sharding import ShardedLookup, TableWisePlan
+
+    B, dev = 64, torch.device("cuda", 0)
+    specs, _ = _specs_and_batches(B)
+    plan = TableWisePlan([0] * len(specs), [s.dim for s in specs], 1)
+    sl = ShardedLookup(specs, plan, 0, B, dev, torch.float16, mode="p2p", num_buffers=2)
+    tables = {t: sl.tables[t].cpu().numpy() for t in sl.local}
+    calls = [sl.make_step_call(b, slot=80 + b) for b in range(2)]
+    stream = torch.cuda.Stream()
+    for step in range(6):
+        _, host = _specs_and_batches(B, seed=50 + step)
+        idx = [torch.from_numpy(host[t][0]).cuda() for t in sl.local]
+        off = [torch.from_numpy(host[t][1]).cuda() for t in sl.local]
+        b = step % 2
+        args = calls[b].device_args(idx, off, None)
+        stream.wait_stream(torch.cuda.current_stream())
+        release_inside = step >= 4
+        n = calls[b].step_device(args, release_inside, stream.cuda_stream)
+        assert n == step // 2 + 1
+        with torch.cuda.stream(stream):
+            got = sl.out[b].cpu().numpy()          # ordered after the ready wait
+        if not release_inside:
+            calls[b].release(n, stream.cuda_stream)
+        ok, info = F.status_read(80 + b)
+        assert ok, info
+        want = _oracle_rows(oracle, specs, plan, tables, host, 0, B)
+        np.testing.assert_array_equal(got.view(np.uint16), want.view(np.uint16))
+    # a bad index is reported in the handle's slot, and the next step is clean
+    _, host = _specs_and_batches(B, seed=60)
+    host[1][0][3] = -5
+    idx = [torch.from_numpy(host[t][0]).cuda() for t in sl.local]
+    off = [torch.from_numpy(host[t][1]).cuda() for t in sl.local]
+    calls[0].step_device(calls[0].device_args(idx, off, None), True, stream.cuda_stream)
+    stream.synchronize()
+    ok, info = F.status_read(80)
+    assert not ok and info[0] == 1 and info[3] == -5
+    with pytest.raises(_capi.Fbgemmb200Error):
+        calls[0].release(99, stream.cuda_stream)      # not a step of this handle
+    for c in calls:
+        c.close()
