@@ -713,7 +713,7 @@ def main_multi(args):
     def make_step_calls(lookup):
         """One handle per output buffer that enqueues a whole ordered step with one call from the host, and its
         pointer arrays for every input set: the host side of a global batch is then a single C call."""
-        if not (p2p and plans is None and lookup.local):
+        if not (plans is None and lookup.local):
             return None, None
         calls_ = [lookup.make_step_call(b, slot=460 + b) for b in range(nbuf)]
         args_ = {s: calls_[0].device_args([sets[s][t].indices for t in lookup.local],
@@ -749,7 +749,9 @@ def main_multi(args):
                             plan=plans[(s, b)] if plans else None)
                 sl.release(b, n)   # this benchmark's consumer has nothing to do with the rows
             else:
-                if plans:
+                if step_calls:
+                    step_calls[b].step_device(step_args[s], False, lanes[b].cuda_stream)
+                elif plans:
                     plans[(s, b)].launch(lanes[b].cuda_stream)
                 else:
                     for st in side[b]:

@@ -417,7 +417,18 @@ class ShardedLookup:
         (``MultiTableHostCall.device_args`` / ``step_device``): the whole
         ordered step - ack wait, this rank's lookups over four streams, ready
         signal and wait, release - in one call from the host per global batch."""
-        return self.make_host_call(buffer, {t: 0 for t in self.local}, slot, timeout_us)
+        if self.mode == "p2p":
+            return self.make_host_call(buffer, {t: 0 for t in self.local}, slot, timeout_us)
+        # the all-to-all baseline: the same one call for the lookups, rows into this rank's [B, local_dim] block
+        from .embedding import MultiTableHostCall
+
+        tables, col = [], 0
+        esize = self.local_out[buffer].element_size()
+        for t in self.local:
+            tables.append((self.kernels[t], self.B, self.specs[t].rows, self.tables[t],
+                           self.local_out[buffer].data_ptr() + col * esize, 0))
+            col += self.specs[t].dim
+        return MultiTableHostCall(tables, self.local_out[buffer], self.device.index, slot)
 
     def barrier(self) -> None:
         """All ranks' kernels (and therefore their peer stores) are complete."""
