@@ -924,32 +924,34 @@ def main_multi(args):
             c.close()
         del sl_h, host_sets, host_out
 
-    # ---- the same steps with no store leaving the GPU (what the peer stores cost) -----------------------------
+    # ---- the same steps with no store leaving the GPU, and with every store leaving it (what the peer stores cost) ----
     peer_ab = None
     if args.peer_ab and p2p and world > 1:
-        sl_main = sl
-        sl = ShardedLookup(specs, plan, rank, B, dev, torch.float16, mode="p2p", num_buffers=nbuf, tables=sl_main.tables,
-                           weighted=weighted, index_dtype=tnp, offset_dtype=tnp, route_local=True)
-        main_calls = step_calls
-        step_calls, step_args = make_step_calls(sl)
-        for _ in range(3 * bps):
-            global_batch()
-        barrier()
-        m0, m1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        m0.record()
-        fork_lanes()
-        for _ in range(args.steps * bps):
-            global_batch()
-        join_lanes()
-        m1.record()
-        torch.cuda.synchronize(dev)
-        barrier()
-        local_ms = torch.tensor([m0.elapsed_time(m1)], device=dev, dtype=torch.float64)
         import torch.distributed as dist
 
-        dist.all_reduce(local_ms, op=dist.ReduceOp.MAX)
-        peer_ab = {"local_only_ms_per_global_batch": float(local_ms) / (args.steps * bps)}
-        sl = sl_main
+        sl_main, main_calls, main_args = sl, step_calls, step_args
+        peer_ab = {}
+        for key, route in (("local_only_ms_per_global_batch", True), ("all_to_next_rank_ms_per_global_batch", "next")):
+            sl = ShardedLookup(specs, plan, rank, B, dev, torch.float16, mode="p2p", num_buffers=nbuf,
+                               tables=sl_main.tables, weighted=weighted, index_dtype=tnp, offset_dtype=tnp,
+                               route_local=route)
+            step_calls, step_args = make_step_calls(sl)
+            for _ in range(3 * bps):
+                global_batch()
+            barrier()
+            m0, m1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            m0.record()
+            fork_lanes()
+            for _ in range(args.steps * bps):
+                global_batch()
+            join_lanes()
+            m1.record()
+            torch.cuda.synchronize(dev)
+            barrier()
+            t_ms = torch.tensor([m0.elapsed_time(m1)], device=dev, dtype=torch.float64)
+            dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
+            peer_ab[key] = float(t_ms) / (args.steps * bps)
+        sl, step_calls, step_args = sl_main, main_calls, main_args
 
     # ---- reduce over ranks ---------------------------------------------------------------------
     red = torch.tensor([ms, -float(ok)], device=dev, dtype=torch.float64)
@@ -1035,7 +1037,8 @@ def main_multi(args):
             "e2e": e2e, "cpu_baseline": cpu, "single_table": single,
             "peer_store_ab": dict(peer_ab, peer_stores_ms_per_global_batch=ms / nbatches,
                                   note="the same lookups, counters and launch order with every pooled row stored into the "
-                                       "rank's own buffer (no store crosses NVLink) against the benchmark's routing, where "
+                                       "rank's own buffer (no store crosses NVLink), with every row stored into the next "
+                                       "rank's buffer (all of them cross it), and with the benchmark's routing, where "
                                        "(N-1)/N of each rank's rows are peer stores") if peer_ab else None}))
     if world > 1:
         import torch.distributed as dist

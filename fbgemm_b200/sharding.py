@@ -154,7 +154,7 @@ class ShardedLookup:
     def __init__(self, specs: list[TableSpec], plan: TableWisePlan, rank: int, global_batch: int,
                  device: torch.device, out_dtype=torch.float16, mode: str = "p2p", num_buffers: int = 1,
                  tables: dict[int, torch.Tensor] | None = None, group=None, weighted: bool = False,
-                 index_dtype=np.int32, offset_dtype=np.int32, route_local: bool = False,
+                 index_dtype=np.int32, offset_dtype=np.int32, route_local: bool | str = False,
                  rendezvous: str = "symmetric_memory"):
         import torch.distributed as dist
 
@@ -215,8 +215,12 @@ class ShardedLookup:
                 for t in self.local:
                     col = plan.column_start(t) * esize
                     # route_local (a measuring aid): every slice's rows go to THIS rank's buffer, so the same
-                    # kernels run with no store leaving the GPU; the buffer's contents are then meaningless
-                    dest = [base[self.rank if route_local else r] for r in range(self.world)]
+                    # kernels run with no store leaving the GPU - or, with route_local="next", to the next
+                    # rank's buffer, so that every store crosses NVLink; the buffer's contents are then meaningless
+                    if route_local == "next":
+                        dest = [base[(self.rank + 1) % self.world]] * self.world
+                    else:
+                        dest = [base[self.rank if route_local else r] for r in range(self.world)]
                     arr = (C.c_void_p * self.world)(*[d + b * buf_bytes + col for d in dest])
                     self._peer_ptrs[(b, t)] = arr
         else:
