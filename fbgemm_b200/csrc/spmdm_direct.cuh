@@ -373,41 +373,6 @@ __device__ __forceinline__ void store_columns(const SpmdmParams& p, int64_t bag,
   }
 }
 
-// 16 columns per lane as fp16/bf16 are 32 bytes, i.e. two 16-byte stores whose
-// neighbours in the instruction lie 32 bytes apart: every store instruction
-// then writes half of each 32-byte sector, and where the row lives in a peer
-// GPU's memory each half travels and lands on its own.  Lane pairs swap halves
-// instead (the even lane hands over its second half, the odd lane its first),
-// so that each instruction writes whole sectors: the pair's first 32 bytes,
-// then its second 32 bytes.  All lanes of the group call this together
-// (exact-fit kernels only), `o` is the lane's own 32-byte slot.
-__device__ __forceinline__ void store_paired_16(const SpmdmParams& p, uint16_t* o, const u64* pairs, unsigned gmask, bool odd) {
-  float v[16];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    unpack2(pairs[i], v[2 * i], v[2 * i + 1]);
-  }
-  const bool bf16 = p.flags & kOutBf16;
-  uint32_t h[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    h[i] = (uint32_t)to_16bit(v[2 * i], bf16) | ((uint32_t)to_16bit(v[2 * i + 1], bf16) << 16);
-  }
-  uint32_t got[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    got[i] = __shfl_xor_sync(gmask, odd ? h[i] : h[4 + i], 1);
-  }
-  uint4* q = reinterpret_cast<uint4*>(o);
-  if (odd) {
-    q[-1] = make_uint4(got[0], got[1], got[2], got[3]);   // the even lane's second half
-    q[1] = make_uint4(h[4], h[5], h[6], h[7]);
-  } else {
-    q[0] = make_uint4(h[0], h[1], h[2], h[3]);
-    q[2] = make_uint4(got[0], got[1], got[2], got[3]);    // the odd lane's first half
-  }
-}
-
 // The work of one thread block: block `block` of the launch that covers the
 // bags of `p` (32/LPB bags per warp, kWarpsPerBlock warps).
 template <int BITS, int VEC, int LPB, int CPL, bool EXACT>
@@ -564,17 +529,6 @@ __device__ __forceinline__ void direct_block(const SpmdmParams& p, int64_t block
       for (int j = 0; j < PAIRS; ++j) {
         acc[ci][j] = mul2(acc[ci][j], inv2);
       }
-    }
-  }
-  if constexpr (EXACT && CPC == 16) {
-    // every lane of the group holds a whole chunk inside the row: whole-sector stores by lane pairs
-    if ((p.flags & (kOutHalf | kOutBf16)) && (p.flags & kOutVec)) {
-#pragma unroll
-      for (int ci = 0; ci < CPL; ++ci) {
-        const int c = gl + ci * LPB;
-        store_paired_16(p, reinterpret_cast<uint16_t*>(output_row(p, bag, 2)) + c * CPC, acc[ci], gmask, gl & 1);
-      }
-      return;
     }
   }
 #pragma unroll
@@ -810,17 +764,6 @@ __device__ __forceinline__ void direct_block_compact(const SpmdmParams& p, int64
       for (int j = 0; j < PAIRS; ++j) {
         acc[ci][j] = mul2(acc[ci][j], inv2);
       }
-    }
-  }
-  if constexpr (EXACT && CPC == 16) {
-    // every lane of the group holds a whole chunk inside the row: whole-sector stores by lane pairs
-    if ((p.flags & (kOutHalf | kOutBf16)) && (p.flags & kOutVec)) {
-#pragma unroll
-      for (int ci = 0; ci < CPL; ++ci) {
-        const int c = gl + ci * LPB;
-        store_paired_16(p, reinterpret_cast<uint16_t*>(output_row(p, bag, 2)) + c * CPC, acc[ci], gmask, gl & 1);
-      }
-      return;
     }
   }
 #pragma unroll
