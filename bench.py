@@ -893,14 +893,19 @@ def main_multi(args):
         torch.cuda.synchronize(dev)
         dt = time.perf_counter() - t0
         barrier()
-        # the slice that came back last holds input set (nb - 1) % NUM_SETS: the sampled bags are compared only when
-        # that is the set the oracle pooled above
-        if (nb - 1) % NUM_SETS == s0 and mine:
-            hb = host_out[(nb - 1) % nbuf]
+        phases = np.mean([c.last_step_ms() for c in calls], axis=0)    # this rank's last timed step on each handle
+        # one more step, untimed, on the input set whose sampled bags the oracle pooled above: the rows that come
+        # back to the host are compared bit for bit
+        hs = host_sets[s0]
+        calls[0].submit([hs[t][0] for t in sl.local], [hs[t][1] for t in sl.local],
+                        [hs[t][2] for t in sl.local] if weighted else None, host_out[0])
+        good = calls[0].wait()[0] and good
+        barrier()
+        if mine:
+            hb = host_out[0]
             for t in range(len(specs)):
                 c0 = plan.column_start(t)
                 good = good and same_bits(hb[sample[mine] - rank * rows][:, c0:c0 + specs[t].dim], expected[t][mine])
-        phases = np.mean([c.last_step_ms() for c in calls], axis=0)    # this rank's last step on each handle
         h2d = float(np.mean([sum(a.nbytes for tup in hs.values() for a in tup if a is not None) for hs in host_sets]))
         d2h = float(host_out[0].nbytes + 16)
         red = torch.tensor([dt, -float(good), h2d, d2h], device=dev, dtype=torch.float64)
